@@ -1,0 +1,146 @@
+/*
+ * b200proj.h -- C ABI of the B200 (sm_100a) Fourier-slice operators.
+ *
+ * One entry point per raw operator of warpem/torch-projectors
+ * (schemas: csrc/torch_projectors.cpp:23-36 of the reference).  Each entry point replaces
+ * the reference's CUDA host wrapper + kernel for that operator and is what a binding layer
+ * (the reference's TORCH_LIBRARY_IMPL(torch_projectors, CUDA, ...) block,
+ * csrc/torch_projectors.cpp:82-95) would call.
+ *
+ * Conventions
+ *  - No torch types: raw DEVICE pointers, explicit sizes, a CUDA stream handle
+ *    (cudaStream_t passed as void*; NULL = the legacy default stream).
+ *  - All tensors are contiguous, PyTorch rfft layout (origin at index 0, last axis holds the
+ *    non-negative x frequencies).  Complex tensors are interleaved float pairs (complex64).
+ *        rec    [B, (R,) R, Rh]  complex   Rh = R/2 + 1
+ *        proj   [B, P, N, Nh]    complex   Nh = N/2 + 1
+ *        rot    [B_rot, P, dim, dim] float (dim = 2 or 3), applied as given
+ *        shifts [B_shift, P, 2]  float     ([..,0] pairs with rows, [..,1] with columns)
+ *    B_rot and B_shift are 1 (shared by all batch items) or B.  shifts may be NULL
+ *    (then B_shift is ignored).
+ *  - interpolation: B200PROJ_LINEAR or B200PROJ_CUBIC (Catmull-Rom, a = -0.5).
+ *  - fourier_radius_cutoff is in projection frequency units; pixels with
+ *    kr*kr + kc*kc > cutoff*cutoff are excluded.  Pass N/2.0 for the reference's default.
+ *  - Calls are asynchronous on the given stream, allocate nothing and never synchronise.
+ *    The device of the pointers must be current.
+ *  - Return value: B200PROJ_OK or a negative error code; b200proj_last_error() gives the
+ *    message of the calling thread's last failure.  Argument errors are detected before
+ *    anything is launched.
+ *  - Outputs that are accumulated with atomics are zero-filled by the entry point itself
+ *    (cudaMemsetAsync on the stream) unless stated otherwise.
+ */
+#ifndef B200PROJ_H
+#define B200PROJ_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200PROJ_LINEAR 0
+#define B200PROJ_CUBIC 1
+
+#define B200PROJ_OK 0
+#define B200PROJ_ERR_ARGUMENT (-1)   /* bad size / flag / NULL pointer */
+#define B200PROJ_ERR_LIMIT (-2)      /* size beyond what the kernels index */
+#define B200PROJ_ERR_CUDA (-3)       /* a CUDA runtime call failed */
+
+/* Library version (major*10000 + minor*100 + patch). */
+int b200proj_version(void);
+
+/* Message of the calling thread's last failing call ("" if none). */
+const char* b200proj_last_error(void);
+
+/* Volume box a back-projection of N-pixel projections produces: ceil(N*oversampling),
+ * rounded up to even.
+ * replaces: csrc/cuda/3d/backprojection_2d_to_3d_kernels.cu:1039-1041 */
+int64_t b200proj_rec_boxsize(int64_t N, double oversampling);
+
+/* ---- forward projection (gather) -------------------------------------------------------
+ * out[b,p,i,j] = interp(rec[b], R_p * os * (j, freq(i)[, 0])) * exp(-2 pi i k.s / N);
+ * every stored pixel is written (0 outside the cutoff), so `out` needs no pre-fill.
+ * replaces: project_2d_forw_cuda       csrc/cuda/2d/projection_2d_kernels.cu:633-757
+ *           project_3d_to_2d_forw_cuda csrc/cuda/3d/projection_3d_to_2d_kernels.cu:814-1015 */
+int b200proj_project_2d_forw(const float* rec, int64_t B, int64_t R,
+                             const float* rot, int64_t B_rot,
+                             const float* shifts, int64_t B_shift,
+                             int64_t P, int64_t N, int interpolation, double oversampling,
+                             double fourier_radius_cutoff, float* out, void* stream);
+int b200proj_project_3d_to_2d_forw(const float* rec, int64_t B, int64_t R,
+                                   const float* rot, int64_t B_rot,
+                                   const float* shifts, int64_t B_shift,
+                                   int64_t P, int64_t N, int interpolation, double oversampling,
+                                   double fourier_radius_cutoff, float* out, void* stream);
+
+/* ---- backward of forward projection ----------------------------------------------------
+ * grad_rec [B,(R,)R,Rh] is zero-filled here and accumulated with atomics.
+ * grad_rot [B_rot,P,dim,dim] / grad_shifts [B_shift,P,2]: pass NULL when the gradient is
+ * not needed (the reference decides this from requires_grad inside the op:
+ * csrc/cuda/3d/projection_3d_to_2d_kernels.cu:1066-1067); when given they are zero-filled
+ * here.  grad_shifts requires shifts.
+ * replaces: project_2d_back_cuda       csrc/cuda/2d/projection_2d_kernels.cu:760-919
+ *           project_3d_to_2d_back_cuda csrc/cuda/3d/projection_3d_to_2d_kernels.cu:1018-1179 */
+int b200proj_project_2d_back(const float* grad_proj, const float* rec, int64_t B, int64_t R,
+                             const float* rot, int64_t B_rot,
+                             const float* shifts, int64_t B_shift,
+                             int64_t P, int64_t N, int interpolation, double oversampling,
+                             double fourier_radius_cutoff,
+                             float* grad_rec, float* grad_rot, float* grad_shifts, void* stream);
+int b200proj_project_3d_to_2d_back(const float* grad_proj, const float* rec, int64_t B, int64_t R,
+                                   const float* rot, int64_t B_rot,
+                                   const float* shifts, int64_t B_shift,
+                                   int64_t P, int64_t N, int interpolation, double oversampling,
+                                   double fourier_radius_cutoff,
+                                   float* grad_rec, float* grad_rot, float* grad_shifts,
+                                   void* stream);
+
+/* ---- back-projection (scatter) ---------------------------------------------------------
+ * data_rec [B,(R,)R,Rh] complex and, when weights != NULL, weight_rec (same shape, float)
+ * receive the projections / weights; R must equal b200proj_rec_boxsize(N, oversampling).
+ * accumulate == 0: both volumes are zero-filled first (the reference's behaviour);
+ * accumulate != 0: the call adds into the existing contents (for streaming many chunks of
+ * projections into one volume without a per-chunk sum).
+ * replaces: backproject_2d_forw_cuda       csrc/cuda/2d/backprojection_2d_kernels.cu:827-976
+ *           backproject_2d_to_3d_forw_cuda csrc/cuda/3d/backprojection_2d_to_3d_kernels.cu:1001-1188 */
+int b200proj_backproject_2d_forw(const float* proj, const float* weights, int64_t B, int64_t R,
+                                 const float* rot, int64_t B_rot,
+                                 const float* shifts, int64_t B_shift,
+                                 int64_t P, int64_t N, int interpolation, double oversampling,
+                                 double fourier_radius_cutoff,
+                                 float* data_rec, float* weight_rec, int accumulate, void* stream);
+int b200proj_backproject_2d_to_3d_forw(const float* proj, const float* weights, int64_t B,
+                                       int64_t R, const float* rot, int64_t B_rot,
+                                       const float* shifts, int64_t B_shift,
+                                       int64_t P, int64_t N, int interpolation,
+                                       double oversampling, double fourier_radius_cutoff,
+                                       float* data_rec, float* weight_rec, int accumulate,
+                                       void* stream);
+
+/* ---- backward of back-projection (gather) ----------------------------------------------
+ * grad_proj [B,P,N,Nh] complex is fully written.  grad_weights [B,P,N,Nh] float is written
+ * only when grad_weight_rec and grad_weights are both non-NULL (always tri/bi-linear).
+ * grad_rot / grad_shifts as above (NULL = not needed; zero-filled here when given).
+ * replaces: backproject_2d_back_cuda       csrc/cuda/2d/backprojection_2d_kernels.cu:979-1190
+ *           backproject_2d_to_3d_back_cuda csrc/cuda/3d/backprojection_2d_to_3d_kernels.cu:1191-1404 */
+int b200proj_backproject_2d_back(const float* grad_data_rec, const float* grad_weight_rec,
+                                 const float* proj, int64_t B, int64_t R,
+                                 const float* rot, int64_t B_rot,
+                                 const float* shifts, int64_t B_shift,
+                                 int64_t P, int64_t N, int interpolation, double oversampling,
+                                 double fourier_radius_cutoff,
+                                 float* grad_proj, float* grad_weights, float* grad_rot,
+                                 float* grad_shifts, void* stream);
+int b200proj_backproject_2d_to_3d_back(const float* grad_data_rec, const float* grad_weight_rec,
+                                       const float* proj, int64_t B, int64_t R,
+                                       const float* rot, int64_t B_rot,
+                                       const float* shifts, int64_t B_shift,
+                                       int64_t P, int64_t N, int interpolation,
+                                       double oversampling, double fourier_radius_cutoff,
+                                       float* grad_proj, float* grad_weights, float* grad_rot,
+                                       float* grad_shifts, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200PROJ_H */

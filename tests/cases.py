@@ -1,0 +1,150 @@
+"""Seeded synthetic inputs and error metrics shared by the tests, the golden-vector
+generator and the benchmark.  No dataset is involved: the reference itself benchmarks and
+tests on ``torch.randn`` data (paper/results/benchmarks/benchmark_base.py:146-174 there)."""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field, asdict
+from typing import Optional
+
+import torch
+
+
+@dataclass(frozen=True)
+class Case:
+    name: str
+    dim: int                 # 2 or 3
+    interp: str              # 'linear' | 'cubic'
+    B: int
+    P: int
+    N: int                   # projection box
+    R: int                   # reconstruction box for the projection ops
+    os: float                # oversampling
+    cutoff: Optional[float] = None
+    B_rot: int = 1
+    B_shift: int = 1         # 0 = no shifts
+    weights: bool = True
+    shift_range: float = 4.0
+    seed: int = 0
+    special_poses: bool = True   # pose 0 identity, pose 1 a 90-degree turn (exact lattice hits)
+
+    def as_dict(self):
+        return asdict(self)
+
+
+def random_rotations_3d(P: int, gen: torch.Generator, dtype=torch.float32) -> torch.Tensor:
+    """Uniform SO(3) from normalised N(0,1) quaternions."""
+    q = torch.randn(P, 4, generator=gen, dtype=torch.float64)
+    q = q / q.norm(dim=1, keepdim=True)
+    w, x, y, z = q.unbind(1)
+    m = torch.stack([1 - 2 * (y * y + z * z), 2 * (x * y - z * w), 2 * (x * z + y * w),
+                     2 * (x * y + z * w), 1 - 2 * (x * x + z * z), 2 * (y * z - x * w),
+                     2 * (x * z - y * w), 2 * (y * z + x * w), 1 - 2 * (x * x + y * y)], 1)
+    return m.reshape(P, 3, 3).to(dtype)
+
+
+def random_rotations_2d(P: int, gen: torch.Generator, dtype=torch.float32) -> torch.Tensor:
+    a = torch.rand(P, generator=gen, dtype=torch.float64) * (2 * math.pi)
+    return torch.stack([a.cos(), -a.sin(), a.sin(), a.cos()], 1).reshape(P, 2, 2).to(dtype)
+
+
+def make_rotations(dim: int, B_rot: int, P: int, gen: torch.Generator, special: bool = True,
+                   dtype=torch.float32) -> torch.Tensor:
+    f = random_rotations_3d if dim == 3 else random_rotations_2d
+    rot = f(B_rot * P, gen, dtype).reshape(B_rot, P, dim, dim).clone()
+    if special and P >= 1:
+        rot[0, 0] = torch.eye(dim, dtype=dtype)
+    if special and P >= 2:
+        turn = torch.zeros(dim, dim, dtype=dtype)
+        turn[0, 1], turn[1, 0] = -1.0, 1.0          # (c, r) -> (-r, c): half the samples mirror
+        if dim == 3:
+            turn[2, 2] = 1.0
+        rot[0, 1] = turn
+    return rot
+
+
+def hermitian_dc_column_(proj: torch.Tensor) -> torch.Tensor:
+    """Make the j = 0 column of rfft-format slices [..., N, Nh] consistent with a real image:
+    p[N-i, 0] = conj(p[i, 0]); imaginary part 0 at i = 0 and i = N/2."""
+    N = proj.shape[-2]
+    col = proj[..., :, 0]
+    col[..., 0] = col[..., 0].real.to(col.dtype)
+    col[..., N // 2] = col[..., N // 2].real.to(col.dtype)
+    idx = torch.arange(1, N // 2)
+    col[..., N - idx] = col[..., idx].conj()
+    return proj
+
+
+def make_inputs(case: Case, device="cpu", cdtype=torch.complex64):
+    """All tensors any of the eight operators of `case` needs (on `device`)."""
+    rdtype = torch.float32 if cdtype == torch.complex64 else torch.float64
+    gen = torch.Generator().manual_seed(1234 + case.seed)
+    Rh, Nh = case.R // 2 + 1, case.N // 2 + 1
+    rec_shape = (case.B, case.R, case.R, Rh) if case.dim == 3 else (case.B, case.R, Rh)
+    rec = torch.randn(rec_shape, generator=gen, dtype=torch.float64) + 1j * torch.randn(rec_shape, generator=gen, dtype=torch.float64)
+    rot = make_rotations(case.dim, case.B_rot, case.P, gen, case.special_poses, rdtype)
+    shifts = None
+    if case.B_shift:
+        shifts = ((torch.rand(case.B_shift, case.P, 2, generator=gen, dtype=torch.float64) * 2 - 1) * case.shift_range).to(rdtype)
+    pshape = (case.B, case.P, case.N, Nh)
+    proj = torch.randn(pshape, generator=gen, dtype=torch.float64) + 1j * torch.randn(pshape, generator=gen, dtype=torch.float64)
+    weights = torch.rand(pshape, generator=gen, dtype=torch.float64).to(rdtype) if case.weights else None
+    # gradient volumes for the backward of back-projection (box from the size rule)
+    raw = math.ceil(case.N * case.os)
+    Rb = raw + raw % 2
+    bshape = (case.B, Rb, Rb, Rb // 2 + 1) if case.dim == 3 else (case.B, Rb, Rb // 2 + 1)
+    grad_data = torch.randn(bshape, generator=gen, dtype=torch.float64) + 1j * torch.randn(bshape, generator=gen, dtype=torch.float64)
+    grad_weight = torch.randn(bshape, generator=gen, dtype=torch.float64).to(rdtype)
+    out = dict(rec=rec.to(cdtype), rot=rot, shifts=shifts, proj=proj.to(cdtype), weights=weights,
+               grad_data=grad_data.to(cdtype), grad_weight=grad_weight)
+    return {k: (v.to(device) if v is not None else None) for k, v in out.items()}
+
+
+def rel_err(a: torch.Tensor, ref: torch.Tensor) -> float:
+    """max|a - ref| / max|ref| over the whole tensor (point-wise relative error is
+    meaningless at the zeros outside the cutoff)."""
+    if a.shape != ref.shape:
+        raise AssertionError(f"shape mismatch {tuple(a.shape)} vs {tuple(ref.shape)}")
+    if ref.numel() == 0:
+        return 0.0
+    a = a.detach().cpu()
+    ref = ref.detach().cpu()
+    if a.is_complex():
+        a, ref = a.to(torch.complex128), ref.to(torch.complex128)
+    else:
+        a, ref = a.to(torch.float64), ref.to(torch.float64)
+    denom = ref.abs().max().item()
+    num = (a - ref).abs().max().item()
+    return num / denom if denom > 0 else num
+
+
+# Tolerances of the parity contract: global-normalised max error against the reference's
+# fp32 CPU result.
+TOL_FORWARD = 1e-5        # forward projection (gather)
+TOL_ATOMIC = 1e-4         # atomically accumulated back-projection and all gradients
+
+
+SMALL_CASES = [
+    Case("3d_lin_os2", 3, "linear", 1, 6, 16, 32, 2.0, None, 1, 1),
+    Case("3d_cub_os2", 3, "cubic", 1, 6, 16, 32, 2.0, None, 1, 1, seed=1),
+    Case("3d_lin_batch_bcast", 3, "linear", 2, 5, 12, 12, 1.0, None, 1, 2, seed=2),
+    Case("3d_cub_batch_full", 3, "cubic", 2, 4, 12, 18, 1.5, 5.0, 2, 2, seed=3),
+    Case("3d_lin_noshift", 3, "linear", 1, 4, 16, 16, 1.0, None, 1, 0, seed=4),
+    Case("3d_cub_overreach", 3, "cubic", 1, 4, 16, 16, 1.5, None, 1, 0, seed=5),   # samples leave the volume: clamp / drop
+    Case("3d_lin_overreach", 3, "linear", 2, 3, 8, 10, 1.5, 3.0, 1, 2, seed=6),
+    Case("3d_lin_tiny", 3, "linear", 1, 3, 6, 6, 1.0, None, 1, 1, seed=7),
+    Case("3d_cub_tiny_noweights", 3, "cubic", 1, 3, 6, 10, 1.5, None, 1, 1, weights=False, seed=8),
+    Case("2d_lin_os2", 2, "linear", 1, 8, 16, 32, 2.0, None, 1, 1, seed=9),
+    Case("2d_cub_os2", 2, "cubic", 1, 8, 16, 32, 2.0, None, 1, 1, seed=10),
+    Case("2d_lin_batch", 2, "linear", 3, 4, 12, 12, 1.0, 4.5, 3, 1, seed=11),
+    Case("2d_cub_batch", 2, "cubic", 2, 5, 10, 16, 1.5, None, 1, 2, seed=12),
+    Case("2d_lin_overreach", 2, "linear", 1, 4, 16, 16, 1.5, None, 1, 0, seed=13),
+    Case("2d_cub_noweights", 2, "cubic", 1, 4, 8, 8, 1.0, None, 1, 1, weights=False, seed=14),
+]
+
+MEDIUM_CASES = [
+    Case("3d_cub_cfg2_like", 3, "cubic", 1, 24, 64, 128, 2.0, 32.0, 1, 1, shift_range=8.0, seed=20, special_poses=False),
+    Case("3d_lin_cfg3_like", 3, "linear", 1, 32, 64, 128, 2.0, None, 1, 1, shift_range=8.0, seed=21, special_poses=False),
+    Case("2d_lin_cfg1_like", 2, "linear", 1, 64, 64, 128, 2.0, None, 1, 1, seed=22, special_poses=False),
+    Case("3d_cub_odd_tiles", 3, "cubic", 2, 5, 34, 70, 2.0, None, 2, 2, seed=23),
+]

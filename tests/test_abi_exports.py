@@ -1,0 +1,77 @@
+"""The C-ABI library loads without a GPU, exports every symbol include/b200proj.h declares,
+and rejects bad arguments with error codes before touching the device."""
+import ctypes as C
+import re
+from pathlib import Path
+
+import pytest
+
+from torch_projectors_b200 import _abi
+
+HEADER = Path(__file__).resolve().parent.parent / "include" / "b200proj.h"
+
+
+def declared_symbols():
+    text = re.sub(r"/\*.*?\*/", "", HEADER.read_text(), flags=re.S)
+    return sorted(set(re.findall(r"\b(b200proj_\w+)\s*\(", text)))
+
+
+def test_header_declares_the_eight_operators():
+    names = declared_symbols()
+    for op in ("project_2d_forw", "project_2d_back", "backproject_2d_forw", "backproject_2d_back",
+               "project_3d_to_2d_forw", "project_3d_to_2d_back", "backproject_2d_to_3d_forw",
+               "backproject_2d_to_3d_back"):
+        assert f"b200proj_{op}" in names
+
+
+def test_library_exports_every_declared_symbol():
+    lib = _abi.load()
+    for name in declared_symbols():
+        assert hasattr(lib, name), f"{name} declared in b200proj.h but not exported"
+    # and the binding table covers the operators one to one
+    assert set(_abi.EXPORTS) <= set(declared_symbols())
+
+
+def test_version_and_size_rule_need_no_gpu():
+    assert _abi.version() >= 100
+    assert _abi.rec_boxsize(6, 1.5) == 10
+    assert _abi.rec_boxsize(8, 1.3) == 12
+    assert _abi.rec_boxsize(10, 2.0) == 20
+    assert _abi.rec_boxsize(128, 2.0) == 256
+
+
+def _forw(lib, **over):
+    a = dict(rec=1, B=1, R=8, rot=1, B_rot=1, shifts=0, B_shift=0, P=1, N=8, interp=0, os=1.0,
+             cutoff=4.0, out=1, stream=0)
+    a.update(over)
+    return lib.b200proj_project_3d_to_2d_forw(a["rec"], a["B"], a["R"], a["rot"], a["B_rot"], a["shifts"],
+                                              a["B_shift"], a["P"], a["N"], a["interp"], a["os"],
+                                              a["cutoff"], a["out"], a["stream"])
+
+
+@pytest.mark.parametrize("over,fragment", [
+    (dict(interp=7), "interpolation"),
+    (dict(N=7), "must be even"),
+    (dict(R=9), "must be even"),
+    (dict(B_rot=3, B=2), "rotations must be 1 or same"),
+    (dict(shifts=1, B_shift=3, B=2), "shifts must be 1 or same"),
+    (dict(os=0.0), "oversampling"),
+    (dict(rot=0), "NULL"),
+    (dict(rec=0), "NULL"),
+    (dict(R=4096), "exceeds"),
+])
+def test_argument_errors_are_reported_without_a_device(over, fragment):
+    lib = _abi.load()
+    rc = _forw(lib, **over)       # pointers are dummies: validation must fail before any use
+    assert rc < 0
+    msg = lib.b200proj_last_error().decode()
+    assert fragment in msg, msg
+
+
+def test_backprojection_checks_volume_size_rule():
+    lib = _abi.load()
+    rc = lib.b200proj_backproject_2d_to_3d_forw(1, 0, 1, 10, 1, 1, 0, 0, 1, 8, 0, 2.0, 4.0, 1, 0, 0, 0)
+    assert rc == -1
+    assert "does not match" in lib.b200proj_last_error().decode()
+    rc = lib.b200proj_backproject_2d_to_3d_forw(1, 1, 1, 16, 1, 1, 0, 0, 1, 8, 0, 2.0, 4.0, 1, 0, 0, 0)
+    assert rc == -1 and "given together" in lib.b200proj_last_error().decode()

@@ -1,0 +1,262 @@
+"""Parity of the CUDA kernels (called through torch ops -> ctypes -> C ABI) with the CPU
+oracle and with the golden vectors made by the reference's own CPU operators.
+
+Tolerances (global-normalised max error, see cases.rel_err): 1e-5 for forward projection,
+1e-4 for atomically accumulated back-projection and for all gradients."""
+import glob
+from pathlib import Path
+
+import pytest
+import torch
+
+from cases import (Case, MEDIUM_CASES, SMALL_CASES, TOL_ATOMIC, TOL_FORWARD, hermitian_dc_column_,
+                   make_inputs, make_rotations, rel_err)
+from runners import load_golden, run_case, tolerance_for
+
+pytestmark = pytest.mark.gpu
+
+GOLDEN = sorted(glob.glob(str(Path(__file__).parent / "golden" / "*.npz")))
+
+
+@pytest.fixture(scope="module")
+def tp(cuda_device):
+    import torch_projectors_b200
+    return torch_projectors_b200
+
+
+def _compare(got: dict, want: dict):
+    assert set(got) == set(want)
+    for k in want:
+        assert got[k].shape == want[k].shape, (k, got[k].shape, want[k].shape)
+        err = rel_err(got[k], want[k])
+        assert err <= tolerance_for(k), f"{k}: rel err {err:.3e} > {tolerance_for(k):.0e}"
+
+
+@pytest.mark.parametrize("path", GOLDEN, ids=lambda p: Path(p).stem)
+def test_cuda_matches_reference_golden_vectors(tp, path):
+    case, t, want = load_golden(path)
+    _compare(run_case("cuda", case, t), want)
+
+
+@pytest.mark.parametrize("case", SMALL_CASES + MEDIUM_CASES, ids=lambda c: c.name)
+def test_cuda_matches_oracle(tp, case):
+    t = make_inputs(case)
+    _compare(run_case("cuda", case, t), run_case("port", case, t))
+
+
+def test_gradient_flags_follow_requires_grad(tp):
+    case = SMALL_CASES[0]
+    t = {k: (v.cuda() if v is not None else None) for k, v in make_inputs(case).items()}
+    ops = torch.ops.torch_projectors_b200
+    g_rec, g_rot, g_sh = ops.project_3d_to_2d_back(t["proj"], t["rec"], t["rot"], t["shifts"], case.interp, case.os, None)
+    assert g_rec.shape == t["rec"].shape and g_rot.shape == (0,) and g_sh.shape == (0,)
+    rot_g = t["rot"].clone().requires_grad_(True)
+    _, g_rot, g_sh = ops.project_3d_to_2d_back(t["proj"], t["rec"], rot_g, t["shifts"], case.interp, case.os, None)
+    assert g_rot.shape == t["rot"].shape and g_sh.shape == (0,)
+    assert (g_rot[..., 2] == 0).all()            # column 2 of the 3x3 gradient is identically 0
+    data, w = ops.backproject_2d_to_3d_forw(t["proj"], None, t["rot"], t["shifts"], case.interp, case.os, None)
+    assert w.shape == (0,) and data.shape[-1] == data.shape[-2] // 2 + 1
+    gp, gw, gr, gs = ops.backproject_2d_to_3d_back(t["grad_data"], None, t["proj"], t["weights"], t["rot"], t["shifts"], case.interp, case.os, None)
+    assert gw.shape == t["proj"].shape and (gw == 0).all() and gr.shape == (0,) and gs.shape == (0,)
+
+
+@pytest.mark.parametrize("interp", ["linear", "cubic"])
+def test_autograd_through_public_api_3d(tp, interp):
+    from oracle import port
+    case = Case("ag3", 3, interp, 2, 5, 12, 24, 2.0, None, 1, 2, seed=31)
+    t = make_inputs(case)
+    rec = t["rec"].cuda().requires_grad_(True)
+    rot = t["rot"].cuda().requires_grad_(True)
+    sh = t["shifts"].cuda().requires_grad_(True)
+    out = tp.project_3d_to_2d_forw(rec, rot, sh, output_shape=(case.N, case.N), interpolation=interp, oversampling=case.os)
+    g = t["proj"].cuda()
+    out.backward(g)
+    want_out = port.project_3d_to_2d_forw(t["rec"], t["rot"], t["shifts"], [case.N, case.N], interp, case.os)
+    w_rec, w_rot, w_sh = port.project_3d_to_2d_back(t["proj"], t["rec"], t["rot"], t["shifts"], interp, case.os, None, True, True)
+    assert rel_err(out, want_out) <= TOL_FORWARD
+    assert rel_err(rec.grad, w_rec) <= TOL_ATOMIC
+    assert rel_err(rot.grad, w_rot) <= TOL_ATOMIC
+    assert rel_err(sh.grad, w_sh) <= TOL_ATOMIC
+
+
+@pytest.mark.parametrize("dim", [2, 3])
+def test_autograd_through_public_api_backprojection(tp, dim):
+    from oracle import port
+    case = Case("agb", dim, "linear", 1, 6, 12, 24, 2.0, None, 1, 1, seed=32)
+    t = make_inputs(case)
+    proj = t["proj"].cuda().requires_grad_(True)
+    w = t["weights"].cuda().requires_grad_(True)
+    rot = t["rot"].cuda().requires_grad_(True)
+    sh = t["shifts"].cuda().requires_grad_(True)
+    f = tp.backproject_2d_to_3d_forw if dim == 3 else tp.backproject_2d_forw
+    data, wrec = f(proj, rot, weights=w, shifts=sh, interpolation="linear", oversampling=case.os)
+    torch.autograd.backward([data, wrec], [t["grad_data"].cuda(), t["grad_weight"].cuda()])
+    fo = port.backproject_2d_to_3d_forw if dim == 3 else port.backproject_2d_forw
+    bo = port.backproject_2d_to_3d_back if dim == 3 else port.backproject_2d_back
+    d_want, w_want = fo(t["proj"], t["weights"], t["rot"], t["shifts"], "linear", case.os)
+    gp, gw, gr, gs = bo(t["grad_data"], t["grad_weight"], t["proj"], t["weights"], t["rot"], t["shifts"], "linear", case.os, None, True, True)
+    assert rel_err(data, d_want) <= TOL_ATOMIC and rel_err(wrec, w_want) <= TOL_ATOMIC
+    assert rel_err(proj.grad, gp) <= TOL_ATOMIC
+    assert rel_err(w.grad, gw) <= TOL_ATOMIC
+    assert rel_err(rot.grad, gr) <= TOL_ATOMIC
+    assert rel_err(sh.grad, gs) <= TOL_ATOMIC
+
+
+def test_rank_canonicalisation_and_none_gradients(tp):
+    # un-batched volume, [P,3,3] rotations, no shifts (reference: torch_projectors/ops.py:352-366)
+    case = Case("canon", 3, "linear", 1, 3, 8, 8, 1.0, None, 1, 0, seed=33)
+    t = make_inputs(case)
+    rec = t["rec"][0].cuda().requires_grad_(True)
+    rot = t["rot"][0].cuda()
+    out = tp.project_3d_to_2d_forw(rec, rot)
+    assert out.shape == (1, 3, 8, 5)
+    out.abs().sum().backward()
+    assert rec.grad is not None and rec.grad.shape == rec.shape
+    same = tp.project_3d_to_2d_forw(t["rec"].cuda(), t["rot"].cuda(), torch.zeros(1, 3, 2, device="cuda"))
+    assert torch.allclose(same, out.detach(), atol=1e-6)       # zero shift == no shift
+
+
+def test_batched_call_equals_per_item_calls_bitwise(tp):
+    case = Case("batch", 3, "cubic", 3, 4, 12, 24, 2.0, None, 3, 3, seed=34)
+    t = {k: (v.cuda() if v is not None else None) for k, v in make_inputs(case).items()}
+    full = tp.project_3d_to_2d_forw(t["rec"], t["rot"], t["shifts"], output_shape=(12, 12), interpolation="cubic", oversampling=2.0)
+    for b in range(case.B):
+        one = tp.project_3d_to_2d_forw(t["rec"][b:b + 1], t["rot"][b:b + 1], t["shifts"][b:b + 1], output_shape=(12, 12),
+                                       interpolation="cubic", oversampling=2.0)
+        assert torch.equal(full[b:b + 1], one)
+    again = tp.project_3d_to_2d_forw(t["rec"], t["rot"], t["shifts"], output_shape=(12, 12), interpolation="cubic", oversampling=2.0)
+    assert torch.equal(full, again)                              # gathers are deterministic
+
+
+def test_non_contiguous_and_broadcast_poses(tp):
+    # expanded (stride-0) and sliced pose tensors are legal inputs
+    # (reference: tests/3d/back/test_batching_back_2d_to_3d.py:274, tests/3d/forw/test_basic_projection_3d_to_2d.py:212)
+    case = Case("nc", 3, "linear", 2, 4, 8, 16, 2.0, None, 1, 1, seed=35)
+    t = {k: (v.cuda() if v is not None else None) for k, v in make_inputs(case).items()}
+    a = tp.project_3d_to_2d_forw(t["rec"], t["rot"], t["shifts"], output_shape=(8, 8), oversampling=2.0)
+    b = tp.project_3d_to_2d_forw(t["rec"], t["rot"].expand(2, -1, -1, -1), t["shifts"].expand(2, -1, -1), output_shape=(8, 8), oversampling=2.0)
+    assert torch.equal(a, b)
+    c = tp.project_3d_to_2d_forw(t["rec"], t["rot"][:, :1], t["shifts"][:, :1], output_shape=(8, 8), oversampling=2.0)
+    assert torch.equal(a[:, :1], c)
+    rec_t = t["rec"].transpose(1, 2)                              # non-contiguous volume
+    d = tp.project_3d_to_2d_forw(rec_t, t["rot"], None, output_shape=(8, 8), oversampling=2.0)
+    e = tp.project_3d_to_2d_forw(rec_t.contiguous(), t["rot"], None, output_shape=(8, 8), oversampling=2.0)
+    assert torch.equal(d, e)
+
+
+def test_empty_pose_list_and_unsupported_precision(tp):
+    rec = torch.zeros(1, 8, 8, 5, dtype=torch.complex64, device="cuda")
+    out = tp.project_3d_to_2d_forw(rec, torch.zeros(1, 0, 3, 3, device="cuda"))
+    assert out.shape == (1, 0, 8, 5)
+    data, _ = tp.backproject_2d_to_3d_forw(torch.zeros(1, 0, 8, 5, dtype=torch.complex64, device="cuda"), torch.zeros(1, 0, 3, 3, device="cuda"))
+    assert data.shape == (1, 8, 8, 5) and (data == 0).all()
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        tp.project_3d_to_2d_forw(rec.to(torch.complex128), torch.eye(3, dtype=torch.float64, device="cuda").view(1, 1, 3, 3))
+    with pytest.raises(RuntimeError, match="Number of poses in shifts"):
+        tp.project_3d_to_2d_forw(rec, torch.eye(3, device="cuda").expand(1, 2, 3, 3), torch.zeros(1, 3, 2, device="cuda"))
+    with pytest.raises(RuntimeError, match="interpolation"):
+        tp.project_3d_to_2d_forw(rec, torch.eye(3, device="cuda").view(1, 1, 3, 3), interpolation="nearest")
+
+
+def test_accumulate_equals_one_shot_and_sum_of_chunks(tp):
+    # reference usage: chunk results are summed by the caller
+    # (tests/3d/back/test_performance_back_2d_to_3d.py:348-382 there, max diff < 5e-4)
+    case = Case("acc", 3, "linear", 1, 40, 16, 32, 2.0, None, 1, 1, seed=36, special_poses=False)
+    t = {k: (v.cuda() if v is not None else None) for k, v in make_inputs(case).items()}
+    d_all, w_all = tp.backproject_2d_to_3d_forw(t["proj"], t["rot"], weights=t["weights"], shifts=t["shifts"], oversampling=2.0)
+    d_acc, w_acc = torch.zeros_like(d_all), torch.zeros_like(w_all)
+    for lo in range(0, 40, 16):
+        sl = slice(lo, lo + 16)
+        tp.backproject_2d_to_3d_accumulate_(d_acc, w_acc, t["proj"][:, sl], t["rot"][:, sl], t["weights"][:, sl], t["shifts"][:, sl], oversampling=2.0)
+    assert rel_err(d_acc, d_all) <= TOL_ATOMIC and rel_err(w_acc, w_all) <= TOL_ATOMIC
+    assert (w_all >= 0).all()
+    from torch_projectors_b200 import sharding
+    vols = sharding.backproject_2d_to_3d_sharded(t["proj"], t["rot"], t["weights"], t["shifts"], oversampling=2.0, chunk=16)
+    assert rel_err(vols.data, d_all) <= TOL_ATOMIC and rel_err(vols.weights, w_all) <= TOL_ATOMIC
+
+
+@pytest.mark.parametrize("interp", ["linear", "cubic"])
+def test_known_answer_identity_rotation(tp, interp):
+    # reference: tests/3d/forw/test_basic_projection_3d_to_2d.py:47-94 (atol 1e-5)
+    torch.manual_seed(0)
+    N = 32
+    rec = torch.randn(1, N, N, N // 2 + 1, dtype=torch.complex64, device="cuda")
+    out = tp.project_3d_to_2d_forw(rec, torch.eye(3, device="cuda").view(1, 1, 3, 3), interpolation=interp)
+    kr = torch.arange(N, device="cuda").float()
+    kr = torch.where(kr <= N // 2, kr, kr - N)
+    mask = (kr[:, None] ** 2 + torch.arange(N // 2 + 1, device="cuda")[None, :] ** 2) <= (N / 2) ** 2
+    assert torch.allclose(out[0, 0], rec[0, 0] * mask, atol=1e-5)
+
+
+# ---- the benchmark configurations at full size: subsets against the oracle + properties ----
+def _cfg2_inputs(P, seed=2):
+    gen = torch.Generator().manual_seed(seed)
+    vol = torch.randn(128, 128, 128, generator=gen)
+    pad = torch.nn.functional.pad(vol, (64, 64) * 3)
+    rec = torch.fft.rfftn(torch.fft.fftshift(pad), norm="forward").to(torch.complex64).unsqueeze(0)
+    rot = make_rotations(3, 1, P, gen, special=False)
+    shifts = (torch.rand(1, P, 2, generator=gen) * 2 - 1) * 8.0
+    return rec, rot, shifts
+
+
+def test_full_size_projection_config(tp):
+    """Box-256 2x-oversampled volume, 128x128 output, cubic, cutoff 64 (the headline
+    projection workload): a subset of poses against the oracle, plus linearity."""
+    from oracle import port
+    P = 512
+    rec, rot, shifts = _cfg2_inputs(P)
+    kw = dict(output_shape=(128, 128), interpolation="cubic", oversampling=2.0, fourier_radius_cutoff=64.0)
+    out = tp.project_3d_to_2d_forw(rec.cuda(), rot.cuda(), shifts.cuda(), **kw)
+    pick = torch.tensor([0, 1, 17, 255, 511])
+    want = port.project_3d_to_2d_forw(rec, rot[:, pick], shifts[:, pick], [128, 128], "cubic", 2.0, 64.0)
+    assert rel_err(out[:, pick.cuda()], want) <= TOL_FORWARD
+    # linearity in the volume: P(a*x + y) = a*P(x) + P(y)
+    rec2 = torch.roll(rec, 3, dims=1).cuda()
+    lhs = tp.project_3d_to_2d_forw(2.5 * rec.cuda() + rec2, rot.cuda(), shifts.cuda(), **kw)
+    rhs = 2.5 * out + tp.project_3d_to_2d_forw(rec2, rot.cuda(), shifts.cuda(), **kw)
+    assert rel_err(lhs, rhs) <= TOL_FORWARD
+
+
+def test_full_size_backprojection_config(tp):
+    """128x128 slices into a box-256 volume, linear, with weights (the headline
+    back-projection workload): a subset against the oracle, chunk additivity, linearity."""
+    from oracle import port
+    P = 2048
+    gen = torch.Generator().manual_seed(3)
+    proj = torch.complex(torch.randn(1, P, 128, 65, generator=gen), torch.randn(1, P, 128, 65, generator=gen))
+    hermitian_dc_column_(proj)
+    weights = torch.rand(1, P, 128, 65, generator=gen)
+    rot = make_rotations(3, 1, P, gen, special=False)
+    shifts = (torch.rand(1, P, 2, generator=gen) * 2 - 1) * 8.0
+    c = lambda x: x.cuda()  # noqa: E731
+    d_all, w_all = tp.backproject_2d_to_3d_forw(c(proj), c(rot), weights=c(weights), shifts=c(shifts), oversampling=2.0)
+    assert d_all.shape == (1, 256, 256, 129) and w_all.shape == (1, 256, 256, 129)
+    n = 48
+    d_sub, w_sub = tp.backproject_2d_to_3d_forw(c(proj[:, :n]), c(rot[:, :n]), weights=c(weights[:, :n]), shifts=c(shifts[:, :n]), oversampling=2.0)
+    d_want, w_want = port.backproject_2d_to_3d_forw(proj[:, :n], weights[:, :n], rot[:, :n], shifts[:, :n], "linear", 2.0)
+    assert rel_err(d_sub, d_want) <= TOL_ATOMIC and rel_err(w_sub, w_want) <= TOL_ATOMIC
+    d_rest, w_rest = tp.backproject_2d_to_3d_forw(c(proj[:, n:]), c(rot[:, n:]), weights=c(weights[:, n:]), shifts=c(shifts[:, n:]), oversampling=2.0)
+    assert rel_err(d_sub + d_rest, d_all) <= TOL_ATOMIC and rel_err(w_sub + w_rest, w_all) <= TOL_ATOMIC
+    d_twice, _ = tp.backproject_2d_to_3d_forw(2 * c(proj), c(rot), weights=c(weights), shifts=c(shifts), oversampling=2.0)
+    assert rel_err(d_twice, 2 * d_all) <= TOL_ATOMIC
+
+
+def test_autograd_step_config_reduced(tp):
+    """The full-autograd-step workload (cubic, 2x oversampling, all gradients) on a reduced
+    volume the oracle finishes in seconds: MSE loss against a target, all three gradients."""
+    from oracle import port
+    case = Case("step", 3, "cubic", 1, 16, 32, 64, 2.0, None, 1, 1, shift_range=5.0, seed=40, special_poses=False)
+    t = make_inputs(case)
+    rec = t["rec"].cuda().requires_grad_(True)
+    rot = t["rot"].cuda().requires_grad_(True)
+    sh = t["shifts"].cuda().requires_grad_(True)
+    target = t["proj"].cuda()
+    out = tp.project_3d_to_2d_forw(rec, rot, sh, output_shape=(32, 32), interpolation="cubic", oversampling=2.0)
+    loss = ((out - target).abs() ** 2).mean()
+    loss.backward()
+    out_cpu = port.project_3d_to_2d_forw(t["rec"], t["rot"], t["shifts"], [32, 32], "cubic", 2.0)
+    g = 2 * (out_cpu - t["proj"]) / out_cpu.numel()           # d mean|o - t|^2 / d conj(o), torch's convention
+    w_rec, w_rot, w_sh = port.project_3d_to_2d_back(g, t["rec"], t["rot"], t["shifts"], "cubic", 2.0, None, True, True)
+    assert rel_err(rec.grad, w_rec) <= TOL_ATOMIC
+    assert rel_err(rot.grad, w_rot) <= TOL_ATOMIC
+    assert rel_err(sh.grad, w_sh) <= TOL_ATOMIC

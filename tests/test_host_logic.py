@@ -1,0 +1,177 @@
+"""Host-side logic that needs no GPU: the public API's validation (same errors as the
+reference's Python layer), the absence of any CPU fallback, and the pose-sharding layer
+driven by two gloo ranks with the CPU oracle standing in for the CUDA operators."""
+import os
+import socket
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+import torch_projectors_b200 as tp
+from torch_projectors_b200 import sharding
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+# ---- validation (reference: torch_projectors/ops.py:19-36, 98-115, 153-172, 246-262) -------
+def test_project_2d_validation_messages():
+    rot = torch.eye(2).view(1, 1, 2, 2)
+    with pytest.raises(ValueError, match="expected boxsize .* to match"):
+        tp.project_2d_forw(torch.zeros(8, 6, dtype=torch.complex64), rot)
+    with pytest.raises(ValueError, match="Boxsize .* must be even"):
+        tp.project_2d_forw(torch.zeros(7, 4, dtype=torch.complex64), rot)
+    with pytest.raises(ValueError, match="must be square"):
+        tp.project_2d_forw(torch.zeros(8, 5, dtype=torch.complex64), rot, output_shape=(8, 6))
+    with pytest.raises(ValueError, match="must be even"):
+        tp.project_2d_forw(torch.zeros(8, 5, dtype=torch.complex64), rot, output_shape=(7, 7))
+
+
+def test_project_3d_validation_messages():
+    rot = torch.eye(3).view(1, 1, 3, 3)
+    with pytest.raises(ValueError, match="must be a 4D tensor"):
+        tp.project_3d_to_2d_forw(torch.zeros(8, 8, 5, dtype=torch.complex64), rot)
+    with pytest.raises(ValueError, match="must be even"):
+        tp.project_3d_to_2d_forw(torch.zeros(1, 7, 7, 4, dtype=torch.complex64), rot)
+
+
+def test_backprojection_validation_messages():
+    rot = torch.eye(3).view(1, 1, 3, 3)
+    with pytest.raises(ValueError, match="Projections must be a 4D tensor"):
+        tp.backproject_2d_to_3d_forw(torch.zeros(8, 5, dtype=torch.complex64), rot)
+    with pytest.raises(ValueError, match="Weights shape .* must match projections shape"):
+        tp.backproject_2d_forw(torch.zeros(1, 1, 8, 5, dtype=torch.complex64), torch.eye(2).view(1, 1, 2, 2),
+                               weights=torch.zeros(1, 1, 8, 4))
+    with pytest.raises(ValueError, match="real-valued"):
+        tp.backproject_2d_forw(torch.zeros(1, 1, 8, 5, dtype=torch.complex64), torch.eye(2).view(1, 1, 2, 2),
+                               weights=torch.zeros(1, 1, 8, 5, dtype=torch.complex64))
+
+
+def test_rotation_batch_mismatch_is_a_value_error():
+    rec = torch.zeros(2, 8, 8, 5, dtype=torch.complex64)
+    with pytest.raises(ValueError, match="Batch size of rotations"):
+        tp.project_3d_to_2d_forw(rec, torch.eye(3).expand(3, 1, 3, 3))
+
+
+def test_no_cpu_fallback():
+    rec = torch.zeros(1, 8, 8, 5, dtype=torch.complex64)
+    with pytest.raises((NotImplementedError, RuntimeError)):
+        tp.project_3d_to_2d_forw(rec, torch.eye(3).view(1, 1, 3, 3))
+    with pytest.raises((NotImplementedError, RuntimeError)):
+        tp.backproject_2d_to_3d_forw(torch.zeros(1, 1, 8, 5, dtype=torch.complex64), torch.eye(3).view(1, 1, 3, 3))
+
+
+def test_product_package_does_not_import_the_oracle():
+    pkg = ROOT / "torch-projectors_b200"
+    for path in list(pkg.rglob("*.py")) + list(pkg.rglob("*.cu")) + list(pkg.rglob("*.cuh")):
+        text = path.read_text()
+        assert "import oracle" not in text and "from oracle" not in text and "oracle/" not in text, path
+
+
+def test_public_names_match_the_reference_api():
+    for name in ("project_2d_forw", "project_2d_back", "project_3d_to_2d_forw", "project_3d_to_2d_back",
+                 "backproject_2d_forw", "backproject_2d_to_3d_forw", "backproject_2d_to_3d_back"):
+        assert callable(getattr(tp, name))
+    ns = torch.ops.torch_projectors_b200
+    for name in ("project_2d_forw", "project_2d_back", "backproject_2d_forw", "backproject_2d_back",
+                 "project_3d_to_2d_forw", "project_3d_to_2d_back", "backproject_2d_to_3d_forw",
+                 "backproject_2d_to_3d_back"):
+        assert hasattr(ns, name)
+
+
+# ---- pose sharding ------------------------------------------------------------------------
+@pytest.mark.parametrize("P,world", [(10, 1), (10, 2), (10, 3), (7, 8), (0, 4), (200000, 8)])
+def test_pose_range_partitions_exactly(P, world):
+    spans = [sharding.pose_range(P, r, world) for r in range(world)]
+    assert spans[0][0] == 0 and spans[-1][1] == P
+    for (a0, a1), (b0, b1) in zip(spans, spans[1:]):
+        assert a1 == b0
+    sizes = [b - a for a, b in spans]
+    assert max(sizes) - min(sizes) <= 1
+
+
+def test_pose_range_rejects_bad_rank():
+    with pytest.raises(ValueError):
+        sharding.pose_range(10, 2, 2)
+
+
+def test_partial_volumes_layout_is_one_buffer():
+    v = sharding.PartialVolumes(2, 8, "cpu", with_weights=True)
+    n = 2 * 8 * 8 * 5
+    assert v.flat.numel() == 3 * n and v.data.shape == (2, 8, 8, 5) and v.weights.shape == (2, 8, 8, 5)
+    v.data[1, 2, 3, 4] = 1 + 2j
+    v.weights[1, 2, 3, 4] = 5.0
+    assert v.flat.sum().item() == 8.0
+    assert sharding.PartialVolumes(1, 8, "cpu", with_weights=False).weights is None
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _gloo_worker(rank, world, port, tmp):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    sys.path[:0] = [str(ROOT), str(ROOT / "tests"), str(ROOT / "torch-projectors_b200")]
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from oracle import port as orc          # CPU stand-in for the CUDA operators (tests only)
+        from cases import Case, make_inputs
+        case = Case("shard", 3, "linear", 1, 7, 8, 16, 2.0, None, 1, 1, seed=77)
+        t = make_inputs(case)
+        lo, hi = sharding.pose_range(case.P, rank, world)
+
+        # projection: each rank its pose range, gathered result equals the unsharded call
+        def project_fn(rec, rot, shifts, **kw):
+            return orc.project_3d_to_2d_forw(rec, rot, shifts, [case.N, case.N], case.interp, case.os)
+        full = sharding.project_3d_to_2d_sharded(t["rec"], t["rot"], t["shifts"], gather=True, project_fn=project_fn)
+        want = project_fn(t["rec"], t["rot"], t["shifts"])
+        assert torch.equal(full, want)
+        local = sharding.project_3d_to_2d_sharded(t["rec"], t["rot"], t["shifts"], project_fn=project_fn)
+        assert torch.equal(local, want[:, lo:hi])
+
+        # back-projection: local chunks -> partial volumes -> one reduce
+        def accumulate_fn(data, wrec, proj, rot, weights, shifts, *, interpolation, oversampling, fourier_radius_cutoff):
+            orc.backproject_2d_to_3d_forw(proj, weights, rot, shifts, interpolation, oversampling,
+                                          fourier_radius_cutoff, out=(data, wrec))
+        vols = sharding.backproject_2d_to_3d_sharded(
+            t["proj"][:, lo:hi], t["rot"][:, lo:hi], t["weights"][:, lo:hi], t["shifts"][:, lo:hi],
+            interpolation=case.interp, oversampling=case.os, chunk=2, dst=None,
+            accumulate_fn=accumulate_fn, rec_boxsize_fn=orc.rec_boxsize)
+        d_want, w_want = orc.backproject_2d_to_3d_forw(t["proj"], t["weights"], t["rot"], t["shifts"], case.interp, case.os)
+        assert torch.allclose(vols.data, d_want, atol=1e-4)
+        assert torch.allclose(vols.weights, w_want, atol=1e-4)
+
+        # reduce to rank 0 only
+        vols0 = sharding.backproject_2d_to_3d_sharded(
+            t["proj"][:, lo:hi], t["rot"][:, lo:hi], None, None,
+            interpolation=case.interp, oversampling=case.os, chunk=8192, dst=0,
+            accumulate_fn=accumulate_fn, rec_boxsize_fn=orc.rec_boxsize)
+        if rank == 0:
+            d0, _ = orc.backproject_2d_to_3d_forw(t["proj"], None, t["rot"], None, case.interp, case.os)
+            assert torch.allclose(vols0.data, d0, atol=1e-4)
+            assert vols0.weights is None
+        Path(tmp, f"ok{rank}").write_text("ok")
+    finally:
+        dist.destroy_process_group()
+
+
+def test_sharded_pipeline_on_two_gloo_ranks(tmp_path):
+    world = 2
+    mp.spawn(_gloo_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    assert all((tmp_path / f"ok{r}").exists() for r in range(world))
+
+
+def test_sharding_without_process_group_is_single_rank():
+    calls = []
+
+    def project_fn(rec, rot, shifts, **kw):
+        calls.append(rot.shape[1])
+        return torch.zeros(1, rot.shape[1], 4, 3, dtype=torch.complex64)
+    out = sharding.project_3d_to_2d_sharded(torch.zeros(1, 4, 4, 3, dtype=torch.complex64),
+                                            torch.eye(3).expand(1, 5, 3, 3), None, project_fn=project_fn)
+    assert out.shape[1] == 5 and calls == [5]

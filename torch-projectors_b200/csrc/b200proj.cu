@@ -1,0 +1,306 @@
+// C ABI of the sm_100a Fourier-slice operators: argument validation, geometry set-up,
+// zero-fill of atomically accumulated outputs and kernel dispatch.  Declarations and the
+// reference interfaces each entry point replaces are in include/b200proj.h.
+#include "b200proj.h"
+
+#include <cmath>
+#include <cstdarg>
+#include <cstdio>
+#include <climits>
+
+#include "fourier_slice_kernels.cuh"
+
+namespace {
+
+using namespace b200proj;
+
+thread_local char g_error[512] = "";
+
+int fail(int code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_error, sizeof(g_error), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+int cuda_fail(cudaError_t e, const char* what) {
+    return fail(B200PROJ_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
+}
+
+struct Launch {
+    SliceGeom g;
+    dim3 grid;
+    int64_t B, P;
+    size_t rec_count;    // voxels in [B, (R,) R, Rh]
+    size_t pix_count;    // pixels in [B, P, N, Nh]
+};
+
+// Validate the arguments common to all operators and derive the kernel geometry.
+int prepare(Launch& L, int dim, int64_t B, int64_t R, int64_t B_rot, const float* rot,
+            const float* shifts, int64_t B_shift, int64_t P, int64_t N, int interpolation,
+            double oversampling, double cutoff) {
+    g_error[0] = 0;
+    if (interpolation != B200PROJ_LINEAR && interpolation != B200PROJ_CUBIC)
+        return fail(B200PROJ_ERR_ARGUMENT, "Supported interpolation methods: 'linear', 'cubic'");
+    if (B < 1 || P < 0) return fail(B200PROJ_ERR_ARGUMENT, "batch size must be >= 1 and pose count >= 0 (B=%lld, P=%lld)", (long long)B, (long long)P);
+    if (N < 2 || (N % 2) != 0) return fail(B200PROJ_ERR_ARGUMENT, "projection boxsize (%lld) must be even and >= 2", (long long)N);
+    if (R < 2 || (R % 2) != 0) return fail(B200PROJ_ERR_ARGUMENT, "reconstruction boxsize (%lld) must be even and >= 2", (long long)R);
+    if (rot == nullptr) return fail(B200PROJ_ERR_ARGUMENT, "rotations pointer is NULL");
+    if (B_rot != 1 && B_rot != B) return fail(B200PROJ_ERR_ARGUMENT, "Batch size of rotations must be 1 or same as reconstruction (B_rot=%lld, B=%lld)", (long long)B_rot, (long long)B);
+    if (shifts != nullptr && B_shift != 1 && B_shift != B)
+        return fail(B200PROJ_ERR_ARGUMENT, "Batch size of shifts must be 1 or same as reconstruction (B_shift=%lld, B=%lld)", (long long)B_shift, (long long)B);
+    if (!(oversampling > 0.0) || !std::isfinite(oversampling))
+        return fail(B200PROJ_ERR_ARGUMENT, "oversampling must be a positive finite number");
+    if (std::isnan(cutoff)) return fail(B200PROJ_ERR_ARGUMENT, "fourier_radius_cutoff is NaN");
+
+    const int64_t Nh = N / 2 + 1, Rh = R / 2 + 1;
+    const int64_t vol = (dim == 3 ? R : 1) * R * Rh;
+    if (vol > INT_MAX) return fail(B200PROJ_ERR_LIMIT, "reconstruction of box %lld exceeds 2^31-1 voxels per batch item", (long long)R);
+    if (N > 65536) return fail(B200PROJ_ERR_LIMIT, "projection boxsize %lld too large", (long long)N);
+    if (P * dim * dim > INT_MAX / 2) return fail(B200PROJ_ERR_LIMIT, "too many poses per batch item (%lld)", (long long)P);
+
+    SliceGeom& g = L.g;
+    g.N = (int)N; g.Nh = (int)Nh; g.R = (int)R; g.Rh = (int)Rh; g.half = (int)(R / 2);
+    g.P = (int)P;
+    g.tiles_j = (int)((Nh + kTileJ - 1) / kTileJ);
+    g.tiles_i = (int)((N + kTileI - 1) / kTileI);
+    g.rot_stride_b = (B_rot == 1) ? 0 : (int)(P * dim * dim);
+    g.has_shift = shifts != nullptr;
+    g.shift_stride_b = (!g.has_shift || B_shift == 1) ? 0 : (int)(P * 2);
+    const float rc = (float)cutoff;
+    g.cutoff_sq = rc * rc;
+    g.os = oversampling;
+    g.phase_scale = -2.0 * M_PI / (double)(float)N;
+    g.shift_scale = -2.0 * M_PI / (double)N;
+    g.vol_elems = vol;
+
+    const int64_t blocks = B * P * (int64_t)g.tiles_j * g.tiles_i;
+    if (blocks > INT_MAX) return fail(B200PROJ_ERR_LIMIT, "B*P*tiles = %lld exceeds the grid limit; split the poses into chunks", (long long)blocks);
+    L.grid = dim3((unsigned)blocks, 1, 1);
+    L.B = B; L.P = P;
+    L.rec_count = (size_t)B * (size_t)vol;
+    L.pix_count = (size_t)B * (size_t)P * (size_t)N * (size_t)Nh;
+    return B200PROJ_OK;
+}
+
+int check_launch(const char* what) {
+    const cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? B200PROJ_OK : cuda_fail(e, what);
+}
+
+int zero_async(void* p, size_t bytes, cudaStream_t s) {
+    if (p == nullptr || bytes == 0) return B200PROJ_OK;
+    const cudaError_t e = cudaMemsetAsync(p, 0, bytes, s);
+    return e == cudaSuccess ? B200PROJ_OK : cuda_fail(e, "cudaMemsetAsync");
+}
+
+// ---- operator bodies, templated on the dimensionality ------------------------------------
+template <int DIM>
+int project_forw(const float* rec, int64_t B, int64_t R, const float* rot, int64_t B_rot,
+                 const float* shifts, int64_t B_shift, int64_t P, int64_t N, int interpolation,
+                 double os, double cutoff, float* out, void* stream) {
+    Launch L;
+    if (int rc = prepare(L, DIM, B, R, B_rot, rot, shifts, B_shift, P, N, interpolation, os, cutoff)) return rc;
+    if (rec == nullptr || out == nullptr) return fail(B200PROJ_ERR_ARGUMENT, "reconstruction / output pointer is NULL");
+    if (P == 0) return B200PROJ_OK;
+    cudaStream_t s = (cudaStream_t)stream;
+    const float2* v = (const float2*)rec;
+    float2* o = (float2*)out;
+    if (interpolation == B200PROJ_CUBIC)
+        project_forw_kernel<DIM, true><<<L.grid, kBlockThreads, 0, s>>>(v, rot, shifts, o, L.g);
+    else
+        project_forw_kernel<DIM, false><<<L.grid, kBlockThreads, 0, s>>>(v, rot, shifts, o, L.g);
+    return check_launch("project_forw launch");
+}
+
+template <int DIM, bool CUBIC>
+void launch_project_back(const Launch& L, cudaStream_t s, const float2* gp, const float2* rec,
+                         const float* rot, const float* shifts, float2* grad_rec, float* grad_rot,
+                         float* grad_shift) {
+    const bool nr = grad_rot != nullptr, ns = grad_shift != nullptr;
+#define B200PROJ_PB(NR, NS) \
+    project_back_kernel<DIM, CUBIC, NR, NS><<<L.grid, kBlockThreads, 0, s>>>(gp, rec, rot, shifts, grad_rec, grad_rot, grad_shift, L.g)
+    if (nr && ns) B200PROJ_PB(true, true);
+    else if (nr) B200PROJ_PB(true, false);
+    else if (ns) B200PROJ_PB(false, true);
+    else B200PROJ_PB(false, false);
+#undef B200PROJ_PB
+}
+
+template <int DIM>
+int project_back(const float* grad_proj, const float* rec, int64_t B, int64_t R, const float* rot,
+                 int64_t B_rot, const float* shifts, int64_t B_shift, int64_t P, int64_t N,
+                 int interpolation, double os, double cutoff, float* grad_rec, float* grad_rot,
+                 float* grad_shifts, void* stream) {
+    Launch L;
+    if (int rc = prepare(L, DIM, B, R, B_rot, rot, shifts, B_shift, P, N, interpolation, os, cutoff)) return rc;
+    if (grad_proj == nullptr || rec == nullptr || grad_rec == nullptr)
+        return fail(B200PROJ_ERR_ARGUMENT, "grad_projections / reconstruction / grad_reconstruction pointer is NULL");
+    if (grad_shifts != nullptr && shifts == nullptr)
+        return fail(B200PROJ_ERR_ARGUMENT, "grad_shifts requested but no shifts given");
+    cudaStream_t s = (cudaStream_t)stream;
+    if (int rc = zero_async(grad_rec, L.rec_count * sizeof(float2), s)) return rc;
+    if (int rc = zero_async(grad_rot, (size_t)B_rot * P * DIM * DIM * sizeof(float), s)) return rc;
+    if (int rc = zero_async(grad_shifts, (size_t)(shifts ? B_shift : 0) * P * 2 * sizeof(float), s)) return rc;
+    if (P == 0) return B200PROJ_OK;
+    if (interpolation == B200PROJ_CUBIC)
+        launch_project_back<DIM, true>(L, s, (const float2*)grad_proj, (const float2*)rec, rot, shifts, (float2*)grad_rec, grad_rot, grad_shifts);
+    else
+        launch_project_back<DIM, false>(L, s, (const float2*)grad_proj, (const float2*)rec, rot, shifts, (float2*)grad_rec, grad_rot, grad_shifts);
+    return check_launch("project_back launch");
+}
+
+template <int DIM>
+int backproject_forw(const float* proj, const float* weights, int64_t B, int64_t R,
+                     const float* rot, int64_t B_rot, const float* shifts, int64_t B_shift,
+                     int64_t P, int64_t N, int interpolation, double os, double cutoff,
+                     float* data_rec, float* weight_rec, int accumulate, void* stream) {
+    Launch L;
+    if (int rc = prepare(L, DIM, B, R, B_rot, rot, shifts, B_shift, P, N, interpolation, os, cutoff)) return rc;
+    if (proj == nullptr || data_rec == nullptr) return fail(B200PROJ_ERR_ARGUMENT, "projections / data_reconstruction pointer is NULL");
+    if ((weights != nullptr) != (weight_rec != nullptr))
+        return fail(B200PROJ_ERR_ARGUMENT, "weights and weight_reconstruction must be given together");
+    if (R != b200proj_rec_boxsize(N, os))
+        return fail(B200PROJ_ERR_ARGUMENT, "reconstruction boxsize %lld does not match ceil(N*oversampling) rounded up to even = %lld",
+                    (long long)R, (long long)b200proj_rec_boxsize(N, os));
+    cudaStream_t s = (cudaStream_t)stream;
+    if (!accumulate) {
+        if (int rc = zero_async(data_rec, L.rec_count * sizeof(float2), s)) return rc;
+        if (int rc = zero_async(weight_rec, L.rec_count * sizeof(float), s)) return rc;
+    }
+    if (P == 0) return B200PROJ_OK;
+    const float2* p = (const float2*)proj;
+    float2* d = (float2*)data_rec;
+    const bool cubic = interpolation == B200PROJ_CUBIC, hw = weights != nullptr;
+#define B200PROJ_BP(C, W) \
+    backproject_forw_kernel<DIM, C, W><<<L.grid, kBlockThreads, 0, s>>>(p, weights, rot, shifts, d, weight_rec, L.g)
+    if (cubic && hw) B200PROJ_BP(true, true);
+    else if (cubic) B200PROJ_BP(true, false);
+    else if (hw) B200PROJ_BP(false, true);
+    else B200PROJ_BP(false, false);
+#undef B200PROJ_BP
+    return check_launch("backproject_forw launch");
+}
+
+template <int DIM, bool CUBIC>
+void launch_backproject_back(const Launch& L, cudaStream_t s, const float2* gd, const float* gw,
+                             const float2* proj, const float* rot, const float* shifts,
+                             float2* grad_proj, float* grad_weights, float* grad_rot,
+                             float* grad_shift) {
+    const bool nr = grad_rot != nullptr, ns = grad_shift != nullptr;
+#define B200PROJ_BB(NR, NS) \
+    backproject_back_kernel<DIM, CUBIC, NR, NS><<<L.grid, kBlockThreads, 0, s>>>(gd, gw, proj, rot, shifts, grad_proj, grad_weights, grad_rot, grad_shift, L.g)
+    if (nr && ns) B200PROJ_BB(true, true);
+    else if (nr) B200PROJ_BB(true, false);
+    else if (ns) B200PROJ_BB(false, true);
+    else B200PROJ_BB(false, false);
+#undef B200PROJ_BB
+}
+
+template <int DIM>
+int backproject_back(const float* grad_data_rec, const float* grad_weight_rec, const float* proj,
+                     int64_t B, int64_t R, const float* rot, int64_t B_rot, const float* shifts,
+                     int64_t B_shift, int64_t P, int64_t N, int interpolation, double os,
+                     double cutoff, float* grad_proj, float* grad_weights, float* grad_rot,
+                     float* grad_shifts, void* stream) {
+    Launch L;
+    if (int rc = prepare(L, DIM, B, R, B_rot, rot, shifts, B_shift, P, N, interpolation, os, cutoff)) return rc;
+    if (grad_data_rec == nullptr || grad_proj == nullptr)
+        return fail(B200PROJ_ERR_ARGUMENT, "grad_data_rec / grad_projections pointer is NULL");
+    if ((grad_rot != nullptr || grad_shifts != nullptr) && proj == nullptr)
+        return fail(B200PROJ_ERR_ARGUMENT, "projections are needed for rotation / shift gradients");
+    if (grad_shifts != nullptr && shifts == nullptr)
+        return fail(B200PROJ_ERR_ARGUMENT, "grad_shifts requested but no shifts given");
+    if (R != b200proj_rec_boxsize(N, os))
+        return fail(B200PROJ_ERR_ARGUMENT, "grad_data_rec boxsize %lld does not match ceil(N*oversampling) rounded up to even = %lld",
+                    (long long)R, (long long)b200proj_rec_boxsize(N, os));
+    cudaStream_t s = (cudaStream_t)stream;
+    if (int rc = zero_async(grad_rot, (size_t)B_rot * P * DIM * DIM * sizeof(float), s)) return rc;
+    if (int rc = zero_async(grad_shifts, (size_t)(shifts ? B_shift : 0) * P * 2 * sizeof(float), s)) return rc;
+    if (grad_weights != nullptr && grad_weight_rec == nullptr)   // weights given, no incoming gradient: zeros
+        if (int rc = zero_async(grad_weights, L.pix_count * sizeof(float), s)) return rc;
+    if (P == 0) return B200PROJ_OK;
+    if (interpolation == B200PROJ_CUBIC)
+        launch_backproject_back<DIM, true>(L, s, (const float2*)grad_data_rec, grad_weight_rec, (const float2*)proj, rot, shifts, (float2*)grad_proj, grad_weights, grad_rot, grad_shifts);
+    else
+        launch_backproject_back<DIM, false>(L, s, (const float2*)grad_data_rec, grad_weight_rec, (const float2*)proj, rot, shifts, (float2*)grad_proj, grad_weights, grad_rot, grad_shifts);
+    return check_launch("backproject_back launch");
+}
+
+}  // namespace
+
+extern "C" {
+
+int b200proj_version(void) { return 100; }
+
+const char* b200proj_last_error(void) { return g_error; }
+
+int64_t b200proj_rec_boxsize(int64_t N, double oversampling) {
+    const int64_t raw = (int64_t)std::ceil((double)N * oversampling);
+    return raw + (raw % 2);
+}
+
+int b200proj_project_2d_forw(const float* rec, int64_t B, int64_t R, const float* rot, int64_t B_rot,
+                             const float* shifts, int64_t B_shift, int64_t P, int64_t N,
+                             int interpolation, double oversampling, double cutoff, float* out,
+                             void* stream) {
+    return project_forw<2>(rec, B, R, rot, B_rot, shifts, B_shift, P, N, interpolation, oversampling, cutoff, out, stream);
+}
+int b200proj_project_3d_to_2d_forw(const float* rec, int64_t B, int64_t R, const float* rot,
+                                   int64_t B_rot, const float* shifts, int64_t B_shift, int64_t P,
+                                   int64_t N, int interpolation, double oversampling, double cutoff,
+                                   float* out, void* stream) {
+    return project_forw<3>(rec, B, R, rot, B_rot, shifts, B_shift, P, N, interpolation, oversampling, cutoff, out, stream);
+}
+
+int b200proj_project_2d_back(const float* grad_proj, const float* rec, int64_t B, int64_t R,
+                             const float* rot, int64_t B_rot, const float* shifts, int64_t B_shift,
+                             int64_t P, int64_t N, int interpolation, double oversampling,
+                             double cutoff, float* grad_rec, float* grad_rot, float* grad_shifts,
+                             void* stream) {
+    return project_back<2>(grad_proj, rec, B, R, rot, B_rot, shifts, B_shift, P, N, interpolation, oversampling, cutoff, grad_rec, grad_rot, grad_shifts, stream);
+}
+int b200proj_project_3d_to_2d_back(const float* grad_proj, const float* rec, int64_t B, int64_t R,
+                                   const float* rot, int64_t B_rot, const float* shifts,
+                                   int64_t B_shift, int64_t P, int64_t N, int interpolation,
+                                   double oversampling, double cutoff, float* grad_rec,
+                                   float* grad_rot, float* grad_shifts, void* stream) {
+    return project_back<3>(grad_proj, rec, B, R, rot, B_rot, shifts, B_shift, P, N, interpolation, oversampling, cutoff, grad_rec, grad_rot, grad_shifts, stream);
+}
+
+int b200proj_backproject_2d_forw(const float* proj, const float* weights, int64_t B, int64_t R,
+                                 const float* rot, int64_t B_rot, const float* shifts,
+                                 int64_t B_shift, int64_t P, int64_t N, int interpolation,
+                                 double oversampling, double cutoff, float* data_rec,
+                                 float* weight_rec, int accumulate, void* stream) {
+    return backproject_forw<2>(proj, weights, B, R, rot, B_rot, shifts, B_shift, P, N, interpolation, oversampling, cutoff, data_rec, weight_rec, accumulate, stream);
+}
+int b200proj_backproject_2d_to_3d_forw(const float* proj, const float* weights, int64_t B,
+                                       int64_t R, const float* rot, int64_t B_rot,
+                                       const float* shifts, int64_t B_shift, int64_t P, int64_t N,
+                                       int interpolation, double oversampling, double cutoff,
+                                       float* data_rec, float* weight_rec, int accumulate,
+                                       void* stream) {
+    return backproject_forw<3>(proj, weights, B, R, rot, B_rot, shifts, B_shift, P, N, interpolation, oversampling, cutoff, data_rec, weight_rec, accumulate, stream);
+}
+
+int b200proj_backproject_2d_back(const float* grad_data_rec, const float* grad_weight_rec,
+                                 const float* proj, int64_t B, int64_t R, const float* rot,
+                                 int64_t B_rot, const float* shifts, int64_t B_shift, int64_t P,
+                                 int64_t N, int interpolation, double oversampling, double cutoff,
+                                 float* grad_proj, float* grad_weights, float* grad_rot,
+                                 float* grad_shifts, void* stream) {
+    return backproject_back<2>(grad_data_rec, grad_weight_rec, proj, B, R, rot, B_rot, shifts, B_shift, P, N, interpolation, oversampling, cutoff, grad_proj, grad_weights, grad_rot, grad_shifts, stream);
+}
+int b200proj_backproject_2d_to_3d_back(const float* grad_data_rec, const float* grad_weight_rec,
+                                       const float* proj, int64_t B, int64_t R, const float* rot,
+                                       int64_t B_rot, const float* shifts, int64_t B_shift,
+                                       int64_t P, int64_t N, int interpolation,
+                                       double oversampling, double cutoff, float* grad_proj,
+                                       float* grad_weights, float* grad_rot, float* grad_shifts,
+                                       void* stream) {
+    return backproject_back<3>(grad_data_rec, grad_weight_rec, proj, B, R, rot, B_rot, shifts, B_shift, P, N, interpolation, oversampling, cutoff, grad_proj, grad_weights, grad_rot, grad_shifts, stream);
+}
+
+}  // extern "C"

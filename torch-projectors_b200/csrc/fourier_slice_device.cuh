@@ -1,0 +1,420 @@
+// Device-side building blocks of the sm_100a Fourier-slice kernels: pixel -> sample
+// geometry, separable interpolation weights, gather (clamping) and scatter (dropping)
+// footprints in the rfft half-volume, phase ramps and block reductions.
+//
+// Numerical contract (reference: csrc/cpu in warpem/torch-projectors, the CPU backend is
+// the parity target):
+//  * sample coordinates reproduce the reference's fp32 rounding sequence exactly
+//    (csrc/cpu/3d/projection_3d_to_2d_kernels.cpp:163-188): k*os is formed in double and
+//    rounded once, the rotation is separately rounded fp32 multiplies and adds (no FMA),
+//    so floor() and the fractional parts agree bit for bit with the CPU result;
+//  * the phase of the shift ramp is float(double(float(kr*s0 + kc*s1)) * (-2*pi/N))
+//    (csrc/cpu/common/projection_utils.h:82-94) followed by an accurate sincosf;
+//  * tap sums are re-associated (separable form); that moves results by ~1e-7 relative.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace b200proj {
+
+constexpr int kTileJ = 16;            // block tile: 16 columns x 16 rows of one slice
+constexpr int kTileI = 16;
+constexpr int kBlockThreads = kTileJ * kTileI;
+constexpr int kWarps = kBlockThreads / 32;
+
+// Kernel parameters shared by the eight operators (passed by value).
+struct SliceGeom {
+    int N, Nh;              // projection box and stored width N/2+1
+    int R, Rh, half;        // volume box, stored width R/2+1, R/2
+    int P;                  // poses per batch item
+    int tiles_j, tiles_i;   // block tiles per slice
+    int rot_stride_b;       // elements between batch items of rot (0 = shared)
+    int shift_stride_b;     // elements between batch items of shifts (0 = shared)
+    int has_shift;
+    float cutoff_sq;
+    double os;              // oversampling factor
+    double phase_scale;     // -2*pi / float(N)
+    double shift_scale;     // -2*pi / N   (d phase / d shift per unit frequency)
+    long long vol_elems;    // voxels per batch item
+};
+
+struct Pixel {
+    float kr, kc;           // projection frequencies (row, column)
+    float sc, sr;           // oversampled sample coordinates before rotation
+    float c, r, d;          // rotated sample position in the volume (x, y, z)
+};
+
+// Lane -> pixel inside the block tile.  A warp covers 8 columns x 4 rows so that its
+// samples form a compact patch of the slice plane (cache locality of the taps) while each
+// row segment is 64 contiguous bytes of the output.
+__device__ __forceinline__ void tile_pixel(const SliceGeom& g, int tile, int& i, int& j) {
+    const int tj = tile % g.tiles_j, ti = tile / g.tiles_j;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    j = tj * kTileJ + (warp & 1) * 8 + (lane & 7);
+    i = ti * kTileI + (warp >> 1) * 4 + (lane >> 3);
+}
+
+// Frequencies, cutoff test and rotated sample position of output pixel (i, j).
+// Returns false when the pixel lies outside the cutoff radius.
+template <int DIM>
+__device__ __forceinline__ bool pixel_setup(const SliceGeom& g, const float* __restrict__ rm,
+                                            int i, int j, Pixel& px) {
+    px.kr = (float)((i <= g.N / 2) ? i : i - g.N);
+    px.kc = (float)j;
+    const float rad = __fadd_rn(__fmul_rn(px.kr, px.kr), __fmul_rn(px.kc, px.kc));
+    if (rad > g.cutoff_sq) return false;
+    px.sc = (float)((double)px.kc * g.os);
+    px.sr = (float)((double)px.kr * g.os);
+    if (DIM == 3) {
+        px.c = __fadd_rn(__fmul_rn(__ldg(rm + 0), px.sc), __fmul_rn(__ldg(rm + 1), px.sr));
+        px.r = __fadd_rn(__fmul_rn(__ldg(rm + 3), px.sc), __fmul_rn(__ldg(rm + 4), px.sr));
+        px.d = __fadd_rn(__fmul_rn(__ldg(rm + 6), px.sc), __fmul_rn(__ldg(rm + 7), px.sr));
+    } else {
+        px.c = __fadd_rn(__fmul_rn(__ldg(rm + 0), px.sc), __fmul_rn(__ldg(rm + 1), px.sr));
+        px.r = __fadd_rn(__fmul_rn(__ldg(rm + 2), px.sc), __fmul_rn(__ldg(rm + 3), px.sr));
+        px.d = 0.f;
+    }
+    return true;
+}
+
+// exp(-2*pi*i*(kr*s0 + kc*s1)/N) as (cos, sin).
+__device__ __forceinline__ float2 phase_ramp(const SliceGeom& g, const Pixel& px, float s0, float s1) {
+    const float dot = __fadd_rn(__fmul_rn(px.kr, s0), __fmul_rn(px.kc, s1));
+    const float ph = (float)((double)dot * g.phase_scale);
+    float sn, cs;
+    sincosf(ph, &sn, &cs);
+    return make_float2(cs, sn);
+}
+
+__device__ __forceinline__ float2 cmul(float2 a, float2 b) {
+    return make_float2(a.x * b.x - a.y * b.y, a.x * b.y + a.y * b.x);
+}
+__device__ __forceinline__ float2 cmul_conj(float2 a, float2 b) {   // a * conj(b)
+    return make_float2(a.x * b.x + a.y * b.y, a.y * b.x - a.x * b.y);
+}
+
+// Catmull-Rom weight (a = -0.5) and its derivative for |s| <= 2.
+__device__ __forceinline__ float cubic_w(float s) {
+    s = fabsf(s);
+    const float inner = (1.5f * s - 2.5f) * s * s + 1.0f;
+    const float outer = ((-0.5f * s + 2.5f) * s - 4.0f) * s + 2.0f;
+    return s <= 1.0f ? inner : (s <= 2.0f ? outer : 0.0f);
+}
+__device__ __forceinline__ float cubic_dw(float s) {
+    const float sign = s < 0.f ? -1.f : 1.f;
+    s = fabsf(s);
+    const float inner = (4.5f * s - 5.0f) * s;
+    const float outer = (-1.5f * s + 5.0f) * s - 4.0f;
+    return sign * (s <= 1.0f ? inner : (s <= 2.0f ? outer : 0.0f));
+}
+
+// Per-axis interpolation weights: T = 2 (linear: taps at floor, floor+1) or
+// T = 4 (cubic: taps at floor-1 .. floor+2).  base = index of the first tap.
+template <int T>
+struct AxisWeights {
+    int base;
+    float w[T];
+    float dw[T];
+};
+
+template <int T, bool WITH_DERIV>
+__device__ __forceinline__ void axis_weights(float x, AxisWeights<T>& a) {
+    const float fl = floorf(x);
+    const float f = x - fl;
+    if (T == 2) {
+        a.base = (int)fl;
+        a.w[0] = 1.f - f;
+        a.w[1] = f;
+        if (WITH_DERIV) { a.dw[0] = -1.f; a.dw[1] = 1.f; }
+    } else {
+        a.base = (int)fl - 1;
+#pragma unroll
+        for (int t = 0; t < T; ++t) {
+            const float s = f - (float)(t - 1);
+            a.w[t] = cubic_w(s);
+            if (WITH_DERIV) a.dw[t] = cubic_dw(s);
+        }
+    }
+}
+
+// ---- gather addressing (values outside the stored half-volume replicate the edge) -------
+// reference: csrc/cpu/common/fftw_sampling.h:96-137 and, for cubic, the pre-clamp of
+// csrc/cpu/common/interpolation_kernels.h:331-342.
+
+// Column index of signed column c; `mirrored` tells whether the Friedel mate is read.
+template <bool CUBIC>
+__device__ __forceinline__ int gather_col(const SliceGeom& g, int c, bool& mirrored) {
+    if (CUBIC) {
+        if (c >= g.Rh) c = g.Rh - 1;
+        if (c <= -g.Rh) c = -(g.Rh - 1);
+    }
+    mirrored = c < 0;
+    c = mirrored ? -c : c;
+    return min(c, g.Rh - 1);
+}
+
+// Row / plane index of signed coordinate r, for a tap that is (not) mirrored.
+template <bool CUBIC>
+__device__ __forceinline__ int gather_line(const SliceGeom& g, int r, bool mirrored) {
+    if (CUBIC) r = max(-g.half + 1, min(r, g.half));
+    if (mirrored) r = -r;
+    r = min(g.half, max(r, -g.half + 1));
+    return r < 0 ? r + g.R : r;
+}
+
+// Separable interpolation of a complex half-volume at px, optionally with the spatial
+// derivatives (d/dc, d/dr, d/dd).  vol points at the batch item.
+template <int DIM, bool CUBIC, bool WITH_DERIV>
+__device__ __forceinline__ void interpolate(const SliceGeom& g, const float2* __restrict__ vol,
+                                            const Pixel& px, float2& val, float2& g_c,
+                                            float2& g_r, float2& g_d) {
+    constexpr int T = CUBIC ? 4 : 2;
+    constexpr int TD = (DIM == 3) ? T : 1;
+    AxisWeights<T> ac, ar, ad;
+    axis_weights<T, WITH_DERIV>(px.c, ac);
+    axis_weights<T, WITH_DERIV>(px.r, ar);
+    if (DIM == 3) axis_weights<T, WITH_DERIV>(px.d, ad);
+
+    int col[T];
+    unsigned mirror_mask = 0;
+#pragma unroll
+    for (int t = 0; t < T; ++t) {
+        bool m;
+        col[t] = gather_col<CUBIC>(g, ac.base + t, m);
+        mirror_mask |= (m ? 1u : 0u) << t;
+    }
+    const int plane_stride = g.R * g.Rh;
+
+    val = make_float2(0.f, 0.f);
+    g_c = g_r = g_d = val;
+
+    const bool uniform = mirror_mask == 0u || mirror_mask == (1u << T) - 1u;
+    if (uniform) {
+        // the whole footprint lies on one side of the mirror plane
+        const bool neg = mirror_mask != 0u;
+        int row[T];
+#pragma unroll
+        for (int t = 0; t < T; ++t) row[t] = gather_line<CUBIC>(g, ar.base + t, neg) * g.Rh;
+#pragma unroll
+        for (int k = 0; k < TD; ++k) {
+            const int pl = (DIM == 3) ? gather_line<CUBIC>(g, ad.base + k, neg) * plane_stride : 0;
+            float2 A = make_float2(0.f, 0.f), Bq = A, Cq = A;
+#pragma unroll
+            for (int i = 0; i < T; ++i) {
+                const float2* __restrict__ rowp = vol + (pl + row[i]);
+                float2 s = make_float2(0.f, 0.f), ds = s;
+#pragma unroll
+                for (int j = 0; j < T; ++j) {
+                    const float2 v = __ldg(rowp + col[j]);
+                    s.x = fmaf(ac.w[j], v.x, s.x);
+                    s.y = fmaf(ac.w[j], v.y, s.y);
+                    if (WITH_DERIV) {
+                        ds.x = fmaf(ac.dw[j], v.x, ds.x);
+                        ds.y = fmaf(ac.dw[j], v.y, ds.y);
+                    }
+                }
+                A.x = fmaf(ar.w[i], s.x, A.x);
+                A.y = fmaf(ar.w[i], s.y, A.y);
+                if (WITH_DERIV) {
+                    Bq.x = fmaf(ar.dw[i], s.x, Bq.x);
+                    Bq.y = fmaf(ar.dw[i], s.y, Bq.y);
+                    Cq.x = fmaf(ar.w[i], ds.x, Cq.x);
+                    Cq.y = fmaf(ar.w[i], ds.y, Cq.y);
+                }
+            }
+            const float wd = (DIM == 3) ? ad.w[k] : 1.f;
+            val.x = fmaf(wd, A.x, val.x);
+            val.y = fmaf(wd, A.y, val.y);
+            if (WITH_DERIV) {
+                g_r.x = fmaf(wd, Bq.x, g_r.x);
+                g_r.y = fmaf(wd, Bq.y, g_r.y);
+                g_c.x = fmaf(wd, Cq.x, g_c.x);
+                g_c.y = fmaf(wd, Cq.y, g_c.y);
+                if (DIM == 3) {
+                    g_d.x = fmaf(ad.dw[k], A.x, g_d.x);
+                    g_d.y = fmaf(ad.dw[k], A.y, g_d.y);
+                }
+            }
+        }
+        if (neg) {   // every tap was a conjugated Friedel mate
+            val.y = -val.y;
+            g_c.y = -g_c.y;
+            g_r.y = -g_r.y;
+            g_d.y = -g_d.y;
+        }
+    } else {
+        // footprint straddles c = 0: mirrored and direct taps use different rows / planes
+#pragma unroll
+        for (int k = 0; k < TD; ++k) {
+            const float wd = (DIM == 3) ? ad.w[k] : 1.f;
+            const float dwd = (DIM == 3 && WITH_DERIV) ? ad.dw[k] : 0.f;
+#pragma unroll
+            for (int i = 0; i < T; ++i) {
+#pragma unroll
+                for (int j = 0; j < T; ++j) {
+                    const bool m = (mirror_mask >> j) & 1u;
+                    const int pl = (DIM == 3) ? gather_line<CUBIC>(g, ad.base + k, m) * plane_stride : 0;
+                    const int rw = gather_line<CUBIC>(g, ar.base + i, m) * g.Rh;
+                    float2 v = __ldg(vol + (pl + rw + col[j]));
+                    if (m) v.y = -v.y;
+                    const float w = wd * ar.w[i] * ac.w[j];
+                    val.x = fmaf(w, v.x, val.x);
+                    val.y = fmaf(w, v.y, val.y);
+                    if (WITH_DERIV) {
+                        const float wc_ = wd * ar.w[i] * ac.dw[j];
+                        const float wr_ = wd * ar.dw[i] * ac.w[j];
+                        g_c.x = fmaf(wc_, v.x, g_c.x);
+                        g_c.y = fmaf(wc_, v.y, g_c.y);
+                        g_r.x = fmaf(wr_, v.x, g_r.x);
+                        g_r.y = fmaf(wr_, v.y, g_r.y);
+                        if (DIM == 3) {
+                            const float wd_ = dwd * ar.w[i] * ac.w[j];
+                            g_d.x = fmaf(wd_, v.x, g_d.x);
+                            g_d.y = fmaf(wd_, v.y, g_d.y);
+                        }
+                    }
+                }
+            }
+        }
+    }
+}
+
+// ---- scatter addressing (taps outside the stored half-volume are dropped) ---------------
+// reference: csrc/cpu/common/projection_utils.h:414-493.
+
+// Index of signed row / plane coordinate r for a (non-)mirrored tap, or -1 when dropped.
+__device__ __forceinline__ int scatter_line(const SliceGeom& g, int r, bool mirrored) {
+    if (mirrored) r = -r;
+    if (r > g.half || r < -g.half + 1) return -1;
+    return r < 0 ? r + g.R : r;
+}
+
+__device__ __forceinline__ void red_add_v2(float2* addr, float a, float b) {
+    asm volatile("red.global.add.v2.f32 [%0], {%1, %2};" ::"l"(addr), "f"(a), "f"(b) : "memory");
+}
+__device__ __forceinline__ void red_add(float* addr, float a) {
+    asm volatile("red.global.add.f32 [%0], %1;" ::"l"(addr), "f"(a) : "memory");
+}
+
+// Distribute `v` (and, when WEIGHTS, wval * |tap weight|) to the taps around px.
+// WITH_DUP adds the conjugate to the Friedel partner of taps on the c == 0 plane
+// (back-projection does; the gradient of the forward projection does not).
+template <int DIM, bool CUBIC, bool WEIGHTS, bool WITH_DUP>
+__device__ __forceinline__ void scatter(const SliceGeom& g, float2* __restrict__ vol,
+                                        float* __restrict__ wvol, const Pixel& px, float2 v,
+                                        float wval) {
+    constexpr int T = CUBIC ? 4 : 2;
+    constexpr int TD = (DIM == 3) ? T : 1;
+    AxisWeights<T> ac, ar, ad;
+    axis_weights<T, false>(px.c, ac);
+    axis_weights<T, false>(px.r, ar);
+    if (DIM == 3) axis_weights<T, false>(px.d, ad);
+    const int plane_stride = g.R * g.Rh;
+
+#pragma unroll
+    for (int j = 0; j < T; ++j) {
+        int c = ac.base + j;
+        const bool m = c < 0;
+        c = m ? -c : c;
+        if (c >= g.Rh) continue;
+        const float wc = ac.w[j];
+        if (wc == 0.f) continue;
+        const float sgn = m ? -1.f : 1.f;
+#pragma unroll
+        for (int k = 0; k < TD; ++k) {
+            int dl = 0;
+            float wd = 1.f;
+            if (DIM == 3) {
+                dl = scatter_line(g, ad.base + k, m);
+                wd = ad.w[k];
+                if (dl < 0 || wd == 0.f) continue;
+            }
+#pragma unroll
+            for (int i = 0; i < T; ++i) {
+                const int rl = scatter_line(g, ar.base + i, m);
+                const float wr = ar.w[i];
+                if (rl < 0 || wr == 0.f) continue;
+                const float w = wd * wr * wc;
+                const int off = dl * plane_stride + rl * g.Rh + c;
+                const float re = v.x * w, im = v.y * w * sgn;
+                red_add_v2(vol + off, re, im);
+                float fw = 0.f;
+                if (WEIGHTS) {
+                    fw = wval * fabsf(w);
+                    red_add(wvol + off, fw);
+                }
+                if (WITH_DUP && c == 0) {
+                    // Friedel partner (-d, -r, 0); skipped when it is the same voxel
+                    const int rl2 = (rl == 0) ? 0 : g.R - rl;
+                    const int dl2 = (DIM == 3) ? ((dl == 0) ? 0 : g.R - dl) : 0;
+                    if (rl2 != rl || dl2 != dl) {
+                        const int off2 = dl2 * plane_stride + rl2 * g.Rh;
+                        red_add_v2(vol + off2, re, -im);
+                        if (WEIGHTS) red_add(wvol + off2, fw);
+                    }
+                }
+            }
+        }
+    }
+}
+
+// Real-valued tri/bi-linear read of the weight-gradient volume: Friedel mirror without
+// conjugation, zero outside.  reference: csrc/cpu/3d/backprojection_2d_to_3d_kernels.cpp:466-515
+template <int DIM>
+__device__ __forceinline__ float gather_weight_grad(const SliceGeom& g, const float* __restrict__ wv,
+                                                    const Pixel& px) {
+    AxisWeights<2> ac, ar, ad;
+    axis_weights<2, false>(px.c, ac);
+    axis_weights<2, false>(px.r, ar);
+    if (DIM == 3) axis_weights<2, false>(px.d, ad);
+    const int plane_stride = g.R * g.Rh;
+    float acc = 0.f;
+#pragma unroll
+    for (int k = 0; k < (DIM == 3 ? 2 : 1); ++k) {
+        float pk = 0.f;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            float ri = 0.f;
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                int c = ac.base + j;
+                const bool m = c < 0;
+                c = m ? -c : c;
+                float q = 0.f;
+                const int rl = scatter_line(g, ar.base + i, m);
+                const int dl = (DIM == 3) ? scatter_line(g, ad.base + k, m) : 0;
+                if (c < g.Rh && rl >= 0 && dl >= 0) q = __ldg(wv + (dl * plane_stride + rl * g.Rh + c));
+                ri = fmaf(ac.w[j], q, ri);
+            }
+            pk = fmaf(ar.w[i], ri, pk);
+        }
+        acc = fmaf((DIM == 3) ? ad.w[k] : 1.f, pk, acc);
+    }
+    return acc;
+}
+
+// Sum NV per-thread values over the block and add them to global memory with one atomic
+// per value per block.  dst[v] may be nullptr-guarded by the caller through `active`.
+template <int NV>
+__device__ __forceinline__ void block_reduce_add(float (&vals)[NV], float* const (&dst)[NV]) {
+    __shared__ float red[kWarps][NV];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+        float x = vals[v];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) x += __shfl_xor_sync(0xffffffffu, x, o);
+        if (lane == 0) red[warp][v] = x;
+    }
+    __syncthreads();
+    if (threadIdx.x < NV) {
+        float x = 0.f;
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w) x += red[w][threadIdx.x];
+        float* p = dst[threadIdx.x];
+        if (p != nullptr && x != 0.f) atomicAdd(p, x);
+    }
+}
+
+}  // namespace b200proj

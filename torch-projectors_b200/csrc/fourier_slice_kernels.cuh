@@ -1,0 +1,215 @@
+// The four kernel families of the Fourier-slice operators, each templated on the
+// dimensionality (2: image -> image, 3: volume -> slice) and the interpolation.
+//
+//   project_forw_kernel      gather   rec -> projections            (forward projection)
+//   project_back_kernel      scatter  grad_proj -> grad_rec, + pose gradients
+//   backproject_forw_kernel  scatter  projections (+weights) -> data / weight volumes
+//   backproject_back_kernel  gather   grad volumes -> grad_proj / grad_weights, + pose grads
+//
+// One block handles one 16x16 tile of one slice (pose p of batch item b); blockIdx.x
+// enumerates (b, p, tile).  No kernel waits on another block, so none can hang.
+#pragma once
+
+#include "fourier_slice_device.cuh"
+
+namespace b200proj {
+
+struct BlockWork {
+    int b, p, i, j;
+    bool in_image;
+    size_t pix;     // element offset of (b, p, i, j) in a [B, P, N, Nh] tensor
+};
+
+__device__ __forceinline__ BlockWork block_work(const SliceGeom& g) {
+    BlockWork w;
+    const int tiles = g.tiles_j * g.tiles_i;
+    const int bp = blockIdx.x / tiles;
+    const int tile = blockIdx.x - bp * tiles;
+    w.b = bp / g.P;
+    w.p = bp - w.b * g.P;
+    tile_pixel(g, tile, w.i, w.j);
+    w.in_image = w.i < g.N && w.j < g.Nh;
+    w.pix = ((size_t)bp * (size_t)g.N + (size_t)w.i) * (size_t)g.Nh + (size_t)w.j;
+    return w;
+}
+
+template <int DIM>
+__device__ __forceinline__ const float* pose_rot(const SliceGeom& g, const float* rot, int b, int p) {
+    return rot + (size_t)b * g.rot_stride_b + (size_t)p * (DIM * DIM);
+}
+__device__ __forceinline__ const float* pose_shift(const SliceGeom& g, const float* shifts, int b, int p) {
+    return shifts + (size_t)b * g.shift_stride_b + (size_t)p * 2;
+}
+
+// ---- forward projection -----------------------------------------------------------------
+// reference semantics: csrc/cpu/3d/projection_3d_to_2d_kernels.cpp:155-207
+template <int DIM, bool CUBIC>
+__global__ void __launch_bounds__(kBlockThreads)
+project_forw_kernel(const float2* __restrict__ rec, const float* __restrict__ rot,
+                    const float* __restrict__ shifts, float2* __restrict__ out, const SliceGeom g) {
+    const BlockWork w = block_work(g);
+    if (!w.in_image) return;
+    Pixel px;
+    float2 v = make_float2(0.f, 0.f);
+    if (pixel_setup<DIM>(g, pose_rot<DIM>(g, rot, w.b, w.p), w.i, w.j, px)) {
+        float2 gc, gr, gd;
+        interpolate<DIM, CUBIC, false>(g, rec + (size_t)w.b * g.vol_elems, px, v, gc, gr, gd);
+        if (g.has_shift) {
+            const float* s = pose_shift(g, shifts, w.b, w.p);
+            v = cmul(v, phase_ramp(g, px, __ldg(s), __ldg(s + 1)));
+        }
+    }
+    // streaming store: the projections are written once and never re-read by this kernel,
+    // keep the cache for the volume
+    __stcs(out + w.pix, v);
+}
+
+// Pose-gradient terms shared by the two backward kernels.
+//   rotation:  dL/dR[a][m] += s_m * Re(u * conj(grad_a)),  a: (c, r, d) rows, s = (sc, sr, 0)
+//   shift:     dL/ds[n]    += q_n * (u.y * val.x - u.x * val.y),  q = -2*pi*k_n/N
+template <int DIM, bool NEED_ROT, bool NEED_SHIFT>
+__device__ __forceinline__ void pose_grad_terms(const SliceGeom& g, const Pixel& px, float2 u_rot,
+                                                float2 u_shift, float2 val_shift, float2 g_c,
+                                                float2 g_r, float2 g_d,
+                                                float (&acc)[2 * DIM + 2]) {
+    if (NEED_ROT) {
+        const float dc = u_rot.x * g_c.x + u_rot.y * g_c.y;
+        const float dr = u_rot.x * g_r.x + u_rot.y * g_r.y;
+        acc[0] += dc * px.sc;
+        acc[1] += dc * px.sr;
+        acc[2] += dr * px.sc;
+        acc[3] += dr * px.sr;
+        if (DIM == 3) {
+            const float dd = u_rot.x * g_d.x + u_rot.y * g_d.y;
+            acc[4] += dd * px.sc;
+            acc[5] += dd * px.sr;
+        }
+    }
+    if (NEED_SHIFT) {
+        const float cross = u_shift.y * val_shift.x - u_shift.x * val_shift.y;
+        acc[2 * DIM + 0] += (float)(g.shift_scale * (double)px.kr) * cross;
+        acc[2 * DIM + 1] += (float)(g.shift_scale * (double)px.kc) * cross;
+    }
+}
+
+template <int DIM>
+__device__ __forceinline__ void pose_grad_flush(const SliceGeom& g, float (&acc)[2 * DIM + 2],
+                                                float* grad_rot, float* grad_shift, int b, int p) {
+    float* dst[2 * DIM + 2];
+    float* gr = grad_rot ? grad_rot + (size_t)b * g.rot_stride_b + (size_t)p * (DIM * DIM) : nullptr;
+    float* gs = grad_shift ? grad_shift + (size_t)b * g.shift_stride_b + (size_t)p * 2 : nullptr;
+#pragma unroll
+    for (int a = 0; a < DIM; ++a) {
+        dst[2 * a + 0] = gr ? gr + a * DIM + 0 : nullptr;   // column 2 of a 3x3 gradient stays 0
+        dst[2 * a + 1] = gr ? gr + a * DIM + 1 : nullptr;
+    }
+    dst[2 * DIM + 0] = gs;
+    dst[2 * DIM + 1] = gs ? gs + 1 : nullptr;
+    block_reduce_add<2 * DIM + 2>(acc, dst);
+}
+
+// ---- backward of forward projection -----------------------------------------------------
+// reference semantics: csrc/cpu/3d/projection_3d_to_2d_kernels.cpp:283-396
+template <int DIM, bool CUBIC, bool NEED_ROT, bool NEED_SHIFT>
+__global__ void __launch_bounds__(kBlockThreads)
+project_back_kernel(const float2* __restrict__ grad_proj, const float2* __restrict__ rec,
+                    const float* __restrict__ rot, const float* __restrict__ shifts,
+                    float2* __restrict__ grad_rec, float* __restrict__ grad_rot,
+                    float* __restrict__ grad_shift, const SliceGeom g) {
+    const BlockWork w = block_work(g);
+    float acc[2 * DIM + 2];
+#pragma unroll
+    for (int q = 0; q < 2 * DIM + 2; ++q) acc[q] = 0.f;
+    Pixel px;
+    const bool active = w.in_image &&
+                        pixel_setup<DIM>(g, pose_rot<DIM>(g, rot, w.b, w.p), w.i, w.j, px) &&
+                        !(w.j == 0 && w.i >= g.N / 2);
+    if (active) {
+        const float2 orig = __ldcs(grad_proj + w.pix);
+        float2 ph = make_float2(1.f, 0.f);
+        float2 u = orig;
+        if (g.has_shift) {
+            const float* s = pose_shift(g, shifts, w.b, w.p);
+            ph = phase_ramp(g, px, __ldg(s), __ldg(s + 1));
+            u = cmul_conj(orig, ph);
+        }
+        scatter<DIM, CUBIC, false, false>(g, grad_rec + (size_t)w.b * g.vol_elems, nullptr, px, u, 0.f);
+        if (NEED_ROT || NEED_SHIFT) {
+            float2 val, gc, gr, gd;
+            interpolate<DIM, CUBIC, NEED_ROT>(g, rec + (size_t)w.b * g.vol_elems, px, val, gc, gr, gd);
+            const float2 mod = g.has_shift ? cmul(val, ph) : val;
+            pose_grad_terms<DIM, NEED_ROT, NEED_SHIFT>(g, px, u, orig, mod, gc, gr, gd, acc);
+        }
+    }
+    if (NEED_ROT || NEED_SHIFT) pose_grad_flush<DIM>(g, acc, grad_rot, grad_shift, w.b, w.p);
+}
+
+// ---- back-projection --------------------------------------------------------------------
+// reference semantics: csrc/cpu/3d/backprojection_2d_to_3d_kernels.cpp:177-291
+template <int DIM, bool CUBIC, bool WEIGHTS>
+__global__ void __launch_bounds__(kBlockThreads)
+backproject_forw_kernel(const float2* __restrict__ proj, const float* __restrict__ weights,
+                        const float* __restrict__ rot, const float* __restrict__ shifts,
+                        float2* __restrict__ data_rec, float* __restrict__ weight_rec,
+                        const SliceGeom g) {
+    const BlockWork w = block_work(g);
+    if (!w.in_image || (w.j == 0 && w.i >= g.N / 2)) return;
+    Pixel px;
+    if (!pixel_setup<DIM>(g, pose_rot<DIM>(g, rot, w.b, w.p), w.i, w.j, px)) return;
+    float2 v = __ldcs(proj + w.pix);
+    if (g.has_shift) {
+        const float* s = pose_shift(g, shifts, w.b, w.p);
+        v = cmul_conj(v, phase_ramp(g, px, __ldg(s), __ldg(s + 1)));
+    }
+    const float wv = WEIGHTS ? __ldcs(weights + w.pix) : 0.f;
+    scatter<DIM, CUBIC, WEIGHTS, true>(g, data_rec + (size_t)w.b * g.vol_elems,
+                                       WEIGHTS ? weight_rec + (size_t)w.b * g.vol_elems : nullptr,
+                                       px, v, wv);
+}
+
+// ---- backward of back-projection --------------------------------------------------------
+// reference semantics: csrc/cpu/3d/backprojection_2d_to_3d_kernels.cpp:417-583
+template <int DIM, bool CUBIC, bool NEED_ROT, bool NEED_SHIFT>
+__global__ void __launch_bounds__(kBlockThreads)
+backproject_back_kernel(const float2* __restrict__ grad_data_rec,
+                        const float* __restrict__ grad_weight_rec,
+                        const float2* __restrict__ proj, const float* __restrict__ rot,
+                        const float* __restrict__ shifts, float2* __restrict__ grad_proj,
+                        float* __restrict__ grad_weights, float* __restrict__ grad_rot,
+                        float* __restrict__ grad_shift, const SliceGeom g) {
+    const BlockWork w = block_work(g);
+    float acc[2 * DIM + 2];
+#pragma unroll
+    for (int q = 0; q < 2 * DIM + 2; ++q) acc[q] = 0.f;
+    Pixel px;
+    const bool active = w.in_image &&
+                        pixel_setup<DIM>(g, pose_rot<DIM>(g, rot, w.b, w.p), w.i, w.j, px) &&
+                        !(w.j == 0 && w.i >= g.N / 2);
+    const bool write_w = grad_weight_rec != nullptr && grad_weights != nullptr;
+    if (active) {
+        float2 raw, gc, gr, gd;
+        interpolate<DIM, CUBIC, NEED_ROT>(g, grad_data_rec + (size_t)w.b * g.vol_elems, px, raw, gc, gr, gd);
+        float2 ph = make_float2(1.f, 0.f);
+        float2 v = raw;
+        if (g.has_shift) {
+            const float* s = pose_shift(g, shifts, w.b, w.p);
+            ph = phase_ramp(g, px, __ldg(s), __ldg(s + 1));
+            v = cmul(raw, ph);
+        }
+        __stcs(grad_proj + w.pix, v);
+        if (write_w)
+            __stcs(grad_weights + w.pix,
+                   gather_weight_grad<DIM>(g, grad_weight_rec + (size_t)w.b * g.vol_elems, px));
+        if (NEED_ROT || NEED_SHIFT) {
+            float2 pv = __ldcs(proj + w.pix);
+            if (g.has_shift) pv = cmul_conj(pv, ph);
+            pose_grad_terms<DIM, NEED_ROT, NEED_SHIFT>(g, px, pv, pv, raw, gc, gr, gd, acc);
+        }
+    } else if (w.in_image) {
+        __stcs(grad_proj + w.pix, make_float2(0.f, 0.f));
+        if (write_w) __stcs(grad_weights + w.pix, 0.f);
+    }
+    if (NEED_ROT || NEED_SHIFT) pose_grad_flush<DIM>(g, acc, grad_rot, grad_shift, w.b, w.p);
+}
+
+}  // namespace b200proj

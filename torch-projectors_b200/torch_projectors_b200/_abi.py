@@ -1,0 +1,138 @@
+"""ctypes binding of ``libb200proj.so`` (the C ABI declared in ``include/b200proj.h``).
+
+This is the only place that hands raw device pointers to the CUDA library.  Tensors given
+to the functions below must already be validated, contiguous CUDA tensors of
+complex64 / float32; the stream is torch's current stream of the tensors' device.
+
+There is no fallback of any kind: if the library is missing and cannot be built, importing
+the package fails; if a call returns an error code, ``RuntimeError`` is raised with the
+library's message.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional
+
+import torch
+
+from . import build as _build
+
+LINEAR, CUBIC = 0, 1
+
+_i64, _dbl, _int, _ptr = C.c_int64, C.c_double, C.c_int, C.c_void_p
+
+# name -> argument ctypes, mirroring include/b200proj.h
+_COMMON = [_i64, _i64, _ptr, _i64, _ptr, _i64, _i64, _i64, _int, _dbl, _dbl]  # B,R,rot,B_rot,shifts,B_shift,P,N,interp,os,cutoff
+SIGNATURES = {
+    "b200proj_project_2d_forw": [_ptr] + _COMMON + [_ptr, _ptr],
+    "b200proj_project_3d_to_2d_forw": [_ptr] + _COMMON + [_ptr, _ptr],
+    "b200proj_project_2d_back": [_ptr, _ptr] + _COMMON + [_ptr, _ptr, _ptr, _ptr],
+    "b200proj_project_3d_to_2d_back": [_ptr, _ptr] + _COMMON + [_ptr, _ptr, _ptr, _ptr],
+    "b200proj_backproject_2d_forw": [_ptr, _ptr] + _COMMON + [_ptr, _ptr, _int, _ptr],
+    "b200proj_backproject_2d_to_3d_forw": [_ptr, _ptr] + _COMMON + [_ptr, _ptr, _int, _ptr],
+    "b200proj_backproject_2d_back": [_ptr, _ptr, _ptr] + _COMMON + [_ptr, _ptr, _ptr, _ptr, _ptr],
+    "b200proj_backproject_2d_to_3d_back": [_ptr, _ptr, _ptr] + _COMMON + [_ptr, _ptr, _ptr, _ptr, _ptr],
+}
+EXPORTS = list(SIGNATURES) + ["b200proj_version", "b200proj_last_error", "b200proj_rec_boxsize"]
+
+_lib: Optional[C.CDLL] = None
+
+
+def library_path():
+    return _build.LIB_PATH
+
+
+def load() -> C.CDLL:
+    """Load (building first if the file is absent) the CUDA library; raises ImportError
+    when that is impossible.  Never substitutes another implementation."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    path = _build.LIB_PATH
+    if not path.exists():
+        try:
+            _build.build()
+        except Exception as e:  # noqa: BLE001
+            raise ImportError(
+                f"torch_projectors_b200: {path} is not built and building it failed ({e}); "
+                "run `python -m torch_projectors_b200.build` on a machine with nvcc") from e
+    try:
+        lib = C.CDLL(str(path))
+    except OSError as e:
+        raise ImportError(f"torch_projectors_b200: cannot load {path}: {e}") from e
+    for name, argtypes in SIGNATURES.items():
+        fn = getattr(lib, name)
+        fn.argtypes = argtypes
+        fn.restype = _int
+    lib.b200proj_version.restype = _int
+    lib.b200proj_version.argtypes = []
+    lib.b200proj_last_error.restype = C.c_char_p
+    lib.b200proj_last_error.argtypes = []
+    lib.b200proj_rec_boxsize.restype = _i64
+    lib.b200proj_rec_boxsize.argtypes = [_i64, _dbl]
+    _lib = lib
+    return lib
+
+
+def version() -> int:
+    return int(load().b200proj_version())
+
+
+def rec_boxsize(N: int, oversampling: float) -> int:
+    return int(load().b200proj_rec_boxsize(int(N), float(oversampling)))
+
+
+def _p(t: Optional[torch.Tensor]) -> int:
+    return 0 if t is None else t.data_ptr()
+
+
+def _call(name: str, anchor: torch.Tensor, *args) -> None:
+    """Invoke an entry point on the current stream of anchor's device."""
+    if not anchor.is_cuda:
+        raise RuntimeError(f"{name}: tensors must be on a CUDA device (there is no CPU path)")
+    lib = load()
+    with torch.cuda.device(anchor.device):
+        stream = torch.cuda.current_stream(anchor.device).cuda_stream
+        rc = getattr(lib, name)(*args, stream)
+    if rc != 0:
+        msg = lib.b200proj_last_error().decode("utf-8", "replace")
+        raise RuntimeError(f"{name}: {msg} (code {rc})")
+
+
+def _geom(B, R, rot, shifts, P, N, interp, oversampling, cutoff):
+    return (int(B), int(R), _p(rot), int(rot.shape[0]), _p(shifts),
+            int(shifts.shape[0]) if shifts is not None else 0, int(P), int(N), int(interp),
+            float(oversampling), float(cutoff))
+
+
+def project_forw(dim, rec, rot, shifts, P, N, interp, oversampling, cutoff, out):
+    name = "b200proj_project_2d_forw" if dim == 2 else "b200proj_project_3d_to_2d_forw"
+    B, R = rec.shape[0], rec.shape[-2]
+    _call(name, rec, _p(rec), *_geom(B, R, rot, shifts, P, N, interp, oversampling, cutoff), _p(out))
+
+
+def project_back(dim, grad_proj, rec, rot, shifts, P, N, interp, oversampling, cutoff,
+                 grad_rec, grad_rot, grad_shifts):
+    name = "b200proj_project_2d_back" if dim == 2 else "b200proj_project_3d_to_2d_back"
+    B, R = rec.shape[0], rec.shape[-2]
+    _call(name, rec, _p(grad_proj), _p(rec), *_geom(B, R, rot, shifts, P, N, interp, oversampling, cutoff),
+          _p(grad_rec), _p(grad_rot), _p(grad_shifts))
+
+
+def backproject_forw(dim, proj, weights, rot, shifts, interp, oversampling, cutoff,
+                     data_rec, weight_rec, accumulate):
+    name = "b200proj_backproject_2d_forw" if dim == 2 else "b200proj_backproject_2d_to_3d_forw"
+    B, P, N = proj.shape[0], proj.shape[1], proj.shape[2]
+    R = data_rec.shape[-2]
+    _call(name, proj, _p(proj), _p(weights), *_geom(B, R, rot, shifts, P, N, interp, oversampling, cutoff),
+          _p(data_rec), _p(weight_rec), int(bool(accumulate)))
+
+
+def backproject_back(dim, grad_data_rec, grad_weight_rec, proj, rot, shifts, interp, oversampling,
+                     cutoff, grad_proj, grad_weights, grad_rot, grad_shifts):
+    name = "b200proj_backproject_2d_back" if dim == 2 else "b200proj_backproject_2d_to_3d_back"
+    B, P, N = proj.shape[0], proj.shape[1], proj.shape[2]
+    R = grad_data_rec.shape[-2]
+    _call(name, proj, _p(grad_data_rec), _p(grad_weight_rec), _p(proj),
+          *_geom(B, R, rot, shifts, P, N, interp, oversampling, cutoff),
+          _p(grad_proj), _p(grad_weights), _p(grad_rot), _p(grad_shifts))

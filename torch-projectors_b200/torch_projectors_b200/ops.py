@@ -1,0 +1,529 @@
+"""Public API, autograd glue and raw-operator registration.
+
+The seven public functions and the eight raw operators keep the names, argument lists,
+defaults and error behaviour of warpem/torch-projectors (``torch_projectors/ops.py`` and
+``csrc/torch_projectors.cpp:23-36`` in the reference) so that user code switches by
+changing the import.  The raw operators are registered under the op namespace
+``torch_projectors_b200`` for the CUDA dispatch key only: calling them with CPU (or MPS)
+tensors raises from the dispatcher -- there is no CPU fallback.  complex128 / float64
+inputs, which the reference's CUDA wrappers silently route through its CPU kernels
+(``csrc/cuda/3d/projection_3d_to_2d_kernels.cu:902-918``), raise ``RuntimeError`` here.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from . import _abi
+
+NAMESPACE = "torch_projectors_b200"
+
+# ---------------------------------------------------------------------------------------
+# raw operators (schemas verbatim from the reference: csrc/torch_projectors.cpp:23-36)
+# ---------------------------------------------------------------------------------------
+_lib = torch.library.Library(NAMESPACE, "DEF")
+_PROJECT_FORW = "(Tensor reconstruction, Tensor rotations, Tensor? shifts, int[] output_shape, str interpolation, float oversampling, float? fourier_radius_cutoff) -> Tensor"
+_PROJECT_BACK = "(Tensor grad_projections, Tensor reconstruction, Tensor rotations, Tensor? shifts, str interpolation, float oversampling, float? fourier_radius_cutoff) -> (Tensor, Tensor, Tensor)"
+_BACKPROJECT_FORW = "(Tensor projections, Tensor? weights, Tensor rotations, Tensor? shifts, str interpolation, float oversampling, float? fourier_radius_cutoff) -> (Tensor, Tensor)"
+_BACKPROJECT_BACK = "(Tensor grad_data_rec, Tensor? grad_weight_rec, Tensor projections, Tensor? weights, Tensor rotations, Tensor? shifts, str interpolation, float oversampling, float? fourier_radius_cutoff) -> (Tensor, Tensor, Tensor, Tensor)"
+_lib.define("project_2d_forw" + _PROJECT_FORW)
+_lib.define("project_2d_back" + _PROJECT_BACK)
+_lib.define("backproject_2d_forw" + _BACKPROJECT_FORW)
+_lib.define("backproject_2d_back" + _BACKPROJECT_BACK)
+_lib.define("project_3d_to_2d_forw" + _PROJECT_FORW)
+_lib.define("project_3d_to_2d_back" + _PROJECT_BACK)
+_lib.define("backproject_2d_to_3d_forw" + _BACKPROJECT_FORW)
+_lib.define("backproject_2d_to_3d_back" + _BACKPROJECT_BACK)
+
+
+def _check(cond: bool, msg: str) -> None:
+    if not cond:
+        raise RuntimeError(msg)
+
+
+def _interp_code(interpolation: str) -> int:
+    _check(interpolation in ("linear", "cubic"), "Supported interpolation methods: 'linear', 'cubic'")
+    return _abi.CUBIC if interpolation == "cubic" else _abi.LINEAR
+
+
+def _check_fp32(name: str, t: torch.Tensor, complex_: bool) -> None:
+    want = torch.complex64 if complex_ else torch.float32
+    if t.dtype != want:
+        raise RuntimeError(
+            f"{name} has dtype {t.dtype}; the B200 kernels compute in "
+            f"{'complex64' if complex_ else 'float32'} only and there is no CPU fallback for other precisions")
+
+
+def _check_pose_inputs(dim: int, what: str, B: int, rotations, shifts, like: torch.Tensor):
+    """Shape / device / dtype checks shared by all operators; returns (P, rot, shifts)
+    as contiguous tensors (expanded or sliced pose tensors are legal inputs)."""
+    _check(rotations.is_cuda, "Input rotations must be on CUDA device")
+    _check(rotations.dim() == 4 and rotations.size(2) == dim and rotations.size(3) == dim,
+           f"Rotations must be (B_rot, P, {dim}, {dim})")
+    _check(rotations.device == like.device, "rotations must be on the same device as the data")
+    _check_fp32("rotations", rotations, False)
+    B_rot, P = rotations.size(0), rotations.size(1)
+    _check(B_rot == B or B_rot == 1, f"Batch size of rotations must be 1 or same as {what}")
+    if shifts is not None:
+        _check(shifts.is_cuda, "Shifts must be on CUDA device")
+        _check(shifts.dim() == 3, "Shifts must be (B_shift, P, 2)")
+        _check(shifts.size(2) == 2, "Shifts must have 2 components (x, y)")
+        _check(shifts.size(0) == B or shifts.size(0) == 1, f"Batch size of shifts must be 1 or same as {what}")
+        _check(shifts.size(1) == P, "Number of poses in shifts must match rotations")
+        _check(shifts.dtype == rotations.dtype, "Shifts and rotations must have the same dtype")
+        _check(shifts.device == like.device, "shifts must be on the same device as the data")
+        shifts = shifts.contiguous()
+    return P, rotations.contiguous(), shifts
+
+
+def _cutoff(fourier_radius_cutoff: Optional[float], N: int) -> float:
+    # default: Nyquist radius of the projection (reference: projection_3d_to_2d_kernels.cu:892)
+    return float(fourier_radius_cutoff) if fourier_radius_cutoff is not None else N / 2.0
+
+
+def _rec_dims_ok(dim: int, rec: torch.Tensor) -> None:
+    _check(rec.dim() == dim + 1, f"Reconstruction must have {dim + 1} dimensions")
+    R, Rh = rec.size(-2), rec.size(-1)
+    _check(R % 2 == 0 and Rh == R // 2 + 1, f"Reconstruction must be rfft-shaped with an even box (got {tuple(rec.shape)})")
+    if dim == 3:
+        _check(rec.size(1) == R, "Reconstruction volume must be cubic (depth == height)")
+
+
+def _project_forw_impl(dim, reconstruction, rotations, shifts, output_shape, interpolation,
+                       oversampling, fourier_radius_cutoff):
+    _check(reconstruction.is_cuda, "Input reconstruction must be on CUDA device")
+    _check(reconstruction.is_complex(), "Reconstruction must be a complex tensor")
+    interp = _interp_code(interpolation)
+    _rec_dims_ok(dim, reconstruction)
+    _check_fp32("reconstruction", reconstruction, True)
+    B = reconstruction.size(0)
+    P, rot, sh = _check_pose_inputs(dim, "reconstruction", B, rotations, shifts, reconstruction)
+    _check(len(output_shape) >= 1, "output_shape must have at least one element")
+    N = int(output_shape[0])          # only element 0 is used, as in the reference
+    _check(N >= 2 and N % 2 == 0, f"Output boxsize {N} must be even")
+    rec = reconstruction.contiguous()
+    out = torch.empty((B, P, N, N // 2 + 1), dtype=rec.dtype, device=rec.device)
+    if out.numel():
+        _abi.project_forw(dim, rec, rot, sh, P, N, interp, oversampling, _cutoff(fourier_radius_cutoff, N), out)
+    return out
+
+
+def _project_back_impl(dim, grad_projections, reconstruction, rotations, shifts, interpolation,
+                       oversampling, fourier_radius_cutoff):
+    _check(grad_projections.is_cuda, "Input grad_projections must be on CUDA device")
+    _check(reconstruction.is_cuda, "Input reconstruction must be on CUDA device")
+    _check(grad_projections.is_complex(), "Projections must be a complex tensor")
+    _check(reconstruction.is_complex(), "Reconstruction must be a complex tensor")
+    interp = _interp_code(interpolation)
+    _check(grad_projections.dim() == 4, "Projections must be a 4D tensor (B, P, H, W/2+1)")
+    _rec_dims_ok(dim, reconstruction)
+    _check_fp32("grad_projections", grad_projections, True)
+    _check_fp32("reconstruction", reconstruction, True)
+    B, P_g, N, Nh = grad_projections.shape
+    _check(N % 2 == 0 and Nh == N // 2 + 1, "grad_projections must be rfft-shaped with an even box")
+    _check(reconstruction.size(0) == B, "Batch size of grad_projections must match reconstruction")
+    P, rot, sh = _check_pose_inputs(dim, "reconstruction", B, rotations, shifts, reconstruction)
+    _check(P == P_g, "Number of poses in rotations must match grad_projections")
+    need_rot = rotations.requires_grad
+    need_shift = shifts is not None and shifts.requires_grad
+    gp = grad_projections.contiguous()
+    rec = reconstruction.contiguous()
+    dev = rec.device
+    grad_rec = torch.empty_like(rec)                      # zero-filled by the library call
+    grad_rot = torch.empty(rot.shape, dtype=rot.dtype, device=dev) if need_rot else None
+    grad_sh = torch.empty(sh.shape, dtype=sh.dtype, device=dev) if need_shift else None
+    _abi.project_back(dim, gp, rec, rot, sh, P, N, interp, oversampling,
+                      _cutoff(fourier_radius_cutoff, N), grad_rec, grad_rot, grad_sh)
+    empty = lambda: torch.empty((0,), dtype=rot.dtype, device=dev)  # noqa: E731
+    return grad_rec, (grad_rot if need_rot else empty()), (grad_sh if need_shift else empty())
+
+
+def _backproject_forw_impl(dim, projections, weights, rotations, shifts, interpolation,
+                           oversampling, fourier_radius_cutoff):
+    _check(projections.is_cuda, "Input projections must be on CUDA device")
+    _check(projections.is_complex(), "Projections must be a complex tensor")
+    interp = _interp_code(interpolation)
+    _check(projections.dim() == 4, "Projections must be (B, P, height, width/2+1)")
+    _check_fp32("projections", projections, True)
+    B, P_p, N, Nh = projections.shape
+    _check(N % 2 == 0 and Nh == N // 2 + 1, "projections must be rfft-shaped with an even box")
+    if weights is not None:
+        _check(weights.is_cuda, "Weights must be on CUDA device")
+        _check(weights.is_floating_point(), "Weights must be a real-valued tensor")
+        _check(weights.dim() == 4, "Weights must be (B, P, height, width/2+1)")
+        _check(weights.shape == projections.shape, "Weights and projections must have the same shape")
+        _check_fp32("weights", weights, False)
+        weights = weights.contiguous()
+    P, rot, sh = _check_pose_inputs(dim, "projections", B, rotations, shifts, projections)
+    _check(P == P_p, "Number of poses in rotations must match projections")
+    proj = projections.contiguous()
+    dev = proj.device
+    R = _abi.rec_boxsize(N, oversampling)
+    shape = (B, R, R, R // 2 + 1) if dim == 3 else (B, R, R // 2 + 1)
+    data_rec = torch.empty(shape, dtype=proj.dtype, device=dev)          # zero-filled by the call
+    weight_rec = torch.empty(shape, dtype=torch.float32, device=dev) if weights is not None else None
+    _abi.backproject_forw(dim, proj, weights, rot, sh, interp, oversampling,
+                          _cutoff(fourier_radius_cutoff, N), data_rec, weight_rec, False)
+    if weight_rec is None:
+        weight_rec = torch.empty((0,), dtype=rot.dtype, device=dev)
+    return data_rec, weight_rec
+
+
+def _backproject_back_impl(dim, grad_data_rec, grad_weight_rec, projections, weights, rotations,
+                           shifts, interpolation, oversampling, fourier_radius_cutoff):
+    _check(grad_data_rec.is_cuda, "Input grad_data_rec must be on CUDA device")
+    _check(projections.is_cuda, "Input projections must be on CUDA device")
+    _check(grad_data_rec.is_complex(), "grad_data_rec must be a complex tensor")
+    _check(projections.is_complex(), "projections must be a complex tensor")
+    interp = _interp_code(interpolation)
+    _check(grad_data_rec.dim() == dim + 1, "grad_data_rec must be (B, D, H, W/2+1)" if dim == 3 else "grad_data_rec must be (B, H, W/2+1)")
+    _check(projections.dim() == 4, "projections must be a 4D tensor (B, P, boxsize, boxsize/2+1)")
+    _check_fp32("grad_data_rec", grad_data_rec, True)
+    _check_fp32("projections", projections, True)
+    B, P_p, N, Nh = projections.shape
+    if grad_weight_rec is not None:
+        _check(grad_weight_rec.is_cuda, "grad_weight_rec must be on CUDA device")
+        _check(grad_weight_rec.is_floating_point(), "grad_weight_rec must be a real-valued tensor")
+        _check(grad_weight_rec.shape == grad_data_rec.shape, "grad_weight_rec and grad_data_rec must have same shape")
+        _check_fp32("grad_weight_rec", grad_weight_rec, False)
+        grad_weight_rec = grad_weight_rec.contiguous()
+    R = _abi.rec_boxsize(N, oversampling)
+    want = (B, R, R, R // 2 + 1) if dim == 3 else (B, R, R // 2 + 1)
+    _check(tuple(grad_data_rec.shape) == want, "grad_data_rec shape must match expected reconstruction size")
+    if weights is not None:
+        _check(weights.is_cuda, "weights must be on CUDA device")
+    P, rot, sh = _check_pose_inputs(dim, "projections", B, rotations, shifts, projections)
+    _check(P == P_p, "Number of poses in rotations must match projections")
+    need_rot = rotations.requires_grad
+    need_shift = shifts is not None and shifts.requires_grad
+    gd = grad_data_rec.contiguous()
+    proj = projections.contiguous()
+    dev = proj.device
+    grad_proj = torch.empty_like(proj)
+    grad_w = torch.empty(proj.shape, dtype=torch.float32, device=dev) if weights is not None else None
+    grad_rot = torch.empty(rot.shape, dtype=rot.dtype, device=dev) if need_rot else None
+    grad_sh = torch.empty(sh.shape, dtype=sh.dtype, device=dev) if need_shift else None
+    if proj.numel():
+        _abi.backproject_back(dim, gd, grad_weight_rec, proj, rot, sh, interp, oversampling,
+                              _cutoff(fourier_radius_cutoff, N), grad_proj, grad_w, grad_rot, grad_sh)
+    empty = lambda: torch.empty((0,), dtype=rot.dtype, device=dev)  # noqa: E731
+    return (grad_proj, (grad_w if grad_w is not None else empty()),
+            (grad_rot if need_rot else empty()), (grad_sh if need_shift else empty()))
+
+
+def _register(name, dim, impl):
+    def cuda_impl(*args):
+        return impl(dim, *args)
+    cuda_impl.__name__ = f"{name}_cuda"
+    _lib.impl(name, cuda_impl, "CUDA")
+
+
+_register("project_2d_forw", 2, _project_forw_impl)
+_register("project_2d_back", 2, _project_back_impl)
+_register("backproject_2d_forw", 2, _backproject_forw_impl)
+_register("backproject_2d_back", 2, _backproject_back_impl)
+_register("project_3d_to_2d_forw", 3, _project_forw_impl)
+_register("project_3d_to_2d_back", 3, _project_back_impl)
+_register("backproject_2d_to_3d_forw", 3, _backproject_forw_impl)
+_register("backproject_2d_to_3d_back", 3, _backproject_back_impl)
+
+_ops = getattr(torch.ops, NAMESPACE)
+
+
+# ---------------------------------------------------------------------------------------
+# public functions (reference: torch_projectors/ops.py:6-296)
+# ---------------------------------------------------------------------------------------
+def _validate_rec_box(boxsize: int, boxsize_half: int) -> None:
+    if boxsize % 2 != 0:
+        raise ValueError(f"Boxsize ({boxsize}) must be even. Only even dimensions are supported.")
+    if boxsize != (boxsize_half - 1) * 2:
+        raise ValueError(f"Reconstruction shape mismatch: expected boxsize {boxsize} to match 2*(boxsize_half-1) = {(boxsize_half - 1) * 2}")
+
+
+def _validate_output_shape(output_shape, boxsize: int):
+    if output_shape is None:
+        return (boxsize, boxsize)
+    if len(output_shape) != 2 or output_shape[0] != output_shape[1]:
+        raise ValueError(f"Output shape {output_shape} must be square (height == width)")
+    if output_shape[0] % 2 != 0:
+        raise ValueError(f"Output boxsize {output_shape[0]} must be even")
+    return output_shape
+
+
+def _validate_projections(projections, weights) -> None:
+    if projections.dim() != 4:
+        raise ValueError("Projections must be a 4D tensor (B, P, height, width/2+1)")
+    _, _, proj_boxsize, proj_boxsize_half = projections.shape
+    if proj_boxsize % 2 != 0:
+        raise ValueError(f"Projection boxsize ({proj_boxsize}) must be even. Only even dimensions are supported.")
+    if proj_boxsize != (proj_boxsize_half - 1) * 2:
+        raise ValueError(f"Projection shape mismatch: expected boxsize {proj_boxsize} to match 2*(boxsize_half-1) = {(proj_boxsize_half - 1) * 2}")
+    if weights is not None:
+        if weights.shape != projections.shape:
+            raise ValueError(f"Weights shape {weights.shape} must match projections shape {projections.shape}")
+        if not weights.is_floating_point():
+            raise ValueError("Weights must be real-valued (floating point)")
+
+
+def project_2d_forw(reconstruction: torch.Tensor, rotations: torch.Tensor,
+                    shifts: Optional[torch.Tensor] = None,
+                    output_shape: Optional[tuple[int, ...]] = None,
+                    interpolation: str = "linear", oversampling: float = 1.0,
+                    fourier_radius_cutoff: Optional[float] = None) -> torch.Tensor:
+    """Sample P rotated 2D rfft images from 2D rfft reconstructions [B, H, W/2+1]
+    -> [B, P, H_out, W_out/2+1].  (reference: torch_projectors/ops.py:6-38)"""
+    if reconstruction.dim() < 2:
+        raise ValueError("Reconstruction must have at least 2 dimensions")
+    _validate_rec_box(reconstruction.shape[-2], reconstruction.shape[-1])
+    output_shape = _validate_output_shape(output_shape, reconstruction.shape[-2])
+    return _Project2D.apply(reconstruction, rotations, shifts, output_shape, interpolation,
+                            oversampling, fourier_radius_cutoff)
+
+
+def project_2d_back(projections: torch.Tensor, reconstruction: torch.Tensor,
+                    rotations: torch.Tensor, shifts: Optional[torch.Tensor] = None,
+                    interpolation: str = "linear", oversampling: float = 1.0) -> torch.Tensor:
+    """Gradient of ``project_2d_forw`` w.r.t. the reconstruction only.
+    (reference: torch_projectors/ops.py:40-59)"""
+    grad_reconstruction, _, _ = _ops.project_2d_back(
+        projections, reconstruction, rotations, shifts, interpolation, oversampling, None)
+    return grad_reconstruction
+
+
+def backproject_2d_forw(projections: torch.Tensor, rotations: torch.Tensor,
+                        weights: Optional[torch.Tensor] = None,
+                        shifts: Optional[torch.Tensor] = None, interpolation: str = "linear",
+                        oversampling: float = 1.0,
+                        fourier_radius_cutoff: Optional[float] = None
+                        ) -> tuple[torch.Tensor, torch.Tensor]:
+    """Adjoint of ``project_2d_forw``: accumulate projections [B, P, H, W/2+1] (and optional
+    real weights) into 2D rfft reconstructions.  Returns (data, weights); the second is an
+    empty ``(0,)`` tensor without weights.  (reference: torch_projectors/ops.py:61-117)"""
+    _validate_projections(projections, weights)
+    return _Backproject2D.apply(projections, weights, rotations, shifts, interpolation,
+                                oversampling, fourier_radius_cutoff)
+
+
+def project_3d_to_2d_forw(reconstruction: torch.Tensor, rotations: torch.Tensor,
+                          shifts: Optional[torch.Tensor] = None,
+                          output_shape: Optional[tuple[int, ...]] = None,
+                          interpolation: str = "linear", oversampling: float = 1.0,
+                          fourier_radius_cutoff: Optional[float] = None) -> torch.Tensor:
+    """Sample P rotated central slices from 3D rfft volumes [B, D, H, W/2+1]
+    -> [B, P, H_out, W_out/2+1].  (reference: torch_projectors/ops.py:119-174)"""
+    if reconstruction.dim() != 4:
+        raise ValueError("Reconstruction must be a 4D tensor (B, D, H, W/2+1)")
+    _validate_rec_box(reconstruction.shape[2], reconstruction.shape[3])
+    output_shape = _validate_output_shape(output_shape, reconstruction.shape[2])
+    return _Project3DTo2D.apply(reconstruction, rotations, shifts, output_shape, interpolation,
+                                oversampling, fourier_radius_cutoff)
+
+
+def project_3d_to_2d_back(projections: torch.Tensor, reconstruction: torch.Tensor,
+                          rotations: torch.Tensor, shifts: Optional[torch.Tensor] = None,
+                          interpolation: str = "linear", oversampling: float = 1.0) -> torch.Tensor:
+    """Gradient of ``project_3d_to_2d_forw`` w.r.t. the volume only.
+    (reference: torch_projectors/ops.py:176-206)"""
+    grad_reconstruction, _, _ = _ops.project_3d_to_2d_back(
+        projections, reconstruction, rotations, shifts, interpolation, oversampling, None)
+    return grad_reconstruction
+
+
+def backproject_2d_to_3d_forw(projections: torch.Tensor, rotations: torch.Tensor,
+                              weights: Optional[torch.Tensor] = None,
+                              shifts: Optional[torch.Tensor] = None,
+                              interpolation: str = "linear", oversampling: float = 1.0,
+                              fourier_radius_cutoff: Optional[float] = None
+                              ) -> tuple[torch.Tensor, torch.Tensor]:
+    """Adjoint of ``project_3d_to_2d_forw``: accumulate 2D slices (and optional real weights)
+    into cubic 3D rfft volumes of box ceil(N*oversampling) rounded up to even.
+    (reference: torch_projectors/ops.py:208-264)"""
+    _validate_projections(projections, weights)
+    return _Backproject2DTo3D.apply(projections, weights, rotations, shifts, interpolation,
+                                    oversampling, fourier_radius_cutoff)
+
+
+def backproject_2d_to_3d_back(reconstruction: torch.Tensor, projections: torch.Tensor,
+                              rotations: torch.Tensor, shifts: Optional[torch.Tensor] = None,
+                              interpolation: str = "linear", oversampling: float = 1.0) -> torch.Tensor:
+    """Gradient of ``backproject_2d_to_3d_forw`` w.r.t. the projections only, given the
+    gradient of the data volume.  (reference: torch_projectors/ops.py:266-296; the reference
+    wrapper passes 7 arguments to a 9-argument operator and cannot run -- this one passes
+    ``None`` for the weight-related arguments, which is what its docstring describes.)"""
+    grad_projections, _, _, _ = _ops.backproject_2d_to_3d_back(
+        reconstruction, None, projections, None, rotations, shifts, interpolation, oversampling, None)
+    return grad_projections
+
+
+def backproject_2d_to_3d_accumulate_(data_rec: torch.Tensor, weight_rec: Optional[torch.Tensor],
+                                     projections: torch.Tensor, rotations: torch.Tensor,
+                                     weights: Optional[torch.Tensor] = None,
+                                     shifts: Optional[torch.Tensor] = None,
+                                     interpolation: str = "linear", oversampling: float = 1.0,
+                                     fourier_radius_cutoff: Optional[float] = None) -> None:
+    """In-place streaming variant of ``backproject_2d_to_3d_forw`` (no autograd): adds the
+    given chunk of projections into existing volumes instead of returning fresh ones, so
+    that many chunks accumulate without a per-chunk volume-sized sum.  Not in the reference
+    API; its callers sum per-call outputs
+    (tests/3d/back/test_performance_back_2d_to_3d.py:357-369 there)."""
+    _validate_projections(projections, weights)
+    if projections.dim() == 4 and rotations.dim() == 3:
+        rotations = rotations.unsqueeze(0)
+    if shifts is not None and shifts.dim() == 2:
+        shifts = shifts.unsqueeze(0)
+    _check(projections.is_cuda and projections.dtype == torch.complex64, "projections must be CUDA complex64")
+    B, P_p, N, _ = projections.shape
+    interp = _interp_code(interpolation)
+    if weights is not None:
+        _check(weight_rec is not None, "weights given but weight_rec is None")
+        _check(weights.is_cuda, "Weights must be on CUDA device")
+        _check_fp32("weights", weights, False)
+        weights = weights.contiguous()
+    P, rot, sh = _check_pose_inputs(3, "projections", B, rotations, shifts, projections)
+    _check(P == P_p, "Number of poses in rotations must match projections")
+    R = _abi.rec_boxsize(N, oversampling)
+    want = (B, R, R, R // 2 + 1)
+    _check(tuple(data_rec.shape) == want and data_rec.dtype == torch.complex64 and data_rec.is_contiguous()
+           and data_rec.device == projections.device, f"data_rec must be a contiguous complex64 tensor of shape {want}")
+    if weights is not None:
+        _check(tuple(weight_rec.shape) == want and weight_rec.dtype == torch.float32 and weight_rec.is_contiguous()
+               and weight_rec.device == projections.device, f"weight_rec must be a contiguous float32 tensor of shape {want}")
+    _abi.backproject_forw(3, projections.contiguous(), weights, rot, sh, interp, oversampling,
+                          _cutoff(fourier_radius_cutoff, N), data_rec,
+                          weight_rec if weights is not None else None, True)
+
+
+# ---------------------------------------------------------------------------------------
+# autograd glue (reference: torch_projectors/ops.py:300-514)
+# ---------------------------------------------------------------------------------------
+def _canon_poses(rotations, shifts):
+    if rotations.dim() == 2:
+        rotations = rotations.unsqueeze(0)
+    if rotations.dim() == 3:
+        rotations = rotations.unsqueeze(0)
+    if shifts is not None:
+        if shifts.dim() == 1:
+            shifts = shifts.unsqueeze(0)
+        if shifts.dim() == 2:
+            shifts = shifts.unsqueeze(0)
+    return rotations, shifts
+
+
+class _ProjectBase(torch.autograd.Function):
+    _rec_rank = 0          # rank of an un-batched reconstruction
+    _forw = None
+    _back = None
+
+    @classmethod
+    def _run_forward(cls, ctx, reconstruction, rotations, shifts, output_shape, interpolation,
+                     oversampling, fourier_radius_cutoff):
+        if reconstruction.dim() == cls._rec_rank:
+            reconstruction = reconstruction.unsqueeze(0)
+        rotations, shifts = _canon_poses(rotations, shifts)
+        if rotations.size(0) != reconstruction.size(0) and rotations.size(0) != 1:
+            raise ValueError("Batch size of rotations must be 1 or match reconstruction")
+        projection = getattr(_ops, cls._forw)(reconstruction, rotations, shifts, output_shape,
+                                              interpolation, oversampling, fourier_radius_cutoff)
+        ctx.save_for_backward(reconstruction, rotations, shifts)
+        ctx.interpolation = interpolation
+        ctx.oversampling = oversampling
+        ctx.fourier_radius_cutoff = fourier_radius_cutoff
+        return projection
+
+    @classmethod
+    def _run_backward(cls, ctx, grad_output):
+        reconstruction, rotations, shifts = ctx.saved_tensors
+        grad_reconstruction, grad_rotations, grad_shifts = getattr(_ops, cls._back)(
+            grad_output.contiguous(), reconstruction, rotations, shifts, ctx.interpolation,
+            ctx.oversampling, ctx.fourier_radius_cutoff)
+        if shifts is None:
+            grad_shifts = None
+        return grad_reconstruction, grad_rotations, grad_shifts, None, None, None, None
+
+
+class _Project2D(_ProjectBase):
+    _rec_rank, _forw, _back = 2, "project_2d_forw", "project_2d_back"
+
+    @staticmethod
+    def forward(ctx, *args):
+        return _Project2D._run_forward(ctx, *args)
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        return _Project2D._run_backward(ctx, grad_output)
+
+
+class _Project3DTo2D(_ProjectBase):
+    _rec_rank, _forw, _back = 3, "project_3d_to_2d_forw", "project_3d_to_2d_back"
+
+    @staticmethod
+    def forward(ctx, *args):
+        return _Project3DTo2D._run_forward(ctx, *args)
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        return _Project3DTo2D._run_backward(ctx, grad_output)
+
+
+class _BackprojectBase(torch.autograd.Function):
+    _forw = None
+    _back = None
+
+    @classmethod
+    def _run_forward(cls, ctx, projections, weights, rotations, shifts, interpolation,
+                     oversampling, fourier_radius_cutoff):
+        if projections.dim() == 3:
+            projections = projections.unsqueeze(0)
+        rotations, shifts = _canon_poses(rotations, shifts)
+        if weights is not None and weights.dim() == 3:
+            weights = weights.unsqueeze(0)
+        if rotations.size(0) != projections.size(0) and rotations.size(0) != 1:
+            raise ValueError("Batch size of rotations must be 1 or match projections")
+        data_reconstruction, weight_reconstruction = getattr(_ops, cls._forw)(
+            projections, weights, rotations, shifts, interpolation, oversampling, fourier_radius_cutoff)
+        ctx.save_for_backward(projections, weights, rotations, shifts)
+        ctx.interpolation = interpolation
+        ctx.oversampling = oversampling
+        ctx.fourier_radius_cutoff = fourier_radius_cutoff
+        return data_reconstruction, weight_reconstruction
+
+    @classmethod
+    def _run_backward(cls, ctx, grad_data_rec, grad_weight_rec):
+        projections, weights, rotations, shifts = ctx.saved_tensors
+        if grad_weight_rec is not None and grad_weight_rec.numel() == 0:
+            grad_weight_rec = None
+        grad_projections, grad_weights, grad_rotations, grad_shifts = getattr(_ops, cls._back)(
+            grad_data_rec.contiguous(),
+            grad_weight_rec.contiguous() if grad_weight_rec is not None else None,
+            projections, weights, rotations, shifts, ctx.interpolation, ctx.oversampling,
+            ctx.fourier_radius_cutoff)
+        if weights is None:
+            grad_weights = None
+        if shifts is None:
+            grad_shifts = None
+        return grad_projections, grad_weights, grad_rotations, grad_shifts, None, None, None
+
+
+class _Backproject2D(_BackprojectBase):
+    _forw, _back = "backproject_2d_forw", "backproject_2d_back"
+
+    @staticmethod
+    def forward(ctx, *args):
+        return _Backproject2D._run_forward(ctx, *args)
+
+    @staticmethod
+    def backward(ctx, grad_data_rec, grad_weight_rec):
+        return _Backproject2D._run_backward(ctx, grad_data_rec, grad_weight_rec)
+
+
+class _Backproject2DTo3D(_BackprojectBase):
+    _forw, _back = "backproject_2d_to_3d_forw", "backproject_2d_to_3d_back"
+
+    @staticmethod
+    def forward(ctx, *args):
+        return _Backproject2DTo3D._run_forward(ctx, *args)
+
+    @staticmethod
+    def backward(ctx, grad_data_rec, grad_weight_rec):
+        return _Backproject2DTo3D._run_backward(ctx, grad_data_rec, grad_weight_rec)

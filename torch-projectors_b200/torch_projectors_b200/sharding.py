@@ -1,0 +1,140 @@
+"""Pose sharding across the GPUs of one node (one process per GPU, ``torch.distributed``).
+
+The Fourier-slice path shards over poses: every slice is independent in projection, and
+back-projection is a sum over slices.
+
+* projection: the volume is replicated, each rank projects its own contiguous range of
+  poses; no collective is needed (an all-gather is offered for callers that want every
+  projection on every rank).
+* back-projection: each rank accumulates its slices into its own partial data and weight
+  volumes, which live side by side in ONE float32 buffer so that a single NCCL reduce
+  (or all-reduce) over NVLink combines both.  Partial volumes are final only after the
+  rank's last slice, so the collective is a tail, not something to overlap tile by tile.
+
+The reference has no multi-GPU layer; this module is new.  The compute callables are
+parameters (defaulting to the CUDA operators of this package) so that the host logic --
+ranges, buffer layout, collectives -- can be exercised with ``gloo`` on CPU ranks.
+"""
+from __future__ import annotations
+
+from typing import Callable, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+
+def pose_range(num_poses: int, rank: int, world_size: int) -> Tuple[int, int]:
+    """Contiguous, balanced [start, stop) range of poses owned by `rank`: the first
+    ``num_poses % world_size`` ranks hold one extra pose."""
+    if world_size < 1 or not (0 <= rank < world_size):
+        raise ValueError(f"bad rank {rank} / world_size {world_size}")
+    if num_poses < 0:
+        raise ValueError("num_poses must be >= 0")
+    base, extra = divmod(num_poses, world_size)
+    start = rank * base + min(rank, extra)
+    return start, start + base + (1 if rank < extra else 0)
+
+
+def _world(group) -> Tuple[int, int]:
+    if dist.is_available() and dist.is_initialized():
+        return dist.get_rank(group), dist.get_world_size(group)
+    return 0, 1
+
+
+def project_3d_to_2d_sharded(reconstruction: torch.Tensor, rotations: torch.Tensor,
+                             shifts: Optional[torch.Tensor] = None, *, group=None,
+                             gather: bool = False, project_fn: Optional[Callable] = None,
+                             **kwargs) -> torch.Tensor:
+    """Project this rank's range of the GLOBAL pose list.
+
+    rotations [B_rot, P, 3, 3] and shifts [B_s, P, 2] hold all P poses on every rank; the
+    volume must already be replicated (e.g. ``dist.broadcast`` once, or built from the
+    same seed).  Returns [B, P_local, N, Nh], or with ``gather=True`` the concatenation
+    over ranks [B, P, N, Nh] on every rank.
+    """
+    if project_fn is None:
+        from .ops import project_3d_to_2d_forw as project_fn
+    rank, world = _world(group)
+    if rotations.dim() == 3:
+        rotations = rotations.unsqueeze(0)
+    if shifts is not None and shifts.dim() == 2:
+        shifts = shifts.unsqueeze(0)
+    P = rotations.shape[1]
+    lo, hi = pose_range(P, rank, world)
+    local = project_fn(reconstruction, rotations[:, lo:hi],
+                       shifts[:, lo:hi] if shifts is not None else None, **kwargs)
+    if not gather or world == 1:
+        return local
+    # ranks may hold different pose counts: pad to the largest share, gather, trim
+    counts = [pose_range(P, r, world)[1] - pose_range(P, r, world)[0] for r in range(world)]
+    pmax = max(counts)
+    B, _, N, Nh = local.shape
+    padded = torch.zeros((B, pmax, N, Nh), dtype=local.dtype, device=local.device)
+    padded[:, : hi - lo] = local
+    parts = [torch.empty_like(padded) for _ in range(world)]
+    dist.all_gather(parts, padded, group=group)
+    return torch.cat([part[:, :n] for part, n in zip(parts, counts)], dim=1)
+
+
+class PartialVolumes:
+    """Data (complex64) and weight (float32) volumes of one rank, adjacent in one float32
+    buffer: [ data.re/im interleaved | weights ], so one collective reduces both."""
+
+    def __init__(self, batch: int, box: int, device, with_weights: bool = True):
+        self.shape = (batch, box, box, box // 2 + 1)
+        n = batch * box * box * (box // 2 + 1)
+        self.flat = torch.zeros(n * (3 if with_weights else 2), dtype=torch.float32, device=device)
+        self.data = torch.view_as_complex(self.flat[: 2 * n].view(*self.shape, 2))
+        self.weights = self.flat[2 * n:].view(self.shape) if with_weights else None
+
+    def reduce(self, dst: Optional[int] = 0, group=None) -> None:
+        """Sum the partial volumes over ranks: onto rank `dst`, or onto every rank when
+        dst is None.  No-op outside an initialised process group."""
+        _, world = _world(group)
+        if world == 1:
+            return
+        if dst is None:
+            dist.all_reduce(self.flat, op=dist.ReduceOp.SUM, group=group)
+        else:
+            dist.reduce(self.flat, dst=dst, op=dist.ReduceOp.SUM, group=group)
+
+
+def backproject_2d_to_3d_sharded(projections: torch.Tensor, rotations: torch.Tensor,
+                                 weights: Optional[torch.Tensor] = None,
+                                 shifts: Optional[torch.Tensor] = None, *,
+                                 interpolation: str = "linear", oversampling: float = 1.0,
+                                 fourier_radius_cutoff: Optional[float] = None,
+                                 chunk: int = 8192, dst: Optional[int] = 0, group=None,
+                                 into: Optional[PartialVolumes] = None, reduce: bool = True,
+                                 accumulate_fn: Optional[Callable] = None,
+                                 rec_boxsize_fn: Optional[Callable] = None) -> PartialVolumes:
+    """Back-project this rank's LOCAL slices [B, P_local, N, Nh] into its partial volumes
+    in chunks of `chunk` poses, then (``reduce=True``) combine the ranks' partial volumes
+    with one reduce.  Pass ``into=`` to keep accumulating into existing partial volumes
+    over several calls and ``reduce=False`` to postpone the collective to the last call.
+    """
+    if accumulate_fn is None:
+        from .ops import backproject_2d_to_3d_accumulate_ as accumulate_fn
+    if rec_boxsize_fn is None:
+        from ._abi import rec_boxsize as rec_boxsize_fn
+    if projections.dim() != 4:
+        raise ValueError("Projections must be a 4D tensor (B, P, height, width/2+1)")
+    if rotations.dim() == 3:
+        rotations = rotations.unsqueeze(0)
+    if shifts is not None and shifts.dim() == 2:
+        shifts = shifts.unsqueeze(0)
+    B, P, N, _ = projections.shape
+    vols = into
+    if vols is None:
+        vols = PartialVolumes(B, rec_boxsize_fn(N, oversampling), projections.device,
+                              with_weights=weights is not None)
+    for lo in range(0, P, max(1, chunk)):
+        hi = min(P, lo + chunk)
+        accumulate_fn(vols.data, vols.weights, projections[:, lo:hi], rotations[:, lo:hi],
+                      weights[:, lo:hi] if weights is not None else None,
+                      shifts[:, lo:hi] if shifts is not None else None,
+                      interpolation=interpolation, oversampling=oversampling,
+                      fourier_radius_cutoff=fourier_radius_cutoff)
+    if reduce:
+        vols.reduce(dst=dst, group=group)
+    return vols
