@@ -1,0 +1,404 @@
+#!/usr/bin/env python
+"""Benchmark of the Fourier-slice hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Headline workload (one "step" = one pass of the operator over all poses of the batch):
+``project_3d_to_2d_forw`` on a box-256 volume (a 128^3 map zero-padded 2x, fftshifted and
+rfftn'd to [1,256,256,129] complex64), 10,000 uniform-SO(3) poses with shifts in +-8 px,
+128x128 output, cubic interpolation, oversampling 2, radius cutoff 64.  The JSON line also
+carries the back-projection workload (50,000 slices of 128x128 with weights into a box-256
+volume, linear interpolation) under ``"backproject"``.
+
+With N > 1 (launched by torch.distributed.run, one rank per GPU) every rank processes the
+same number of poses on its own replica of the volume (weak scaling, no collective on the
+projection path); the back-projection step ends with one NCCL reduce of the partial
+data+weight volumes onto rank 0.
+
+``--impl reference`` times the reference's own CPU operators (built by
+``oracle/build_ref.py`` into ``oracle/_ref``; the C restatement oracle when that build is
+absent) on a bounded sample of the same workload, on rank 0 only.
+
+All inputs are seeded synthetic data of the stated shapes and distributions.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+for _p in (ROOT, ROOT / "torch-projectors_b200", ROOT / "tests"):
+    if str(_p) not in sys.path:
+        sys.path.insert(0, str(_p))
+
+import torch  # noqa: E402
+
+# ---- workload definitions ---------------------------------------------------------------
+PROJ = dict(name="project_3d_to_2d_forw box-256 (128^3 padded 2x), 10000 poses, 128x128 out, cubic, os=2, cutoff=64",
+            vol_box=128, pad=2, P=10_000, N=128, interp="cubic", os=2.0, cutoff=64.0, shift=8.0)
+BACK = dict(name="backproject_2d_to_3d_forw 50000 slices 128x128 + weights -> box-256 volumes, linear, os=2",
+            P=50_000, N=128, interp="linear", os=2.0, shift=8.0)
+
+# Algorithmic (compulsory) bytes per slice: every distinct input element read once, every
+# output element written once, plus one zero-fill pass for atomically accumulated outputs.
+PROJ_BYTES_PER_SLICE = 128 * 65 * 8 + 44 + (256 * 256 * 129 * 8) / PROJ["P"]                    # 73,367
+BACK_BYTES_PER_SLICE = 128 * 65 * 8 + 128 * 65 * 4 + 44 + 2 * (256 * 256 * 129 * 12) / BACK["P"]  # 103,942
+
+# DRAM traffic per slice of the dominant kernels from ncu captures of a smaller launch of the
+# same kernels (profiles/): None until a capture has been summarised there.
+PROJ_TRAFFIC_PER_SLICE = None
+BACK_TRAFFIC_PER_SLICE = None
+
+
+def measured_peak_gbs():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            return float(json.loads(p.read_text())["hbm_gbs"]), "measured"
+        except Exception:  # noqa: BLE001
+            pass
+    return 6650.0, "fallback"
+
+
+def uniform_rotations(P, gen, device):
+    from cases import random_rotations_3d
+    return random_rotations_3d(P, gen).reshape(1, P, 3, 3).to(device)
+
+
+def make_projection_inputs(device, seed):
+    gen = torch.Generator().manual_seed(seed)
+    b = PROJ["vol_box"]
+    vol = torch.randn(b, b, b, generator=gen).to(device)
+    half = b * (PROJ["pad"] - 1) // 2
+    pad = torch.nn.functional.pad(vol, (half, half) * 3)
+    rec = torch.fft.rfftn(torch.fft.fftshift(pad), norm="forward").to(torch.complex64).unsqueeze(0).contiguous()
+    rot = uniform_rotations(PROJ["P"], gen, device)
+    shifts = ((torch.rand(1, PROJ["P"], 2, generator=gen) * 2 - 1) * PROJ["shift"]).to(device)
+    return rec, rot, shifts
+
+
+def make_backprojection_inputs(device, seed, P):
+    from cases import hermitian_dc_column_
+    gen = torch.Generator(device=device).manual_seed(seed)
+    N, Nh = BACK["N"], BACK["N"] // 2 + 1
+    proj = torch.complex(torch.randn(1, P, N, Nh, generator=gen, device=device),
+                         torch.randn(1, P, N, Nh, generator=gen, device=device))
+    hermitian_dc_column_(proj)
+    weights = torch.rand(1, P, N, Nh, generator=gen, device=device)
+    cgen = torch.Generator().manual_seed(seed)
+    rot = uniform_rotations(P, cgen, device)
+    shifts = ((torch.rand(1, P, 2, generator=cgen) * 2 - 1) * BACK["shift"]).to(device)
+    return proj, weights, rot, shifts
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks / throttle reasons of one GPU while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.lines, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=lambda: self.lines.extend(self.proc.stdout), daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, smax, power, reasons = [], [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 8:
+                continue
+            try:
+                sm.append(float(f[0])); smax.append(float(f[1])); power.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(names, f[4:8]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(smax) if smax else None,
+                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def timed_steps(fn, steps, warmup, flush, barrier):
+    """W untimed + K timed calls of fn(); each timed call is bracketed by CUDA events on the
+    current stream; L2 is flushed (outside the events) before every call.  Returns the list
+    of per-step milliseconds."""
+    for _ in range(warmup):
+        flush()
+        fn()
+    torch.cuda.synchronize()
+    barrier()
+    torch.cuda.synchronize()
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+    for a, b in evs:
+        flush()
+        a.record()
+        fn()
+        b.record()
+    torch.cuda.synchronize()
+    barrier()
+    torch.cuda.synchronize()
+    return [a.elapsed_time(b) for a, b in evs]
+
+
+def run_cpu_sample(kind_wanted="reference"):
+    """Time the CPU implementation of the projection workload on a bounded sample of poses.
+    Returns (slices/s, kind, cores, sample description)."""
+    import oracle
+    gen = torch.Generator().manual_seed(1)
+    rec, rot, shifts = make_projection_inputs("cpu", seed=1)
+    if kind_wanted == "reference" and oracle.reference_available():
+        ops, kind, cores = oracle.reference_ops(), "reference", torch.get_num_threads()
+        f = ops.project_3d_to_2d_forw
+    else:
+        from oracle import port
+        kind, cores = "port", 1
+        f = port.project_3d_to_2d_forw
+    del gen
+
+    def run(n):
+        t0 = time.perf_counter()
+        f(rec, rot[:, :n].contiguous(), shifts[:, :n].contiguous(), [PROJ["N"], PROJ["N"]], PROJ["interp"], PROJ["os"], PROJ["cutoff"])
+        return time.perf_counter() - t0
+    probe = 64 if kind == "reference" else 8
+    dt = run(probe)                                   # also the warm-up
+    n = int(min(PROJ["P"], max(probe, probe * 12.0 / max(dt, 1e-3))))   # ~12 s of CPU work
+    dt = run(n)
+    return n / dt, kind, cores, f"{n} of the {PROJ['P']} poses of the projection workload, one call, {dt:.1f} s wall"
+
+
+def reference_arm(args):
+    """Time the reference's CPU operators; rank 0 only."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    per_step = []
+    kind = cores = sample = None
+    for k in range(args.warmup + args.steps):
+        if k < args.warmup and k > 0:
+            continue                                   # one warm-up pass is enough for a CPU loop
+        v, kind, cores, sample = run_cpu_sample("reference")
+        if k >= args.warmup:
+            per_step.append(v)
+        if len(per_step) >= 3:
+            break                                      # bounded: a few samples of ~12 s each
+    value = statistics.median(per_step)
+    line = {
+        "impl": "reference", "metric": "Fourier slices/sec (project_3d_to_2d_forw, box 256, 2x oversampling)",
+        "value": value, "unit": "slices/s", "n_gpus": args.gpus, "steps": len(per_step), "warmup": min(args.warmup, 1),
+        "ms_per_step": 1e3 * PROJ["P"] / value, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": PROJ["name"], "device": "host CPU", "note": "each step is a bounded sample of the poses; ms_per_step is extrapolated to all 10000"},
+        "cpu_baseline": {"value": value, "unit": "slices/s", "cores": cores, "kind": kind, "sample": sample},
+        "e2e": {"value": value, "unit": "slices/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def profile_case(args):
+    """A small, self-terminating run of one kernel for profiler captures: the same volume
+    and slice geometry as the benchmark workloads (so footprints exceed L2 together with the
+    pose-major tensors) but only --profile-poses poses, two launches."""
+    import torch_projectors_b200 as tp
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    P = args.profile_poses
+    rec, rot, shifts = make_projection_inputs(dev, seed=1234)
+    rot, shifts = rot[:, :P].contiguous(), shifts[:, :P].contiguous()
+    kw = dict(interpolation=PROJ["interp"], oversampling=PROJ["os"], fourier_radius_cutoff=PROJ["cutoff"])
+    for _ in range(2):
+        if args.profile_case == "project":
+            tp.project_3d_to_2d_forw(rec, rot, shifts, output_shape=(PROJ["N"], PROJ["N"]), **kw)
+        elif args.profile_case == "project_back":
+            g = torch.randn(1, P, PROJ["N"], PROJ["N"] // 2 + 1, dtype=torch.complex64, device=dev)
+            torch.ops.torch_projectors_b200.project_3d_to_2d_back(
+                g, rec, rot.clone().requires_grad_(True), shifts.clone().requires_grad_(True),
+                PROJ["interp"], PROJ["os"], PROJ["cutoff"])
+        else:
+            proj, weights, brot, bshifts = make_backprojection_inputs(dev, 4321, P)
+            tp.backproject_2d_to_3d_forw(proj, brot, weights=weights, shifts=bshifts, interpolation=BACK["interp"], oversampling=BACK["os"])
+    torch.cuda.synchronize()
+    print(f"profile case {args.profile_case}: {P} poses, 2 launches done")
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--skip-cpu", action="store_true", help="omit the CPU-baseline leg")
+    ap.add_argument("--skip-backproject", action="store_true")
+    ap.add_argument("--profile-case", choices=["project", "backproject", "project_back"], default=None,
+                    help="run a few launches of one kernel on a reduced pose count (for ncu captures); prints no bench line")
+    ap.add_argument("--profile-poses", type=int, default=2048)
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
+
+    if args.profile_case:
+        profile_case(args)
+        return
+
+    if args.impl == "reference":
+        reference_arm(args)
+        return
+
+    import torch.distributed as dist
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the B200 path has no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+
+    import torch_projectors_b200 as tp
+    from torch_projectors_b200 import sharding
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+
+    def max_over_ranks(x):
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    def flush():
+        flush_buf.zero_()        # 256 MiB > the 126 MB L2
+
+    peak, peak_kind = measured_peak_gbs()
+
+    # ---- projection: device-resident inputs --------------------------------------------
+    rec, rot, shifts = make_projection_inputs(dev, seed=1234 + rank)
+    kw = dict(output_shape=(PROJ["N"], PROJ["N"]), interpolation=PROJ["interp"], oversampling=PROJ["os"],
+              fourier_radius_cutoff=PROJ["cutoff"])
+    out_holder = {}
+
+    def proj_step():
+        out_holder["out"] = tp.project_3d_to_2d_forw(rec, rot, shifts, **kw)
+
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    ms = timed_steps(proj_step, args.steps, args.warmup, flush, barrier)
+    clocks = sampler.stop()
+    ms_per_step = max_over_ranks(sum(ms) / len(ms))
+    value = world * PROJ["P"] / (ms_per_step * 1e-3)
+    kernel_ms = max_over_ranks(statistics.median(ms))       # one kernel launch per step
+    achieved = PROJ_BYTES_PER_SLICE * PROJ["P"] / (kernel_ms * 1e-3) / 1e9
+    roofline = {"bound": "hbm", "kernel": "project_forw_kernel<3,cubic>", "achieved": achieved, "peak": peak,
+                "peak_source": peak_kind, "unit": "GB/s", "frac": achieved / peak,
+                "traffic": (PROJ_TRAFFIC_PER_SLICE * PROJ["P"]) if PROJ_TRAFFIC_PER_SLICE else None,
+                "algorithmic_bytes_per_launch": PROJ_BYTES_PER_SLICE * PROJ["P"], "launch_ms": kernel_ms}
+
+    # ---- projection end to end: pinned host inputs in, projections back to the host ----
+    h_rec = rec.cpu().pin_memory()
+    h_rot = rot.cpu().pin_memory()
+    h_sh = shifts.cpu().pin_memory()
+    h_out = torch.empty((1, PROJ["P"], PROJ["N"], PROJ["N"] // 2 + 1), dtype=torch.complex64).pin_memory()
+
+    def e2e_step():
+        d_rec = h_rec.to(dev, non_blocking=True)
+        d_rot = h_rot.to(dev, non_blocking=True)
+        d_sh = h_sh.to(dev, non_blocking=True)
+        o = tp.project_3d_to_2d_forw(d_rec, d_rot, d_sh, **kw)
+        h_out.copy_(o, non_blocking=True)
+
+    e2e_ms = timed_steps(e2e_step, max(3, args.steps // 2), 3, flush, barrier)
+    e2e_ms_per_step = max_over_ranks(sum(e2e_ms) / len(e2e_ms))
+    h2d = h_rec.numel() * 8 + h_rot.numel() * 4 + h_sh.numel() * 4
+    d2h = h_out.numel() * 8
+    e2e = {"value": world * PROJ["P"] / (e2e_ms_per_step * 1e-3), "unit": "slices/s", "ms_per_step": e2e_ms_per_step,
+           "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}
+    launches = args.steps + args.warmup + len(e2e_ms) + 3
+    del h_out, out_holder
+    torch.cuda.empty_cache()
+
+    # ---- back-projection ----------------------------------------------------------------
+    back = None
+    if not args.skip_backproject:
+        proj, weights, brot, bshifts = make_backprojection_inputs(dev, 4321 + rank, BACK["P"])
+        R = tp._abi.rec_boxsize(BACK["N"], BACK["os"])
+        vols = sharding.PartialVolumes(1, R, dev, with_weights=True)
+        scatter_ev = []
+
+        def back_step():
+            # zero-fill + scatter (one library call), then the cross-rank reduce when N > 1
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            tp._abi.backproject_forw(3, proj, weights, brot, bshifts, tp._abi.LINEAR, BACK["os"], BACK["N"] / 2.0,
+                                     vols.data, vols.weights, False)
+            b.record()
+            scatter_ev.append((a, b))
+            vols.reduce(dst=0)
+
+        bms = timed_steps(back_step, args.steps, args.warmup, flush, barrier)
+        bms_per_step = max_over_ranks(sum(bms) / len(bms))
+        scat = max_over_ranks(statistics.median([a.elapsed_time(b) for a, b in scatter_ev[args.warmup:]]))
+        bach = BACK_BYTES_PER_SLICE * BACK["P"] / (scat * 1e-3) / 1e9
+        back = {"metric": "Fourier slices/sec (backproject_2d_to_3d_forw, box 256, 2x oversampling)",
+                "value": world * BACK["P"] / (bms_per_step * 1e-3), "unit": "slices/s", "ms_per_step": bms_per_step,
+                "config": {"workload": BACK["name"], "collective": "NCCL reduce of data+weight partial volumes to rank 0" if world > 1 else "none"},
+                "roofline": {"bound": "hbm", "kernel": "memset + backproject_forw_kernel<3,linear,weights>", "achieved": bach,
+                             "peak": peak, "peak_source": peak_kind, "unit": "GB/s", "frac": bach / peak,
+                             "traffic": (BACK_TRAFFIC_PER_SLICE * BACK["P"]) if BACK_TRAFFIC_PER_SLICE else None,
+                             "algorithmic_bytes_per_launch": BACK_BYTES_PER_SLICE * BACK["P"], "launch_ms": scat}}
+        launches += args.steps + args.warmup
+        del proj, weights
+        torch.cuda.empty_cache()
+
+    # ---- CPU baseline (rank 0, single-GPU runs only) ------------------------------------
+    cpu = None
+    if rank == 0 and world == 1 and not args.skip_cpu:
+        v, kind, cores, sample = run_cpu_sample("reference")
+        cpu = {"value": v, "unit": "slices/s", "cores": cores, "kind": kind, "sample": sample}
+
+    if rank == 0:
+        line = {
+            "metric": "Fourier slices/sec (project_3d_to_2d_forw, box 256, 2x oversampling)",
+            "value": value, "unit": "slices/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic",
+            "config": {"workload": PROJ["name"], "poses_per_gpu": PROJ["P"], "parallelism": f"poses sharded over {world} GPU(s), volume replicated",
+                       "l2": "flushed before every step (256 MiB memset outside the timed events)"},
+            "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches, "clocks": clocks,
+            "backproject": back,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -103,16 +103,21 @@ def test_autograd_through_public_api_backprojection(tp, dim):
 
 
 def test_rank_canonicalisation_and_none_gradients(tp):
-    # un-batched volume, [P,3,3] rotations, no shifts (reference: torch_projectors/ops.py:352-366)
+    # [P,3,3] rotations and [P,2] shifts get a batch axis; an un-batched 3D volume is rejected by
+    # the public function as in the reference (torch_projectors/ops.py:153-154, 352-366)
     case = Case("canon", 3, "linear", 1, 3, 8, 8, 1.0, None, 1, 0, seed=33)
     t = make_inputs(case)
-    rec = t["rec"][0].cuda().requires_grad_(True)
+    with pytest.raises(ValueError, match="must be a 4D tensor"):
+        tp.project_3d_to_2d_forw(t["rec"][0].cuda(), t["rot"][0].cuda())
+    rec = t["rec"].cuda().requires_grad_(True)
     rot = t["rot"][0].cuda()
     out = tp.project_3d_to_2d_forw(rec, rot)
     assert out.shape == (1, 3, 8, 5)
+    out2d = tp.project_2d_forw(t["rec"][0, 0].cuda(), torch.eye(2, device="cuda"))   # 2D API accepts un-batched input
+    assert out2d.shape == (1, 1, 8, 5)
     out.abs().sum().backward()
     assert rec.grad is not None and rec.grad.shape == rec.shape
-    same = tp.project_3d_to_2d_forw(t["rec"].cuda(), t["rot"].cuda(), torch.zeros(1, 3, 2, device="cuda"))
+    same = tp.project_3d_to_2d_forw(t["rec"].cuda(), t["rot"].cuda(), torch.zeros(3, 2, device="cuda"))
     assert torch.allclose(same, out.detach(), atol=1e-6)       # zero shift == no shift
 
 

@@ -133,8 +133,11 @@ def _project_back_impl(dim, grad_projections, reconstruction, rotations, shifts,
     grad_rec = torch.empty_like(rec)                      # zero-filled by the library call
     grad_rot = torch.empty(rot.shape, dtype=rot.dtype, device=dev) if need_rot else None
     grad_sh = torch.empty(sh.shape, dtype=sh.dtype, device=dev) if need_shift else None
-    _abi.project_back(dim, gp, rec, rot, sh, P, N, interp, oversampling,
-                      _cutoff(fourier_radius_cutoff, N), grad_rec, grad_rot, grad_sh)
+    if P == 0:                      # nothing to launch: pointers of empty tensors are NULL
+        grad_rec.zero_()
+    else:
+        _abi.project_back(dim, gp, rec, rot, sh, P, N, interp, oversampling,
+                          _cutoff(fourier_radius_cutoff, N), grad_rec, grad_rot, grad_sh)
     empty = lambda: torch.empty((0,), dtype=rot.dtype, device=dev)  # noqa: E731
     return grad_rec, (grad_rot if need_rot else empty()), (grad_sh if need_shift else empty())
 
@@ -163,8 +166,13 @@ def _backproject_forw_impl(dim, projections, weights, rotations, shifts, interpo
     shape = (B, R, R, R // 2 + 1) if dim == 3 else (B, R, R // 2 + 1)
     data_rec = torch.empty(shape, dtype=proj.dtype, device=dev)          # zero-filled by the call
     weight_rec = torch.empty(shape, dtype=torch.float32, device=dev) if weights is not None else None
-    _abi.backproject_forw(dim, proj, weights, rot, sh, interp, oversampling,
-                          _cutoff(fourier_radius_cutoff, N), data_rec, weight_rec, False)
+    if P == 0:                      # nothing to launch: pointers of empty tensors are NULL
+        data_rec.zero_()
+        if weight_rec is not None:
+            weight_rec.zero_()
+    else:
+        _abi.backproject_forw(dim, proj, weights, rot, sh, interp, oversampling,
+                              _cutoff(fourier_radius_cutoff, N), data_rec, weight_rec, False)
     if weight_rec is None:
         weight_rec = torch.empty((0,), dtype=rot.dtype, device=dev)
     return data_rec, weight_rec
@@ -389,6 +397,8 @@ def backproject_2d_to_3d_accumulate_(data_rec: torch.Tensor, weight_rec: Optiona
     if weights is not None:
         _check(tuple(weight_rec.shape) == want and weight_rec.dtype == torch.float32 and weight_rec.is_contiguous()
                and weight_rec.device == projections.device, f"weight_rec must be a contiguous float32 tensor of shape {want}")
+    if P == 0:
+        return
     _abi.backproject_forw(3, projections.contiguous(), weights, rot, sh, interp, oversampling,
                           _cutoff(fourier_radius_cutoff, N), data_rec,
                           weight_rec if weights is not None else None, True)
