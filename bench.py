@@ -351,6 +351,8 @@ def main():
         proj, weights, brot, bshifts = make_backprojection_inputs(dev, 4321 + rank, BACK["P"])
         R = tp._abi.rec_boxsize(BACK["N"], BACK["os"])
         vols = sharding.PartialVolumes(1, R, dev, with_weights=True)
+        ws_bytes = tp._abi.backproject_workspace_bytes(3, 1, R, BACK["P"], BACK["N"], tp._abi.LINEAR, True)
+        workspace = torch.empty(ws_bytes, dtype=torch.uint8, device=dev) if ws_bytes else None
         scatter_ev = []
 
         def back_step():
@@ -358,7 +360,7 @@ def main():
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a.record()
             tp._abi.backproject_forw(3, proj, weights, brot, bshifts, tp._abi.LINEAR, BACK["os"], BACK["N"] / 2.0,
-                                     vols.data, vols.weights, False)
+                                     vols.data, vols.weights, False, workspace)
             b.record()
             scatter_ev.append((a, b))
             vols.reduce(dst=0)

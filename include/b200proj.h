@@ -32,6 +32,7 @@
 #ifndef B200PROJ_H
 #define B200PROJ_H
 
+#include <stddef.h>
 #include <stdint.h>
 
 #ifdef __cplusplus
@@ -101,6 +102,12 @@ int b200proj_project_3d_to_2d_back(const float* grad_proj, const float* rec, int
  * accumulate == 0: both volumes are zero-filled first (the reference's behaviour);
  * accumulate != 0: the call adds into the existing contents (for streaming many chunks of
  * projections into one volume without a per-chunk sum).
+ * workspace: optional scratch in device memory, 16-byte aligned, of at least
+ * b200proj_backproject_workspace_bytes(...) bytes, or NULL.  With weights and a workspace the
+ * kernel accumulates data and weight of each voxel in one 16-byte slot of the workspace (one
+ * vector reduction per tap instead of two), then folds the workspace into data_rec /
+ * weight_rec; results are the same up to summation order.  Without a workspace (or without
+ * weights) it reduces straight into the outputs.  The workspace holds no state between calls.
  * replaces: backproject_2d_forw_cuda       csrc/cuda/2d/backprojection_2d_kernels.cu:827-976
  *           backproject_2d_to_3d_forw_cuda csrc/cuda/3d/backprojection_2d_to_3d_kernels.cu:1001-1188 */
 int b200proj_backproject_2d_forw(const float* proj, const float* weights, int64_t B, int64_t R,
@@ -108,14 +115,21 @@ int b200proj_backproject_2d_forw(const float* proj, const float* weights, int64_
                                  const float* shifts, int64_t B_shift,
                                  int64_t P, int64_t N, int interpolation, double oversampling,
                                  double fourier_radius_cutoff,
-                                 float* data_rec, float* weight_rec, int accumulate, void* stream);
+                                 float* data_rec, float* weight_rec, int accumulate,
+                                 void* workspace, size_t workspace_bytes, void* stream);
 int b200proj_backproject_2d_to_3d_forw(const float* proj, const float* weights, int64_t B,
                                        int64_t R, const float* rot, int64_t B_rot,
                                        const float* shifts, int64_t B_shift,
                                        int64_t P, int64_t N, int interpolation,
                                        double oversampling, double fourier_radius_cutoff,
                                        float* data_rec, float* weight_rec, int accumulate,
-                                       void* stream);
+                                       void* workspace, size_t workspace_bytes, void* stream);
+
+/* Bytes of workspace with which a back-projection of these sizes runs faster, or 0 when a
+ * workspace would not help (no weights, or too few slices to pay for two extra passes over
+ * the volume).  dim = 2 or 3.  No counterpart in the reference (its kernels use no scratch). */
+size_t b200proj_backproject_workspace_bytes(int dim, int64_t B, int64_t R, int64_t P, int64_t N,
+                                            int interpolation, int has_weights);
 
 /* ---- backward of back-projection (gather) ----------------------------------------------
  * grad_proj [B,P,N,Nh] complex is fully written.  grad_weights [B,P,N,Nh] float is written

@@ -70,8 +70,15 @@ def test_argument_errors_are_reported_without_a_device(over, fragment):
 
 def test_backprojection_checks_volume_size_rule():
     lib = _abi.load()
-    rc = lib.b200proj_backproject_2d_to_3d_forw(1, 0, 1, 10, 1, 1, 0, 0, 1, 8, 0, 2.0, 4.0, 1, 0, 0, 0)
+    rc = lib.b200proj_backproject_2d_to_3d_forw(1, 0, 1, 10, 1, 1, 0, 0, 1, 8, 0, 2.0, 4.0, 1, 0, 0, 0, 0, 0)
     assert rc == -1
     assert "does not match" in lib.b200proj_last_error().decode()
-    rc = lib.b200proj_backproject_2d_to_3d_forw(1, 1, 1, 16, 1, 1, 0, 0, 1, 8, 0, 2.0, 4.0, 1, 0, 0, 0)
+    rc = lib.b200proj_backproject_2d_to_3d_forw(1, 1, 1, 16, 1, 1, 0, 0, 1, 8, 0, 2.0, 4.0, 1, 0, 0, 0, 0, 0)
     assert rc == -1 and "given together" in lib.b200proj_last_error().decode()
+
+
+def test_workspace_query_needs_no_gpu():
+    # box-256 volumes, 50,000 slices with weights: one 16-byte slot per voxel
+    assert _abi.backproject_workspace_bytes(3, 1, 256, 50000, 128, _abi.LINEAR, True) == 256 * 256 * 129 * 16
+    assert _abi.backproject_workspace_bytes(3, 1, 256, 50000, 128, _abi.LINEAR, False) == 0     # no weights
+    assert _abi.backproject_workspace_bytes(3, 1, 256, 1, 128, _abi.LINEAR, True) == 0          # too few slices

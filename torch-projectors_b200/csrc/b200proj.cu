@@ -7,6 +7,7 @@
 #include <cstdarg>
 #include <cstdio>
 #include <climits>
+#include <cstdint>
 
 #include "fourier_slice_kernels.cuh"
 
@@ -155,7 +156,8 @@ template <int DIM>
 int backproject_forw(const float* proj, const float* weights, int64_t B, int64_t R,
                      const float* rot, int64_t B_rot, const float* shifts, int64_t B_shift,
                      int64_t P, int64_t N, int interpolation, double os, double cutoff,
-                     float* data_rec, float* weight_rec, int accumulate, void* stream) {
+                     float* data_rec, float* weight_rec, int accumulate, void* workspace,
+                     size_t workspace_bytes, void* stream) {
     Launch L;
     if (int rc = prepare(L, DIM, B, R, B_rot, rot, shifts, B_shift, P, N, interpolation, os, cutoff)) return rc;
     if (proj == nullptr || data_rec == nullptr) return fail(B200PROJ_ERR_ARGUMENT, "projections / data_reconstruction pointer is NULL");
@@ -165,6 +167,23 @@ int backproject_forw(const float* proj, const float* weights, int64_t B, int64_t
         return fail(B200PROJ_ERR_ARGUMENT, "reconstruction boxsize %lld does not match ceil(N*oversampling) rounded up to even = %lld",
                     (long long)R, (long long)b200proj_rec_boxsize(N, os));
     cudaStream_t s = (cudaStream_t)stream;
+    const bool cubic = interpolation == B200PROJ_CUBIC, hw = weights != nullptr;
+    // Interleaved path: data and weight of a voxel share one 16-byte slot of the workspace
+    // (one v4 reduction per tap), folded into the outputs afterwards.
+    const size_t ws_need = L.rec_count * sizeof(float4);
+    if (hw && P > 0 && workspace != nullptr && workspace_bytes >= ws_need &&
+        (reinterpret_cast<uintptr_t>(workspace) & 15u) == 0) {
+        if (int rc = zero_async(workspace, ws_need, s)) return rc;
+        float4* acc = (float4*)workspace;
+        if (cubic)
+            backproject_forw_interleaved_kernel<DIM, true><<<L.grid, kBlockThreads, 0, s>>>((const float2*)proj, weights, rot, shifts, acc, L.g);
+        else
+            backproject_forw_interleaved_kernel<DIM, false><<<L.grid, kBlockThreads, 0, s>>>((const float2*)proj, weights, rot, shifts, acc, L.g);
+        if (int rc = check_launch("backproject_forw (interleaved) launch")) return rc;
+        const size_t blocks = (L.rec_count + 255) / 256;
+        fold_interleaved_kernel<<<(unsigned)(blocks < 148 * 16 ? blocks : 148 * 16), 256, 0, s>>>(acc, (float2*)data_rec, weight_rec, L.rec_count, accumulate != 0);
+        return check_launch("fold_interleaved launch");
+    }
     if (!accumulate) {
         if (int rc = zero_async(data_rec, L.rec_count * sizeof(float2), s)) return rc;
         if (int rc = zero_async(weight_rec, L.rec_count * sizeof(float), s)) return rc;
@@ -172,7 +191,6 @@ int backproject_forw(const float* proj, const float* weights, int64_t B, int64_t
     if (P == 0) return B200PROJ_OK;
     const float2* p = (const float2*)proj;
     float2* d = (float2*)data_rec;
-    const bool cubic = interpolation == B200PROJ_CUBIC, hw = weights != nullptr;
 #define B200PROJ_BP(C, W) \
     backproject_forw_kernel<DIM, C, W><<<L.grid, kBlockThreads, 0, s>>>(p, weights, rot, shifts, d, weight_rec, L.g)
     if (cubic && hw) B200PROJ_BP(true, true);
@@ -236,6 +254,17 @@ int b200proj_version(void) { return 100; }
 
 const char* b200proj_last_error(void) { return g_error; }
 
+size_t b200proj_backproject_workspace_bytes(int dim, int64_t B, int64_t R, int64_t P, int64_t N,
+                                           int interpolation, int has_weights) {
+    if (!has_weights || (dim != 2 && dim != 3) || B < 1 || R < 2 || P < 1 || N < 2) return 0;
+    const double voxels = (double)B * (dim == 3 ? R : 1) * R * (R / 2 + 1);
+    const int t = interpolation == B200PROJ_CUBIC ? 4 : 2;
+    const double taps = (double)B * P * N * (N / 2 + 1) * (dim == 3 ? t * t * t : t * t);
+    // worth it once the scatter outweighs the two extra passes over the volume
+    if (taps < 4.0 * voxels) return 0;
+    return (size_t)voxels * sizeof(float4);
+}
+
 int64_t b200proj_rec_boxsize(int64_t N, double oversampling) {
     const int64_t raw = (int64_t)std::ceil((double)N * oversampling);
     return raw + (raw % 2);
@@ -273,16 +302,15 @@ int b200proj_backproject_2d_forw(const float* proj, const float* weights, int64_
                                  const float* rot, int64_t B_rot, const float* shifts,
                                  int64_t B_shift, int64_t P, int64_t N, int interpolation,
                                  double oversampling, double cutoff, float* data_rec,
-                                 float* weight_rec, int accumulate, void* stream) {
-    return backproject_forw<2>(proj, weights, B, R, rot, B_rot, shifts, B_shift, P, N, interpolation, oversampling, cutoff, data_rec, weight_rec, accumulate, stream);
+                                 float* weight_rec, int accumulate, void* workspace, size_t workspace_bytes, void* stream) {
+    return backproject_forw<2>(proj, weights, B, R, rot, B_rot, shifts, B_shift, P, N, interpolation, oversampling, cutoff, data_rec, weight_rec, accumulate, workspace, workspace_bytes, stream);
 }
 int b200proj_backproject_2d_to_3d_forw(const float* proj, const float* weights, int64_t B,
                                        int64_t R, const float* rot, int64_t B_rot,
                                        const float* shifts, int64_t B_shift, int64_t P, int64_t N,
                                        int interpolation, double oversampling, double cutoff,
-                                       float* data_rec, float* weight_rec, int accumulate,
-                                       void* stream) {
-    return backproject_forw<3>(proj, weights, B, R, rot, B_rot, shifts, B_shift, P, N, interpolation, oversampling, cutoff, data_rec, weight_rec, accumulate, stream);
+                                       float* data_rec, float* weight_rec, int accumulate,                                        void* workspace, size_t workspace_bytes, void* stream) {
+    return backproject_forw<3>(proj, weights, B, R, rot, B_rot, shifts, B_shift, P, N, interpolation, oversampling, cutoff, data_rec, weight_rec, accumulate, workspace, workspace_bytes, stream);
 }
 
 int b200proj_backproject_2d_back(const float* grad_data_rec, const float* grad_weight_rec,

@@ -163,119 +163,119 @@ __device__ __forceinline__ int gather_line(const SliceGeom& g, int r, bool mirro
     return r < 0 ? r + g.R : r;
 }
 
-// Separable interpolation of a complex half-volume at px, optionally with the spatial
-// derivatives (d/dc, d/dr, d/dd).  vol points at the batch item.
+// Cooperative separable interpolation of a complex half-volume, optionally with the spatial
+// derivatives (d/dc, d/dr, d/dd).  The T lanes of a group (T = 2 linear, 4 cubic; groups
+// are aligned runs of lanes, whose pixels are T consecutive columns of one slice row) work
+// on ONE pixel at a time: lane q fetches column tap q of every footprint row, so that a
+// group's loads of one row are T adjacent voxels (one or two 32-byte sectors) instead of T
+// separate requests by one lane.  Measured on B200 (cubic, box 256): ~14 instead of ~30
+// sectors per warp request and 1.57x the throughput of one-lane-per-pixel gathers.
+// Each lane keeps the partial sums of its column, weights them and the group adds them up
+// with shuffles.  Because lane q only ever touches column q, the Friedel mirror of that
+// column (which decides rows and planes, see gather_line) is a per-lane constant and the
+// footprints that straddle c = 0 need no special case.
+// MUST be called by all 32 lanes of the warp; lanes without a pixel pass valid_own = false.
+// vol points at the batch item.
 template <int DIM, bool CUBIC, bool WITH_DERIV>
-__device__ __forceinline__ void interpolate(const SliceGeom& g, const float2* __restrict__ vol,
-                                            const Pixel& px, float2& val, float2& g_c,
-                                            float2& g_r, float2& g_d) {
+__device__ __forceinline__ void interpolate_coop(const SliceGeom& g, const float2* __restrict__ vol,
+                                                 const Pixel& px, bool valid_own, float2& val,
+                                                 float2& g_c, float2& g_r, float2& g_d) {
     constexpr int T = CUBIC ? 4 : 2;
     constexpr int TD = (DIM == 3) ? T : 1;
-    AxisWeights<T> ac, ar, ad;
-    axis_weights<T, WITH_DERIV>(px.c, ac);
-    axis_weights<T, WITH_DERIV>(px.r, ar);
-    if (DIM == 3) axis_weights<T, WITH_DERIV>(px.d, ad);
-
-    int col[T];
-    unsigned mirror_mask = 0;
-#pragma unroll
-    for (int t = 0; t < T; ++t) {
-        bool m;
-        col[t] = gather_col<CUBIC>(g, ac.base + t, m);
-        mirror_mask |= (m ? 1u : 0u) << t;
-    }
+    constexpr unsigned kFull = 0xffffffffu;
+    const int lane = threadIdx.x & 31;
+    const int q = lane & (T - 1);
     const int plane_stride = g.R * g.Rh;
-
     val = make_float2(0.f, 0.f);
     g_c = g_r = g_d = val;
 
-    const bool uniform = mirror_mask == 0u || mirror_mask == (1u << T) - 1u;
-    if (uniform) {
-        // the whole footprint lies on one side of the mirror plane
-        const bool neg = mirror_mask != 0u;
-        int row[T];
 #pragma unroll
-        for (int t = 0; t < T; ++t) row[t] = gather_line<CUBIC>(g, ar.base + t, neg) * g.Rh;
+    for (int s = 0; s < T; ++s) {
+        const int src = (lane & ~(T - 1)) | s;
+        const float pc = __shfl_sync(kFull, px.c, src);
+        const float pr = __shfl_sync(kFull, px.r, src);
+        const float pd = (DIM == 3) ? __shfl_sync(kFull, px.d, src) : 0.f;
+        const bool valid = __shfl_sync(kFull, (int)valid_own, src) != 0;
+
+        float2 cv = make_float2(0.f, 0.f), cgc = cv, cgr = cv, cgd = cv;
+        if (valid) {
+            AxisWeights<T> ar, ad;
+            axis_weights<T, WITH_DERIV>(pr, ar);
+            if (DIM == 3) axis_weights<T, WITH_DERIV>(pd, ad);
+            // this lane's column tap
+            const float flc = floorf(pc);
+            const float fc = pc - flc;
+            const int cbase = CUBIC ? (int)flc - 1 : (int)flc;
+            bool m;
+            const int col = gather_col<CUBIC>(g, cbase + q, m);
+            float wc, dwc = 0.f;
+            if (CUBIC) {
+                wc = cubic_w(fc - (float)(q - 1));
+                if (WITH_DERIV) dwc = cubic_dw(fc - (float)(q - 1));
+            } else {
+                wc = q ? fc : 1.f - fc;
+                dwc = q ? 1.f : -1.f;
+            }
+            int rowcol[T];
 #pragma unroll
-        for (int k = 0; k < TD; ++k) {
-            const int pl = (DIM == 3) ? gather_line<CUBIC>(g, ad.base + k, neg) * plane_stride : 0;
-            float2 A = make_float2(0.f, 0.f), Bq = A, Cq = A;
+            for (int i = 0; i < T; ++i) rowcol[i] = gather_line<CUBIC>(g, ar.base + i, m) * g.Rh + col;
+
+            float2 A = make_float2(0.f, 0.f), Bq = A, Dq = A;
 #pragma unroll
-            for (int i = 0; i < T; ++i) {
-                const float2* __restrict__ rowp = vol + (pl + row[i]);
-                float2 s = make_float2(0.f, 0.f), ds = s;
+            for (int k = 0; k < TD; ++k) {
+                const float2* __restrict__ pl =
+                    vol + ((DIM == 3) ? gather_line<CUBIC>(g, ad.base + k, m) * plane_stride : 0);
+                float2 rs = make_float2(0.f, 0.f), rds = rs;
 #pragma unroll
-                for (int j = 0; j < T; ++j) {
-                    const float2 v = __ldg(rowp + col[j]);
-                    s.x = fmaf(ac.w[j], v.x, s.x);
-                    s.y = fmaf(ac.w[j], v.y, s.y);
+                for (int i = 0; i < T; ++i) {
+                    const float2 v = __ldg(pl + rowcol[i]);
+                    rs.x = fmaf(ar.w[i], v.x, rs.x);
+                    rs.y = fmaf(ar.w[i], v.y, rs.y);
                     if (WITH_DERIV) {
-                        ds.x = fmaf(ac.dw[j], v.x, ds.x);
-                        ds.y = fmaf(ac.dw[j], v.y, ds.y);
+                        rds.x = fmaf(ar.dw[i], v.x, rds.x);
+                        rds.y = fmaf(ar.dw[i], v.y, rds.y);
                     }
                 }
-                A.x = fmaf(ar.w[i], s.x, A.x);
-                A.y = fmaf(ar.w[i], s.y, A.y);
+                const float wd = (DIM == 3) ? ad.w[k] : 1.f;
+                A.x = fmaf(wd, rs.x, A.x);
+                A.y = fmaf(wd, rs.y, A.y);
                 if (WITH_DERIV) {
-                    Bq.x = fmaf(ar.dw[i], s.x, Bq.x);
-                    Bq.y = fmaf(ar.dw[i], s.y, Bq.y);
-                    Cq.x = fmaf(ar.w[i], ds.x, Cq.x);
-                    Cq.y = fmaf(ar.w[i], ds.y, Cq.y);
-                }
-            }
-            const float wd = (DIM == 3) ? ad.w[k] : 1.f;
-            val.x = fmaf(wd, A.x, val.x);
-            val.y = fmaf(wd, A.y, val.y);
-            if (WITH_DERIV) {
-                g_r.x = fmaf(wd, Bq.x, g_r.x);
-                g_r.y = fmaf(wd, Bq.y, g_r.y);
-                g_c.x = fmaf(wd, Cq.x, g_c.x);
-                g_c.y = fmaf(wd, Cq.y, g_c.y);
-                if (DIM == 3) {
-                    g_d.x = fmaf(ad.dw[k], A.x, g_d.x);
-                    g_d.y = fmaf(ad.dw[k], A.y, g_d.y);
-                }
-            }
-        }
-        if (neg) {   // every tap was a conjugated Friedel mate
-            val.y = -val.y;
-            g_c.y = -g_c.y;
-            g_r.y = -g_r.y;
-            g_d.y = -g_d.y;
-        }
-    } else {
-        // footprint straddles c = 0: mirrored and direct taps use different rows / planes
-#pragma unroll
-        for (int k = 0; k < TD; ++k) {
-            const float wd = (DIM == 3) ? ad.w[k] : 1.f;
-            const float dwd = (DIM == 3 && WITH_DERIV) ? ad.dw[k] : 0.f;
-#pragma unroll
-            for (int i = 0; i < T; ++i) {
-#pragma unroll
-                for (int j = 0; j < T; ++j) {
-                    const bool m = (mirror_mask >> j) & 1u;
-                    const int pl = (DIM == 3) ? gather_line<CUBIC>(g, ad.base + k, m) * plane_stride : 0;
-                    const int rw = gather_line<CUBIC>(g, ar.base + i, m) * g.Rh;
-                    float2 v = __ldg(vol + (pl + rw + col[j]));
-                    if (m) v.y = -v.y;
-                    const float w = wd * ar.w[i] * ac.w[j];
-                    val.x = fmaf(w, v.x, val.x);
-                    val.y = fmaf(w, v.y, val.y);
-                    if (WITH_DERIV) {
-                        const float wc_ = wd * ar.w[i] * ac.dw[j];
-                        const float wr_ = wd * ar.dw[i] * ac.w[j];
-                        g_c.x = fmaf(wc_, v.x, g_c.x);
-                        g_c.y = fmaf(wc_, v.y, g_c.y);
-                        g_r.x = fmaf(wr_, v.x, g_r.x);
-                        g_r.y = fmaf(wr_, v.y, g_r.y);
-                        if (DIM == 3) {
-                            const float wd_ = dwd * ar.w[i] * ac.w[j];
-                            g_d.x = fmaf(wd_, v.x, g_d.x);
-                            g_d.y = fmaf(wd_, v.y, g_d.y);
-                        }
+                    Bq.x = fmaf(wd, rds.x, Bq.x);
+                    Bq.y = fmaf(wd, rds.y, Bq.y);
+                    if (DIM == 3) {
+                        Dq.x = fmaf(ad.dw[k], rs.x, Dq.x);
+                        Dq.y = fmaf(ad.dw[k], rs.y, Dq.y);
                     }
                 }
             }
+            const float sg = m ? -1.f : 1.f;          // a mirrored column holds conjugated values
+            cv = make_float2(wc * A.x, sg * wc * A.y);
+            if (WITH_DERIV) {
+                cgc = make_float2(dwc * A.x, sg * dwc * A.y);
+                cgr = make_float2(wc * Bq.x, sg * wc * Bq.y);
+                cgd = make_float2(wc * Dq.x, sg * wc * Dq.y);
+            }
+        }
+#pragma unroll
+        for (int o = 1; o < T; o <<= 1) {
+            cv.x += __shfl_xor_sync(kFull, cv.x, o);
+            cv.y += __shfl_xor_sync(kFull, cv.y, o);
+            if (WITH_DERIV) {
+                cgc.x += __shfl_xor_sync(kFull, cgc.x, o);
+                cgc.y += __shfl_xor_sync(kFull, cgc.y, o);
+                cgr.x += __shfl_xor_sync(kFull, cgr.x, o);
+                cgr.y += __shfl_xor_sync(kFull, cgr.y, o);
+                if (DIM == 3) {
+                    cgd.x += __shfl_xor_sync(kFull, cgd.x, o);
+                    cgd.y += __shfl_xor_sync(kFull, cgd.y, o);
+                }
+            }
+        }
+        if (q == s) {
+            val = cv;
+            g_c = cgc;
+            g_r = cgr;
+            g_d = cgd;
         }
     }
 }
@@ -353,6 +353,64 @@ __device__ __forceinline__ void scatter(const SliceGeom& g, float2* __restrict__
                         red_add_v2(vol + off2, re, -im);
                         if (WEIGHTS) red_add(wvol + off2, fw);
                     }
+                }
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ void red_add_v4(float4* addr, float a, float b, float c, float d) {
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
+// Back-projection into an INTERLEAVED accumulation volume whose voxels are 16 bytes
+// (re, im, weight, 0): the data and the weight of a tap go out as one
+// red.global.add.v4.f32 instead of a v2 plus a scalar reduction.  The L2 retires one
+// reduction per lane and instruction, so this halves the work of the unit that bounds the
+// kernel (measured on B200, linear, box 256: 1.66x).  Same tap rules as scatter<> with
+// weights and the x = 0 Friedel duplicate.
+template <int DIM, bool CUBIC>
+__device__ __forceinline__ void scatter_interleaved(const SliceGeom& g, float4* __restrict__ vol,
+                                                    const Pixel& px, float2 v, float wval) {
+    constexpr int T = CUBIC ? 4 : 2;
+    constexpr int TD = (DIM == 3) ? T : 1;
+    AxisWeights<T> ac, ar, ad;
+    axis_weights<T, false>(px.c, ac);
+    axis_weights<T, false>(px.r, ar);
+    if (DIM == 3) axis_weights<T, false>(px.d, ad);
+    const int plane_stride = g.R * g.Rh;
+#pragma unroll
+    for (int j = 0; j < T; ++j) {
+        int c = ac.base + j;
+        const bool m = c < 0;
+        c = m ? -c : c;
+        if (c >= g.Rh) continue;
+        const float wc = ac.w[j];
+        if (wc == 0.f) continue;
+        const float sgn = m ? -1.f : 1.f;
+#pragma unroll
+        for (int k = 0; k < TD; ++k) {
+            int dl = 0;
+            float wd = 1.f;
+            if (DIM == 3) {
+                dl = scatter_line(g, ad.base + k, m);
+                wd = ad.w[k];
+                if (dl < 0 || wd == 0.f) continue;
+            }
+#pragma unroll
+            for (int i = 0; i < T; ++i) {
+                const int rl = scatter_line(g, ar.base + i, m);
+                const float wr = ar.w[i];
+                if (rl < 0 || wr == 0.f) continue;
+                const float w = wd * wr * wc;
+                const int off = dl * plane_stride + rl * g.Rh + c;
+                const float re = v.x * w, im = v.y * w * sgn, fw = wval * fabsf(w);
+                red_add_v4(vol + off, re, im, fw, 0.f);
+                if (c == 0) {
+                    const int rl2 = (rl == 0) ? 0 : g.R - rl;
+                    const int dl2 = (DIM == 3) ? ((dl == 0) ? 0 : g.R - dl) : 0;
+                    if (rl2 != rl || dl2 != dl)
+                        red_add_v4(vol + (dl2 * plane_stride + rl2 * g.Rh), re, -im, fw, 0.f);
                 }
             }
         }

@@ -48,16 +48,16 @@ __global__ void __launch_bounds__(kBlockThreads)
 project_forw_kernel(const float2* __restrict__ rec, const float* __restrict__ rot,
                     const float* __restrict__ shifts, float2* __restrict__ out, const SliceGeom g) {
     const BlockWork w = block_work(g);
-    if (!w.in_image) return;
     Pixel px;
-    float2 v = make_float2(0.f, 0.f);
-    if (pixel_setup<DIM>(g, pose_rot<DIM>(g, rot, w.b, w.p), w.i, w.j, px)) {
-        float2 gc, gr, gd;
-        interpolate<DIM, CUBIC, false>(g, rec + (size_t)w.b * g.vol_elems, px, v, gc, gr, gd);
-        if (g.has_shift) {
-            const float* s = pose_shift(g, shifts, w.b, w.p);
-            v = cmul(v, phase_ramp(g, px, __ldg(s), __ldg(s + 1)));
-        }
+    px.c = px.r = px.d = 0.f;
+    const bool valid = w.in_image && pixel_setup<DIM>(g, pose_rot<DIM>(g, rot, w.b, w.p), w.i, w.j, px);
+    float2 v, gc, gr, gd;
+    // all 32 lanes take part: the lanes of a group fetch each other's taps
+    interpolate_coop<DIM, CUBIC, false>(g, rec + (size_t)w.b * g.vol_elems, px, valid, v, gc, gr, gd);
+    if (!w.in_image) return;
+    if (valid && g.has_shift) {
+        const float* s = pose_shift(g, shifts, w.b, w.p);
+        v = cmul(v, phase_ramp(g, px, __ldg(s), __ldg(s + 1)));
     }
     // streaming store: the projections are written once and never re-read by this kernel,
     // keep the cache for the volume
@@ -121,9 +121,13 @@ project_back_kernel(const float2* __restrict__ grad_proj, const float2* __restri
 #pragma unroll
     for (int q = 0; q < 2 * DIM + 2; ++q) acc[q] = 0.f;
     Pixel px;
+    px.c = px.r = px.d = px.sc = px.sr = px.kr = px.kc = 0.f;
     const bool active = w.in_image &&
                         pixel_setup<DIM>(g, pose_rot<DIM>(g, rot, w.b, w.p), w.i, w.j, px) &&
                         !(w.j == 0 && w.i >= g.N / 2);
+    float2 val = make_float2(0.f, 0.f), gc = val, gr = val, gd = val;
+    if (NEED_ROT || NEED_SHIFT)      // cooperative gather: every lane of the warp takes part
+        interpolate_coop<DIM, CUBIC, NEED_ROT>(g, rec + (size_t)w.b * g.vol_elems, px, active, val, gc, gr, gd);
     if (active) {
         const float2 orig = __ldcs(grad_proj + w.pix);
         float2 ph = make_float2(1.f, 0.f);
@@ -135,8 +139,6 @@ project_back_kernel(const float2* __restrict__ grad_proj, const float2* __restri
         }
         scatter<DIM, CUBIC, false, false>(g, grad_rec + (size_t)w.b * g.vol_elems, nullptr, px, u, 0.f);
         if (NEED_ROT || NEED_SHIFT) {
-            float2 val, gc, gr, gd;
-            interpolate<DIM, CUBIC, NEED_ROT>(g, rec + (size_t)w.b * g.vol_elems, px, val, gc, gr, gd);
             const float2 mod = g.has_shift ? cmul(val, ph) : val;
             pose_grad_terms<DIM, NEED_ROT, NEED_SHIFT>(g, px, u, orig, mod, gc, gr, gd, acc);
         }
@@ -167,6 +169,45 @@ backproject_forw_kernel(const float2* __restrict__ proj, const float* __restrict
                                        px, v, wv);
 }
 
+// Back-projection with weights into the interleaved accumulation volume (workspace), and
+// the pass that folds it into the caller's data / weight volumes.
+template <int DIM, bool CUBIC>
+__global__ void __launch_bounds__(kBlockThreads)
+backproject_forw_interleaved_kernel(const float2* __restrict__ proj, const float* __restrict__ weights,
+                                    const float* __restrict__ rot, const float* __restrict__ shifts,
+                                    float4* __restrict__ accum, const SliceGeom g) {
+    const BlockWork w = block_work(g);
+    if (!w.in_image || (w.j == 0 && w.i >= g.N / 2)) return;
+    Pixel px;
+    if (!pixel_setup<DIM>(g, pose_rot<DIM>(g, rot, w.b, w.p), w.i, w.j, px)) return;
+    float2 v = __ldcs(proj + w.pix);
+    if (g.has_shift) {
+        const float* s = pose_shift(g, shifts, w.b, w.p);
+        v = cmul_conj(v, phase_ramp(g, px, __ldg(s), __ldg(s + 1)));
+    }
+    scatter_interleaved<DIM, CUBIC>(g, accum + (size_t)w.b * g.vol_elems, px, v, __ldcs(weights + w.pix));
+}
+
+// data[k] (+)= accum[k].xy, weight[k] (+)= accum[k].z
+__global__ void __launch_bounds__(256)
+fold_interleaved_kernel(const float4* __restrict__ accum, float2* __restrict__ data,
+                        float* __restrict__ weight, size_t n, int accumulate) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t k = (size_t)blockIdx.x * blockDim.x + threadIdx.x; k < n; k += stride) {
+        const float4 a = __ldcs(accum + k);
+        float2 d = make_float2(a.x, a.y);
+        float wv = a.z;
+        if (accumulate) {
+            const float2 d0 = data[k];
+            d.x += d0.x;
+            d.y += d0.y;
+            wv += weight[k];
+        }
+        data[k] = d;
+        weight[k] = wv;
+    }
+}
+
 // ---- backward of back-projection --------------------------------------------------------
 // reference semantics: csrc/cpu/3d/backprojection_2d_to_3d_kernels.cpp:417-583
 template <int DIM, bool CUBIC, bool NEED_ROT, bool NEED_SHIFT>
@@ -182,13 +223,15 @@ backproject_back_kernel(const float2* __restrict__ grad_data_rec,
 #pragma unroll
     for (int q = 0; q < 2 * DIM + 2; ++q) acc[q] = 0.f;
     Pixel px;
+    px.c = px.r = px.d = px.sc = px.sr = px.kr = px.kc = 0.f;
     const bool active = w.in_image &&
                         pixel_setup<DIM>(g, pose_rot<DIM>(g, rot, w.b, w.p), w.i, w.j, px) &&
                         !(w.j == 0 && w.i >= g.N / 2);
     const bool write_w = grad_weight_rec != nullptr && grad_weights != nullptr;
+    float2 raw, gc, gr, gd;
+    // cooperative gather: every lane of the warp takes part
+    interpolate_coop<DIM, CUBIC, NEED_ROT>(g, grad_data_rec + (size_t)w.b * g.vol_elems, px, active, raw, gc, gr, gd);
     if (active) {
-        float2 raw, gc, gr, gd;
-        interpolate<DIM, CUBIC, NEED_ROT>(g, grad_data_rec + (size_t)w.b * g.vol_elems, px, raw, gc, gr, gd);
         float2 ph = make_float2(1.f, 0.f);
         float2 v = raw;
         if (g.has_shift) {

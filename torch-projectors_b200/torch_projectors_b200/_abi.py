@@ -28,12 +28,13 @@ SIGNATURES = {
     "b200proj_project_3d_to_2d_forw": [_ptr] + _COMMON + [_ptr, _ptr],
     "b200proj_project_2d_back": [_ptr, _ptr] + _COMMON + [_ptr, _ptr, _ptr, _ptr],
     "b200proj_project_3d_to_2d_back": [_ptr, _ptr] + _COMMON + [_ptr, _ptr, _ptr, _ptr],
-    "b200proj_backproject_2d_forw": [_ptr, _ptr] + _COMMON + [_ptr, _ptr, _int, _ptr],
-    "b200proj_backproject_2d_to_3d_forw": [_ptr, _ptr] + _COMMON + [_ptr, _ptr, _int, _ptr],
+    "b200proj_backproject_2d_forw": [_ptr, _ptr] + _COMMON + [_ptr, _ptr, _int, _ptr, C.c_size_t, _ptr],
+    "b200proj_backproject_2d_to_3d_forw": [_ptr, _ptr] + _COMMON + [_ptr, _ptr, _int, _ptr, C.c_size_t, _ptr],
     "b200proj_backproject_2d_back": [_ptr, _ptr, _ptr] + _COMMON + [_ptr, _ptr, _ptr, _ptr, _ptr],
     "b200proj_backproject_2d_to_3d_back": [_ptr, _ptr, _ptr] + _COMMON + [_ptr, _ptr, _ptr, _ptr, _ptr],
 }
-EXPORTS = list(SIGNATURES) + ["b200proj_version", "b200proj_last_error", "b200proj_rec_boxsize"]
+EXPORTS = list(SIGNATURES) + ["b200proj_version", "b200proj_last_error", "b200proj_rec_boxsize",
+                                "b200proj_backproject_workspace_bytes"]
 
 _lib: Optional[C.CDLL] = None
 
@@ -43,19 +44,20 @@ def library_path():
 
 
 def load() -> C.CDLL:
-    """Load (building first if the file is absent) the CUDA library; raises ImportError
+    """Load (building first if the file is absent or older than its sources) the CUDA library; raises ImportError
     when that is impossible.  Never substitutes another implementation."""
     global _lib
     if _lib is not None:
         return _lib
     path = _build.LIB_PATH
-    if not path.exists():
+    if _build.needs_build():          # missing, or older than its sources
         try:
             _build.build()
         except Exception as e:  # noqa: BLE001
-            raise ImportError(
-                f"torch_projectors_b200: {path} is not built and building it failed ({e}); "
-                "run `python -m torch_projectors_b200.build` on a machine with nvcc") from e
+            if not path.exists():
+                raise ImportError(
+                    f"torch_projectors_b200: {path} is not built and building it failed ({e}); "
+                    "run `python -m torch_projectors_b200.build` on a machine with nvcc") from e
     try:
         lib = C.CDLL(str(path))
     except OSError as e:
@@ -70,6 +72,8 @@ def load() -> C.CDLL:
     lib.b200proj_last_error.argtypes = []
     lib.b200proj_rec_boxsize.restype = _i64
     lib.b200proj_rec_boxsize.argtypes = [_i64, _dbl]
+    lib.b200proj_backproject_workspace_bytes.restype = C.c_size_t
+    lib.b200proj_backproject_workspace_bytes.argtypes = [_int, _i64, _i64, _i64, _i64, _int, _int]
     _lib = lib
     return lib
 
@@ -80,6 +84,10 @@ def version() -> int:
 
 def rec_boxsize(N: int, oversampling: float) -> int:
     return int(load().b200proj_rec_boxsize(int(N), float(oversampling)))
+
+
+def backproject_workspace_bytes(dim: int, B: int, R: int, P: int, N: int, interp: int, has_weights: bool) -> int:
+    return int(load().b200proj_backproject_workspace_bytes(dim, B, R, P, N, interp, int(has_weights)))
 
 
 def _p(t: Optional[torch.Tensor]) -> int:
@@ -120,12 +128,14 @@ def project_back(dim, grad_proj, rec, rot, shifts, P, N, interp, oversampling, c
 
 
 def backproject_forw(dim, proj, weights, rot, shifts, interp, oversampling, cutoff,
-                     data_rec, weight_rec, accumulate):
+                     data_rec, weight_rec, accumulate, workspace=None):
+    """workspace: optional uint8 CUDA tensor (see backproject_workspace_bytes)."""
     name = "b200proj_backproject_2d_forw" if dim == 2 else "b200proj_backproject_2d_to_3d_forw"
     B, P, N = proj.shape[0], proj.shape[1], proj.shape[2]
     R = data_rec.shape[-2]
     _call(name, proj, _p(proj), _p(weights), *_geom(B, R, rot, shifts, P, N, interp, oversampling, cutoff),
-          _p(data_rec), _p(weight_rec), int(bool(accumulate)))
+          _p(data_rec), _p(weight_rec), int(bool(accumulate)), _p(workspace),
+          0 if workspace is None else workspace.numel() * workspace.element_size())
 
 
 def backproject_back(dim, grad_data_rec, grad_weight_rec, proj, rot, shifts, interp, oversampling,

@@ -77,6 +77,14 @@ def _check_pose_inputs(dim: int, what: str, B: int, rotations, shifts, like: tor
     return P, rotations.contiguous(), shifts
 
 
+def _backproject_workspace(dim, B, R, P, N, interp, weights, device):
+    """Scratch for the interleaved accumulation path of the back-projection kernels (from
+    torch's caching allocator, so nothing is freed behind the stream); None when the
+    library says a workspace would not help."""
+    n = _abi.backproject_workspace_bytes(dim, B, R, P, N, interp, weights is not None)
+    return torch.empty(n, dtype=torch.uint8, device=device) if n else None
+
+
 def _cutoff(fourier_radius_cutoff: Optional[float], N: int) -> float:
     # default: Nyquist radius of the projection (reference: projection_3d_to_2d_kernels.cu:892)
     return float(fourier_radius_cutoff) if fourier_radius_cutoff is not None else N / 2.0
@@ -172,7 +180,8 @@ def _backproject_forw_impl(dim, projections, weights, rotations, shifts, interpo
             weight_rec.zero_()
     else:
         _abi.backproject_forw(dim, proj, weights, rot, sh, interp, oversampling,
-                              _cutoff(fourier_radius_cutoff, N), data_rec, weight_rec, False)
+                              _cutoff(fourier_radius_cutoff, N), data_rec, weight_rec, False,
+                              _backproject_workspace(dim, B, R, P, N, interp, weights, dev))
     if weight_rec is None:
         weight_rec = torch.empty((0,), dtype=rot.dtype, device=dev)
     return data_rec, weight_rec
@@ -401,7 +410,8 @@ def backproject_2d_to_3d_accumulate_(data_rec: torch.Tensor, weight_rec: Optiona
         return
     _abi.backproject_forw(3, projections.contiguous(), weights, rot, sh, interp, oversampling,
                           _cutoff(fourier_radius_cutoff, N), data_rec,
-                          weight_rec if weights is not None else None, True)
+                          weight_rec if weights is not None else None, True,
+                          _backproject_workspace(3, B, R, P, N, interp, weights, projections.device))
 
 
 # ---------------------------------------------------------------------------------------
