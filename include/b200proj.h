@@ -131,6 +131,35 @@ int b200proj_backproject_2d_to_3d_forw(const float* proj, const float* weights, 
 size_t b200proj_backproject_workspace_bytes(int dim, int64_t B, int64_t R, int64_t P, int64_t N,
                                             int interpolation, int has_weights);
 
+/* ---- back-projection without any allocation --------------------------------------------
+ * No counterpart in the reference.  Same result as b200proj_backproject_2d_to_3d_forw with
+ * weights (data_rec and weight_rec are both required), for callers that are not allowed to
+ * allocate device memory: a plugin inside a host application that hands out one fixed arena
+ * at start-up and forbids cudaMalloc afterwards, a service whose GPU memory was partitioned
+ * between tenants in advance, or a latency-bound loop that cannot afford the implicit
+ * device-wide synchronisation of cudaMalloc / cudaFree.  Such callers can provide inputs and
+ * outputs but no workspace, so the 16-byte-per-voxel accumulation volume lives in a
+ * statically sized array inside the library (B200PROJ_NOALLOC_MAX_VOXELS * 16 bytes = 2.06 MiB
+ * of device memory, held by every GPU that loads the library until the process exits).
+ *  - Limit: B*R*R*(R/2+1) <= B200PROJ_NOALLOC_MAX_VOXELS (box 64 for one batch item, i.e.
+ *    32-pixel projections at oversampling 2); larger problems are refused with
+ *    B200PROJ_ERR_LIMIT before anything is launched.
+ *  - The entry point calls no cudaMalloc, cudaFree or allocating library routine.
+ *  - The first call on each device looks up the array's device address
+ *    (cudaGetSymbolAddress, with that device current) and caches it; make that first call
+ *    before any stream capture begins.
+ *  - All calls on a device share the one array, which keeps the previous call's sums; each
+ *    call clears the part it uses on its stream first.  Two calls that overlap on the GPU
+ *    (different streams, or different host threads) race on the array: serialise them. */
+#define B200PROJ_NOALLOC_MAX_VOXELS 135168   /* 64 * 64 * 33 */
+int b200proj_backproject_2d_to_3d_forw_noalloc(const float* proj, const float* weights, int64_t B,
+                                               int64_t R, const float* rot, int64_t B_rot,
+                                               const float* shifts, int64_t B_shift,
+                                               int64_t P, int64_t N, int interpolation,
+                                               double oversampling, double fourier_radius_cutoff,
+                                               float* data_rec, float* weight_rec, int accumulate,
+                                               void* stream);
+
 /* ---- backward of back-projection (gather) ----------------------------------------------
  * grad_proj [B,P,N,Nh] complex is fully written.  grad_weights [B,P,N,Nh] float is written
  * only when grad_weight_rec and grad_weights are both non-NULL (always tri/bi-linear).

@@ -82,3 +82,12 @@ def test_workspace_query_needs_no_gpu():
     assert _abi.backproject_workspace_bytes(3, 1, 256, 50000, 128, _abi.LINEAR, True) == 256 * 256 * 129 * 16
     assert _abi.backproject_workspace_bytes(3, 1, 256, 50000, 128, _abi.LINEAR, False) == 0     # no weights
     assert _abi.backproject_workspace_bytes(3, 1, 256, 1, 128, _abi.LINEAR, True) == 0          # too few slices
+
+
+def test_no_alloc_entry_reports_its_limit_without_a_device():
+    lib = _abi.load()
+    # box 68 > the built-in scratch (box 64): refused before any CUDA call
+    rc = lib.b200proj_backproject_2d_to_3d_forw_noalloc(1, 1, 1, 68, 1, 1, 0, 0, 1, 34, 0, 2.0, 17.0, 1, 1, 0, 0)
+    assert rc == -2 and "built-in scratch" in lib.b200proj_last_error().decode()
+    rc = lib.b200proj_backproject_2d_to_3d_forw_noalloc(1, 0, 1, 64, 1, 1, 0, 0, 1, 32, 0, 2.0, 16.0, 1, 1, 0, 0)
+    assert rc == -1 and "required" in lib.b200proj_last_error().decode()

@@ -8,6 +8,7 @@
 #include <cstdio>
 #include <climits>
 #include <cstdint>
+#include <mutex>
 
 #include "fourier_slice_kernels.cuh"
 
@@ -246,6 +247,36 @@ int backproject_back(const float* grad_data_rec, const float* grad_weight_rec, c
     return check_launch("backproject_back launch");
 }
 
+
+// ---- built-in scratch of the allocation-free back-projection entry point -----------------
+// The array lives in every GPU context that loads this library, from load until exit.
+constexpr long long kNoAllocMaxVoxels = B200PROJ_NOALLOC_MAX_VOXELS;
+static __device__ __align__(256) float4 g_noalloc_accum[kNoAllocMaxVoxels];
+
+constexpr int kNoAllocMaxDevices = 64;
+float4* g_noalloc_ptr[kNoAllocMaxDevices] = {};
+std::mutex g_noalloc_mutex;
+
+// Device address of the built-in scratch on the CURRENT device.  In host code the array's
+// name is only a stand-in; the address a kernel can use comes from cudaGetSymbolAddress,
+// asked once per device with that device current.
+int noalloc_scratch(float4** out) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
+    if (dev < 0 || dev >= kNoAllocMaxDevices)
+        return fail(B200PROJ_ERR_LIMIT, "device ordinal %d is beyond the %d devices the allocation-free entry point tracks", dev, kNoAllocMaxDevices);
+    std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+    if (g_noalloc_ptr[dev] == nullptr) {
+        float4* ptr = nullptr;
+        e = cudaGetSymbolAddress((void**)&ptr, g_noalloc_accum);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress");
+        g_noalloc_ptr[dev] = ptr;
+    }
+    *out = g_noalloc_ptr[dev];
+    return B200PROJ_OK;
+}
+
 }  // namespace
 
 extern "C" {
@@ -329,6 +360,40 @@ int b200proj_backproject_2d_to_3d_back(const float* grad_data_rec, const float* 
                                        float* grad_weights, float* grad_rot, float* grad_shifts,
                                        void* stream) {
     return backproject_back<3>(grad_data_rec, grad_weight_rec, proj, B, R, rot, B_rot, shifts, B_shift, P, N, interpolation, oversampling, cutoff, grad_proj, grad_weights, grad_rot, grad_shifts, stream);
+}
+
+int b200proj_backproject_2d_to_3d_forw_noalloc(const float* proj, const float* weights, int64_t B,
+                                               int64_t R, const float* rot, int64_t B_rot,
+                                               const float* shifts, int64_t B_shift, int64_t P,
+                                               int64_t N, int interpolation, double oversampling,
+                                               double cutoff, float* data_rec, float* weight_rec,
+                                               int accumulate, void* stream) {
+    Launch L;
+    if (int rc = prepare(L, 3, B, R, B_rot, rot, shifts, B_shift, P, N, interpolation, oversampling, cutoff)) return rc;
+    if (proj == nullptr || weights == nullptr || data_rec == nullptr || weight_rec == nullptr)
+        return fail(B200PROJ_ERR_ARGUMENT, "projections, weights, data_reconstruction and weight_reconstruction are all required");
+    if (R != b200proj_rec_boxsize(N, oversampling))
+        return fail(B200PROJ_ERR_ARGUMENT, "reconstruction boxsize %lld does not match ceil(N*oversampling) rounded up to even = %lld",
+                    (long long)R, (long long)b200proj_rec_boxsize(N, oversampling));
+    if ((long long)L.rec_count > kNoAllocMaxVoxels)
+        return fail(B200PROJ_ERR_LIMIT, "B*R*R*(R/2+1) = %lld voxels exceed the built-in scratch of %lld voxels (box 64, one batch item); "
+                    "use b200proj_backproject_2d_to_3d_forw with a caller-provided workspace",
+                    (long long)L.rec_count, kNoAllocMaxVoxels);
+    float4* acc = nullptr;
+    if (int rc = noalloc_scratch(&acc)) return rc;
+    cudaStream_t s = (cudaStream_t)stream;
+    // the scratch keeps the previous call's sums: clear the part this call uses
+    if (int rc = zero_async(acc, L.rec_count * sizeof(float4), s)) return rc;
+    if (P > 0) {
+        if (interpolation == B200PROJ_CUBIC)
+            backproject_forw_interleaved_kernel<3, true><<<L.grid, kBlockThreads, 0, s>>>((const float2*)proj, weights, rot, shifts, acc, L.g);
+        else
+            backproject_forw_interleaved_kernel<3, false><<<L.grid, kBlockThreads, 0, s>>>((const float2*)proj, weights, rot, shifts, acc, L.g);
+        if (int rc = check_launch("backproject_forw (built-in scratch) launch")) return rc;
+    }
+    const size_t blocks = (L.rec_count + 255) / 256;
+    fold_interleaved_kernel<<<(unsigned)(blocks < 148 * 16 ? blocks : 148 * 16), 256, 0, s>>>(acc, (float2*)data_rec, weight_rec, L.rec_count, accumulate != 0);
+    return check_launch("fold_interleaved launch");
 }
 
 }  // extern "C"

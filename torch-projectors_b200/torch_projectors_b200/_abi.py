@@ -30,6 +30,7 @@ SIGNATURES = {
     "b200proj_project_3d_to_2d_back": [_ptr, _ptr] + _COMMON + [_ptr, _ptr, _ptr, _ptr],
     "b200proj_backproject_2d_forw": [_ptr, _ptr] + _COMMON + [_ptr, _ptr, _int, _ptr, C.c_size_t, _ptr],
     "b200proj_backproject_2d_to_3d_forw": [_ptr, _ptr] + _COMMON + [_ptr, _ptr, _int, _ptr, C.c_size_t, _ptr],
+    "b200proj_backproject_2d_to_3d_forw_noalloc": [_ptr, _ptr] + _COMMON + [_ptr, _ptr, _int, _ptr],
     "b200proj_backproject_2d_back": [_ptr, _ptr, _ptr] + _COMMON + [_ptr, _ptr, _ptr, _ptr, _ptr],
     "b200proj_backproject_2d_to_3d_back": [_ptr, _ptr, _ptr] + _COMMON + [_ptr, _ptr, _ptr, _ptr, _ptr],
 }
@@ -136,6 +137,21 @@ def backproject_forw(dim, proj, weights, rot, shifts, interp, oversampling, cuto
     _call(name, proj, _p(proj), _p(weights), *_geom(B, R, rot, shifts, P, N, interp, oversampling, cutoff),
           _p(data_rec), _p(weight_rec), int(bool(accumulate)), _p(workspace),
           0 if workspace is None else workspace.numel() * workspace.element_size())
+
+
+NOALLOC_MAX_VOXELS = 64 * 64 * 33
+
+
+def backproject_2d_to_3d_forw_noalloc(proj, weights, rot, shifts, interp, oversampling, cutoff,
+                                      data_rec, weight_rec, accumulate):
+    """Weighted 2D->3D back-projection through the library's built-in scratch: for callers that
+    may not allocate device memory (no workspace tensor is involved).  Volumes are limited to
+    NOALLOC_MAX_VOXELS voxels; calls that overlap on the GPU race on the shared scratch."""
+    B, P, N = proj.shape[0], proj.shape[1], proj.shape[2]
+    R = data_rec.shape[-2]
+    _call("b200proj_backproject_2d_to_3d_forw_noalloc", proj, _p(proj), _p(weights),
+          *_geom(B, R, rot, shifts, P, N, interp, oversampling, cutoff),
+          _p(data_rec), _p(weight_rec), int(bool(accumulate)))
 
 
 def backproject_back(dim, grad_data_rec, grad_weight_rec, proj, rot, shifts, interp, oversampling,
