@@ -168,6 +168,11 @@ def run_cpu_sample(kind_wanted="reference"):
     """Time the CPU implementation of the projection workload on a bounded sample of poses.
     Returns (slices/s, kind, cores, sample description)."""
     import oracle
+    # all host cores this process may use (torch.distributed.run exports OMP_NUM_THREADS=1)
+    try:
+        torch.set_num_threads(max(1, len(os.sched_getaffinity(0))))
+    except (AttributeError, RuntimeError):
+        pass
     gen = torch.Generator().manual_seed(1)
     rec, rot, shifts = make_projection_inputs("cpu", seed=1)
     if kind_wanted == "reference" and oracle.reference_available():

@@ -128,16 +128,20 @@ project_back_kernel(const float2* __restrict__ grad_proj, const float2* __restri
     float2 val = make_float2(0.f, 0.f), gc = val, gr = val, gd = val;
     if (NEED_ROT || NEED_SHIFT)      // cooperative gather: every lane of the warp takes part
         interpolate_coop<DIM, CUBIC, NEED_ROT>(g, rec + (size_t)w.b * g.vol_elems, px, active, val, gc, gr, gd);
+    float2 orig = make_float2(0.f, 0.f), u = orig, ph = make_float2(1.f, 0.f);
     if (active) {
-        const float2 orig = __ldcs(grad_proj + w.pix);
-        float2 ph = make_float2(1.f, 0.f);
-        float2 u = orig;
+        orig = __ldcs(grad_proj + w.pix);
+        u = orig;
         if (g.has_shift) {
             const float* s = pose_shift(g, shifts, w.b, w.p);
             ph = phase_ramp(g, px, __ldg(s), __ldg(s + 1));
             u = cmul_conj(orig, ph);
         }
-        scatter<DIM, CUBIC, false, false>(g, grad_rec + (size_t)w.b * g.vol_elems, nullptr, px, u, 0.f);
+    }
+    // cooperative scatter: every lane of the warp takes part
+    scatter_coop<DIM, CUBIC, false, false, false>(g, grad_rec + (size_t)w.b * g.vol_elems, nullptr, nullptr,
+                                                  px, active, u, 0.f);
+    if (active) {
         if (NEED_ROT || NEED_SHIFT) {
             const float2 mod = g.has_shift ? cmul(val, ph) : val;
             pose_grad_terms<DIM, NEED_ROT, NEED_SHIFT>(g, px, u, orig, mod, gc, gr, gd, acc);
@@ -148,6 +152,30 @@ project_back_kernel(const float2* __restrict__ grad_proj, const float2* __restri
 
 // ---- back-projection --------------------------------------------------------------------
 // reference semantics: csrc/cpu/3d/backprojection_2d_to_3d_kernels.cpp:177-291
+// Slice value with the conjugate shift ramp applied, and its weight (shared by both kernels).
+template <int DIM, bool WEIGHTS>
+__device__ __forceinline__ bool backproject_pixel(const SliceGeom& g, const BlockWork& w,
+                                                  const float2* __restrict__ proj,
+                                                  const float* __restrict__ weights,
+                                                  const float* __restrict__ rot,
+                                                  const float* __restrict__ shifts, Pixel& px,
+                                                  float2& v, float& wv) {
+    px.c = px.r = px.d = 0.f;
+    v = make_float2(0.f, 0.f);
+    wv = 0.f;
+    const bool active = w.in_image && !(w.j == 0 && w.i >= g.N / 2) &&
+                        pixel_setup<DIM>(g, pose_rot<DIM>(g, rot, w.b, w.p), w.i, w.j, px);
+    if (active) {
+        v = __ldcs(proj + w.pix);
+        if (g.has_shift) {
+            const float* s = pose_shift(g, shifts, w.b, w.p);
+            v = cmul_conj(v, phase_ramp(g, px, __ldg(s), __ldg(s + 1)));
+        }
+        if (WEIGHTS) wv = __ldcs(weights + w.pix);
+    }
+    return active;
+}
+
 template <int DIM, bool CUBIC, bool WEIGHTS>
 __global__ void __launch_bounds__(kBlockThreads)
 backproject_forw_kernel(const float2* __restrict__ proj, const float* __restrict__ weights,
@@ -155,18 +183,13 @@ backproject_forw_kernel(const float2* __restrict__ proj, const float* __restrict
                         float2* __restrict__ data_rec, float* __restrict__ weight_rec,
                         const SliceGeom g) {
     const BlockWork w = block_work(g);
-    if (!w.in_image || (w.j == 0 && w.i >= g.N / 2)) return;
     Pixel px;
-    if (!pixel_setup<DIM>(g, pose_rot<DIM>(g, rot, w.b, w.p), w.i, w.j, px)) return;
-    float2 v = __ldcs(proj + w.pix);
-    if (g.has_shift) {
-        const float* s = pose_shift(g, shifts, w.b, w.p);
-        v = cmul_conj(v, phase_ramp(g, px, __ldg(s), __ldg(s + 1)));
-    }
-    const float wv = WEIGHTS ? __ldcs(weights + w.pix) : 0.f;
-    scatter<DIM, CUBIC, WEIGHTS, true>(g, data_rec + (size_t)w.b * g.vol_elems,
-                                       WEIGHTS ? weight_rec + (size_t)w.b * g.vol_elems : nullptr,
-                                       px, v, wv);
+    float2 v;
+    float wv;
+    const bool active = backproject_pixel<DIM, WEIGHTS>(g, w, proj, weights, rot, shifts, px, v, wv);
+    scatter_coop<DIM, CUBIC, WEIGHTS, true, false>(g, data_rec + (size_t)w.b * g.vol_elems,
+                                                   WEIGHTS ? weight_rec + (size_t)w.b * g.vol_elems : nullptr,
+                                                   nullptr, px, active, v, wv);
 }
 
 // Back-projection with weights into the interleaved accumulation volume (workspace), and
@@ -177,15 +200,12 @@ backproject_forw_interleaved_kernel(const float2* __restrict__ proj, const float
                                     const float* __restrict__ rot, const float* __restrict__ shifts,
                                     float4* __restrict__ accum, const SliceGeom g) {
     const BlockWork w = block_work(g);
-    if (!w.in_image || (w.j == 0 && w.i >= g.N / 2)) return;
     Pixel px;
-    if (!pixel_setup<DIM>(g, pose_rot<DIM>(g, rot, w.b, w.p), w.i, w.j, px)) return;
-    float2 v = __ldcs(proj + w.pix);
-    if (g.has_shift) {
-        const float* s = pose_shift(g, shifts, w.b, w.p);
-        v = cmul_conj(v, phase_ramp(g, px, __ldg(s), __ldg(s + 1)));
-    }
-    scatter_interleaved<DIM, CUBIC>(g, accum + (size_t)w.b * g.vol_elems, px, v, __ldcs(weights + w.pix));
+    float2 v;
+    float wv;
+    const bool active = backproject_pixel<DIM, true>(g, w, proj, weights, rot, shifts, px, v, wv);
+    scatter_coop<DIM, CUBIC, true, true, true>(g, nullptr, nullptr, accum + (size_t)w.b * g.vol_elems,
+                                               px, active, v, wv);
 }
 
 // data[k] (+)= accum[k].xy, weight[k] (+)= accum[k].z
