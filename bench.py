@@ -51,10 +51,11 @@ BACK = dict(name="backproject_2d_to_3d_forw 50000 slices 128x128 + weights -> bo
 PROJ_BYTES_PER_SLICE = 128 * 65 * 8 + 44 + (256 * 256 * 129 * 8) / PROJ["P"]                    # 73,367
 BACK_BYTES_PER_SLICE = 128 * 65 * 8 + 128 * 65 * 4 + 44 + 2 * (256 * 256 * 129 * 12) / BACK["P"]  # 103,942
 
-# DRAM traffic per slice of the dominant kernels from ncu captures of a smaller launch of the
-# same kernels (profiles/): None until a capture has been summarised there.
-PROJ_TRAFFIC_PER_SLICE = None
-BACK_TRAFFIC_PER_SLICE = None
+# DRAM traffic per slice of the dominant kernels (dram__bytes_read.sum + dram__bytes_write.sum) from
+# ncu captures of a smaller launch of the same kernels, scaled by the slices a launch processes
+# (traffic grows in proportion to the slices: the volumes are touched the same way by every slice).
+PROJ_TRAFFIC_PER_SLICE = (48.83e6 + 105.61e6) / 2048      # profiles/project_forw_3d_cubic_box256_2048poses.md
+BACK_TRAFFIC_PER_SLICE = (512.2e6 + 1344.1e6) / 4096      # profiles/backproject_forw_3d_linear_box256_4096slices.md
 
 
 def measured_peak_gbs():
@@ -250,6 +251,174 @@ def profile_case(args):
     print(f"profile case {args.profile_case}: {P} poses, 2 launches done")
 
 
+# ---- additional workloads (not part of the default line) --------------------------------
+STEP = dict(name="autograd step of project_3d_to_2d_forw: box-512 volume (256^3 padded 2x), 4096 poses, 256x256 out, cubic, os=2, MSE loss, grads w.r.t. volume, rotations, shifts",
+            vol_box=256, P=4096, N=256, shift=10.0)
+SHARD = dict(name="sharded backproject_2d_to_3d_forw: 200000 slices of 400x400 + weights -> box-800 volumes, linear, os=2, chunks of 8192, NCCL reduce",
+             P_total=200_000, N=400, chunk=8192, shift=12.0)
+# op bytes per autograd step (volume read twice, projections written once and their gradient
+# read once, gradient volume zero-filled and written): 4.32 GB = 1.055 MB per slice
+STEP_BYTES_PER_SLICE = (2 * 512 * 512 * 257 * 8 + 2 * 4096 * 256 * 129 * 8 + 2 * 512 * 512 * 257 * 8) / 4096
+SHARD_BYTES_PER_SLICE = 400 * 201 * 8 + 400 * 201 * 4 + 44
+
+
+def _dist_setup():
+    import torch.distributed as dist
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the B200 path has no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1 and not dist.is_initialized():
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    return dist, rank, world, local_rank, dev
+
+
+def autograd_step_workload(args):
+    """BASELINE config 4: forward + MSE loss + backward, all three gradients; every rank runs
+    the same step on its own replica (weak scaling, no collective)."""
+    import torch_projectors_b200 as tp
+    dist, rank, world, local_rank, dev = _dist_setup()
+    gen = torch.Generator().manual_seed(77 + rank)
+    b = STEP["vol_box"]
+    vol = torch.randn(b, b, b, generator=gen).to(dev)
+    pad = torch.nn.functional.pad(vol, (b // 2, b // 2) * 3)
+    rec = torch.fft.rfftn(torch.fft.fftshift(pad), norm="forward").to(torch.complex64).unsqueeze(0).contiguous()
+    del vol, pad
+    rec.requires_grad_(True)
+    rot = uniform_rotations(STEP["P"], gen, dev).requires_grad_(True)
+    shifts = ((torch.rand(1, STEP["P"], 2, generator=gen) * 2 - 1) * STEP["shift"]).to(dev).requires_grad_(True)
+    ggen = torch.Generator(device=dev).manual_seed(78 + rank)
+    shape = (1, STEP["P"], STEP["N"], STEP["N"] // 2 + 1)
+    target = torch.complex(torch.randn(shape, generator=ggen, device=dev), torch.randn(shape, generator=ggen, device=dev))
+    flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    fwd_ev, bwd_ev = [], []
+
+    def step():
+        for t in (rec, rot, shifts):
+            t.grad = None
+        e0, e1, e2, e3 = (torch.cuda.Event(enable_timing=True) for _ in range(4))
+        e0.record()
+        out = tp.project_3d_to_2d_forw(rec, rot, shifts, output_shape=(STEP["N"], STEP["N"]), interpolation="cubic", oversampling=2.0)
+        e1.record()
+        diff = out - target
+        loss = (diff.real.square() + diff.imag.square()).mean()
+        grad_out = diff * (2.0 / diff.numel())          # d loss / d conj(out) in torch's convention
+        e2.record()
+        out.backward(grad_out)
+        e3.record()
+        fwd_ev.append((e0, e1)); bwd_ev.append((e2, e3))
+        return loss
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+
+    def max_over_ranks(x):
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    ms = timed_steps(step, args.steps, args.warmup, flush_buf.zero_, barrier)
+    clocks = sampler.stop()
+    ms_per_step = max_over_ranks(sum(ms) / len(ms))
+    f = statistics.median([a.elapsed_time(b) for a, b in fwd_ev[args.warmup:]])
+    bw = statistics.median([a.elapsed_time(b) for a, b in bwd_ev[args.warmup:]])
+    peak, peak_kind = measured_peak_gbs()
+    op_ms = max_over_ranks(f + bw)
+    achieved = STEP_BYTES_PER_SLICE * STEP["P"] / (op_ms * 1e-3) / 1e9
+    if rank == 0:
+        print(json.dumps({
+            "metric": "Fourier slices/sec (autograd step of project_3d_to_2d_forw, box 512, 2x oversampling)",
+            "value": world * STEP["P"] / (ms_per_step * 1e-3), "unit": "slices/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic",
+            "config": {"workload": STEP["name"], "l2": "inputs (539 MB volume, 1.08 GB projections) exceed L2; 256 MiB flush before every step"},
+            "kernels_ms": {"project_forw_kernel<3,cubic>": f, "project_back_kernel<3,cubic,rot,shift> (+ memsets)": bw,
+                           "loss and its gradient (torch elementwise)": ms_per_step - f - bw},
+            "roofline": {"bound": "hbm", "kernel": "project_forw + project_back (op time only)", "achieved": achieved, "peak": peak,
+                         "peak_source": peak_kind, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+                         "algorithmic_bytes_per_launch": STEP_BYTES_PER_SLICE * STEP["P"], "launch_ms": op_ms},
+            "gpu_launches": 2 * (args.steps + args.warmup), "clocks": clocks}), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def sharded_backprojection_workload(args):
+    """BASELINE config 5: 200,000 box-400 slices split over the ranks (strong scaling), generated
+    on the device per rank seed in chunks of 8192 outside the timed region; CUDA events around the
+    accumulate calls only, plus the final NCCL reduce of the partial volumes."""
+    import torch_projectors_b200 as tp
+    from torch_projectors_b200 import sharding
+    dist, rank, world, local_rank, dev = _dist_setup()
+    total = args.total_slices or SHARD["P_total"]
+    lo, hi = sharding.pose_range(total, rank, world)
+    N, Nh = SHARD["N"], SHARD["N"] // 2 + 1
+    R = tp._abi.rec_boxsize(N, 2.0)
+    vols = sharding.PartialVolumes(1, R, dev, with_weights=True)
+    gen = torch.Generator(device=dev).manual_seed(900 + rank)
+    cgen = torch.Generator().manual_seed(900 + rank)
+    op_ms = 0.0
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    launches = 0
+    for c0 in range(lo, hi, SHARD["chunk"]):
+        n = min(SHARD["chunk"], hi - c0)
+        proj = torch.complex(torch.randn(1, n, N, Nh, generator=gen, device=dev), torch.randn(1, n, N, Nh, generator=gen, device=dev))
+        weights = torch.rand(1, n, N, Nh, generator=gen, device=dev)
+        rot = uniform_rotations(n, cgen, dev)
+        shifts = ((torch.rand(1, n, 2, generator=cgen) * 2 - 1) * SHARD["shift"]).to(dev)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        tp.backproject_2d_to_3d_accumulate_(vols.data, vols.weights, proj, rot, weights, shifts, interpolation="linear", oversampling=2.0)
+        b.record()
+        torch.cuda.synchronize()
+        op_ms += a.elapsed_time(b)
+        launches += 2
+        del proj, weights
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if world > 1:
+        dist.barrier()
+    a.record()
+    vols.reduce(dst=0)
+    b.record()
+    torch.cuda.synchronize()
+    reduce_ms = a.elapsed_time(b)
+    clocks = sampler.stop()
+    t = torch.tensor([op_ms, reduce_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    op_ms, reduce_ms = float(t[0]), float(t[1])
+    total_ms = op_ms + reduce_ms
+    peak, peak_kind = measured_peak_gbs()
+    per_rank = (hi - lo)
+    achieved = (SHARD_BYTES_PER_SLICE * per_rank + 2 * vols.flat.numel() * 4) / (op_ms * 1e-3) / 1e9
+    if rank == 0:
+        print(json.dumps({
+            "metric": "Fourier slices/sec (sharded backproject_2d_to_3d_forw, box 400 -> 800, 2x oversampling)",
+            "value": total / (total_ms * 1e-3), "unit": "slices/s", "n_gpus": world, "steps": 1, "warmup": 0,
+            "ms_per_step": total_ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": SHARD["name"], "total_slices": total, "slices_per_rank": per_rank,
+                       "timing": "sum of CUDA-event times of the accumulate calls (max over ranks) + NCCL reduce; chunk generation excluded",
+                       "l2": "each 8192-slice chunk (7.9 GB) and the 3.1 GB volumes exceed L2"},
+            "scatter_ms": op_ms, "reduce_ms": reduce_ms,
+            "roofline": {"bound": "hbm", "kernel": "backproject_forw_interleaved_kernel<3,linear> + fold", "achieved": achieved, "peak": peak,
+                         "peak_source": peak_kind, "unit": "GB/s", "frac": achieved / peak, "traffic": None, "launch_ms": op_ms},
+            "gpu_launches": launches, "clocks": clocks}), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -261,11 +430,20 @@ def main():
     ap.add_argument("--profile-case", choices=["project", "backproject", "project_back"], default=None,
                     help="run a few launches of one kernel on a reduced pose count (for ncu captures); prints no bench line")
     ap.add_argument("--profile-poses", type=int, default=2048)
+    ap.add_argument("--workload", choices=["default", "autograd_step", "sharded_backproject"], default="default",
+                    help="default: projection (+ back-projection) headline line; the other two print their own line")
+    ap.add_argument("--total-slices", type=int, default=0, help="sharded_backproject: total slices over all ranks (default 200000)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
 
     if args.profile_case:
         profile_case(args)
+        return
+    if args.impl == "b200" and args.workload == "autograd_step":
+        autograd_step_workload(args)
+        return
+    if args.impl == "b200" and args.workload == "sharded_backproject":
+        sharded_backprojection_workload(args)
         return
 
     if args.impl == "reference":
