@@ -292,3 +292,19 @@ def test_workspace_path_equals_direct_path_and_oracle(tp, dim, interp):
     for use_ws in (False, True):
         assert rel_err(outs[use_ws][0], 2 * d_want) <= TOL_ATOMIC
         assert rel_err(outs[use_ws][1], 2 * w_want) <= TOL_ATOMIC
+
+
+def test_host_streaming_wrappers_match_device_calls(tp):
+    """project_3d_to_2d_to_host / backproject_2d_to_3d_from_host (chunked, copies on a second
+    stream) give what the plain device calls give."""
+    case = Case("stream", 3, "linear", 1, 37, 16, 32, 2.0, None, 1, 1, seed=70, special_poses=False)
+    t = make_inputs(case)
+    pin = lambda x: x.pin_memory()  # noqa: E731
+    out = tp.project_3d_to_2d_to_host(pin(t["rec"]), pin(t["rot"]), pin(t["shifts"]), chunk=8, output_shape=(16, 16),
+                                      interpolation="linear", oversampling=2.0)
+    torch.cuda.current_stream().synchronize()
+    want = tp.project_3d_to_2d_forw(t["rec"].cuda(), t["rot"].cuda(), t["shifts"].cuda(), output_shape=(16, 16), oversampling=2.0)
+    assert not out.is_cuda and torch.equal(out, want.cpu())
+    vols = tp.backproject_2d_to_3d_from_host(pin(t["proj"]), t["rot"], pin(t["weights"]), t["shifts"], chunk=8, oversampling=2.0)
+    d_want, w_want = tp.backproject_2d_to_3d_forw(t["proj"].cuda(), t["rot"].cuda(), weights=t["weights"].cuda(), shifts=t["shifts"].cuda(), oversampling=2.0)
+    assert rel_err(vols.data, d_want) <= TOL_ATOMIC and rel_err(vols.weights, w_want) <= TOL_ATOMIC
