@@ -236,6 +236,17 @@ def profile_case(args):
     rec, rot, shifts = make_projection_inputs(dev, seed=1234)
     rot, shifts = rot[:, :P].contiguous(), shifts[:, :P].contiguous()
     kw = dict(interpolation=PROJ["interp"], oversampling=PROJ["os"], fourier_radius_cutoff=PROJ["cutoff"])
+    if args.profile_case == "backproject_slab":
+        # 256x256 slices into box-512 volumes (808 MB > L2): the slab-ordered kernel
+        gen = torch.Generator(device=dev).manual_seed(5)
+        proj = torch.complex(torch.randn(1, P, 256, 129, generator=gen, device=dev), torch.randn(1, P, 256, 129, generator=gen, device=dev))
+        weights = torch.rand(1, P, 256, 129, generator=gen, device=dev)
+        brot = uniform_rotations(P, torch.Generator().manual_seed(5), dev)
+        for _ in range(2):
+            tp.backproject_2d_to_3d_forw(proj, brot, weights=weights, interpolation="linear", oversampling=2.0)
+        torch.cuda.synchronize()
+        print(f"profile case backproject_slab: {P} slices of 256x256 into box 512, 2 launches done")
+        return
     for _ in range(2):
         if args.profile_case == "project":
             tp.project_3d_to_2d_forw(rec, rot, shifts, output_shape=(PROJ["N"], PROJ["N"]), **kw)
@@ -427,7 +438,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--skip-cpu", action="store_true", help="omit the CPU-baseline leg")
     ap.add_argument("--skip-backproject", action="store_true")
-    ap.add_argument("--profile-case", choices=["project", "backproject", "project_back"], default=None,
+    ap.add_argument("--profile-case", choices=["project", "backproject", "project_back", "backproject_slab"], default=None,
                     help="run a few launches of one kernel on a reduced pose count (for ncu captures); prints no bench line")
     ap.add_argument("--profile-poses", type=int, default=2048)
     ap.add_argument("--workload", choices=["default", "autograd_step", "sharded_backproject"], default="default",

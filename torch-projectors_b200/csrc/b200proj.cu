@@ -6,6 +6,7 @@
 #include <cmath>
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <climits>
 #include <cstdint>
 #include <mutex>
@@ -97,6 +98,21 @@ int zero_async(void* p, size_t bytes, cudaStream_t s) {
     return e == cudaSuccess ? B200PROJ_OK : cuda_fail(e, "cudaMemsetAsync");
 }
 
+// Slab plan of the slab-ordered 3D back-projection: volumes whose data (+ weight) planes of
+// one batch item exceed `min_mb` are processed in slabs of at most `slab_mb` MB of planes.
+// Tunable for experiments through B200PROJ_SLAB_MB / B200PROJ_SLAB_MIN_MB (read once).
+struct SlabPlan { int slabs, planes; };
+SlabPlan slab_plan(int64_t R, bool has_weights) {
+    static const double slab_mb = [] { const char* e = getenv("B200PROJ_SLAB_MB"); return e ? atof(e) : 48.0; }();
+    static const double min_mb = [] { const char* e = getenv("B200PROJ_SLAB_MIN_MB"); return e ? atof(e) : 160.0; }();
+    const double plane_bytes = (double)R * (double)(R / 2 + 1) * (has_weights ? 12.0 : 8.0);
+    if (slab_mb <= 0.0 || plane_bytes * (double)R <= min_mb * 1e6) return {1, (int)R};
+    int planes = (int)(slab_mb * 1e6 / plane_bytes);
+    if (planes < 1) planes = 1;
+    const int slabs = (int)((R + planes - 1) / planes);
+    return {slabs, planes};
+}
+
 // ---- operator bodies, templated on the dimensionality ------------------------------------
 template <int DIM>
 int project_forw(const float* rec, int64_t B, int64_t R, const float* rot, int64_t B_rot,
@@ -172,7 +188,7 @@ int backproject_forw(const float* proj, const float* weights, int64_t B, int64_t
     // Interleaved path: data and weight of a voxel share one 16-byte slot of the workspace
     // (one v4 reduction per tap), folded into the outputs afterwards.
     const size_t ws_need = L.rec_count * sizeof(float4);
-    if (hw && P > 0 && workspace != nullptr && workspace_bytes >= ws_need &&
+    if (hw && P > 0 && !(DIM == 3 && slab_plan(R, hw).slabs > 1) && workspace != nullptr && workspace_bytes >= ws_need &&
         (reinterpret_cast<uintptr_t>(workspace) & 15u) == 0) {
         if (int rc = zero_async(workspace, ws_need, s)) return rc;
         float4* acc = (float4*)workspace;
@@ -192,6 +208,21 @@ int backproject_forw(const float* proj, const float* weights, int64_t B, int64_t
     if (P == 0) return B200PROJ_OK;
     const float2* p = (const float2*)proj;
     float2* d = (float2*)data_rec;
+    if constexpr (DIM == 3) {
+        // volumes beyond L2: slab-ordered passes that keep the active planes L2-resident
+        const SlabPlan plan = slab_plan(R, hw);
+        if (plan.slabs > 1) {
+            const dim3 grid((unsigned)(B * P), (unsigned)plan.slabs, 1);
+#define B200PROJ_SL(C, W) \
+    backproject_slab_kernel<C, W><<<grid, kBlockThreads, 0, s>>>(p, weights, rot, shifts, d, weight_rec, L.g, plan.planes)
+            if (cubic && hw) B200PROJ_SL(true, true);
+            else if (cubic) B200PROJ_SL(true, false);
+            else if (hw) B200PROJ_SL(false, true);
+            else B200PROJ_SL(false, false);
+#undef B200PROJ_SL
+            return check_launch("backproject_forw (slab-ordered) launch");
+        }
+    }
 #define B200PROJ_BP(C, W) \
     backproject_forw_kernel<DIM, C, W><<<L.grid, kBlockThreads, 0, s>>>(p, weights, rot, shifts, d, weight_rec, L.g)
     if (cubic && hw) B200PROJ_BP(true, true);
@@ -293,6 +324,7 @@ size_t b200proj_backproject_workspace_bytes(int dim, int64_t B, int64_t R, int64
     const double taps = (double)B * P * N * (N / 2 + 1) * (dim == 3 ? t * t * t : t * t);
     // worth it once the scatter outweighs the two extra passes over the volume
     if (taps < 4.0 * voxels) return 0;
+    if (dim == 3 && slab_plan(R, true).slabs > 1) return 0;      // beyond-L2 volumes take the slab-ordered path
     return (size_t)voxels * sizeof(float4);
 }
 

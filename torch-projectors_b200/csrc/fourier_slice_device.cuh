@@ -316,11 +316,13 @@ __device__ __forceinline__ void red_add_v4(float4* addr, float a, float b, float
 // and weight of a tap go out as ONE red.global.add.v4.f32; otherwise vol (complex) and, when
 // WEIGHTS, wvol (float) are reduced into directly (v2 + scalar reduction).
 // MUST be called by all 32 lanes of the warp; lanes without a pixel pass valid_own = false.
-template <int DIM, bool CUBIC, bool WEIGHTS, bool WITH_DUP, bool INTERLEAVED>
+// SLAB: only taps whose signed plane coordinate (after the mirror) lies in [z_lo, z_hi) are
+// written; used by the slab-ordered back-projection, where each pass owns a range of planes.
+template <int DIM, bool CUBIC, bool WEIGHTS, bool WITH_DUP, bool INTERLEAVED, bool SLAB = false>
 __device__ __forceinline__ void scatter_coop(const SliceGeom& g, float2* __restrict__ vol,
                                              float* __restrict__ wvol, float4* __restrict__ vol4,
                                              const Pixel& px, bool valid_own, float2 v_own,
-                                             float w_own) {
+                                             float w_own, int z_lo = 0, int z_hi = 0) {
     constexpr int T = CUBIC ? 4 : 2;
     constexpr int TD = (DIM == 3) ? T : 1;
     constexpr unsigned kFull = 0xffffffffu;
@@ -355,6 +357,10 @@ __device__ __forceinline__ void scatter_coop(const SliceGeom& g, float2* __restr
             int dl = 0;
             float wd = 1.f;
             if (DIM == 3) {
+                if (SLAB) {
+                    const int sd = m ? -(ad.base + k) : ad.base + k;
+                    if (sd < z_lo || sd >= z_hi) continue;
+                }
                 dl = scatter_line(g, ad.base + k, m);
                 wd = ad.w[k];
                 if (dl < 0 || wd == 0.f) continue;

@@ -228,6 +228,158 @@ fold_interleaved_kernel(const float4* __restrict__ accum, float2* __restrict__ d
     }
 }
 
+// ---- slab-ordered back-projection (3D, volumes larger than L2) ---------------------------
+// When the accumulation volumes do not fit the 126 MB L2, reductions of the plain kernel miss
+// it: consecutive slices have unrelated orientations, so a voxel is revisited only after
+// gigabytes of other reductions, and every tap becomes a DRAM read-modify-write of a sector.
+// This kernel reorders the work instead of the data: the volume is cut into slabs of
+// `slab_planes` consecutive z planes (signed plane coordinates [z_lo, z_hi)) small enough to
+// stay in L2, blockIdx.y walks the slabs (slowest grid index, so blocks of one slab run
+// together) and, for its slab, each block visits only the pixels of its slice whose taps can
+// land there.  Those pixels form, in every row of the slice, at most two runs of columns
+// (d and c are linear in the column j; one run for direct taps, one for Friedel-mirrored
+// taps, which land at -d and exist where c < 0); the runs are computed from linear estimates
+// with a small slack, candidates pass a one-FMA prefilter, and each tap is then tested
+// exactly (scatter_coop<SLAB>), so every tap is written by exactly one slab pass.
+// One block = one slice x one slab; each of its 8 warps owns a contiguous band of rows and
+// prepares 32 rows at a time, one per lane.
+// Restrict the column run [ja, jb] to the columns where a*j + b lies in [lo, hi].
+__device__ __forceinline__ void clip_run(float a, float b, float lo, float hi, float& ja, float& jb) {
+    if (fabsf(a) < 1e-6f) {
+        if (b < lo || b > hi) jb = ja - 1.f;        // empty
+        return;
+    }
+    const float x0 = (lo - b) / a, x1 = (hi - b) / a;
+    ja = fmaxf(ja, fminf(x0, x1));
+    jb = fminf(jb, fmaxf(x0, x1));
+}
+
+template <bool CUBIC, bool WEIGHTS>
+__global__ void __launch_bounds__(kBlockThreads)
+backproject_slab_kernel(const float2* __restrict__ proj, const float* __restrict__ weights,
+                        const float* __restrict__ rot, const float* __restrict__ shifts,
+                        float2* __restrict__ data_rec, float* __restrict__ weight_rec,
+                        const SliceGeom g, int slab_planes) {
+    constexpr int T = CUBIC ? 4 : 2;
+    constexpr unsigned kFull = 0xffffffffu;
+    constexpr float kEps = 0.05f;                    // slack of the linear estimates below
+    const int bp = blockIdx.x;
+    const int b = bp / g.P, p = bp - b * g.P;
+    const int z_lo = -g.half + 1 + (int)blockIdx.y * slab_planes;
+    const int z_hi = min(z_lo + slab_planes, g.half + 1);
+    const float* rm = pose_rot<3>(g, rot, b, p);
+    // linear estimates of the sample position along a row: d ~ ad*j + bd*kr, c ~ ac*j + bc*kr
+    const float osf = (float)g.os;
+    const float ac = osf * __ldg(rm + 0), bc = osf * __ldg(rm + 1);
+    const float ad = osf * __ldg(rm + 6), bd = osf * __ldg(rm + 7);
+    // taps of a pixel use planes floor(d)-T/2+1 .. floor(d)+T/2 (mirrored taps their negatives)
+    // and columns floor(c)-T/2+1 .. floor(c)+T/2; direct taps need a column >= 0, mirrored < 0
+    const float band_lo = (float)z_lo - (float)(T / 2) - kEps;
+    const float band_hi = (float)z_hi + (float)(T / 2 - 1) + kEps;
+    const float c_direct_min = -(float)(T / 2) - kEps;
+    const float c_mirror_max = (float)(T / 2 - 1) + kEps;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    float2* data_b = data_rec + (size_t)b * g.vol_elems;
+    float* wrec_b = WEIGHTS ? weight_rec + (size_t)b * g.vol_elems : nullptr;
+    const float cut = sqrtf(g.cutoff_sq);
+    const int rows_per_warp = (g.N + kWarps - 1) / kWarps;
+    const int row_end = min(g.N, (warp + 1) * rows_per_warp);
+
+    for (int i0 = warp * rows_per_warp; i0 < row_end; i0 += 32) {
+        // each lane prepares one row: its direct and mirrored column runs (empty: a > b)
+        int run_a[2] = {1, 1}, run_b[2] = {0, 0};
+        const int irow = i0 + lane;
+        if (irow < row_end) {
+            const float kr = (float)((irow <= g.N / 2) ? irow : irow - g.N);
+            const float room = g.cutoff_sq - kr * kr;
+            if (room >= 0.f) {
+                const float jmax = fminf((float)(g.Nh - 1), fminf(sqrtf(room), cut) + 1.f);
+                const float d0 = bd * kr, c0 = bc * kr;
+#pragma unroll
+                for (int t = 0; t < 2; ++t) {
+                    float ja = 0.f, jb = jmax;
+                    if (t == 0) {
+                        clip_run(ad, d0, band_lo, band_hi, ja, jb);
+                        clip_run(ac, c0, c_direct_min, 3.0e38f, ja, jb);
+                    } else {
+                        clip_run(ad, d0, -band_hi, -band_lo, ja, jb);
+                        clip_run(ac, c0, -3.0e38f, c_mirror_max, ja, jb);
+                    }
+                    if (jb >= ja) {
+                        run_a[t] = max(0, (int)floorf(ja) - 1);
+                        run_b[t] = min((int)jmax, (int)ceilf(jb) + 1);
+                    }
+                }
+                // overlapping or adjacent runs become one (pixels must be visited once per slab)
+                if (run_a[0] <= run_b[0] && run_a[1] <= run_b[1] &&
+                    run_a[0] <= run_b[1] + 1 && run_a[1] <= run_b[0] + 1) {
+                    run_a[0] = min(run_a[0], run_a[1]);
+                    run_b[0] = max(run_b[0], run_b[1]);
+                    run_a[1] = 1;
+                    run_b[1] = 0;
+                }
+            }
+        }
+        // Flatten the candidate columns of these 32 rows into one index space so that the warp
+        // stays full however thin the strips are: lane l holds n_l candidates, an inclusive
+        // scan gives every row its offset, and candidate k finds its row by binary search.
+        const int len0 = max(0, run_b[0] - run_a[0] + 1), len1 = max(0, run_b[1] - run_a[1] + 1);
+        int incl = len0 + len1;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int up = __shfl_up_sync(kFull, incl, o);
+            if (lane >= o) incl += up;
+        }
+        const int total = __shfl_sync(kFull, incl, 31);
+        for (int k0 = 0; k0 < total; k0 += 32) {                                  // warp-uniform trip count
+            const int k = k0 + lane;
+            // smallest row whose inclusive count exceeds k
+            int row = 0;
+#pragma unroll
+            for (int step = 16; step > 0; step >>= 1) {
+                const int probe = __shfl_sync(kFull, incl, (row + step - 1) & 31);
+                if (k >= probe) row += step;
+            }
+            row = min(row, 31);
+            const int r_incl = __shfl_sync(kFull, incl, row);
+            const int r_len0 = __shfl_sync(kFull, len0, row), r_len1 = __shfl_sync(kFull, len1, row);
+            const int r_a0 = __shfl_sync(kFull, run_a[0], row), r_a1 = __shfl_sync(kFull, run_a[1], row);
+            const int local = k - (r_incl - r_len0 - r_len1);
+            const int j = local < r_len0 ? r_a0 + local : r_a1 + (local - r_len0);
+            const int i = i0 + row;
+            const float kr = (float)((i <= g.N / 2) ? i : i - g.N);
+            // one-FMA prefilter with the linear estimates, then the exact test
+            const float de = fmaf(ad, (float)j, bd * kr), ce = fmaf(ac, (float)j, bc * kr);
+            bool active = k < total && !(j == 0 && i >= g.N / 2) &&
+                          ((de >= band_lo && de <= band_hi && ce >= c_direct_min) ||
+                           (-de >= band_lo && -de <= band_hi && ce <= c_mirror_max));
+            Pixel px;
+            px.c = px.r = px.d = 0.f;
+            if (active) active = pixel_setup<3>(g, rm, i, j, px);
+            if (active) {
+                const int pd = (int)floorf(px.d) - (CUBIC ? 1 : 0);
+                const int pc = (int)floorf(px.c) - (CUBIC ? 1 : 0);
+                const bool direct = pc + T - 1 >= 0 && pd < z_hi && pd + T > z_lo;
+                const bool mirror = pc < 0 && -(pd + T - 1) < z_hi && -pd >= z_lo;
+                active = direct || mirror;
+            }
+            if (!__any_sync(kFull, active)) continue;
+            float2 v = make_float2(0.f, 0.f);
+            float wv = 0.f;
+            if (active) {
+                const size_t pix = ((size_t)bp * (size_t)g.N + (size_t)i) * (size_t)g.Nh + (size_t)j;
+                v = __ldcs(proj + pix);
+                if (g.has_shift) {
+                    const float* s = pose_shift(g, shifts, b, p);
+                    v = cmul_conj(v, phase_ramp(g, px, __ldg(s), __ldg(s + 1)));
+                }
+                if (WEIGHTS) wv = __ldcs(weights + pix);
+            }
+            scatter_coop<3, CUBIC, WEIGHTS, true, false, true>(g, data_b, wrec_b, nullptr, px, active, v, wv, z_lo, z_hi);
+        }
+    }
+}
+
 // ---- backward of back-projection --------------------------------------------------------
 // reference semantics: csrc/cpu/3d/backprojection_2d_to_3d_kernels.cpp:417-583
 template <int DIM, bool CUBIC, bool NEED_ROT, bool NEED_SHIFT>
