@@ -103,7 +103,7 @@ int zero_async(void* p, size_t bytes, cudaStream_t s) {
 // Tunable for experiments through B200PROJ_SLAB_MB / B200PROJ_SLAB_MIN_MB (read once).
 struct SlabPlan { int slabs, planes; };
 SlabPlan slab_plan(int64_t R, bool has_weights) {
-    static const double slab_mb = [] { const char* e = getenv("B200PROJ_SLAB_MB"); return e ? atof(e) : 48.0; }();
+    static const double slab_mb = [] { const char* e = getenv("B200PROJ_SLAB_MB"); return e ? atof(e) : 64.0; }();
     static const double min_mb = [] { const char* e = getenv("B200PROJ_SLAB_MIN_MB"); return e ? atof(e) : 160.0; }();
     const double plane_bytes = (double)R * (double)(R / 2 + 1) * (has_weights ? 12.0 : 8.0);
     if (slab_mb <= 0.0 || plane_bytes * (double)R <= min_mb * 1e6) return {1, (int)R};

@@ -94,19 +94,21 @@ __device__ __forceinline__ float2 cmul_conj(float2 a, float2 b) {   // a * conj(
     return make_float2(a.x * b.x + a.y * b.y, a.y * b.x - a.x * b.y);
 }
 
-// Catmull-Rom weight (a = -0.5) and its derivative for |s| <= 2.
-__device__ __forceinline__ float cubic_w(float s) {
-    s = fabsf(s);
-    const float inner = (1.5f * s - 2.5f) * s * s + 1.0f;
-    const float outer = ((-0.5f * s + 2.5f) * s - 4.0f) * s + 2.0f;
-    return s <= 1.0f ? inner : (s <= 2.0f ? outer : 0.0f);
+// Catmull-Rom (a = -0.5) weights of the four taps floor-1 .. floor+2 for a fractional position
+// f in [0, 1), and their derivatives with respect to f.  These are the polynomials
+// w(f - t), t = -1..2, of the reference's piecewise kernel
+// (csrc/cpu/common/cubic_kernels.h:25-66) written out per tap, so that no branch on |s| is needed.
+__device__ __forceinline__ void cubic_weights(float f, float (&w)[4]) {
+    w[0] = ((-0.5f * f + 1.0f) * f - 0.5f) * f;
+    w[1] = (1.5f * f - 2.5f) * f * f + 1.0f;
+    w[2] = ((-1.5f * f + 2.0f) * f + 0.5f) * f;
+    w[3] = (0.5f * f - 0.5f) * f * f;
 }
-__device__ __forceinline__ float cubic_dw(float s) {
-    const float sign = s < 0.f ? -1.f : 1.f;
-    s = fabsf(s);
-    const float inner = (4.5f * s - 5.0f) * s;
-    const float outer = (-1.5f * s + 5.0f) * s - 4.0f;
-    return sign * (s <= 1.0f ? inner : (s <= 2.0f ? outer : 0.0f));
+__device__ __forceinline__ void cubic_dweights(float f, float (&dw)[4]) {
+    dw[0] = (-1.5f * f + 2.0f) * f - 0.5f;
+    dw[1] = (4.5f * f - 5.0f) * f;
+    dw[2] = (-4.5f * f + 4.0f) * f + 0.5f;
+    dw[3] = (1.5f * f - 1.0f) * f;
 }
 
 // Per-axis interpolation weights: T = 2 (linear: taps at floor, floor+1) or
@@ -122,19 +124,15 @@ template <int T, bool WITH_DERIV>
 __device__ __forceinline__ void axis_weights(float x, AxisWeights<T>& a) {
     const float fl = floorf(x);
     const float f = x - fl;
-    if (T == 2) {
+    if constexpr (T == 2) {
         a.base = (int)fl;
         a.w[0] = 1.f - f;
         a.w[1] = f;
         if (WITH_DERIV) { a.dw[0] = -1.f; a.dw[1] = 1.f; }
     } else {
         a.base = (int)fl - 1;
-#pragma unroll
-        for (int t = 0; t < T; ++t) {
-            const float s = f - (float)(t - 1);
-            a.w[t] = cubic_w(s);
-            if (WITH_DERIV) a.dw[t] = cubic_dw(s);
-        }
+        cubic_weights(f, a.w);
+        if (WITH_DERIV) cubic_dweights(f, a.dw);
     }
 }
 
@@ -189,7 +187,9 @@ __device__ __forceinline__ void interpolate_coop(const SliceGeom& g, const float
     val = make_float2(0.f, 0.f);
     g_c = g_r = g_d = val;
 
-#pragma unroll
+    // the loop over the group's pixels stays rolled: its body holds T*T unrolled taps, and T
+    // copies of it overflow the instruction cache (seen as no_instruction stalls)
+#pragma unroll 1
     for (int s = 0; s < T; ++s) {
         const int src = (lane & ~(T - 1)) | s;
         const float pc = __shfl_sync(kFull, px.c, src);
@@ -209,22 +209,47 @@ __device__ __forceinline__ void interpolate_coop(const SliceGeom& g, const float
             bool m;
             const int col = gather_col<CUBIC>(g, cbase + q, m);
             float wc, dwc = 0.f;
-            if (CUBIC) {
-                wc = cubic_w(fc - (float)(q - 1));
-                if (WITH_DERIV) dwc = cubic_dw(fc - (float)(q - 1));
+            if constexpr (CUBIC) {
+                float w4[4];
+                cubic_weights(fc, w4);
+                wc = q == 0 ? w4[0] : q == 1 ? w4[1] : q == 2 ? w4[2] : w4[3];
+                if (WITH_DERIV) {
+                    float d4[4];
+                    cubic_dweights(fc, d4);
+                    dwc = q == 0 ? d4[0] : q == 1 ? d4[1] : q == 2 ? d4[2] : d4[3];
+                }
             } else {
                 wc = q ? fc : 1.f - fc;
                 dwc = q ? 1.f : -1.f;
             }
-            int rowcol[T];
+            // interior footprints (all but a shell one voxel thick) need no clamping: the index
+            // of a signed coordinate is the coordinate (negated for a mirrored column), wrapped
+            const bool interior = ar.base >= -g.half + 1 && ar.base + T - 1 <= g.half - 1 &&
+                                  (DIM == 2 || (ad.base >= -g.half + 1 && ad.base + T - 1 <= g.half - 1));
+            int rowcol[T], plane[TD];
+            if (interior) {
 #pragma unroll
-            for (int i = 0; i < T; ++i) rowcol[i] = gather_line<CUBIC>(g, ar.base + i, m) * g.Rh + col;
+                for (int i = 0; i < T; ++i) {
+                    const int r = m ? -(ar.base + i) : ar.base + i;
+                    rowcol[i] = (r < 0 ? r + g.R : r) * g.Rh + col;
+                }
+#pragma unroll
+                for (int k = 0; k < TD; ++k) {
+                    const int d = (DIM == 3) ? (m ? -(ad.base + k) : ad.base + k) : 0;
+                    plane[k] = (d < 0 ? d + g.R : d) * plane_stride;
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < T; ++i) rowcol[i] = gather_line<CUBIC>(g, ar.base + i, m) * g.Rh + col;
+#pragma unroll
+                for (int k = 0; k < TD; ++k)
+                    plane[k] = (DIM == 3) ? gather_line<CUBIC>(g, ad.base + k, m) * plane_stride : 0;
+            }
 
             float2 A = make_float2(0.f, 0.f), Bq = A, Dq = A;
 #pragma unroll
             for (int k = 0; k < TD; ++k) {
-                const float2* __restrict__ pl =
-                    vol + ((DIM == 3) ? gather_line<CUBIC>(g, ad.base + k, m) * plane_stride : 0);
+                const float2* __restrict__ pl = vol + plane[k];
                 float2 rs = make_float2(0.f, 0.f), rds = rs;
 #pragma unroll
                 for (int i = 0; i < T; ++i) {
@@ -329,7 +354,7 @@ __device__ __forceinline__ void scatter_coop(const SliceGeom& g, float2* __restr
     const int lane = threadIdx.x & 31;
     const int q = lane & (T - 1);
     const int plane_stride = g.R * g.Rh;
-#pragma unroll
+#pragma unroll 1
     for (int s = 0; s < T; ++s) {
         const int src = (lane & ~(T - 1)) | s;
         const float pc = __shfl_sync(kFull, px.c, src);
@@ -344,7 +369,14 @@ __device__ __forceinline__ void scatter_coop(const SliceGeom& g, float2* __restr
         const float flc = floorf(pc);
         const float fc = pc - flc;
         int c = (CUBIC ? (int)flc - 1 : (int)flc) + q;
-        const float wc = CUBIC ? cubic_w(fc - (float)(q - 1)) : (q ? fc : 1.f - fc);
+        float wc;
+        if constexpr (CUBIC) {
+            float w4[4];
+            cubic_weights(fc, w4);
+            wc = q == 0 ? w4[0] : q == 1 ? w4[1] : q == 2 ? w4[2] : w4[3];
+        } else {
+            wc = q ? fc : 1.f - fc;
+        }
         const bool m = c < 0;
         c = m ? -c : c;
         if (c >= g.Rh || wc == 0.f) continue;
