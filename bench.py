@@ -430,6 +430,64 @@ def sharded_backprojection_workload(args):
         dist.destroy_process_group()
 
 
+def ops_table_workload(args):
+    """Device-resident timing of all eight raw operators (slices/s each), linear and cubic, at the
+    sizes of BASELINE configs 1-3: 2D ops on a 128x128 reference (64 px padded 2x), 64x64 output;
+    3D ops on the box-256 volume, 128x128 slices.  One JSON object, one entry per operator."""
+    import torch_projectors_b200 as tp
+    dist, rank, world, local_rank, dev = _dist_setup()
+    ops = torch.ops.torch_projectors_b200
+    gen = torch.Generator().manual_seed(11)
+    ggen = torch.Generator(device=dev).manual_seed(11)
+    flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    rows = {}
+
+    def cplx(*shape):
+        return torch.complex(torch.randn(*shape, generator=ggen, device=dev), torch.randn(*shape, generator=ggen, device=dev))
+
+    def time_op(name, fn, slices):
+        ms = timed_steps(fn, args.steps, args.warmup, flush_buf.zero_, lambda: None)
+        m = statistics.median(ms)
+        rows[name] = {"ms": m, "slices_per_s": slices / (m * 1e-3)}
+
+    # ---- 2D quartet: config 1 geometry (P = 256) and a throughput-sized batch of poses ----
+    from cases import random_rotations_2d
+    rec2 = torch.fft.rfft2(torch.fft.fftshift(torch.nn.functional.pad(torch.randn(64, 64, generator=gen), (32, 32, 32, 32))),
+                           norm="forward").to(torch.complex64).unsqueeze(0).to(dev)
+    for P2 in (256, 65536):
+        rot2 = random_rotations_2d(P2, gen).reshape(1, P2, 2, 2).to(dev).requires_grad_(True)
+        sh2 = ((torch.rand(1, P2, 2, generator=gen) * 2 - 1) * 4).to(dev).requires_grad_(True)
+        proj2 = cplx(1, P2, 64, 33)
+        w2 = torch.rand(1, P2, 64, 33, generator=ggen, device=dev)
+        gd2, gw2 = cplx(1, 128, 65), torch.randn(1, 128, 65, generator=ggen, device=dev)
+        for interp in ("linear", "cubic"):
+            tag = f"[P={P2},{interp}]"
+            time_op("project_2d_forw" + tag, lambda: ops.project_2d_forw(rec2, rot2, sh2, [64, 64], interp, 2.0, None), P2)
+            time_op("project_2d_back" + tag, lambda: ops.project_2d_back(proj2, rec2, rot2, sh2, interp, 2.0, None), P2)
+            time_op("backproject_2d_forw" + tag, lambda: ops.backproject_2d_forw(proj2, w2, rot2, sh2, interp, 2.0, None), P2)
+            time_op("backproject_2d_back" + tag, lambda: ops.backproject_2d_back(gd2, gw2, proj2, w2, rot2, sh2, interp, 2.0, None), P2)
+    # ---- 3D quartet on the box-256 volume ----
+    rec3, rot3, sh3 = make_projection_inputs(dev, seed=12)
+    P3 = 4096
+    rot3 = rot3[:, :P3].contiguous().requires_grad_(True)
+    sh3 = sh3[:, :P3].contiguous().requires_grad_(True)
+    proj3 = cplx(1, P3, 128, 65)
+    w3 = torch.rand(1, P3, 128, 65, generator=ggen, device=dev)
+    gd3, gw3 = cplx(1, 256, 256, 129), torch.randn(1, 256, 256, 129, generator=ggen, device=dev)
+    for interp in ("linear", "cubic"):
+        tag = f"[P={P3},{interp}]"
+        time_op("project_3d_to_2d_forw" + tag, lambda: ops.project_3d_to_2d_forw(rec3, rot3, sh3, [128, 128], interp, 2.0, None), P3)
+        time_op("project_3d_to_2d_back" + tag, lambda: ops.project_3d_to_2d_back(proj3, rec3, rot3, sh3, interp, 2.0, None), P3)
+        time_op("backproject_2d_to_3d_forw" + tag, lambda: ops.backproject_2d_to_3d_forw(proj3, w3, rot3, sh3, interp, 2.0, None), P3)
+        time_op("backproject_2d_to_3d_back" + tag, lambda: ops.backproject_2d_to_3d_back(gd3, gw3, proj3, w3, rot3, sh3, interp, 2.0, None), P3)
+    if rank == 0:
+        print(json.dumps({"metric": "per-operator device time (all gradients requested in the *_back operators)", "unit": "ms / slices/s",
+                          "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "data": "synthetic", "dtype": "f32",
+                          "config": {"workload": "all eight raw operators, oversampling 2, shifts, weights; 2D: 128x128 reference -> 64x64; 3D: box-256 volume <-> 128x128",
+                                     "l2": "256 MiB flush before every call"},
+                          "operators": rows}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -441,7 +499,7 @@ def main():
     ap.add_argument("--profile-case", choices=["project", "backproject", "project_back", "backproject_slab"], default=None,
                     help="run a few launches of one kernel on a reduced pose count (for ncu captures); prints no bench line")
     ap.add_argument("--profile-poses", type=int, default=2048)
-    ap.add_argument("--workload", choices=["default", "autograd_step", "sharded_backproject"], default="default",
+    ap.add_argument("--workload", choices=["default", "autograd_step", "sharded_backproject", "ops_table"], default="default",
                     help="default: projection (+ back-projection) headline line; the other two print their own line")
     ap.add_argument("--total-slices", type=int, default=0, help="sharded_backproject: total slices over all ranks (default 200000)")
     args = ap.parse_args()
@@ -452,6 +510,9 @@ def main():
         return
     if args.impl == "b200" and args.workload == "autograd_step":
         autograd_step_workload(args)
+        return
+    if args.impl == "b200" and args.workload == "ops_table":
+        ops_table_workload(args)
         return
     if args.impl == "b200" and args.workload == "sharded_backproject":
         sharded_backprojection_workload(args)
