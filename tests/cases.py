@@ -147,4 +147,8 @@ MEDIUM_CASES = [
     Case("3d_lin_cfg3_like", 3, "linear", 1, 32, 64, 128, 2.0, None, 1, 1, shift_range=8.0, seed=21, special_poses=False),
     Case("2d_lin_cfg1_like", 2, "linear", 1, 64, 64, 128, 2.0, None, 1, 1, seed=22, special_poses=False),
     Case("3d_cub_odd_tiles", 3, "cubic", 2, 5, 34, 70, 2.0, None, 2, 2, seed=23),
+    # >= 64 poses: the 2D scatter operators take the shared-memory-privatised path
+    Case("2d_cub_private", 2, "cubic", 2, 70, 16, 32, 2.0, None, 2, 2, seed=24),
+    Case("2d_lin_private_noweights", 2, "linear", 1, 80, 12, 24, 2.0, 4.5, 1, 0, weights=False, seed=25),
+    Case("2d_lin_private_overreach", 2, "linear", 1, 66, 16, 16, 1.5, None, 1, 1, seed=26),
 ]
