@@ -488,6 +488,55 @@ def ops_table_workload(args):
                           "operators": rows}), flush=True)
 
 
+def reference_cuda_workload(args):
+    """Informational: the reference's own CUDA kernels (recompiled for sm_100 with its flags into
+    oracle/_ref by `oracle/build_ref.py --cuda`) timed on the same GPU and inputs as the
+    headline workloads, next to this package, with the difference between the two results."""
+    import oracle
+    if not oracle.reference_cuda_available():
+        print(json.dumps({"workload": "reference_cuda", "unavailable": "oracle/_ref/torch_projectors_ref_cuda.so not built"}))
+        return
+    import torch_projectors_b200 as tp
+    from cases import rel_err
+    ref = oracle.reference_cuda_ops()
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    rows = {}
+
+    def both(name, slices, f_ref, f_new, pick):
+        r_ms = statistics.median(timed_steps(f_ref, args.steps, args.warmup, flush_buf.zero_, lambda: None))
+        n_ms = statistics.median(timed_steps(f_new, args.steps, args.warmup, flush_buf.zero_, lambda: None))
+        a, b = pick(f_ref()), pick(f_new())
+        rows[name] = {"reference_cuda_ms": r_ms, "b200_ms": n_ms, "speedup": r_ms / n_ms,
+                      "reference_cuda_slices_per_s": slices / (r_ms * 1e-3), "b200_slices_per_s": slices / (n_ms * 1e-3),
+                      "max_rel_difference": rel_err(b, a)}
+
+    rec, rot, shifts = make_projection_inputs(dev, seed=1234)
+    for interp in ("cubic", "linear"):
+        both(f"project_3d_to_2d_forw[{interp}, 10000 poses, box 256]", PROJ["P"],
+             lambda: ref.project_3d_to_2d_forw(rec, rot, shifts, [128, 128], interp, 2.0, 64.0),
+             lambda: torch.ops.torch_projectors_b200.project_3d_to_2d_forw(rec, rot, shifts, [128, 128], interp, 2.0, 64.0),
+             lambda o: o)
+    Pb = 20_000
+    proj, weights, brot, bshifts = make_backprojection_inputs(dev, 4321, Pb)
+    for interp in ("linear", "cubic"):
+        both(f"backproject_2d_to_3d_forw[{interp}, {Pb} slices, box 256]", Pb,
+             lambda: ref.backproject_2d_to_3d_forw(proj, weights, brot, bshifts, interp, 2.0, None),
+             lambda: torch.ops.torch_projectors_b200.backproject_2d_to_3d_forw(proj, weights, brot, bshifts, interp, 2.0, None),
+             lambda o: o[0])
+    Pg = 2048
+    g = proj[:, :Pg].contiguous()
+    rot_g = rot[:, :Pg].clone().requires_grad_(True)
+    sh_g = shifts[:, :Pg].clone().requires_grad_(True)
+    both(f"project_3d_to_2d_back[cubic, {Pg} poses, all grads]", Pg,
+         lambda: ref.project_3d_to_2d_back(g, rec, rot_g, sh_g, "cubic", 2.0, 64.0),
+         lambda: torch.ops.torch_projectors_b200.project_3d_to_2d_back(g, rec, rot_g, sh_g, "cubic", 2.0, 64.0),
+         lambda o: o[0])
+    print(json.dumps({"metric": "reference CUDA kernels (sm_100 recompile, --use_fast_math) vs this package, same B200, same inputs",
+                      "steps": args.steps, "warmup": args.warmup, "data": "synthetic", "rows": rows}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -499,7 +548,7 @@ def main():
     ap.add_argument("--profile-case", choices=["project", "backproject", "project_back", "backproject_slab"], default=None,
                     help="run a few launches of one kernel on a reduced pose count (for ncu captures); prints no bench line")
     ap.add_argument("--profile-poses", type=int, default=2048)
-    ap.add_argument("--workload", choices=["default", "autograd_step", "sharded_backproject", "ops_table"], default="default",
+    ap.add_argument("--workload", choices=["default", "autograd_step", "sharded_backproject", "ops_table", "reference_cuda"], default="default",
                     help="default: projection (+ back-projection) headline line; the other two print their own line")
     ap.add_argument("--total-slices", type=int, default=0, help="sharded_backproject: total slices over all ranks (default 200000)")
     args = ap.parse_args()
@@ -510,6 +559,9 @@ def main():
         return
     if args.impl == "b200" and args.workload == "autograd_step":
         autograd_step_workload(args)
+        return
+    if args.impl == "b200" and args.workload == "reference_cuda":
+        reference_cuda_workload(args)
         return
     if args.impl == "b200" and args.workload == "ops_table":
         ops_table_workload(args)

@@ -39,3 +39,29 @@ def reference_ops():
         torch.ops.load_library(str(_REF_SO))
         _ref_loaded = True
     return torch.ops.torch_projectors
+
+
+_REF_CUDA_SO = Path(__file__).resolve().parent / "_ref" / "torch_projectors_ref_cuda.so"
+
+
+def reference_cuda_available() -> bool:
+    return _REF_CUDA_SO.exists()
+
+
+def reference_cuda_ops():
+    """``torch.ops.torch_projectors`` backed by the reference's CPU AND CUDA kernels (its CUDA
+    sources recompiled for sm_100 by ``oracle/build_ref.py --cuda``).  Speed comparator only.
+    The CPU-only library and this one define the same op namespace, so a process can load just
+    one of them."""
+    global _ref_loaded
+    import torch
+
+    if _ref_loaded == "cuda":
+        return torch.ops.torch_projectors
+    if _ref_loaded:
+        raise RuntimeError("the CPU-only reference library is already loaded in this process")
+    if not _REF_CUDA_SO.exists():
+        raise FileNotFoundError(f"{_REF_CUDA_SO} not built; run `python oracle/build_ref.py --cuda`")
+    torch.ops.load_library(str(_REF_CUDA_SO))
+    _ref_loaded = "cuda"
+    return torch.ops.torch_projectors

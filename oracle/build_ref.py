@@ -37,6 +37,18 @@ HERE = Path(__file__).resolve().parent
 OUT_DIR = HERE / "_ref"
 OUT_SO = OUT_DIR / "torch_projectors_ref.so"
 
+OUT_SO_CUDA = OUT_DIR / "torch_projectors_ref_cuda.so"
+
+# The reference's CUDA backend (generic SIMT kernels, no sm_100-specific code), compiled with the
+# flags of its own build (setup.py: -O3 --use_fast_math -DUSE_CUDA) for sm_100: the kernels a user
+# of the reference would run on a B200.  Used only as a speed comparator by bench.py.
+CUDA_SOURCES = [
+    "csrc/cuda/2d/projection_2d_kernels.cu",
+    "csrc/cuda/2d/backprojection_2d_kernels.cu",
+    "csrc/cuda/3d/projection_3d_to_2d_kernels.cu",
+    "csrc/cuda/3d/backprojection_2d_to_3d_kernels.cu",
+]
+
 SOURCES = [
     "csrc/torch_projectors.cpp",
     "csrc/cpu/2d/projection_2d_kernels.cpp",
@@ -100,9 +112,59 @@ def build(reference: Path | None = None, force: bool = False, verbose: bool = Tr
     return OUT_SO
 
 
+def build_cuda(reference: Path | None = None, force: bool = False, verbose: bool = True) -> Path | None:
+    """Compile the reference's CPU + CUDA backends into one library (registers the CUDA
+    dispatch key too).  Takes several minutes (nvcc on torch headers); returns the .so path,
+    or a previously built one / None when the reference checkout is absent."""
+    reference = Path(reference) if reference else default_reference()
+    if not (reference / CUDA_SOURCES[0]).exists():
+        return OUT_SO_CUDA if OUT_SO_CUDA.exists() else None
+    if OUT_SO_CUDA.exists() and not force:
+        return OUT_SO_CUDA
+    import torch  # noqa: F401
+    from torch.utils import cpp_extension as ce
+
+    OUT_DIR.mkdir(parents=True, exist_ok=True)
+    obj_dir = OUT_DIR / "obj_cuda"
+    obj_dir.mkdir(exist_ok=True)
+    inc = [f"-I{p}" for p in ce.include_paths()] + [f"-I{sysconfig.get_paths()['include']}", "-I/usr/local/cuda/include"]
+    cxx11 = int(torch._C._GLIBCXX_USE_CXX11_ABI)
+    defs = [f"-D_GLIBCXX_USE_CXX11_ABI={cxx11}", "-DTORCH_EXTENSION_NAME=torch_projectors_ref_cuda",
+            "-DTORCH_API_INCLUDE_EXTENSION_H", "-DUSE_CUDA"]
+    host = ["g++", "-O3", "-std=c++20", "-fopenmp", "-fPIC", "-w"] + defs + inc
+    dev = ["nvcc", "-O3", "--use_fast_math", "-std=c++17", "-gencode", "arch=compute_100,code=sm_100",
+           "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC", "-w",
+           "-D__CUDA_NO_HALF_OPERATORS__", "-D__CUDA_NO_HALF_CONVERSIONS__", "-D__CUDA_NO_HALF2_OPERATORS__",
+           "-D__CUDA_NO_BFLOAT16_CONVERSIONS__"] + defs + inc
+
+    def compile_one(rel: str) -> Path:
+        src = reference / rel
+        obj = obj_dir / (src.stem + ("_cu.o" if src.suffix == ".cu" else ".o"))
+        cmd = (dev if src.suffix == ".cu" else host) + ["-c", str(src), "-o", str(obj)]
+        if verbose:
+            print("[build_ref cuda]", cmd[0], "...", src.name, flush=True)
+        subprocess.run(cmd, check=True)
+        return obj
+
+    with ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 1)) as ex:
+        objs = list(ex.map(compile_one, SOURCES + CUDA_SOURCES))
+    libdirs = ce.library_paths() + ["/usr/local/cuda/lib64"]
+    link = (["g++", "-shared", "-fopenmp", "-o", str(OUT_SO_CUDA)] + [str(o) for o in objs]
+            + [f"-L{d}" for d in libdirs] + [f"-Wl,-rpath,{d}" for d in libdirs]
+            + ["-lc10", "-lc10_cuda", "-ltorch", "-ltorch_cpu", "-ltorch_cuda", "-ltorch_python", "-lcudart"])
+    subprocess.run(link, check=True)
+    if verbose:
+        print(f"[build_ref cuda] wrote {OUT_SO_CUDA}")
+    return OUT_SO_CUDA
+
+
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", default=None)
     ap.add_argument("--force", action="store_true")
+    ap.add_argument("--cuda", action="store_true", help="also build the reference's CUDA backend (minutes)")
     a = ap.parse_args()
-    sys.exit(0 if build(a.reference, a.force) else 1)
+    ok = build(a.reference, a.force)
+    if a.cuda:
+        ok = build_cuda(a.reference, a.force) and ok
+    sys.exit(0 if ok else 1)
