@@ -183,6 +183,69 @@ int b200proj_backproject_2d_to_3d_back(const float* grad_data_rec, const float* 
                                        float* grad_proj, float* grad_weights, float* grad_rot,
                                        float* grad_shifts, void* stream);
 
+
+/* ---- complex128 / float64 variants ------------------------------------------------------
+ * The same eight operators for double precision tensors (complex128 data, float64 poses and
+ * weights): identical arguments with `double` in place of `float`.  The reference's CUDA
+ * wrappers serve these dtypes by copying to the host and running its CPU kernels
+ * (csrc/cuda/3d/projection_3d_to_2d_kernels.cu:902-918, used by its gradcheck tests); here they
+ * run on the GPU with the same kernels instantiated for double.  Reductions use
+ * red.global.add.f64; the workspace arguments of the back-projection entries are accepted and
+ * ignored (the interleaved and slab-ordered paths are fp32 only). */
+int b200proj_project_2d_forw_f64(const double* rec, int64_t B, int64_t R,
+                             const double* rot, int64_t B_rot,
+                             const double* shifts, int64_t B_shift,
+                             int64_t P, int64_t N, int interpolation, double oversampling,
+                             double fourier_radius_cutoff, double* out, void* stream);
+int b200proj_project_3d_to_2d_forw_f64(const double* rec, int64_t B, int64_t R,
+                                   const double* rot, int64_t B_rot,
+                                   const double* shifts, int64_t B_shift,
+                                   int64_t P, int64_t N, int interpolation, double oversampling,
+                                   double fourier_radius_cutoff, double* out, void* stream);
+int b200proj_project_2d_back_f64(const double* grad_proj, const double* rec, int64_t B, int64_t R,
+                             const double* rot, int64_t B_rot,
+                             const double* shifts, int64_t B_shift,
+                             int64_t P, int64_t N, int interpolation, double oversampling,
+                             double fourier_radius_cutoff,
+                             double* grad_rec, double* grad_rot, double* grad_shifts, void* stream);
+int b200proj_project_3d_to_2d_back_f64(const double* grad_proj, const double* rec, int64_t B, int64_t R,
+                                   const double* rot, int64_t B_rot,
+                                   const double* shifts, int64_t B_shift,
+                                   int64_t P, int64_t N, int interpolation, double oversampling,
+                                   double fourier_radius_cutoff,
+                                   double* grad_rec, double* grad_rot, double* grad_shifts,
+                                   void* stream);
+int b200proj_backproject_2d_forw_f64(const double* proj, const double* weights, int64_t B, int64_t R,
+                                 const double* rot, int64_t B_rot,
+                                 const double* shifts, int64_t B_shift,
+                                 int64_t P, int64_t N, int interpolation, double oversampling,
+                                 double fourier_radius_cutoff,
+                                 double* data_rec, double* weight_rec, int accumulate,
+                                 void* workspace, size_t workspace_bytes, void* stream);
+int b200proj_backproject_2d_to_3d_forw_f64(const double* proj, const double* weights, int64_t B,
+                                       int64_t R, const double* rot, int64_t B_rot,
+                                       const double* shifts, int64_t B_shift,
+                                       int64_t P, int64_t N, int interpolation,
+                                       double oversampling, double fourier_radius_cutoff,
+                                       double* data_rec, double* weight_rec, int accumulate,
+                                       void* workspace, size_t workspace_bytes, void* stream);
+int b200proj_backproject_2d_back_f64(const double* grad_data_rec, const double* grad_weight_rec,
+                                 const double* proj, int64_t B, int64_t R,
+                                 const double* rot, int64_t B_rot,
+                                 const double* shifts, int64_t B_shift,
+                                 int64_t P, int64_t N, int interpolation, double oversampling,
+                                 double fourier_radius_cutoff,
+                                 double* grad_proj, double* grad_weights, double* grad_rot,
+                                 double* grad_shifts, void* stream);
+int b200proj_backproject_2d_to_3d_back_f64(const double* grad_data_rec, const double* grad_weight_rec,
+                                       const double* proj, int64_t B, int64_t R,
+                                       const double* rot, int64_t B_rot,
+                                       const double* shifts, int64_t B_shift,
+                                       int64_t P, int64_t N, int interpolation,
+                                       double oversampling, double fourier_radius_cutoff,
+                                       double* grad_proj, double* grad_weights, double* grad_rot,
+                                       double* grad_shifts, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

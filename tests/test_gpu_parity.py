@@ -155,8 +155,10 @@ def test_empty_pose_list_and_unsupported_precision(tp):
     assert out.shape == (1, 0, 8, 5)
     data, _ = tp.backproject_2d_to_3d_forw(torch.zeros(1, 0, 8, 5, dtype=torch.complex64, device="cuda"), torch.zeros(1, 0, 3, 3, device="cuda"))
     assert data.shape == (1, 8, 8, 5) and (data == 0).all()
+    with pytest.raises(RuntimeError, match="mixed precisions"):
+        tp.project_3d_to_2d_forw(rec, torch.eye(3, dtype=torch.float64, device="cuda").view(1, 1, 3, 3))
     with pytest.raises(RuntimeError, match="no CPU fallback"):
-        tp.project_3d_to_2d_forw(rec.to(torch.complex128), torch.eye(3, dtype=torch.float64, device="cuda").view(1, 1, 3, 3))
+        tp.project_3d_to_2d_forw(rec.to(torch.complex32), torch.eye(3, dtype=torch.float16, device="cuda").view(1, 1, 3, 3))
     with pytest.raises(RuntimeError, match="Number of poses in shifts"):
         tp.project_3d_to_2d_forw(rec, torch.eye(3, device="cuda").expand(1, 2, 3, 3), torch.zeros(1, 3, 2, device="cuda"))
     with pytest.raises(RuntimeError, match="interpolation"):
@@ -344,3 +346,54 @@ def test_slab_ordered_backprojection_matches_oracle(tp):
     env = dict(os.environ, B200PROJ_SLAB_MIN_MB="0", B200PROJ_SLAB_MB=str(3.5 * plane_mb))
     r = subprocess.run([sys.executable, "-c", _SLAB_SCRIPT.format(root=root)], env=env, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0 and "SLAB-OK" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
+
+
+
+# ---- complex128 / float64: the same kernels instantiated for double ---------------------------
+F64_TOL = 1e-11      # against the fp64 oracle; sums are re-associated, reductions unordered
+
+
+@pytest.mark.parametrize("case", SMALL_CASES[:6] + SMALL_CASES[9:13] + MEDIUM_CASES[3:5], ids=lambda c: c.name)
+def test_double_precision_matches_fp64_oracle(tp, case):
+    t = make_inputs(case, cdtype=torch.complex128)
+    got = run_case("cuda", case, t)
+    want = run_case("port", case, t)
+    assert set(got) == set(want)
+    for k in want:
+        assert got[k].dtype == want[k].dtype, (k, got[k].dtype, want[k].dtype)
+        assert rel_err(got[k], want[k]) <= F64_TOL, (k, rel_err(got[k], want[k]))
+
+
+@pytest.mark.parametrize("interp", ["linear", "cubic"])
+def test_gradcheck_projection_in_double_precision(tp, interp):
+    # reference: tests/3d/forw/test_gradients_3d_to_2d.py:67-110 -- gradcheck in complex128 with the
+    # Friedel-redundant half of the c = 0 line masked (forward reads it, backward does not write it)
+    torch.manual_seed(42)
+    N = 8
+    rec = torch.randn(1, N, N, N // 2 + 1, dtype=torch.complex128, device="cuda", requires_grad=True)
+    gen = torch.Generator().manual_seed(1)
+    rot = make_rotations(3, 1, 2, gen, special=True, dtype=torch.float64).cuda()
+    mask = torch.ones_like(rec)
+    mask[0, :, N // 2:, 0] = 0
+
+    def func(r):
+        return tp.project_3d_to_2d_forw(r * mask, rot[:, :1], output_shape=(N, N), interpolation=interp)
+    assert torch.autograd.gradcheck(func, rec, atol=1e-4, rtol=1e-2)
+
+
+@pytest.mark.parametrize("interp", ["linear", "cubic"])
+def test_gradcheck_backprojection_in_double_precision(tp, interp):
+    # reference: tests/3d/back/test_gradients_back_2d_to_3d.py:69-110 -- projections only, identity
+    # pose; the column-0 pixels with a distinct Friedel partner are masked, because the forward
+    # pass inserts them twice (x = 0 duplicate) while the backward pass reads them once
+    torch.manual_seed(42)
+    N = 8
+    proj = torch.randn(1, 1, N, N // 2 + 1, dtype=torch.complex128, device="cuda", requires_grad=True)
+    rot = torch.eye(3, dtype=torch.float64, device="cuda").view(1, 1, 3, 3)
+    sh = torch.tensor([[[0.5, -1.25]]], dtype=torch.float64, device="cuda")
+    mask = torch.ones_like(proj)
+    mask[0, 0, 1:N // 2, 0] = 0
+
+    def func(p):
+        return tp.backproject_2d_to_3d_forw(p * mask, rot, shifts=sh, interpolation=interp)[0]
+    assert torch.autograd.gradcheck(func, proj, atol=1e-4, rtol=1e-2)

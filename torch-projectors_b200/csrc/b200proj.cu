@@ -10,6 +10,7 @@
 #include <climits>
 #include <cstdint>
 #include <mutex>
+#include <type_traits>
 
 #include "fourier_slice_kernels.cuh"
 
@@ -40,8 +41,8 @@ struct Launch {
 };
 
 // Validate the arguments common to all operators and derive the kernel geometry.
-int prepare(Launch& L, int dim, int64_t B, int64_t R, int64_t B_rot, const float* rot,
-            const float* shifts, int64_t B_shift, int64_t P, int64_t N, int interpolation,
+int prepare(Launch& L, int dim, int64_t B, int64_t R, int64_t B_rot, const void* rot,
+            const void* shifts, int64_t B_shift, int64_t P, int64_t N, int interpolation,
             double oversampling, double cutoff) {
     g_error[0] = 0;
     if (interpolation != B200PROJ_LINEAR && interpolation != B200PROJ_CUBIC)
@@ -73,6 +74,7 @@ int prepare(Launch& L, int dim, int64_t B, int64_t R, int64_t B_rot, const float
     g.shift_stride_b = (!g.has_shift || B_shift == 1) ? 0 : (int)(P * 2);
     const float rc = (float)cutoff;
     g.cutoff_sq = rc * rc;
+    g.cutoff_sq_d = cutoff * cutoff;
     g.os = oversampling;
     g.phase_scale = -2.0 * M_PI / (double)(float)N;
     g.shift_scale = -2.0 * M_PI / (double)N;
@@ -113,18 +115,18 @@ SlabPlan slab_plan(int64_t R, bool has_weights) {
     return {slabs, planes};
 }
 
-// ---- operator bodies, templated on the dimensionality ------------------------------------
-template <int DIM>
-int project_forw(const float* rec, int64_t B, int64_t R, const float* rot, int64_t B_rot,
-                 const float* shifts, int64_t B_shift, int64_t P, int64_t N, int interpolation,
-                 double os, double cutoff, float* out, void* stream) {
+// ---- operator bodies, templated on the dimensionality and the real type (float | double) ------------------------------------
+template <int DIM, typename Real>
+int project_forw(const Real* rec, int64_t B, int64_t R, const Real* rot, int64_t B_rot,
+                 const Real* shifts, int64_t B_shift, int64_t P, int64_t N, int interpolation,
+                 double os, double cutoff, Real* out, void* stream) {
     Launch L;
     if (int rc = prepare(L, DIM, B, R, B_rot, rot, shifts, B_shift, P, N, interpolation, os, cutoff)) return rc;
     if (rec == nullptr || out == nullptr) return fail(B200PROJ_ERR_ARGUMENT, "reconstruction / output pointer is NULL");
     if (P == 0) return B200PROJ_OK;
     cudaStream_t s = (cudaStream_t)stream;
-    const float2* v = (const float2*)rec;
-    float2* o = (float2*)out;
+    const C2<Real>* v = (const C2<Real>*)rec;
+    C2<Real>* o = (C2<Real>*)out;
     if (interpolation == B200PROJ_CUBIC)
         project_forw_kernel<DIM, true><<<L.grid, kBlockThreads, 0, s>>>(v, rot, shifts, o, L.g);
     else
@@ -132,10 +134,10 @@ int project_forw(const float* rec, int64_t B, int64_t R, const float* rot, int64
     return check_launch("project_forw launch");
 }
 
-template <int DIM, bool CUBIC>
-void launch_project_back(const Launch& L, cudaStream_t s, const float2* gp, const float2* rec,
-                         const float* rot, const float* shifts, float2* grad_rec, float* grad_rot,
-                         float* grad_shift) {
+template <int DIM, bool CUBIC, typename Real>
+void launch_project_back(const Launch& L, cudaStream_t s, const C2<Real>* gp, const C2<Real>* rec,
+                         const Real* rot, const Real* shifts, C2<Real>* grad_rec, Real* grad_rot,
+                         Real* grad_shift) {
     const bool nr = grad_rot != nullptr, ns = grad_shift != nullptr;
 #define B200PROJ_PB(NR, NS) \
     project_back_kernel<DIM, CUBIC, NR, NS><<<L.grid, kBlockThreads, 0, s>>>(gp, rec, rot, shifts, grad_rec, grad_rot, grad_shift, L.g)
@@ -146,11 +148,11 @@ void launch_project_back(const Launch& L, cudaStream_t s, const float2* gp, cons
 #undef B200PROJ_PB
 }
 
-template <int DIM>
-int project_back(const float* grad_proj, const float* rec, int64_t B, int64_t R, const float* rot,
-                 int64_t B_rot, const float* shifts, int64_t B_shift, int64_t P, int64_t N,
-                 int interpolation, double os, double cutoff, float* grad_rec, float* grad_rot,
-                 float* grad_shifts, void* stream) {
+template <int DIM, typename Real>
+int project_back(const Real* grad_proj, const Real* rec, int64_t B, int64_t R, const Real* rot,
+                 int64_t B_rot, const Real* shifts, int64_t B_shift, int64_t P, int64_t N,
+                 int interpolation, double os, double cutoff, Real* grad_rec, Real* grad_rot,
+                 Real* grad_shifts, void* stream) {
     Launch L;
     if (int rc = prepare(L, DIM, B, R, B_rot, rot, shifts, B_shift, P, N, interpolation, os, cutoff)) return rc;
     if (grad_proj == nullptr || rec == nullptr || grad_rec == nullptr)
@@ -158,22 +160,22 @@ int project_back(const float* grad_proj, const float* rec, int64_t B, int64_t R,
     if (grad_shifts != nullptr && shifts == nullptr)
         return fail(B200PROJ_ERR_ARGUMENT, "grad_shifts requested but no shifts given");
     cudaStream_t s = (cudaStream_t)stream;
-    if (int rc = zero_async(grad_rec, L.rec_count * sizeof(float2), s)) return rc;
-    if (int rc = zero_async(grad_rot, (size_t)B_rot * P * DIM * DIM * sizeof(float), s)) return rc;
-    if (int rc = zero_async(grad_shifts, (size_t)(shifts ? B_shift : 0) * P * 2 * sizeof(float), s)) return rc;
+    if (int rc = zero_async(grad_rec, L.rec_count * sizeof(C2<Real>), s)) return rc;
+    if (int rc = zero_async(grad_rot, (size_t)B_rot * P * DIM * DIM * sizeof(Real), s)) return rc;
+    if (int rc = zero_async(grad_shifts, (size_t)(shifts ? B_shift : 0) * P * 2 * sizeof(Real), s)) return rc;
     if (P == 0) return B200PROJ_OK;
     if (interpolation == B200PROJ_CUBIC)
-        launch_project_back<DIM, true>(L, s, (const float2*)grad_proj, (const float2*)rec, rot, shifts, (float2*)grad_rec, grad_rot, grad_shifts);
+        launch_project_back<DIM, true>(L, s, (const C2<Real>*)grad_proj, (const C2<Real>*)rec, rot, shifts, (C2<Real>*)grad_rec, grad_rot, grad_shifts);
     else
-        launch_project_back<DIM, false>(L, s, (const float2*)grad_proj, (const float2*)rec, rot, shifts, (float2*)grad_rec, grad_rot, grad_shifts);
+        launch_project_back<DIM, false>(L, s, (const C2<Real>*)grad_proj, (const C2<Real>*)rec, rot, shifts, (C2<Real>*)grad_rec, grad_rot, grad_shifts);
     return check_launch("project_back launch");
 }
 
-template <int DIM>
-int backproject_forw(const float* proj, const float* weights, int64_t B, int64_t R,
-                     const float* rot, int64_t B_rot, const float* shifts, int64_t B_shift,
+template <int DIM, typename Real>
+int backproject_forw(const Real* proj, const Real* weights, int64_t B, int64_t R,
+                     const Real* rot, int64_t B_rot, const Real* shifts, int64_t B_shift,
                      int64_t P, int64_t N, int interpolation, double os, double cutoff,
-                     float* data_rec, float* weight_rec, int accumulate, void* workspace,
+                     Real* data_rec, Real* weight_rec, int accumulate, void* workspace,
                      size_t workspace_bytes, void* stream) {
     Launch L;
     if (int rc = prepare(L, DIM, B, R, B_rot, rot, shifts, B_shift, P, N, interpolation, os, cutoff)) return rc;
@@ -188,27 +190,30 @@ int backproject_forw(const float* proj, const float* weights, int64_t B, int64_t
     // Interleaved path: data and weight of a voxel share one 16-byte slot of the workspace
     // (one v4 reduction per tap), folded into the outputs afterwards.
     const size_t ws_need = L.rec_count * sizeof(float4);
+    constexpr bool kIsF32 = std::is_same<Real, float>::value;  // workspace and slab paths exist in fp32 only
+    if constexpr (kIsF32) {
     if (hw && P > 0 && !(DIM == 3 && slab_plan(R, hw).slabs > 1) && workspace != nullptr && workspace_bytes >= ws_need &&
         (reinterpret_cast<uintptr_t>(workspace) & 15u) == 0) {
         if (int rc = zero_async(workspace, ws_need, s)) return rc;
         float4* acc = (float4*)workspace;
         if (cubic)
-            backproject_forw_interleaved_kernel<DIM, true><<<L.grid, kBlockThreads, 0, s>>>((const float2*)proj, weights, rot, shifts, acc, L.g);
+            backproject_forw_interleaved_kernel<DIM, true><<<L.grid, kBlockThreads, 0, s>>>((const C2<Real>*)proj, weights, rot, shifts, acc, L.g);
         else
-            backproject_forw_interleaved_kernel<DIM, false><<<L.grid, kBlockThreads, 0, s>>>((const float2*)proj, weights, rot, shifts, acc, L.g);
+            backproject_forw_interleaved_kernel<DIM, false><<<L.grid, kBlockThreads, 0, s>>>((const C2<Real>*)proj, weights, rot, shifts, acc, L.g);
         if (int rc = check_launch("backproject_forw (interleaved) launch")) return rc;
         const size_t blocks = (L.rec_count + 255) / 256;
-        fold_interleaved_kernel<<<(unsigned)(blocks < 148 * 16 ? blocks : 148 * 16), 256, 0, s>>>(acc, (float2*)data_rec, weight_rec, L.rec_count, accumulate != 0);
+        fold_interleaved_kernel<<<(unsigned)(blocks < 148 * 16 ? blocks : 148 * 16), 256, 0, s>>>(acc, (C2<Real>*)data_rec, weight_rec, L.rec_count, accumulate != 0);
         return check_launch("fold_interleaved launch");
     }
+    }
     if (!accumulate) {
-        if (int rc = zero_async(data_rec, L.rec_count * sizeof(float2), s)) return rc;
-        if (int rc = zero_async(weight_rec, L.rec_count * sizeof(float), s)) return rc;
+        if (int rc = zero_async(data_rec, L.rec_count * sizeof(C2<Real>), s)) return rc;
+        if (int rc = zero_async(weight_rec, L.rec_count * sizeof(Real), s)) return rc;
     }
     if (P == 0) return B200PROJ_OK;
-    const float2* p = (const float2*)proj;
-    float2* d = (float2*)data_rec;
-    if constexpr (DIM == 3) {
+    const C2<Real>* p = (const C2<Real>*)proj;
+    C2<Real>* d = (C2<Real>*)data_rec;
+    if constexpr (DIM == 3 && kIsF32) {
         // volumes beyond L2: slab-ordered passes that keep the active planes L2-resident
         const SlabPlan plan = slab_plan(R, hw);
         if (plan.slabs > 1) {
@@ -233,11 +238,11 @@ int backproject_forw(const float* proj, const float* weights, int64_t B, int64_t
     return check_launch("backproject_forw launch");
 }
 
-template <int DIM, bool CUBIC>
-void launch_backproject_back(const Launch& L, cudaStream_t s, const float2* gd, const float* gw,
-                             const float2* proj, const float* rot, const float* shifts,
-                             float2* grad_proj, float* grad_weights, float* grad_rot,
-                             float* grad_shift) {
+template <int DIM, bool CUBIC, typename Real>
+void launch_backproject_back(const Launch& L, cudaStream_t s, const C2<Real>* gd, const Real* gw,
+                             const C2<Real>* proj, const Real* rot, const Real* shifts,
+                             C2<Real>* grad_proj, Real* grad_weights, Real* grad_rot,
+                             Real* grad_shift) {
     const bool nr = grad_rot != nullptr, ns = grad_shift != nullptr;
 #define B200PROJ_BB(NR, NS) \
     backproject_back_kernel<DIM, CUBIC, NR, NS><<<L.grid, kBlockThreads, 0, s>>>(gd, gw, proj, rot, shifts, grad_proj, grad_weights, grad_rot, grad_shift, L.g)
@@ -248,12 +253,12 @@ void launch_backproject_back(const Launch& L, cudaStream_t s, const float2* gd, 
 #undef B200PROJ_BB
 }
 
-template <int DIM>
-int backproject_back(const float* grad_data_rec, const float* grad_weight_rec, const float* proj,
-                     int64_t B, int64_t R, const float* rot, int64_t B_rot, const float* shifts,
+template <int DIM, typename Real>
+int backproject_back(const Real* grad_data_rec, const Real* grad_weight_rec, const Real* proj,
+                     int64_t B, int64_t R, const Real* rot, int64_t B_rot, const Real* shifts,
                      int64_t B_shift, int64_t P, int64_t N, int interpolation, double os,
-                     double cutoff, float* grad_proj, float* grad_weights, float* grad_rot,
-                     float* grad_shifts, void* stream) {
+                     double cutoff, Real* grad_proj, Real* grad_weights, Real* grad_rot,
+                     Real* grad_shifts, void* stream) {
     Launch L;
     if (int rc = prepare(L, DIM, B, R, B_rot, rot, shifts, B_shift, P, N, interpolation, os, cutoff)) return rc;
     if (grad_data_rec == nullptr || grad_proj == nullptr)
@@ -266,15 +271,15 @@ int backproject_back(const float* grad_data_rec, const float* grad_weight_rec, c
         return fail(B200PROJ_ERR_ARGUMENT, "grad_data_rec boxsize %lld does not match ceil(N*oversampling) rounded up to even = %lld",
                     (long long)R, (long long)b200proj_rec_boxsize(N, os));
     cudaStream_t s = (cudaStream_t)stream;
-    if (int rc = zero_async(grad_rot, (size_t)B_rot * P * DIM * DIM * sizeof(float), s)) return rc;
-    if (int rc = zero_async(grad_shifts, (size_t)(shifts ? B_shift : 0) * P * 2 * sizeof(float), s)) return rc;
+    if (int rc = zero_async(grad_rot, (size_t)B_rot * P * DIM * DIM * sizeof(Real), s)) return rc;
+    if (int rc = zero_async(grad_shifts, (size_t)(shifts ? B_shift : 0) * P * 2 * sizeof(Real), s)) return rc;
     if (grad_weights != nullptr && grad_weight_rec == nullptr)   // weights given, no incoming gradient: zeros
-        if (int rc = zero_async(grad_weights, L.pix_count * sizeof(float), s)) return rc;
+        if (int rc = zero_async(grad_weights, L.pix_count * sizeof(Real), s)) return rc;
     if (P == 0) return B200PROJ_OK;
     if (interpolation == B200PROJ_CUBIC)
-        launch_backproject_back<DIM, true>(L, s, (const float2*)grad_data_rec, grad_weight_rec, (const float2*)proj, rot, shifts, (float2*)grad_proj, grad_weights, grad_rot, grad_shifts);
+        launch_backproject_back<DIM, true>(L, s, (const C2<Real>*)grad_data_rec, grad_weight_rec, (const C2<Real>*)proj, rot, shifts, (C2<Real>*)grad_proj, grad_weights, grad_rot, grad_shifts);
     else
-        launch_backproject_back<DIM, false>(L, s, (const float2*)grad_data_rec, grad_weight_rec, (const float2*)proj, rot, shifts, (float2*)grad_proj, grad_weights, grad_rot, grad_shifts);
+        launch_backproject_back<DIM, false>(L, s, (const C2<Real>*)grad_data_rec, grad_weight_rec, (const C2<Real>*)proj, rot, shifts, (C2<Real>*)grad_proj, grad_weights, grad_rot, grad_shifts);
     return check_launch("backproject_back launch");
 }
 
@@ -390,6 +395,68 @@ int b200proj_backproject_2d_to_3d_back(const float* grad_data_rec, const float* 
                                        int64_t P, int64_t N, int interpolation,
                                        double oversampling, double cutoff, float* grad_proj,
                                        float* grad_weights, float* grad_rot, float* grad_shifts,
+                                       void* stream) {
+    return backproject_back<3>(grad_data_rec, grad_weight_rec, proj, B, R, rot, B_rot, shifts, B_shift, P, N, interpolation, oversampling, cutoff, grad_proj, grad_weights, grad_rot, grad_shifts, stream);
+}
+
+// ---- complex128 / float64 variants (same kernels instantiated for double) ----------------
+int b200proj_project_2d_forw_f64(const double* rec, int64_t B, int64_t R, const double* rot, int64_t B_rot,
+                             const double* shifts, int64_t B_shift, int64_t P, int64_t N,
+                             int interpolation, double oversampling, double cutoff, double* out,
+                             void* stream) {
+    return project_forw<2>(rec, B, R, rot, B_rot, shifts, B_shift, P, N, interpolation, oversampling, cutoff, out, stream);
+}
+int b200proj_project_3d_to_2d_forw_f64(const double* rec, int64_t B, int64_t R, const double* rot,
+                                   int64_t B_rot, const double* shifts, int64_t B_shift, int64_t P,
+                                   int64_t N, int interpolation, double oversampling, double cutoff,
+                                   double* out, void* stream) {
+    return project_forw<3>(rec, B, R, rot, B_rot, shifts, B_shift, P, N, interpolation, oversampling, cutoff, out, stream);
+}
+
+int b200proj_project_2d_back_f64(const double* grad_proj, const double* rec, int64_t B, int64_t R,
+                             const double* rot, int64_t B_rot, const double* shifts, int64_t B_shift,
+                             int64_t P, int64_t N, int interpolation, double oversampling,
+                             double cutoff, double* grad_rec, double* grad_rot, double* grad_shifts,
+                             void* stream) {
+    return project_back<2>(grad_proj, rec, B, R, rot, B_rot, shifts, B_shift, P, N, interpolation, oversampling, cutoff, grad_rec, grad_rot, grad_shifts, stream);
+}
+int b200proj_project_3d_to_2d_back_f64(const double* grad_proj, const double* rec, int64_t B, int64_t R,
+                                   const double* rot, int64_t B_rot, const double* shifts,
+                                   int64_t B_shift, int64_t P, int64_t N, int interpolation,
+                                   double oversampling, double cutoff, double* grad_rec,
+                                   double* grad_rot, double* grad_shifts, void* stream) {
+    return project_back<3>(grad_proj, rec, B, R, rot, B_rot, shifts, B_shift, P, N, interpolation, oversampling, cutoff, grad_rec, grad_rot, grad_shifts, stream);
+}
+
+int b200proj_backproject_2d_forw_f64(const double* proj, const double* weights, int64_t B, int64_t R,
+                                 const double* rot, int64_t B_rot, const double* shifts,
+                                 int64_t B_shift, int64_t P, int64_t N, int interpolation,
+                                 double oversampling, double cutoff, double* data_rec,
+                                 double* weight_rec, int accumulate, void* workspace, size_t workspace_bytes, void* stream) {
+    return backproject_forw<2>(proj, weights, B, R, rot, B_rot, shifts, B_shift, P, N, interpolation, oversampling, cutoff, data_rec, weight_rec, accumulate, workspace, workspace_bytes, stream);
+}
+int b200proj_backproject_2d_to_3d_forw_f64(const double* proj, const double* weights, int64_t B,
+                                       int64_t R, const double* rot, int64_t B_rot,
+                                       const double* shifts, int64_t B_shift, int64_t P, int64_t N,
+                                       int interpolation, double oversampling, double cutoff,
+                                       double* data_rec, double* weight_rec, int accumulate,                                        void* workspace, size_t workspace_bytes, void* stream) {
+    return backproject_forw<3>(proj, weights, B, R, rot, B_rot, shifts, B_shift, P, N, interpolation, oversampling, cutoff, data_rec, weight_rec, accumulate, workspace, workspace_bytes, stream);
+}
+
+int b200proj_backproject_2d_back_f64(const double* grad_data_rec, const double* grad_weight_rec,
+                                 const double* proj, int64_t B, int64_t R, const double* rot,
+                                 int64_t B_rot, const double* shifts, int64_t B_shift, int64_t P,
+                                 int64_t N, int interpolation, double oversampling, double cutoff,
+                                 double* grad_proj, double* grad_weights, double* grad_rot,
+                                 double* grad_shifts, void* stream) {
+    return backproject_back<2>(grad_data_rec, grad_weight_rec, proj, B, R, rot, B_rot, shifts, B_shift, P, N, interpolation, oversampling, cutoff, grad_proj, grad_weights, grad_rot, grad_shifts, stream);
+}
+int b200proj_backproject_2d_to_3d_back_f64(const double* grad_data_rec, const double* grad_weight_rec,
+                                       const double* proj, int64_t B, int64_t R, const double* rot,
+                                       int64_t B_rot, const double* shifts, int64_t B_shift,
+                                       int64_t P, int64_t N, int interpolation,
+                                       double oversampling, double cutoff, double* grad_proj,
+                                       double* grad_weights, double* grad_rot, double* grad_shifts,
                                        void* stream) {
     return backproject_back<3>(grad_data_rec, grad_weight_rec, proj, B, R, rot, B_rot, shifts, B_shift, P, N, interpolation, oversampling, cutoff, grad_proj, grad_weights, grad_rot, grad_shifts, stream);
 }

@@ -23,6 +23,37 @@ constexpr int kTileI = 16;
 constexpr int kBlockThreads = kTileJ * kTileI;
 constexpr int kWarps = kBlockThreads / 32;
 
+// ---- real-type helpers -------------------------------------------------------------------
+// The device code is generic over R = float (complex64 tensors, the fast path) and R = double
+// (complex128 / float64, for callers that verify gradients in double precision, as the
+// reference's own gradcheck tests do).  R is the last template parameter of every function
+// and is deduced from the arguments.
+template <typename R> struct Vec2;
+template <> struct Vec2<float> { using type = float2; };
+template <> struct Vec2<double> { using type = double2; };
+template <typename R> using C2 = typename Vec2<R>::type;
+// a parameter type that takes no part in the deduction of R (R comes from the pixel argument)
+template <typename R> struct Identity { using type = R; };
+template <typename R> using NoDeduce = typename Identity<R>::type;
+
+template <typename R> __device__ __forceinline__ C2<R> make2(R a, R b);
+template <> __device__ __forceinline__ float2 make2<float>(float a, float b) { return make_float2(a, b); }
+template <> __device__ __forceinline__ double2 make2<double>(double a, double b) { return make_double2(a, b); }
+
+__device__ __forceinline__ float rfloor(float x) { return floorf(x); }
+__device__ __forceinline__ double rfloor(double x) { return floor(x); }
+__device__ __forceinline__ float rabs(float x) { return fabsf(x); }
+__device__ __forceinline__ double rabs(double x) { return fabs(x); }
+__device__ __forceinline__ float rfma(float a, float b, float c) { return fmaf(a, b, c); }
+__device__ __forceinline__ double rfma(double a, double b, double c) { return fma(a, b, c); }
+// separately rounded multiply / add (never contracted into an FMA)
+__device__ __forceinline__ float mul_rn(float a, float b) { return __fmul_rn(a, b); }
+__device__ __forceinline__ double mul_rn(double a, double b) { return __dmul_rn(a, b); }
+__device__ __forceinline__ float add_rn(float a, float b) { return __fadd_rn(a, b); }
+__device__ __forceinline__ double add_rn(double a, double b) { return __dadd_rn(a, b); }
+__device__ __forceinline__ void rsincos(float x, float* s, float* c) { sincosf(x, s, c); }
+__device__ __forceinline__ void rsincos(double x, double* s, double* c) { sincos(x, s, c); }
+
 // Kernel parameters shared by the eight operators (passed by value).
 struct SliceGeom {
     int N, Nh;              // projection box and stored width N/2+1
@@ -32,18 +63,21 @@ struct SliceGeom {
     int rot_stride_b;       // elements between batch items of rot (0 = shared)
     int shift_stride_b;     // elements between batch items of shifts (0 = shared)
     int has_shift;
-    float cutoff_sq;
+    float cutoff_sq;        // (float(cutoff))^2, the fp32 path compares in float as the reference does
+    double cutoff_sq_d;     // cutoff^2 for the fp64 path
     double os;              // oversampling factor
     double phase_scale;     // -2*pi / float(N)
     double shift_scale;     // -2*pi / N   (d phase / d shift per unit frequency)
     long long vol_elems;    // voxels per batch item
 };
 
-struct Pixel {
-    float kr, kc;           // projection frequencies (row, column)
-    float sc, sr;           // oversampled sample coordinates before rotation
-    float c, r, d;          // rotated sample position in the volume (x, y, z)
+template <typename R>
+struct PixelT {
+    R kr, kc;           // projection frequencies (row, column)
+    R sc, sr;           // oversampled sample coordinates before rotation
+    R c, r, d;          // rotated sample position in the volume (x, y, z)
 };
+using Pixel = PixelT<float>;
 
 // Lane -> pixel inside the block tile.  A warp covers 8 columns x 4 rows so that its
 // samples form a compact patch of the slice plane (cache locality of the taps) while each
@@ -55,56 +89,70 @@ __device__ __forceinline__ void tile_pixel(const SliceGeom& g, int tile, int& i,
     i = ti * kTileI + (warp >> 1) * 4 + (lane >> 3);
 }
 
+__device__ __forceinline__ float cutoff_sq_of(const SliceGeom& g, float) { return g.cutoff_sq; }
+__device__ __forceinline__ double cutoff_sq_of(const SliceGeom& g, double) { return g.cutoff_sq_d; }
+
 // Frequencies, cutoff test and rotated sample position of output pixel (i, j).
 // Returns false when the pixel lies outside the cutoff radius.
-template <int DIM>
-__device__ __forceinline__ bool pixel_setup(const SliceGeom& g, const float* __restrict__ rm,
-                                            int i, int j, Pixel& px) {
-    px.kr = (float)((i <= g.N / 2) ? i : i - g.N);
-    px.kc = (float)j;
-    const float rad = __fadd_rn(__fmul_rn(px.kr, px.kr), __fmul_rn(px.kc, px.kc));
-    if (rad > g.cutoff_sq) return false;
-    px.sc = (float)((double)px.kc * g.os);
-    px.sr = (float)((double)px.kr * g.os);
+template <int DIM, typename R>
+__device__ __forceinline__ bool pixel_setup(const SliceGeom& g, const R* __restrict__ rm,
+                                            int i, int j, PixelT<R>& px) {
+    px.kr = (R)((i <= g.N / 2) ? i : i - g.N);
+    px.kc = (R)j;
+    const R rad = add_rn(mul_rn(px.kr, px.kr), mul_rn(px.kc, px.kc));
+    if (rad > cutoff_sq_of(g, rad)) return false;
+    px.sc = (R)((double)px.kc * g.os);
+    px.sr = (R)((double)px.kr * g.os);
     if (DIM == 3) {
-        px.c = __fadd_rn(__fmul_rn(__ldg(rm + 0), px.sc), __fmul_rn(__ldg(rm + 1), px.sr));
-        px.r = __fadd_rn(__fmul_rn(__ldg(rm + 3), px.sc), __fmul_rn(__ldg(rm + 4), px.sr));
-        px.d = __fadd_rn(__fmul_rn(__ldg(rm + 6), px.sc), __fmul_rn(__ldg(rm + 7), px.sr));
+        px.c = add_rn(mul_rn(__ldg(rm + 0), px.sc), mul_rn(__ldg(rm + 1), px.sr));
+        px.r = add_rn(mul_rn(__ldg(rm + 3), px.sc), mul_rn(__ldg(rm + 4), px.sr));
+        px.d = add_rn(mul_rn(__ldg(rm + 6), px.sc), mul_rn(__ldg(rm + 7), px.sr));
     } else {
-        px.c = __fadd_rn(__fmul_rn(__ldg(rm + 0), px.sc), __fmul_rn(__ldg(rm + 1), px.sr));
-        px.r = __fadd_rn(__fmul_rn(__ldg(rm + 2), px.sc), __fmul_rn(__ldg(rm + 3), px.sr));
+        px.c = add_rn(mul_rn(__ldg(rm + 0), px.sc), mul_rn(__ldg(rm + 1), px.sr));
+        px.r = add_rn(mul_rn(__ldg(rm + 2), px.sc), mul_rn(__ldg(rm + 3), px.sr));
         px.d = 0.f;
     }
     return true;
 }
 
 // exp(-2*pi*i*(kr*s0 + kc*s1)/N) as (cos, sin).
-__device__ __forceinline__ float2 phase_ramp(const SliceGeom& g, const Pixel& px, float s0, float s1) {
-    const float dot = __fadd_rn(__fmul_rn(px.kr, s0), __fmul_rn(px.kc, s1));
-    const float ph = (float)((double)dot * g.phase_scale);
-    float sn, cs;
-    sincosf(ph, &sn, &cs);
-    return make_float2(cs, sn);
+template <typename R>
+__device__ __forceinline__ C2<R> phase_ramp(const SliceGeom& g, const PixelT<R>& px, R s0, R s1) {
+    const R dot = add_rn(mul_rn(px.kr, s0), mul_rn(px.kc, s1));
+    const R ph = (R)((double)dot * g.phase_scale);
+    R sn, cs;
+    rsincos(ph, &sn, &cs);
+    return make2<R>(cs, sn);
 }
 
-__device__ __forceinline__ float2 cmul(float2 a, float2 b) {
-    return make_float2(a.x * b.x - a.y * b.y, a.x * b.y + a.y * b.x);
+template <typename V>
+__device__ __forceinline__ V cmul(V a, V b) {
+    V o;
+    o.x = a.x * b.x - a.y * b.y;
+    o.y = a.x * b.y + a.y * b.x;
+    return o;
 }
-__device__ __forceinline__ float2 cmul_conj(float2 a, float2 b) {   // a * conj(b)
-    return make_float2(a.x * b.x + a.y * b.y, a.y * b.x - a.x * b.y);
+template <typename V>
+__device__ __forceinline__ V cmul_conj(V a, V b) {   // a * conj(b)
+    V o;
+    o.x = a.x * b.x + a.y * b.y;
+    o.y = a.y * b.x - a.x * b.y;
+    return o;
 }
 
 // Catmull-Rom (a = -0.5) weights of the four taps floor-1 .. floor+2 for a fractional position
 // f in [0, 1), and their derivatives with respect to f.  These are the polynomials
 // w(f - t), t = -1..2, of the reference's piecewise kernel
 // (csrc/cpu/common/cubic_kernels.h:25-66) written out per tap, so that no branch on |s| is needed.
-__device__ __forceinline__ void cubic_weights(float f, float (&w)[4]) {
+template <typename R>
+__device__ __forceinline__ void cubic_weights(R f, R (&w)[4]) {
     w[0] = ((-0.5f * f + 1.0f) * f - 0.5f) * f;
     w[1] = (1.5f * f - 2.5f) * f * f + 1.0f;
     w[2] = ((-1.5f * f + 2.0f) * f + 0.5f) * f;
     w[3] = (0.5f * f - 0.5f) * f * f;
 }
-__device__ __forceinline__ void cubic_dweights(float f, float (&dw)[4]) {
+template <typename R>
+__device__ __forceinline__ void cubic_dweights(R f, R (&dw)[4]) {
     dw[0] = (-1.5f * f + 2.0f) * f - 0.5f;
     dw[1] = (4.5f * f - 5.0f) * f;
     dw[2] = (-4.5f * f + 4.0f) * f + 0.5f;
@@ -113,17 +161,17 @@ __device__ __forceinline__ void cubic_dweights(float f, float (&dw)[4]) {
 
 // Per-axis interpolation weights: T = 2 (linear: taps at floor, floor+1) or
 // T = 4 (cubic: taps at floor-1 .. floor+2).  base = index of the first tap.
-template <int T>
+template <typename R, int T>
 struct AxisWeights {
     int base;
-    float w[T];
-    float dw[T];
+    R w[T];
+    R dw[T];
 };
 
-template <int T, bool WITH_DERIV>
-__device__ __forceinline__ void axis_weights(float x, AxisWeights<T>& a) {
-    const float fl = floorf(x);
-    const float f = x - fl;
+template <int T, bool WITH_DERIV, typename R>
+__device__ __forceinline__ void axis_weights(R x, AxisWeights<R, T>& a) {
+    const R fl = rfloor(x);
+    const R f = x - fl;
     if constexpr (T == 2) {
         a.base = (int)fl;
         a.w[0] = 1.f - f;
@@ -174,17 +222,17 @@ __device__ __forceinline__ int gather_line(const SliceGeom& g, int r, bool mirro
 // footprints that straddle c = 0 need no special case.
 // MUST be called by all 32 lanes of the warp; lanes without a pixel pass valid_own = false.
 // vol points at the batch item.
-template <int DIM, bool CUBIC, bool WITH_DERIV>
-__device__ __forceinline__ void interpolate_coop(const SliceGeom& g, const float2* __restrict__ vol,
-                                                 const Pixel& px, bool valid_own, float2& val,
-                                                 float2& g_c, float2& g_r, float2& g_d) {
+template <int DIM, bool CUBIC, bool WITH_DERIV, typename R>
+__device__ __forceinline__ void interpolate_coop(const SliceGeom& g, const C2<R>* __restrict__ vol,
+                                                 const PixelT<R>& px, bool valid_own, C2<R>& val,
+                                                 C2<R>& g_c, C2<R>& g_r, C2<R>& g_d) {
     constexpr int T = CUBIC ? 4 : 2;
     constexpr int TD = (DIM == 3) ? T : 1;
     constexpr unsigned kFull = 0xffffffffu;
     const int lane = threadIdx.x & 31;
     const int q = lane & (T - 1);
     const int plane_stride = g.R * g.Rh;
-    val = make_float2(0.f, 0.f);
+    val = make2<R>(0.f, 0.f);
     g_c = g_r = g_d = val;
 
     // the loop over the group's pixels stays rolled: its body holds T*T unrolled taps, and T
@@ -192,29 +240,29 @@ __device__ __forceinline__ void interpolate_coop(const SliceGeom& g, const float
 #pragma unroll 1
     for (int s = 0; s < T; ++s) {
         const int src = (lane & ~(T - 1)) | s;
-        const float pc = __shfl_sync(kFull, px.c, src);
-        const float pr = __shfl_sync(kFull, px.r, src);
-        const float pd = (DIM == 3) ? __shfl_sync(kFull, px.d, src) : 0.f;
+        const R pc = __shfl_sync(kFull, px.c, src);
+        const R pr = __shfl_sync(kFull, px.r, src);
+        const R pd = (DIM == 3) ? __shfl_sync(kFull, px.d, src) : 0.f;
         const bool valid = __shfl_sync(kFull, (int)valid_own, src) != 0;
 
-        float2 cv = make_float2(0.f, 0.f), cgc = cv, cgr = cv, cgd = cv;
+        C2<R> cv = make2<R>(0.f, 0.f), cgc = cv, cgr = cv, cgd = cv;
         if (valid) {
-            AxisWeights<T> ar, ad;
+            AxisWeights<R, T> ar, ad;
             axis_weights<T, WITH_DERIV>(pr, ar);
             if (DIM == 3) axis_weights<T, WITH_DERIV>(pd, ad);
             // this lane's column tap
-            const float flc = floorf(pc);
-            const float fc = pc - flc;
+            const R flc = rfloor(pc);
+            const R fc = pc - flc;
             const int cbase = CUBIC ? (int)flc - 1 : (int)flc;
             bool m;
             const int col = gather_col<CUBIC>(g, cbase + q, m);
-            float wc, dwc = 0.f;
+            R wc, dwc = 0.f;
             if constexpr (CUBIC) {
-                float w4[4];
+                R w4[4];
                 cubic_weights(fc, w4);
                 wc = q == 0 ? w4[0] : q == 1 ? w4[1] : q == 2 ? w4[2] : w4[3];
                 if (WITH_DERIV) {
-                    float d4[4];
+                    R d4[4];
                     cubic_dweights(fc, d4);
                     dwc = q == 0 ? d4[0] : q == 1 ? d4[1] : q == 2 ? d4[2] : d4[3];
                 }
@@ -246,39 +294,39 @@ __device__ __forceinline__ void interpolate_coop(const SliceGeom& g, const float
                     plane[k] = (DIM == 3) ? gather_line<CUBIC>(g, ad.base + k, m) * plane_stride : 0;
             }
 
-            float2 A = make_float2(0.f, 0.f), Bq = A, Dq = A;
+            C2<R> A = make2<R>(0.f, 0.f), Bq = A, Dq = A;
 #pragma unroll
             for (int k = 0; k < TD; ++k) {
-                const float2* __restrict__ pl = vol + plane[k];
-                float2 rs = make_float2(0.f, 0.f), rds = rs;
+                const C2<R>* __restrict__ pl = vol + plane[k];
+                C2<R> rs = make2<R>(0.f, 0.f), rds = rs;
 #pragma unroll
                 for (int i = 0; i < T; ++i) {
-                    const float2 v = __ldg(pl + rowcol[i]);
-                    rs.x = fmaf(ar.w[i], v.x, rs.x);
-                    rs.y = fmaf(ar.w[i], v.y, rs.y);
+                    const C2<R> v = __ldg(pl + rowcol[i]);
+                    rs.x = rfma(ar.w[i], v.x, rs.x);
+                    rs.y = rfma(ar.w[i], v.y, rs.y);
                     if (WITH_DERIV) {
-                        rds.x = fmaf(ar.dw[i], v.x, rds.x);
-                        rds.y = fmaf(ar.dw[i], v.y, rds.y);
+                        rds.x = rfma(ar.dw[i], v.x, rds.x);
+                        rds.y = rfma(ar.dw[i], v.y, rds.y);
                     }
                 }
-                const float wd = (DIM == 3) ? ad.w[k] : 1.f;
-                A.x = fmaf(wd, rs.x, A.x);
-                A.y = fmaf(wd, rs.y, A.y);
+                const R wd = (DIM == 3) ? ad.w[k] : 1.f;
+                A.x = rfma(wd, rs.x, A.x);
+                A.y = rfma(wd, rs.y, A.y);
                 if (WITH_DERIV) {
-                    Bq.x = fmaf(wd, rds.x, Bq.x);
-                    Bq.y = fmaf(wd, rds.y, Bq.y);
+                    Bq.x = rfma(wd, rds.x, Bq.x);
+                    Bq.y = rfma(wd, rds.y, Bq.y);
                     if (DIM == 3) {
-                        Dq.x = fmaf(ad.dw[k], rs.x, Dq.x);
-                        Dq.y = fmaf(ad.dw[k], rs.y, Dq.y);
+                        Dq.x = rfma(ad.dw[k], rs.x, Dq.x);
+                        Dq.y = rfma(ad.dw[k], rs.y, Dq.y);
                     }
                 }
             }
-            const float sg = m ? -1.f : 1.f;          // a mirrored column holds conjugated values
-            cv = make_float2(wc * A.x, sg * wc * A.y);
+            const R sg = m ? -1.f : 1.f;          // a mirrored column holds conjugated values
+            cv = make2<R>(wc * A.x, sg * wc * A.y);
             if (WITH_DERIV) {
-                cgc = make_float2(dwc * A.x, sg * dwc * A.y);
-                cgr = make_float2(wc * Bq.x, sg * wc * Bq.y);
-                cgd = make_float2(wc * Dq.x, sg * wc * Dq.y);
+                cgc = make2<R>(dwc * A.x, sg * dwc * A.y);
+                cgr = make2<R>(wc * Bq.x, sg * wc * Bq.y);
+                cgd = make2<R>(wc * Dq.x, sg * wc * Dq.y);
             }
         }
 #pragma unroll
@@ -321,6 +369,13 @@ __device__ __forceinline__ void red_add_v2(float2* addr, float a, float b) {
 __device__ __forceinline__ void red_add(float* addr, float a) {
     asm volatile("red.global.add.f32 [%0], %1;" ::"l"(addr), "f"(a) : "memory");
 }
+__device__ __forceinline__ void red_add(double* addr, double a) {
+    asm volatile("red.global.add.f64 [%0], %1;" ::"l"(addr), "d"(a) : "memory");
+}
+__device__ __forceinline__ void red_add_v2(double2* addr, double a, double b) {   // no vector form for f64
+    red_add(&addr->x, a);
+    red_add(&addr->y, b);
+}
 
 __device__ __forceinline__ void red_add_v4(float4* addr, float a, float b, float c, float d) {
     asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
@@ -339,15 +394,15 @@ __device__ __forceinline__ void red_add_v4(float4* addr, float a, float b, float
 // c == 0 plane (back-projection does; the gradient of the forward projection does not).
 // INTERLEAVED: vol4 is a 16-byte-per-voxel (re, im, w, 0) accumulation volume, so that data
 // and weight of a tap go out as ONE red.global.add.v4.f32; otherwise vol (complex) and, when
-// WEIGHTS, wvol (float) are reduced into directly (v2 + scalar reduction).
+// WEIGHTS, wvol (R) are reduced into directly (v2 + scalar reduction).
 // MUST be called by all 32 lanes of the warp; lanes without a pixel pass valid_own = false.
 // SLAB: only taps whose signed plane coordinate (after the mirror) lies in [z_lo, z_hi) are
 // written; used by the slab-ordered back-projection, where each pass owns a range of planes.
-template <int DIM, bool CUBIC, bool WEIGHTS, bool WITH_DUP, bool INTERLEAVED, bool SLAB = false>
-__device__ __forceinline__ void scatter_coop(const SliceGeom& g, float2* __restrict__ vol,
-                                             float* __restrict__ wvol, float4* __restrict__ vol4,
-                                             const Pixel& px, bool valid_own, float2 v_own,
-                                             float w_own, int z_lo = 0, int z_hi = 0) {
+template <int DIM, bool CUBIC, bool WEIGHTS, bool WITH_DUP, bool INTERLEAVED, bool SLAB = false, typename R>
+__device__ __forceinline__ void scatter_coop(const SliceGeom& g, C2<R>* __restrict__ vol,
+                                             NoDeduce<R>* __restrict__ wvol, float4* __restrict__ vol4,
+                                             const PixelT<R>& px, bool valid_own, C2<R> v_own,
+                                             NoDeduce<R> w_own, int z_lo = 0, int z_hi = 0) {
     constexpr int T = CUBIC ? 4 : 2;
     constexpr int TD = (DIM == 3) ? T : 1;
     constexpr unsigned kFull = 0xffffffffu;
@@ -357,21 +412,21 @@ __device__ __forceinline__ void scatter_coop(const SliceGeom& g, float2* __restr
 #pragma unroll 1
     for (int s = 0; s < T; ++s) {
         const int src = (lane & ~(T - 1)) | s;
-        const float pc = __shfl_sync(kFull, px.c, src);
-        const float pr = __shfl_sync(kFull, px.r, src);
-        const float pd = (DIM == 3) ? __shfl_sync(kFull, px.d, src) : 0.f;
-        const float vx = __shfl_sync(kFull, v_own.x, src);
-        const float vy = __shfl_sync(kFull, v_own.y, src);
-        const float wval = WEIGHTS ? __shfl_sync(kFull, w_own, src) : 0.f;
+        const R pc = __shfl_sync(kFull, px.c, src);
+        const R pr = __shfl_sync(kFull, px.r, src);
+        const R pd = (DIM == 3) ? __shfl_sync(kFull, px.d, src) : 0.f;
+        const R vx = __shfl_sync(kFull, v_own.x, src);
+        const R vy = __shfl_sync(kFull, v_own.y, src);
+        const R wval = WEIGHTS ? __shfl_sync(kFull, w_own, src) : 0.f;
         const bool valid = __shfl_sync(kFull, (int)valid_own, src) != 0;
         if (!valid) continue;
         // this lane's column tap
-        const float flc = floorf(pc);
-        const float fc = pc - flc;
+        const R flc = rfloor(pc);
+        const R fc = pc - flc;
         int c = (CUBIC ? (int)flc - 1 : (int)flc) + q;
-        float wc;
+        R wc;
         if constexpr (CUBIC) {
-            float w4[4];
+            R w4[4];
             cubic_weights(fc, w4);
             wc = q == 0 ? w4[0] : q == 1 ? w4[1] : q == 2 ? w4[2] : w4[3];
         } else {
@@ -380,14 +435,14 @@ __device__ __forceinline__ void scatter_coop(const SliceGeom& g, float2* __restr
         const bool m = c < 0;
         c = m ? -c : c;
         if (c >= g.Rh || wc == 0.f) continue;
-        const float sgn = m ? -1.f : 1.f;
-        AxisWeights<T> ar, ad;
+        const R sgn = m ? -1.f : 1.f;
+        AxisWeights<R, T> ar, ad;
         axis_weights<T, false>(pr, ar);
         if (DIM == 3) axis_weights<T, false>(pd, ad);
 #pragma unroll
         for (int k = 0; k < TD; ++k) {
             int dl = 0;
-            float wd = 1.f;
+            R wd = 1.f;
             if (DIM == 3) {
                 if (SLAB) {
                     const int sd = m ? -(ad.base + k) : ad.base + k;
@@ -400,12 +455,12 @@ __device__ __forceinline__ void scatter_coop(const SliceGeom& g, float2* __restr
 #pragma unroll
             for (int i = 0; i < T; ++i) {
                 const int rl = scatter_line(g, ar.base + i, m);
-                const float wr = ar.w[i];
+                const R wr = ar.w[i];
                 if (rl < 0 || wr == 0.f) continue;
-                const float w = wd * wr * wc;
+                const R w = wd * wr * wc;
                 const int off = dl * plane_stride + rl * g.Rh + c;
-                const float re = vx * w, im = vy * w * sgn;
-                const float fw = WEIGHTS ? wval * fabsf(w) : 0.f;
+                const R re = vx * w, im = vy * w * sgn;
+                const R fw = WEIGHTS ? wval * rabs(w) : 0.f;
                 if (INTERLEAVED) {
                     red_add_v4(vol4 + off, re, im, fw, 0.f);
                 } else {
@@ -433,58 +488,58 @@ __device__ __forceinline__ void scatter_coop(const SliceGeom& g, float2* __restr
 
 // Real-valued tri/bi-linear read of the weight-gradient volume: Friedel mirror without
 // conjugation, zero outside.  reference: csrc/cpu/3d/backprojection_2d_to_3d_kernels.cpp:466-515
-template <int DIM>
-__device__ __forceinline__ float gather_weight_grad(const SliceGeom& g, const float* __restrict__ wv,
-                                                    const Pixel& px) {
-    AxisWeights<2> ac, ar, ad;
+template <int DIM, typename R>
+__device__ __forceinline__ R gather_weight_grad(const SliceGeom& g, const R* __restrict__ wv,
+                                                    const PixelT<R>& px) {
+    AxisWeights<R, 2> ac, ar, ad;
     axis_weights<2, false>(px.c, ac);
     axis_weights<2, false>(px.r, ar);
     if (DIM == 3) axis_weights<2, false>(px.d, ad);
     const int plane_stride = g.R * g.Rh;
-    float acc = 0.f;
+    R acc = 0.f;
 #pragma unroll
     for (int k = 0; k < (DIM == 3 ? 2 : 1); ++k) {
-        float pk = 0.f;
+        R pk = 0.f;
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
-            float ri = 0.f;
+            R ri = 0.f;
 #pragma unroll
             for (int j = 0; j < 2; ++j) {
                 int c = ac.base + j;
                 const bool m = c < 0;
                 c = m ? -c : c;
-                float q = 0.f;
+                R q = 0.f;
                 const int rl = scatter_line(g, ar.base + i, m);
                 const int dl = (DIM == 3) ? scatter_line(g, ad.base + k, m) : 0;
                 if (c < g.Rh && rl >= 0 && dl >= 0) q = __ldg(wv + (dl * plane_stride + rl * g.Rh + c));
-                ri = fmaf(ac.w[j], q, ri);
+                ri = rfma(ac.w[j], q, ri);
             }
-            pk = fmaf(ar.w[i], ri, pk);
+            pk = rfma(ar.w[i], ri, pk);
         }
-        acc = fmaf((DIM == 3) ? ad.w[k] : 1.f, pk, acc);
+        acc = rfma((DIM == 3) ? ad.w[k] : 1.f, pk, acc);
     }
     return acc;
 }
 
 // Sum NV per-thread values over the block and add them to global memory with one atomic
 // per value per block.  dst[v] may be nullptr-guarded by the caller through `active`.
-template <int NV>
-__device__ __forceinline__ void block_reduce_add(float (&vals)[NV], float* const (&dst)[NV]) {
-    __shared__ float red[kWarps][NV];
+template <int NV, typename R>
+__device__ __forceinline__ void block_reduce_add(R (&vals)[NV], R* const (&dst)[NV]) {
+    __shared__ R red[kWarps][NV];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 #pragma unroll
     for (int v = 0; v < NV; ++v) {
-        float x = vals[v];
+        R x = vals[v];
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) x += __shfl_xor_sync(0xffffffffu, x, o);
         if (lane == 0) red[warp][v] = x;
     }
     __syncthreads();
     if (threadIdx.x < NV) {
-        float x = 0.f;
+        R x = 0.f;
 #pragma unroll
         for (int w = 0; w < kWarps; ++w) x += red[w][threadIdx.x];
-        float* p = dst[threadIdx.x];
+        R* p = dst[threadIdx.x];
         if (p != nullptr && x != 0.f) atomicAdd(p, x);
     }
 }

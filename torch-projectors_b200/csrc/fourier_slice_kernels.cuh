@@ -33,30 +33,31 @@ __device__ __forceinline__ BlockWork block_work(const SliceGeom& g) {
     return w;
 }
 
-template <int DIM>
-__device__ __forceinline__ const float* pose_rot(const SliceGeom& g, const float* rot, int b, int p) {
+template <int DIM, typename R>
+__device__ __forceinline__ const R* pose_rot(const SliceGeom& g, const R* rot, int b, int p) {
     return rot + (size_t)b * g.rot_stride_b + (size_t)p * (DIM * DIM);
 }
-__device__ __forceinline__ const float* pose_shift(const SliceGeom& g, const float* shifts, int b, int p) {
+template <typename R>
+__device__ __forceinline__ const R* pose_shift(const SliceGeom& g, const R* shifts, int b, int p) {
     return shifts + (size_t)b * g.shift_stride_b + (size_t)p * 2;
 }
 
 // ---- forward projection -----------------------------------------------------------------
 // reference semantics: csrc/cpu/3d/projection_3d_to_2d_kernels.cpp:155-207
-template <int DIM, bool CUBIC>
+template <int DIM, bool CUBIC, typename R>
 __global__ void __launch_bounds__(kBlockThreads)
-project_forw_kernel(const float2* __restrict__ rec, const float* __restrict__ rot,
-                    const float* __restrict__ shifts, float2* __restrict__ out, const SliceGeom g) {
+project_forw_kernel(const C2<R>* __restrict__ rec, const R* __restrict__ rot,
+                    const R* __restrict__ shifts, C2<R>* __restrict__ out, const SliceGeom g) {
     const BlockWork w = block_work(g);
-    Pixel px;
+    PixelT<R> px;
     px.c = px.r = px.d = 0.f;
     const bool valid = w.in_image && pixel_setup<DIM>(g, pose_rot<DIM>(g, rot, w.b, w.p), w.i, w.j, px);
-    float2 v, gc, gr, gd;
+    C2<R> v, gc, gr, gd;
     // all 32 lanes take part: the lanes of a group fetch each other's taps
     interpolate_coop<DIM, CUBIC, false>(g, rec + (size_t)w.b * g.vol_elems, px, valid, v, gc, gr, gd);
     if (!w.in_image) return;
     if (valid && g.has_shift) {
-        const float* s = pose_shift(g, shifts, w.b, w.p);
+        const R* s = pose_shift(g, shifts, w.b, w.p);
         v = cmul(v, phase_ramp(g, px, __ldg(s), __ldg(s + 1)));
     }
     // streaming store: the projections are written once and never re-read by this kernel,
@@ -67,37 +68,37 @@ project_forw_kernel(const float2* __restrict__ rec, const float* __restrict__ ro
 // Pose-gradient terms shared by the two backward kernels.
 //   rotation:  dL/dR[a][m] += s_m * Re(u * conj(grad_a)),  a: (c, r, d) rows, s = (sc, sr, 0)
 //   shift:     dL/ds[n]    += q_n * (u.y * val.x - u.x * val.y),  q = -2*pi*k_n/N
-template <int DIM, bool NEED_ROT, bool NEED_SHIFT>
-__device__ __forceinline__ void pose_grad_terms(const SliceGeom& g, const Pixel& px, float2 u_rot,
-                                                float2 u_shift, float2 val_shift, float2 g_c,
-                                                float2 g_r, float2 g_d,
-                                                float (&acc)[2 * DIM + 2]) {
+template <int DIM, bool NEED_ROT, bool NEED_SHIFT, typename R>
+__device__ __forceinline__ void pose_grad_terms(const SliceGeom& g, const PixelT<R>& px, C2<R> u_rot,
+                                                C2<R> u_shift, C2<R> val_shift, C2<R> g_c,
+                                                C2<R> g_r, C2<R> g_d,
+                                                R (&acc)[2 * DIM + 2]) {
     if (NEED_ROT) {
-        const float dc = u_rot.x * g_c.x + u_rot.y * g_c.y;
-        const float dr = u_rot.x * g_r.x + u_rot.y * g_r.y;
+        const R dc = u_rot.x * g_c.x + u_rot.y * g_c.y;
+        const R dr = u_rot.x * g_r.x + u_rot.y * g_r.y;
         acc[0] += dc * px.sc;
         acc[1] += dc * px.sr;
         acc[2] += dr * px.sc;
         acc[3] += dr * px.sr;
         if (DIM == 3) {
-            const float dd = u_rot.x * g_d.x + u_rot.y * g_d.y;
+            const R dd = u_rot.x * g_d.x + u_rot.y * g_d.y;
             acc[4] += dd * px.sc;
             acc[5] += dd * px.sr;
         }
     }
     if (NEED_SHIFT) {
-        const float cross = u_shift.y * val_shift.x - u_shift.x * val_shift.y;
-        acc[2 * DIM + 0] += (float)(g.shift_scale * (double)px.kr) * cross;
-        acc[2 * DIM + 1] += (float)(g.shift_scale * (double)px.kc) * cross;
+        const R cross = u_shift.y * val_shift.x - u_shift.x * val_shift.y;
+        acc[2 * DIM + 0] += (R)(g.shift_scale * (double)px.kr) * cross;
+        acc[2 * DIM + 1] += (R)(g.shift_scale * (double)px.kc) * cross;
     }
 }
 
-template <int DIM>
-__device__ __forceinline__ void pose_grad_flush(const SliceGeom& g, float (&acc)[2 * DIM + 2],
-                                                float* grad_rot, float* grad_shift, int b, int p) {
-    float* dst[2 * DIM + 2];
-    float* gr = grad_rot ? grad_rot + (size_t)b * g.rot_stride_b + (size_t)p * (DIM * DIM) : nullptr;
-    float* gs = grad_shift ? grad_shift + (size_t)b * g.shift_stride_b + (size_t)p * 2 : nullptr;
+template <int DIM, typename R>
+__device__ __forceinline__ void pose_grad_flush(const SliceGeom& g, R (&acc)[2 * DIM + 2],
+                                                R* grad_rot, R* grad_shift, int b, int p) {
+    R* dst[2 * DIM + 2];
+    R* gr = grad_rot ? grad_rot + (size_t)b * g.rot_stride_b + (size_t)p * (DIM * DIM) : nullptr;
+    R* gs = grad_shift ? grad_shift + (size_t)b * g.shift_stride_b + (size_t)p * 2 : nullptr;
 #pragma unroll
     for (int a = 0; a < DIM; ++a) {
         dst[2 * a + 0] = gr ? gr + a * DIM + 0 : nullptr;   // column 2 of a 3x3 gradient stays 0
@@ -110,30 +111,30 @@ __device__ __forceinline__ void pose_grad_flush(const SliceGeom& g, float (&acc)
 
 // ---- backward of forward projection -----------------------------------------------------
 // reference semantics: csrc/cpu/3d/projection_3d_to_2d_kernels.cpp:283-396
-template <int DIM, bool CUBIC, bool NEED_ROT, bool NEED_SHIFT>
+template <int DIM, bool CUBIC, bool NEED_ROT, bool NEED_SHIFT, typename R>
 __global__ void __launch_bounds__(kBlockThreads)
-project_back_kernel(const float2* __restrict__ grad_proj, const float2* __restrict__ rec,
-                    const float* __restrict__ rot, const float* __restrict__ shifts,
-                    float2* __restrict__ grad_rec, float* __restrict__ grad_rot,
-                    float* __restrict__ grad_shift, const SliceGeom g) {
+project_back_kernel(const C2<R>* __restrict__ grad_proj, const C2<R>* __restrict__ rec,
+                    const R* __restrict__ rot, const R* __restrict__ shifts,
+                    C2<R>* __restrict__ grad_rec, R* __restrict__ grad_rot,
+                    R* __restrict__ grad_shift, const SliceGeom g) {
     const BlockWork w = block_work(g);
-    float acc[2 * DIM + 2];
+    R acc[2 * DIM + 2];
 #pragma unroll
     for (int q = 0; q < 2 * DIM + 2; ++q) acc[q] = 0.f;
-    Pixel px;
+    PixelT<R> px;
     px.c = px.r = px.d = px.sc = px.sr = px.kr = px.kc = 0.f;
     const bool active = w.in_image &&
                         pixel_setup<DIM>(g, pose_rot<DIM>(g, rot, w.b, w.p), w.i, w.j, px) &&
                         !(w.j == 0 && w.i >= g.N / 2);
-    float2 val = make_float2(0.f, 0.f), gc = val, gr = val, gd = val;
+    C2<R> val = make2<R>(0.f, 0.f), gc = val, gr = val, gd = val;
     if (NEED_ROT || NEED_SHIFT)      // cooperative gather: every lane of the warp takes part
         interpolate_coop<DIM, CUBIC, NEED_ROT>(g, rec + (size_t)w.b * g.vol_elems, px, active, val, gc, gr, gd);
-    float2 orig = make_float2(0.f, 0.f), u = orig, ph = make_float2(1.f, 0.f);
+    C2<R> orig = make2<R>(0.f, 0.f), u = orig, ph = make2<R>(1.f, 0.f);
     if (active) {
         orig = __ldcs(grad_proj + w.pix);
         u = orig;
         if (g.has_shift) {
-            const float* s = pose_shift(g, shifts, w.b, w.p);
+            const R* s = pose_shift(g, shifts, w.b, w.p);
             ph = phase_ramp(g, px, __ldg(s), __ldg(s + 1));
             u = cmul_conj(orig, ph);
         }
@@ -143,7 +144,7 @@ project_back_kernel(const float2* __restrict__ grad_proj, const float2* __restri
                                                   px, active, u, 0.f);
     if (active) {
         if (NEED_ROT || NEED_SHIFT) {
-            const float2 mod = g.has_shift ? cmul(val, ph) : val;
+            const C2<R> mod = g.has_shift ? cmul(val, ph) : val;
             pose_grad_terms<DIM, NEED_ROT, NEED_SHIFT>(g, px, u, orig, mod, gc, gr, gd, acc);
         }
     }
@@ -153,22 +154,22 @@ project_back_kernel(const float2* __restrict__ grad_proj, const float2* __restri
 // ---- back-projection --------------------------------------------------------------------
 // reference semantics: csrc/cpu/3d/backprojection_2d_to_3d_kernels.cpp:177-291
 // Slice value with the conjugate shift ramp applied, and its weight (shared by both kernels).
-template <int DIM, bool WEIGHTS>
+template <int DIM, bool WEIGHTS, typename R>
 __device__ __forceinline__ bool backproject_pixel(const SliceGeom& g, const BlockWork& w,
-                                                  const float2* __restrict__ proj,
-                                                  const float* __restrict__ weights,
-                                                  const float* __restrict__ rot,
-                                                  const float* __restrict__ shifts, Pixel& px,
-                                                  float2& v, float& wv) {
+                                                  const C2<R>* __restrict__ proj,
+                                                  const R* __restrict__ weights,
+                                                  const R* __restrict__ rot,
+                                                  const R* __restrict__ shifts, PixelT<R>& px,
+                                                  C2<R>& v, R& wv) {
     px.c = px.r = px.d = 0.f;
-    v = make_float2(0.f, 0.f);
+    v = make2<R>(0.f, 0.f);
     wv = 0.f;
     const bool active = w.in_image && !(w.j == 0 && w.i >= g.N / 2) &&
                         pixel_setup<DIM>(g, pose_rot<DIM>(g, rot, w.b, w.p), w.i, w.j, px);
     if (active) {
         v = __ldcs(proj + w.pix);
         if (g.has_shift) {
-            const float* s = pose_shift(g, shifts, w.b, w.p);
+            const R* s = pose_shift(g, shifts, w.b, w.p);
             v = cmul_conj(v, phase_ramp(g, px, __ldg(s), __ldg(s + 1)));
         }
         if (WEIGHTS) wv = __ldcs(weights + w.pix);
@@ -176,16 +177,16 @@ __device__ __forceinline__ bool backproject_pixel(const SliceGeom& g, const Bloc
     return active;
 }
 
-template <int DIM, bool CUBIC, bool WEIGHTS>
+template <int DIM, bool CUBIC, bool WEIGHTS, typename R>
 __global__ void __launch_bounds__(kBlockThreads)
-backproject_forw_kernel(const float2* __restrict__ proj, const float* __restrict__ weights,
-                        const float* __restrict__ rot, const float* __restrict__ shifts,
-                        float2* __restrict__ data_rec, float* __restrict__ weight_rec,
+backproject_forw_kernel(const C2<R>* __restrict__ proj, const R* __restrict__ weights,
+                        const R* __restrict__ rot, const R* __restrict__ shifts,
+                        C2<R>* __restrict__ data_rec, R* __restrict__ weight_rec,
                         const SliceGeom g) {
     const BlockWork w = block_work(g);
-    Pixel px;
-    float2 v;
-    float wv;
+    PixelT<R> px;
+    C2<R> v;
+    R wv;
     const bool active = backproject_pixel<DIM, WEIGHTS>(g, w, proj, weights, rot, shifts, px, v, wv);
     scatter_coop<DIM, CUBIC, WEIGHTS, true, false>(g, data_rec + (size_t)w.b * g.vol_elems,
                                                    WEIGHTS ? weight_rec + (size_t)w.b * g.vol_elems : nullptr,
@@ -382,32 +383,32 @@ backproject_slab_kernel(const float2* __restrict__ proj, const float* __restrict
 
 // ---- backward of back-projection --------------------------------------------------------
 // reference semantics: csrc/cpu/3d/backprojection_2d_to_3d_kernels.cpp:417-583
-template <int DIM, bool CUBIC, bool NEED_ROT, bool NEED_SHIFT>
+template <int DIM, bool CUBIC, bool NEED_ROT, bool NEED_SHIFT, typename R>
 __global__ void __launch_bounds__(kBlockThreads)
-backproject_back_kernel(const float2* __restrict__ grad_data_rec,
-                        const float* __restrict__ grad_weight_rec,
-                        const float2* __restrict__ proj, const float* __restrict__ rot,
-                        const float* __restrict__ shifts, float2* __restrict__ grad_proj,
-                        float* __restrict__ grad_weights, float* __restrict__ grad_rot,
-                        float* __restrict__ grad_shift, const SliceGeom g) {
+backproject_back_kernel(const C2<R>* __restrict__ grad_data_rec,
+                        const R* __restrict__ grad_weight_rec,
+                        const C2<R>* __restrict__ proj, const R* __restrict__ rot,
+                        const R* __restrict__ shifts, C2<R>* __restrict__ grad_proj,
+                        R* __restrict__ grad_weights, R* __restrict__ grad_rot,
+                        R* __restrict__ grad_shift, const SliceGeom g) {
     const BlockWork w = block_work(g);
-    float acc[2 * DIM + 2];
+    R acc[2 * DIM + 2];
 #pragma unroll
     for (int q = 0; q < 2 * DIM + 2; ++q) acc[q] = 0.f;
-    Pixel px;
+    PixelT<R> px;
     px.c = px.r = px.d = px.sc = px.sr = px.kr = px.kc = 0.f;
     const bool active = w.in_image &&
                         pixel_setup<DIM>(g, pose_rot<DIM>(g, rot, w.b, w.p), w.i, w.j, px) &&
                         !(w.j == 0 && w.i >= g.N / 2);
     const bool write_w = grad_weight_rec != nullptr && grad_weights != nullptr;
-    float2 raw, gc, gr, gd;
+    C2<R> raw, gc, gr, gd;
     // cooperative gather: every lane of the warp takes part
     interpolate_coop<DIM, CUBIC, NEED_ROT>(g, grad_data_rec + (size_t)w.b * g.vol_elems, px, active, raw, gc, gr, gd);
     if (active) {
-        float2 ph = make_float2(1.f, 0.f);
-        float2 v = raw;
+        C2<R> ph = make2<R>(1.f, 0.f);
+        C2<R> v = raw;
         if (g.has_shift) {
-            const float* s = pose_shift(g, shifts, w.b, w.p);
+            const R* s = pose_shift(g, shifts, w.b, w.p);
             ph = phase_ramp(g, px, __ldg(s), __ldg(s + 1));
             v = cmul(raw, ph);
         }
@@ -416,12 +417,12 @@ backproject_back_kernel(const float2* __restrict__ grad_data_rec,
             __stcs(grad_weights + w.pix,
                    gather_weight_grad<DIM>(g, grad_weight_rec + (size_t)w.b * g.vol_elems, px));
         if (NEED_ROT || NEED_SHIFT) {
-            float2 pv = __ldcs(proj + w.pix);
+            C2<R> pv = __ldcs(proj + w.pix);
             if (g.has_shift) pv = cmul_conj(pv, ph);
             pose_grad_terms<DIM, NEED_ROT, NEED_SHIFT>(g, px, pv, pv, raw, gc, gr, gd, acc);
         }
     } else if (w.in_image) {
-        __stcs(grad_proj + w.pix, make_float2(0.f, 0.f));
+        __stcs(grad_proj + w.pix, make2<R>(0.f, 0.f));
         if (write_w) __stcs(grad_weights + w.pix, 0.f);
     }
     if (NEED_ROT || NEED_SHIFT) pose_grad_flush<DIM>(g, acc, grad_rot, grad_shift, w.b, w.p);

@@ -34,6 +34,8 @@ SIGNATURES = {
     "b200proj_backproject_2d_back": [_ptr, _ptr, _ptr] + _COMMON + [_ptr, _ptr, _ptr, _ptr, _ptr],
     "b200proj_backproject_2d_to_3d_back": [_ptr, _ptr, _ptr] + _COMMON + [_ptr, _ptr, _ptr, _ptr, _ptr],
 }
+# complex128 / float64 variants: same argument lists (pointers are void* here)
+SIGNATURES.update({name + "_f64": sig for name, sig in list(SIGNATURES.items()) if not name.endswith("_noalloc")})
 EXPORTS = list(SIGNATURES) + ["b200proj_version", "b200proj_last_error", "b200proj_rec_boxsize",
                                 "b200proj_backproject_workspace_bytes"]
 
@@ -96,7 +98,10 @@ def _p(t: Optional[torch.Tensor]) -> int:
 
 
 def _call(name: str, anchor: torch.Tensor, *args) -> None:
-    """Invoke an entry point on the current stream of anchor's device."""
+    """Invoke an entry point (its _f64 variant for double precision tensors) on the current
+    stream of anchor's device."""
+    if anchor.dtype in (torch.complex128, torch.float64):
+        name += "_f64"
     if not anchor.is_cuda:
         raise RuntimeError(f"{name}: tensors must be on a CUDA device (there is no CPU path)")
     lib = load()

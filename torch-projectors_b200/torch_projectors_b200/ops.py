@@ -7,7 +7,8 @@ changing the import.  The raw operators are registered under the op namespace
 ``torch_projectors_b200`` for the CUDA dispatch key only: calling them with CPU (or MPS)
 tensors raises from the dispatcher -- there is no CPU fallback.  complex128 / float64
 inputs, which the reference's CUDA wrappers silently route through its CPU kernels
-(``csrc/cuda/3d/projection_3d_to_2d_kernels.cu:902-918``), raise ``RuntimeError`` here.
+(``csrc/cuda/3d/projection_3d_to_2d_kernels.cu:902-918``), run on the GPU here (the same
+kernels instantiated for double); mixed precisions raise ``RuntimeError``.
 """
 from __future__ import annotations
 
@@ -47,12 +48,23 @@ def _interp_code(interpolation: str) -> int:
     return _abi.CUBIC if interpolation == "cubic" else _abi.LINEAR
 
 
-def _check_fp32(name: str, t: torch.Tensor, complex_: bool) -> None:
-    want = torch.complex64 if complex_ else torch.float32
-    if t.dtype != want:
+_REAL_OF = {torch.complex64: torch.float32, torch.complex128: torch.float64}
+
+
+def _check_fp32(name: str, t: torch.Tensor, complex_: bool, like: Optional[torch.Tensor] = None) -> None:
+    """Precision check: complex64 with float32 (the fast path) or complex128 with float64 (same
+    kernels instantiated for double); every tensor of a call must be of the same precision as
+    `like` (the call's main complex tensor).  Nothing else is accepted and nothing is converted."""
+    allowed = (torch.complex64, torch.complex128) if complex_ else (torch.float32, torch.float64)
+    if t.dtype not in allowed:
         raise RuntimeError(
-            f"{name} has dtype {t.dtype}; the B200 kernels compute in "
-            f"{'complex64' if complex_ else 'float32'} only and there is no CPU fallback for other precisions")
+            f"{name} has dtype {t.dtype}; the B200 kernels compute in complex64/float32 or "
+            f"complex128/float64 only and there is no CPU fallback for other precisions")
+    if like is not None:
+        want = like.dtype if complex_ else _REAL_OF[like.dtype]
+        if t.dtype != want:
+            raise RuntimeError(f"{name} has dtype {t.dtype} but {want} is needed to match the {like.dtype} data "
+                               f"(mixed precisions are not supported)")
 
 
 def _check_pose_inputs(dim: int, what: str, B: int, rotations, shifts, like: torch.Tensor):
@@ -62,7 +74,7 @@ def _check_pose_inputs(dim: int, what: str, B: int, rotations, shifts, like: tor
     _check(rotations.dim() == 4 and rotations.size(2) == dim and rotations.size(3) == dim,
            f"Rotations must be (B_rot, P, {dim}, {dim})")
     _check(rotations.device == like.device, "rotations must be on the same device as the data")
-    _check_fp32("rotations", rotations, False)
+    _check_fp32("rotations", rotations, False, like)
     B_rot, P = rotations.size(0), rotations.size(1)
     _check(B_rot == B or B_rot == 1, f"Batch size of rotations must be 1 or same as {what}")
     if shifts is not None:
@@ -81,6 +93,8 @@ def _backproject_workspace(dim, B, R, P, N, interp, weights, device):
     """Scratch for the interleaved accumulation path of the back-projection kernels (from
     torch's caching allocator, so nothing is freed behind the stream); None when the
     library says a workspace would not help."""
+    if weights is not None and weights.dtype != torch.float32:
+        return None                      # the interleaved accumulation path is fp32 only
     n = _abi.backproject_workspace_bytes(dim, B, R, P, N, interp, weights is not None)
     return torch.empty(n, dtype=torch.uint8, device=device) if n else None
 
@@ -126,8 +140,8 @@ def _project_back_impl(dim, grad_projections, reconstruction, rotations, shifts,
     interp = _interp_code(interpolation)
     _check(grad_projections.dim() == 4, "Projections must be a 4D tensor (B, P, H, W/2+1)")
     _rec_dims_ok(dim, reconstruction)
-    _check_fp32("grad_projections", grad_projections, True)
     _check_fp32("reconstruction", reconstruction, True)
+    _check_fp32("grad_projections", grad_projections, True, reconstruction)
     B, P_g, N, Nh = grad_projections.shape
     _check(N % 2 == 0 and Nh == N // 2 + 1, "grad_projections must be rfft-shaped with an even box")
     _check(reconstruction.size(0) == B, "Batch size of grad_projections must match reconstruction")
@@ -164,7 +178,7 @@ def _backproject_forw_impl(dim, projections, weights, rotations, shifts, interpo
         _check(weights.is_floating_point(), "Weights must be a real-valued tensor")
         _check(weights.dim() == 4, "Weights must be (B, P, height, width/2+1)")
         _check(weights.shape == projections.shape, "Weights and projections must have the same shape")
-        _check_fp32("weights", weights, False)
+        _check_fp32("weights", weights, False, projections)
         weights = weights.contiguous()
     P, rot, sh = _check_pose_inputs(dim, "projections", B, rotations, shifts, projections)
     _check(P == P_p, "Number of poses in rotations must match projections")
@@ -173,7 +187,7 @@ def _backproject_forw_impl(dim, projections, weights, rotations, shifts, interpo
     R = _abi.rec_boxsize(N, oversampling)
     shape = (B, R, R, R // 2 + 1) if dim == 3 else (B, R, R // 2 + 1)
     data_rec = torch.empty(shape, dtype=proj.dtype, device=dev)          # zero-filled by the call
-    weight_rec = torch.empty(shape, dtype=torch.float32, device=dev) if weights is not None else None
+    weight_rec = torch.empty(shape, dtype=_REAL_OF[proj.dtype], device=dev) if weights is not None else None
     if P == 0:                      # nothing to launch: pointers of empty tensors are NULL
         data_rec.zero_()
         if weight_rec is not None:
@@ -196,20 +210,21 @@ def _backproject_back_impl(dim, grad_data_rec, grad_weight_rec, projections, wei
     interp = _interp_code(interpolation)
     _check(grad_data_rec.dim() == dim + 1, "grad_data_rec must be (B, D, H, W/2+1)" if dim == 3 else "grad_data_rec must be (B, H, W/2+1)")
     _check(projections.dim() == 4, "projections must be a 4D tensor (B, P, boxsize, boxsize/2+1)")
-    _check_fp32("grad_data_rec", grad_data_rec, True)
     _check_fp32("projections", projections, True)
+    _check_fp32("grad_data_rec", grad_data_rec, True, projections)
     B, P_p, N, Nh = projections.shape
     if grad_weight_rec is not None:
         _check(grad_weight_rec.is_cuda, "grad_weight_rec must be on CUDA device")
         _check(grad_weight_rec.is_floating_point(), "grad_weight_rec must be a real-valued tensor")
         _check(grad_weight_rec.shape == grad_data_rec.shape, "grad_weight_rec and grad_data_rec must have same shape")
-        _check_fp32("grad_weight_rec", grad_weight_rec, False)
+        _check_fp32("grad_weight_rec", grad_weight_rec, False, projections)
         grad_weight_rec = grad_weight_rec.contiguous()
     R = _abi.rec_boxsize(N, oversampling)
     want = (B, R, R, R // 2 + 1) if dim == 3 else (B, R, R // 2 + 1)
     _check(tuple(grad_data_rec.shape) == want, "grad_data_rec shape must match expected reconstruction size")
     if weights is not None:
         _check(weights.is_cuda, "weights must be on CUDA device")
+        _check_fp32("weights", weights, False, projections)
     P, rot, sh = _check_pose_inputs(dim, "projections", B, rotations, shifts, projections)
     _check(P == P_p, "Number of poses in rotations must match projections")
     need_rot = rotations.requires_grad
@@ -218,7 +233,7 @@ def _backproject_back_impl(dim, grad_data_rec, grad_weight_rec, projections, wei
     proj = projections.contiguous()
     dev = proj.device
     grad_proj = torch.empty_like(proj)
-    grad_w = torch.empty(proj.shape, dtype=torch.float32, device=dev) if weights is not None else None
+    grad_w = torch.empty(proj.shape, dtype=_REAL_OF[proj.dtype], device=dev) if weights is not None else None
     grad_rot = torch.empty(rot.shape, dtype=rot.dtype, device=dev) if need_rot else None
     grad_sh = torch.empty(sh.shape, dtype=sh.dtype, device=dev) if need_shift else None
     if proj.numel():
@@ -389,23 +404,24 @@ def backproject_2d_to_3d_accumulate_(data_rec: torch.Tensor, weight_rec: Optiona
         rotations = rotations.unsqueeze(0)
     if shifts is not None and shifts.dim() == 2:
         shifts = shifts.unsqueeze(0)
-    _check(projections.is_cuda and projections.dtype == torch.complex64, "projections must be CUDA complex64")
+    _check(projections.is_cuda, "Input projections must be on CUDA device")
+    _check_fp32("projections", projections, True)
     B, P_p, N, _ = projections.shape
     interp = _interp_code(interpolation)
     if weights is not None:
         _check(weight_rec is not None, "weights given but weight_rec is None")
         _check(weights.is_cuda, "Weights must be on CUDA device")
-        _check_fp32("weights", weights, False)
+        _check_fp32("weights", weights, False, projections)
         weights = weights.contiguous()
     P, rot, sh = _check_pose_inputs(3, "projections", B, rotations, shifts, projections)
     _check(P == P_p, "Number of poses in rotations must match projections")
     R = _abi.rec_boxsize(N, oversampling)
     want = (B, R, R, R // 2 + 1)
-    _check(tuple(data_rec.shape) == want and data_rec.dtype == torch.complex64 and data_rec.is_contiguous()
-           and data_rec.device == projections.device, f"data_rec must be a contiguous complex64 tensor of shape {want}")
+    _check(tuple(data_rec.shape) == want and data_rec.dtype == projections.dtype and data_rec.is_contiguous()
+           and data_rec.device == projections.device, f"data_rec must be a contiguous {projections.dtype} tensor of shape {want}")
     if weights is not None:
-        _check(tuple(weight_rec.shape) == want and weight_rec.dtype == torch.float32 and weight_rec.is_contiguous()
-               and weight_rec.device == projections.device, f"weight_rec must be a contiguous float32 tensor of shape {want}")
+        _check(tuple(weight_rec.shape) == want and weight_rec.dtype == _REAL_OF[projections.dtype] and weight_rec.is_contiguous()
+               and weight_rec.device == projections.device, f"weight_rec must be a contiguous {_REAL_OF[projections.dtype]} tensor of shape {want}")
     if P == 0:
         return
     _abi.backproject_forw(3, projections.contiguous(), weights, rot, sh, interp, oversampling,
