@@ -537,6 +537,90 @@ def reference_cuda_workload(args):
                       "steps": args.steps, "warmup": args.warmup, "data": "synthetic", "rows": rows}), flush=True)
 
 
+# Published H100 numbers of the reference (10^3 projections/s; paper/results/tables/*.tex there),
+# keyed like the rows produced below: (op, box, B, interp) -> (Fwd, Fwd+Bwd), all at P = 2048, os = 1.
+PAPER_H100 = {
+    ("project_3d_to_2d", 256, 1, "linear"): (929.5, 149.1), ("project_3d_to_2d", 256, 1, "cubic"): (164.6, 23.0),
+    ("project_3d_to_2d", 256, 8, "linear"): (1838.2, 164.6),
+    ("project_3d_to_2d", 128, 1, "linear"): (3038.7, 556.9), ("project_3d_to_2d", 128, 1, "cubic"): (632.1, 88.5),
+    ("project_3d_to_2d", 128, 8, "linear"): (7729.0, None), ("project_3d_to_2d", 128, 8, "cubic"): (1110.4, None),
+    ("backproject_2d_to_3d", 256, 1, "linear"): (135.8, 114.8), ("backproject_2d_to_3d", 256, 1, "cubic"): (18.5, 17.1),
+    ("backproject_2d_to_3d", 128, 1, "linear"): (570.3, None), ("backproject_2d_to_3d", 128, 1, "cubic"): (72.5, None),
+    ("project_2d", 256, 8, "linear"): (3695.1, 266.8),
+}
+
+
+def paper_matrix_workload(args):
+    """The rows of the reference's published benchmark tables re-measured with its protocol:
+    oversampling 1, no cutoff argument, complex64 randn data, shifts randn*5, P = 2048, 3 warm-up +
+    15 timed runs, median of wall-clock times around the Python call with a device synchronise;
+    'Fwd+Bwd' adds the autograd backward of sum(|out|^2) with only the data tensor requiring
+    gradients (projections and weights for back-projection)."""
+    import torch_projectors_b200 as tp
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    from cases import random_rotations_2d
+    gen = torch.Generator().manual_seed(42)
+    ggen = torch.Generator(device=dev).manual_seed(42)
+    P = 2048
+    rows = {}
+
+    def cplx(*shape):
+        return torch.complex(torch.randn(*shape, generator=ggen, device=dev), torch.randn(*shape, generator=ggen, device=dev))
+
+    def median_rate(fn, slices):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        ts = []
+        for _ in range(15):
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            fn()
+            torch.cuda.synchronize()
+            ts.append(time.perf_counter() - t0)
+        return slices / statistics.median(ts) / 1e3            # 10^3 projections per second
+
+    for (op, box, B, interp), (h_fwd, h_both) in PAPER_H100.items():
+        rot3 = uniform_rotations(P, gen, dev).expand(B, -1, -1, -1).contiguous()
+        shifts = (torch.randn(B, P, 2, generator=gen) * 5.0).to(dev)
+        if op == "project_3d_to_2d":
+            rec = cplx(B, box, box, box // 2 + 1).requires_grad_(True)
+            fwd = lambda: tp.project_3d_to_2d_forw(rec, rot3, shifts, output_shape=(box, box), interpolation=interp)  # noqa: E731
+
+            def both():
+                rec.grad = None
+                (tp.project_3d_to_2d_forw(rec, rot3, shifts, output_shape=(box, box), interpolation=interp).abs() ** 2).sum().backward()
+        elif op == "project_2d":
+            rec = cplx(B, box, box // 2 + 1).requires_grad_(True)
+            rot2 = random_rotations_2d(B * P, gen).reshape(B, P, 2, 2).to(dev)
+            fwd = lambda: tp.project_2d_forw(rec, rot2, shifts, output_shape=(box, box), interpolation=interp)  # noqa: E731
+
+            def both():
+                rec.grad = None
+                (tp.project_2d_forw(rec, rot2, shifts, output_shape=(box, box), interpolation=interp).abs() ** 2).sum().backward()
+        else:
+            proj = cplx(B, P, box, box // 2 + 1).requires_grad_(True)
+            w = torch.rand(B, P, box, box // 2 + 1, generator=ggen, device=dev).requires_grad_(True)
+            fwd = lambda: tp.backproject_2d_to_3d_forw(proj, rot3, weights=w, shifts=shifts, interpolation=interp)  # noqa: E731
+
+            def both():
+                proj.grad = None
+                w.grad = None
+                d, wr = tp.backproject_2d_to_3d_forw(proj, rot3, weights=w, shifts=shifts, interpolation=interp)
+                ((d.abs() ** 2).sum() + (wr ** 2).sum()).backward()
+        with torch.no_grad():
+            r_fwd = median_rate(fwd, B * P)
+        r_both = median_rate(both, B * P)
+        rows[f"{op} box {box} B={B} {interp}"] = {
+            "b200_fwd_kproj_s": r_fwd, "b200_fwd_bwd_kproj_s": r_both, "h100_reference_fwd_kproj_s": h_fwd,
+            "h100_reference_fwd_bwd_kproj_s": h_both, "fwd_ratio": r_fwd / h_fwd,
+            "fwd_bwd_ratio": (r_both / h_both) if h_both else None}
+        torch.cuda.empty_cache()
+    print(json.dumps({"metric": "10^3 projections/s with the reference paper's protocol (P = 2048, os = 1): this package on B200 vs the reference's published H100 numbers",
+                      "data": "synthetic", "dtype": "f32", "rows": rows}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -548,7 +632,7 @@ def main():
     ap.add_argument("--profile-case", choices=["project", "backproject", "project_back", "backproject_slab"], default=None,
                     help="run a few launches of one kernel on a reduced pose count (for ncu captures); prints no bench line")
     ap.add_argument("--profile-poses", type=int, default=2048)
-    ap.add_argument("--workload", choices=["default", "autograd_step", "sharded_backproject", "ops_table", "reference_cuda"], default="default",
+    ap.add_argument("--workload", choices=["default", "autograd_step", "sharded_backproject", "ops_table", "reference_cuda", "paper_matrix"], default="default",
                     help="default: projection (+ back-projection) headline line; the other two print their own line")
     ap.add_argument("--total-slices", type=int, default=0, help="sharded_backproject: total slices over all ranks (default 200000)")
     args = ap.parse_args()
@@ -559,6 +643,9 @@ def main():
         return
     if args.impl == "b200" and args.workload == "autograd_step":
         autograd_step_workload(args)
+        return
+    if args.impl == "b200" and args.workload == "paper_matrix":
+        paper_matrix_workload(args)
         return
     if args.impl == "b200" and args.workload == "reference_cuda":
         reference_cuda_workload(args)

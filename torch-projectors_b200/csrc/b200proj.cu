@@ -61,7 +61,7 @@ int prepare(Launch& L, int dim, int64_t B, int64_t R, int64_t B_rot, const void*
     const int64_t Nh = N / 2 + 1, Rh = R / 2 + 1;
     const int64_t vol = (dim == 3 ? R : 1) * R * Rh;
     if (vol > INT_MAX) return fail(B200PROJ_ERR_LIMIT, "reconstruction of box %lld exceeds 2^31-1 voxels per batch item", (long long)R);
-    if (N > 65536) return fail(B200PROJ_ERR_LIMIT, "projection boxsize %lld too large", (long long)N);
+    if (N > 2048) return fail(B200PROJ_ERR_LIMIT, "projection boxsize %lld exceeds 2048", (long long)N);
     if (P * dim * dim > INT_MAX / 2) return fail(B200PROJ_ERR_LIMIT, "too many poses per batch item (%lld)", (long long)P);
 
     SliceGeom& g = L.g;
@@ -80,9 +80,17 @@ int prepare(Launch& L, int dim, int64_t B, int64_t R, int64_t B_rot, const void*
     g.shift_scale = -2.0 * M_PI / (double)N;
     g.vol_elems = vol;
 
-    const int64_t blocks = B * P * (int64_t)g.tiles_j * g.tiles_i;
-    if (blocks > INT_MAX) return fail(B200PROJ_ERR_LIMIT, "B*P*tiles = %lld exceeds the grid limit; split the poses into chunks", (long long)blocks);
-    L.grid = dim3((unsigned)blocks, 1, 1);
+    if (B * P > INT_MAX / 2) return fail(B200PROJ_ERR_LIMIT, "B*P = %lld slices exceed the grid limit; split the poses into chunks", (long long)(B * P));
+    g.BP = (int)(B * P);
+    g.P_is_all = (B == 1);
+    g.sparse_samples = oversampling >= 1.5;
+    // exact for tile < 2^16 whenever tiles_j <= 2^16 (the numbers of tiles per slice are far below)
+    g.tiles_j_magic = g.tiles_j == 1 ? 0u : (unsigned)(((1ull << 32) + (unsigned long long)g.tiles_j - 1) / (unsigned long long)g.tiles_j);
+    // x = tile, (y, z) = slice index split as y + 32768 * z (see block_work)
+    const int64_t bp = B * P;
+    const unsigned gy = (unsigned)(bp < 32768 ? (bp > 0 ? bp : 1) : 32768);
+    const unsigned gz = (unsigned)((bp + 32767) / 32768 > 0 ? (bp + 32767) / 32768 : 1);
+    L.grid = dim3((unsigned)(g.tiles_j * g.tiles_i), gy, gz);
     L.B = B; L.P = P;
     L.rec_count = (size_t)B * (size_t)vol;
     L.pix_count = (size_t)B * (size_t)P * (size_t)N * (size_t)Nh;

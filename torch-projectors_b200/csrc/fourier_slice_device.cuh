@@ -59,6 +59,10 @@ struct SliceGeom {
     int N, Nh;              // projection box and stored width N/2+1
     int R, Rh, half;        // volume box, stored width R/2+1, R/2
     int P;                  // poses per batch item
+    int BP;                 // B * P, slices of the call
+    int P_is_all;           // B == 1
+    int sparse_samples;     // oversampling >= 1.5
+    unsigned tiles_j_magic; // ceil(2^32 / tiles_j): tile / tiles_j == __umulhi(tile, magic) for tile < 2^16
     int tiles_j, tiles_i;   // block tiles per slice
     int rot_stride_b;       // elements between batch items of rot (0 = shared)
     int shift_stride_b;     // elements between batch items of shifts (0 = shared)
@@ -83,7 +87,9 @@ using Pixel = PixelT<float>;
 // samples form a compact patch of the slice plane (cache locality of the taps) while each
 // row segment is 64 contiguous bytes of the output.
 __device__ __forceinline__ void tile_pixel(const SliceGeom& g, int tile, int& i, int& j) {
-    const int tj = tile % g.tiles_j, ti = tile / g.tiles_j;
+    // tile / tiles_j without a division (a single tile column has no 32-bit magic number)
+    const int ti = g.tiles_j == 1 ? tile : (int)__umulhi((unsigned)tile, g.tiles_j_magic);
+    const int tj = tile - ti * g.tiles_j;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     j = tj * kTileJ + (warp & 1) * 8 + (lane & 7);
     i = ti * kTileI + (warp >> 1) * 4 + (lane >> 3);
@@ -115,13 +121,27 @@ __device__ __forceinline__ bool pixel_setup(const SliceGeom& g, const R* __restr
     return true;
 }
 
+// sin and cos of a phase of tens of radians.  fp32: the phase (already rounded to float as the
+// reference rounds it) is reduced to [-pi, pi] exactly in double, then evaluated with the
+// hardware approximations, whose absolute error there (< 5e-7) is below the fp32 noise of the
+// interpolated value it multiplies; this replaces ~40 instructions of sincosf's full-range
+// path by ~10.  fp64: the accurate library routine.
+__device__ __forceinline__ void phase_sincos(float ph, float* sn, float* cs) {
+    const double x = (double)ph;
+    const double k = rint(x * 0.15915494309189535);                 // 1 / (2*pi)
+    const float r = (float)fma(k, -6.283185307179586, x);
+    *sn = __sinf(r);
+    *cs = __cosf(r);
+}
+__device__ __forceinline__ void phase_sincos(double ph, double* sn, double* cs) { sincos(ph, sn, cs); }
+
 // exp(-2*pi*i*(kr*s0 + kc*s1)/N) as (cos, sin).
 template <typename R>
 __device__ __forceinline__ C2<R> phase_ramp(const SliceGeom& g, const PixelT<R>& px, R s0, R s1) {
     const R dot = add_rn(mul_rn(px.kr, s0), mul_rn(px.kc, s1));
     const R ph = (R)((double)dot * g.phase_scale);
     R sn, cs;
-    rsincos(ph, &sn, &cs);
+    phase_sincos(ph, &sn, &cs);
     return make2<R>(cs, sn);
 }
 
@@ -207,6 +227,86 @@ __device__ __forceinline__ int gather_line(const SliceGeom& g, int r, bool mirro
     if (mirrored) r = -r;
     r = min(g.half, max(r, -g.half + 1));
     return r < 0 ? r + g.R : r;
+}
+
+// One-lane-per-pixel separable interpolation (used for linear interpolation, whose 2-tap rows
+// are too short for lane groups to pay for their shuffles: the linear gathers are bound by
+// instruction issue, not by the L1TEX data pipe).  Same value and derivative conventions as
+// interpolate_coop.
+template <int DIM, bool CUBIC, bool WITH_DERIV, typename R>
+__device__ __forceinline__ void interpolate_lane(const SliceGeom& g, const C2<R>* __restrict__ vol,
+                                                 const PixelT<R>& px, C2<R>& val, C2<R>& g_c,
+                                                 C2<R>& g_r, C2<R>& g_d) {
+    constexpr int T = CUBIC ? 4 : 2;
+    constexpr int TD = (DIM == 3) ? T : 1;
+    AxisWeights<R, T> ac, ar, ad;
+    axis_weights<T, WITH_DERIV>(px.c, ac);
+    axis_weights<T, WITH_DERIV>(px.r, ar);
+    if (DIM == 3) axis_weights<T, WITH_DERIV>(px.d, ad);
+    const int plane_stride = g.R * g.Rh;
+    val = make2<R>(0.f, 0.f);
+    g_c = g_r = g_d = val;
+    const bool interior = ar.base >= -g.half + 1 && ar.base + T - 1 <= g.half - 1 &&
+                          (DIM == 2 || (ad.base >= -g.half + 1 && ad.base + T - 1 <= g.half - 1));
+#pragma unroll
+    for (int j = 0; j < T; ++j) {
+        bool m;
+        const int col = gather_col<CUBIC>(g, ac.base + j, m);
+        C2<R> A = make2<R>(0.f, 0.f), Bq = A, Dq = A;
+#pragma unroll
+        for (int k = 0; k < TD; ++k) {
+            int pl = 0;
+            if (DIM == 3) {
+                if (interior) {
+                    const int d = m ? -(ad.base + k) : ad.base + k;
+                    pl = (d < 0 ? d + g.R : d) * plane_stride;
+                } else {
+                    pl = gather_line<CUBIC>(g, ad.base + k, m) * plane_stride;
+                }
+            }
+            C2<R> rs = make2<R>(0.f, 0.f), rds = rs;
+#pragma unroll
+            for (int i = 0; i < T; ++i) {
+                int rw;
+                if (interior) {
+                    const int r = m ? -(ar.base + i) : ar.base + i;
+                    rw = (r < 0 ? r + g.R : r) * g.Rh;
+                } else {
+                    rw = gather_line<CUBIC>(g, ar.base + i, m) * g.Rh;
+                }
+                const C2<R> v = __ldg(vol + (pl + rw + col));
+                rs.x = rfma(ar.w[i], v.x, rs.x);
+                rs.y = rfma(ar.w[i], v.y, rs.y);
+                if (WITH_DERIV) {
+                    rds.x = rfma(ar.dw[i], v.x, rds.x);
+                    rds.y = rfma(ar.dw[i], v.y, rds.y);
+                }
+            }
+            const R wd = (DIM == 3) ? ad.w[k] : (R)1;
+            A.x = rfma(wd, rs.x, A.x);
+            A.y = rfma(wd, rs.y, A.y);
+            if (WITH_DERIV) {
+                Bq.x = rfma(wd, rds.x, Bq.x);
+                Bq.y = rfma(wd, rds.y, Bq.y);
+                if (DIM == 3) {
+                    Dq.x = rfma(ad.dw[k], rs.x, Dq.x);
+                    Dq.y = rfma(ad.dw[k], rs.y, Dq.y);
+                }
+            }
+        }
+        const R sg = m ? (R)-1 : (R)1;               // a mirrored column holds conjugated values
+        const R wc = ac.w[j];
+        val.x = rfma(wc, A.x, val.x);
+        val.y = rfma(sg * wc, A.y, val.y);
+        if (WITH_DERIV) {
+            g_c.x = rfma(ac.dw[j], A.x, g_c.x);
+            g_c.y = rfma(sg * ac.dw[j], A.y, g_c.y);
+            g_r.x = rfma(wc, Bq.x, g_r.x);
+            g_r.y = rfma(sg * wc, Bq.y, g_r.y);
+            g_d.x = rfma(wc, Dq.x, g_d.x);
+            g_d.y = rfma(sg * wc, Dq.y, g_d.y);
+        }
+    }
 }
 
 // Cooperative separable interpolation of a complex half-volume, optionally with the spatial
@@ -350,6 +450,24 @@ __device__ __forceinline__ void interpolate_coop(const SliceGeom& g, const C2<R>
             g_r = cgr;
             g_d = cgd;
         }
+    }
+}
+
+// Gather used by the kernels: lane groups for cubic footprints, one lane per pixel for linear.
+// MUST be called by all 32 lanes of the warp (lanes without a pixel pass valid = false).
+template <int DIM, bool CUBIC, bool WITH_DERIV, typename R>
+__device__ __forceinline__ void interpolate_any(const SliceGeom& g, const C2<R>* __restrict__ vol,
+                                                const PixelT<R>& px, bool valid, C2<R>& val,
+                                                C2<R>& g_c, C2<R>& g_r, C2<R>& g_d) {
+    // measured on B200: cubic always gains from lane groups; linear gains only in 3D when the
+    // samples are sparse (oversampling >= 1.5, neighbouring pixels 2 voxels apart), otherwise the
+    // shuffles cost more than the saved L1 traffic
+    if (CUBIC || (DIM == 3 && g.sparse_samples)) {          // warp-uniform
+        interpolate_coop<DIM, CUBIC, WITH_DERIV>(g, vol, px, valid, val, g_c, g_r, g_d);
+    } else {
+        val = make2<R>(0.f, 0.f);
+        g_c = g_r = g_d = val;
+        if (valid) interpolate_lane<DIM, CUBIC, WITH_DERIV>(g, vol, px, val, g_c, g_r, g_d);
     }
 }
 

@@ -6,8 +6,8 @@
 //   backproject_forw_kernel  scatter  projections (+weights) -> data / weight volumes
 //   backproject_back_kernel  gather   grad volumes -> grad_proj / grad_weights, + pose grads
 //
-// One block handles one 16x16 tile of one slice (pose p of batch item b); blockIdx.x
-// enumerates (b, p, tile).  No kernel waits on another block, so none can hang.
+// One block handles one 16x16 tile of one slice (pose p of batch item b): blockIdx.x is the
+// tile, (blockIdx.y, blockIdx.z) the slice.  No kernel waits on another block, so none can hang.
 #pragma once
 
 #include "fourier_slice_device.cuh"
@@ -20,15 +20,22 @@ struct BlockWork {
     size_t pix;     // element offset of (b, p, i, j) in a [B, P, N, Nh] tensor
 };
 
+// Grid: x = tile of the slice, (y, z) = slice index b*P + p split as y + 32768*z (so that no
+// integer division is needed to decode a block and any number of slices fits the grid limits).
+constexpr int kGridYBits = 15;
+
 __device__ __forceinline__ BlockWork block_work(const SliceGeom& g) {
     BlockWork w;
-    const int tiles = g.tiles_j * g.tiles_i;
-    const int bp = blockIdx.x / tiles;
-    const int tile = blockIdx.x - bp * tiles;
-    w.b = bp / g.P;
-    w.p = bp - w.b * g.P;
-    tile_pixel(g, tile, w.i, w.j);
-    w.in_image = w.i < g.N && w.j < g.Nh;
+    const int bp = (int)blockIdx.y + ((int)blockIdx.z << kGridYBits);
+    if (g.P_is_all) {            // one batch item: the usual case
+        w.b = 0;
+        w.p = bp;
+    } else {
+        w.b = bp / g.P;
+        w.p = bp - w.b * g.P;
+    }
+    tile_pixel(g, (int)blockIdx.x, w.i, w.j);
+    w.in_image = w.i < g.N && w.j < g.Nh && bp < g.BP;
     w.pix = ((size_t)bp * (size_t)g.N + (size_t)w.i) * (size_t)g.Nh + (size_t)w.j;
     return w;
 }
@@ -54,7 +61,7 @@ project_forw_kernel(const C2<R>* __restrict__ rec, const R* __restrict__ rot,
     const bool valid = w.in_image && pixel_setup<DIM>(g, pose_rot<DIM>(g, rot, w.b, w.p), w.i, w.j, px);
     C2<R> v, gc, gr, gd;
     // all 32 lanes take part: the lanes of a group fetch each other's taps
-    interpolate_coop<DIM, CUBIC, false>(g, rec + (size_t)w.b * g.vol_elems, px, valid, v, gc, gr, gd);
+    interpolate_any<DIM, CUBIC, false>(g, rec + (size_t)w.b * g.vol_elems, px, valid, v, gc, gr, gd);
     if (!w.in_image) return;
     if (valid && g.has_shift) {
         const R* s = pose_shift(g, shifts, w.b, w.p);
@@ -128,7 +135,7 @@ project_back_kernel(const C2<R>* __restrict__ grad_proj, const C2<R>* __restrict
                         !(w.j == 0 && w.i >= g.N / 2);
     C2<R> val = make2<R>(0.f, 0.f), gc = val, gr = val, gd = val;
     if (NEED_ROT || NEED_SHIFT)      // cooperative gather: every lane of the warp takes part
-        interpolate_coop<DIM, CUBIC, NEED_ROT>(g, rec + (size_t)w.b * g.vol_elems, px, active, val, gc, gr, gd);
+        interpolate_any<DIM, CUBIC, NEED_ROT>(g, rec + (size_t)w.b * g.vol_elems, px, active, val, gc, gr, gd);
     C2<R> orig = make2<R>(0.f, 0.f), u = orig, ph = make2<R>(1.f, 0.f);
     if (active) {
         orig = __ldcs(grad_proj + w.pix);
@@ -403,7 +410,7 @@ backproject_back_kernel(const C2<R>* __restrict__ grad_data_rec,
     const bool write_w = grad_weight_rec != nullptr && grad_weights != nullptr;
     C2<R> raw, gc, gr, gd;
     // cooperative gather: every lane of the warp takes part
-    interpolate_coop<DIM, CUBIC, NEED_ROT>(g, grad_data_rec + (size_t)w.b * g.vol_elems, px, active, raw, gc, gr, gd);
+    interpolate_any<DIM, CUBIC, NEED_ROT>(g, grad_data_rec + (size_t)w.b * g.vol_elems, px, active, raw, gc, gr, gd);
     if (active) {
         C2<R> ph = make2<R>(1.f, 0.f);
         C2<R> v = raw;
