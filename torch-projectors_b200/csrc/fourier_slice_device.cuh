@@ -370,29 +370,12 @@ __device__ __forceinline__ void interpolate_coop(const SliceGeom& g, const C2<R>
                 wc = q ? fc : 1.f - fc;
                 dwc = q ? 1.f : -1.f;
             }
-            // interior footprints (all but a shell one voxel thick) need no clamping: the index
-            // of a signed coordinate is the coordinate (negated for a mirrored column), wrapped
-            const bool interior = ar.base >= -g.half + 1 && ar.base + T - 1 <= g.half - 1 &&
-                                  (DIM == 2 || (ad.base >= -g.half + 1 && ad.base + T - 1 <= g.half - 1));
             int rowcol[T], plane[TD];
-            if (interior) {
 #pragma unroll
-                for (int i = 0; i < T; ++i) {
-                    const int r = m ? -(ar.base + i) : ar.base + i;
-                    rowcol[i] = (r < 0 ? r + g.R : r) * g.Rh + col;
-                }
+            for (int i = 0; i < T; ++i) rowcol[i] = gather_line<CUBIC>(g, ar.base + i, m) * g.Rh + col;
 #pragma unroll
-                for (int k = 0; k < TD; ++k) {
-                    const int d = (DIM == 3) ? (m ? -(ad.base + k) : ad.base + k) : 0;
-                    plane[k] = (d < 0 ? d + g.R : d) * plane_stride;
-                }
-            } else {
-#pragma unroll
-                for (int i = 0; i < T; ++i) rowcol[i] = gather_line<CUBIC>(g, ar.base + i, m) * g.Rh + col;
-#pragma unroll
-                for (int k = 0; k < TD; ++k)
-                    plane[k] = (DIM == 3) ? gather_line<CUBIC>(g, ad.base + k, m) * plane_stride : 0;
-            }
+            for (int k = 0; k < TD; ++k)
+                plane[k] = (DIM == 3) ? gather_line<CUBIC>(g, ad.base + k, m) * plane_stride : 0;
 
             C2<R> A = make2<R>(0.f, 0.f), Bq = A, Dq = A;
 #pragma unroll
