@@ -405,7 +405,7 @@ def sharded_backprojection_workload(args):
         torch.cuda.synchronize()
         op_ms += a.elapsed_time(b)
         chunk_ms.append(a.elapsed_time(b))
-        launches += 2
+        launches += 1
         del proj, weights
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     if world > 1:
@@ -747,7 +747,10 @@ def main():
     d2h = h_out.numel() * 8
     e2e = {"value": world * PROJ["P"] / (e2e_ms_per_step * 1e-3), "unit": "slices/s", "ms_per_step": e2e_ms_per_step,
            "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}
-    launches = args.steps + args.warmup + len(e2e_ms) + 3
+    # kernels of this package launched so far: one per device-resident step, one per 1000-pose
+    # chunk in every end-to-end step (warm-ups included)
+    e2e_chunks = (PROJ["P"] + 999) // 1000
+    launches = args.steps + args.warmup + (len(e2e_ms) + 3) * e2e_chunks
     del h_out, out_holder
     torch.cuda.empty_cache()
 
@@ -782,7 +785,7 @@ def main():
                              "peak": peak, "peak_source": peak_kind, "unit": "GB/s", "frac": bach / peak,
                              "traffic": (BACK_TRAFFIC_PER_SLICE * BACK["P"]) if BACK_TRAFFIC_PER_SLICE else None,
                              "algorithmic_bytes_per_launch": BACK_BYTES_PER_SLICE * BACK["P"], "launch_ms": scat}}
-        launches += args.steps + args.warmup
+        launches += (args.steps + args.warmup) * (2 if workspace is not None else 1)     # scatter (+ fold)
         del proj, weights
         torch.cuda.empty_cache()
 

@@ -9,7 +9,8 @@
 //    rounded once, the rotation is separately rounded fp32 multiplies and adds (no FMA),
 //    so floor() and the fractional parts agree bit for bit with the CPU result;
 //  * the phase of the shift ramp is float(double(float(kr*s0 + kc*s1)) * (-2*pi/N))
-//    (csrc/cpu/common/projection_utils.h:82-94) followed by an accurate sincosf;
+//    (csrc/cpu/common/projection_utils.h:82-94), reduced to [-pi, pi] exactly in double and
+//    then evaluated with the hardware sin/cos (fp32) or the library sincos (fp64);
 //  * tap sums are re-associated (separable form); that moves results by ~1e-7 relative.
 #pragma once
 
@@ -51,8 +52,6 @@ __device__ __forceinline__ float mul_rn(float a, float b) { return __fmul_rn(a, 
 __device__ __forceinline__ double mul_rn(double a, double b) { return __dmul_rn(a, b); }
 __device__ __forceinline__ float add_rn(float a, float b) { return __fadd_rn(a, b); }
 __device__ __forceinline__ double add_rn(double a, double b) { return __dadd_rn(a, b); }
-__device__ __forceinline__ void rsincos(float x, float* s, float* c) { sincosf(x, s, c); }
-__device__ __forceinline__ void rsincos(double x, double* s, double* c) { sincos(x, s, c); }
 
 // Kernel parameters shared by the eight operators (passed by value).
 struct SliceGeom {
