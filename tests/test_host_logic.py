@@ -175,3 +175,26 @@ def test_sharding_without_process_group_is_single_rank():
     out = sharding.project_3d_to_2d_sharded(torch.zeros(1, 4, 4, 3, dtype=torch.complex64),
                                             torch.eye(3).expand(1, 5, 3, 3), None, project_fn=project_fn)
     assert out.shape[1] == 5 and calls == [5]
+
+
+# ---- preparation helpers (pure torch, device-agnostic) --------------------------------------
+@pytest.mark.parametrize("dims,n,os", [(3, 8, 2.0), (2, 10, 1.5), (3, 6, 1.0)])
+def test_pad_fftshift_roundtrip_and_layout(dims, n, os):
+    from torch_projectors_b200 import prep
+    torch.manual_seed(0)
+    real = torch.randn((2,) + (n,) * dims)
+    rec = prep.pad_and_fftshift(real, os, dims)
+    m = rec.shape[-2]
+    assert m % 2 == 0 and m >= n and rec.shape[-1] == m // 2 + 1 and rec.is_complex()
+    back = prep.ifftshift_and_crop(rec, m / n, dims)
+    assert back.shape == real.shape and torch.allclose(back, real, atol=1e-5)
+    # origin at index 0: the DC term is the mean of the padded array
+    assert torch.allclose(rec[(slice(None),) + (0,) * dims].real, real.sum(dim=tuple(range(-dims, 0))) / m ** dims, atol=1e-5)
+
+
+def test_normalize_by_weights():
+    from torch_projectors_b200 import prep
+    d = torch.tensor([2.0 + 2j, 1.0 + 0j, 5.0 + 0j])
+    w = torch.tensor([2.0, 0.0, 1e-6])
+    out = prep.normalize_by_weights(d, w, eps=0.5)
+    assert torch.allclose(out, torch.tensor([1.0 + 1j, 2.0 + 0j, 10.0 + 0j]))

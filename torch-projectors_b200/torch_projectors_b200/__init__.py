@@ -26,6 +26,7 @@ from .ops import (  # noqa: E402
 )
 from . import sharding  # noqa: E402
 from . import streaming  # noqa: E402
+from . import prep  # noqa: E402
 from .streaming import backproject_2d_to_3d_from_host, project_3d_to_2d_to_host  # noqa: E402
 
 __version__ = "0.1.0"
@@ -33,6 +34,6 @@ __version__ = "0.1.0"
 __all__ = [
     "project_2d_forw", "project_2d_back", "project_3d_to_2d_forw", "project_3d_to_2d_back",
     "backproject_2d_forw", "backproject_2d_to_3d_forw", "backproject_2d_to_3d_back",
-    "backproject_2d_to_3d_accumulate_", "sharding", "streaming",
+    "backproject_2d_to_3d_accumulate_", "sharding", "streaming", "prep",
     "project_3d_to_2d_to_host", "backproject_2d_to_3d_from_host",
 ]
