@@ -236,6 +236,19 @@ def profile_case(args):
     rec, rot, shifts = make_projection_inputs(dev, seed=1234)
     rot, shifts = rot[:, :P].contiguous(), shifts[:, :P].contiguous()
     kw = dict(interpolation=PROJ["interp"], oversampling=PROJ["os"], fourier_radius_cutoff=PROJ["cutoff"])
+    if args.profile_case == "autograd_step":
+        # box-512 volume (539 MB), 256x256 slices, cubic, all gradients: forward + backward kernels
+        gen = torch.Generator(device=dev).manual_seed(6)
+        rec5 = torch.complex(torch.randn(1, 512, 512, 257, generator=gen, device=dev), torch.randn(1, 512, 512, 257, generator=gen, device=dev))
+        r5 = uniform_rotations(P, torch.Generator().manual_seed(6), dev).requires_grad_(True)
+        s5 = ((torch.rand(1, P, 2, generator=gen, device=dev) * 2 - 1) * 10.0).requires_grad_(True)
+        g5 = torch.complex(torch.randn(1, P, 256, 129, generator=gen, device=dev), torch.randn(1, P, 256, 129, generator=gen, device=dev))
+        for _ in range(2):
+            torch.ops.torch_projectors_b200.project_3d_to_2d_forw(rec5, r5, s5, [256, 256], "cubic", 2.0, None)
+            torch.ops.torch_projectors_b200.project_3d_to_2d_back(g5, rec5, r5, s5, "cubic", 2.0, None)
+        torch.cuda.synchronize()
+        print(f"profile case autograd_step: {P} poses of 256x256 on a box-512 volume, 2 forward + 2 backward launches done")
+        return
     if args.profile_case == "backproject_slab":
         # 256x256 slices into box-512 volumes (808 MB > L2): the slab-ordered kernel
         gen = torch.Generator(device=dev).manual_seed(5)
@@ -643,7 +656,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--skip-cpu", action="store_true", help="omit the CPU-baseline leg")
     ap.add_argument("--skip-backproject", action="store_true")
-    ap.add_argument("--profile-case", choices=["project", "backproject", "project_back", "backproject_slab"], default=None,
+    ap.add_argument("--profile-case", choices=["project", "backproject", "project_back", "backproject_slab", "autograd_step"], default=None,
                     help="run a few launches of one kernel on a reduced pose count (for ncu captures); prints no bench line")
     ap.add_argument("--profile-poses", type=int, default=2048)
     ap.add_argument("--workload", choices=["default", "autograd_step", "sharded_backproject", "ops_table", "reference_cuda", "paper_matrix"], default="default",

@@ -249,8 +249,8 @@ fold_interleaved_kernel(const float4* __restrict__ accum, float2* __restrict__ d
 // taps, which land at -d and exist where c < 0); the runs are computed from linear estimates
 // with a small slack, candidates pass a one-FMA prefilter, and each tap is then tested
 // exactly (scatter_coop<SLAB>), so every tap is written by exactly one slab pass.
-// One block = one slice x one slab; each of its 8 warps owns a contiguous band of rows and
-// prepares 32 rows at a time, one per lane.
+// One block = one slice x one slab; its 8 warps take the rows round-robin and each prepares 32
+// of its rows at a time, one per lane.
 // Restrict the column run [ja, jb] to the columns where a*j + b lies in [lo, hi].
 __device__ __forceinline__ void clip_run(float a, float b, float lo, float hi, float& ja, float& jb) {
     if (fabsf(a) < 1e-6f) {
@@ -290,14 +290,15 @@ backproject_slab_kernel(const float2* __restrict__ proj, const float* __restrict
     float2* data_b = data_rec + (size_t)b * g.vol_elems;
     float* wrec_b = WEIGHTS ? weight_rec + (size_t)b * g.vol_elems : nullptr;
     const float cut = sqrtf(g.cutoff_sq);
+    // rows are dealt to the warps round-robin (row = n * 8 + warp), so that whichever rows a
+    // slab's strip crosses, all warps of the block share them
     const int rows_per_warp = (g.N + kWarps - 1) / kWarps;
-    const int row_end = min(g.N, (warp + 1) * rows_per_warp);
 
-    for (int i0 = warp * rows_per_warp; i0 < row_end; i0 += 32) {
+    for (int n0 = 0; n0 < rows_per_warp; n0 += 32) {
         // each lane prepares one row: its direct and mirrored column runs (empty: a > b)
         int run_a[2] = {1, 1}, run_b[2] = {0, 0};
-        const int irow = i0 + lane;
-        if (irow < row_end) {
+        const int irow = (n0 + lane) * kWarps + warp;
+        if (irow < g.N) {
             const float kr = (float)((irow <= g.N / 2) ? irow : irow - g.N);
             const float room = g.cutoff_sq - kr * kr;
             if (room >= 0.f) {
@@ -354,7 +355,7 @@ backproject_slab_kernel(const float2* __restrict__ proj, const float* __restrict
             const int r_a0 = __shfl_sync(kFull, run_a[0], row), r_a1 = __shfl_sync(kFull, run_a[1], row);
             const int local = k - (r_incl - r_len0 - r_len1);
             const int j = local < r_len0 ? r_a0 + local : r_a1 + (local - r_len0);
-            const int i = i0 + row;
+            const int i = (n0 + row) * kWarps + warp;
             const float kr = (float)((i <= g.N / 2) ? i : i - g.N);
             // one-FMA prefilter with the linear estimates, then the exact test
             const float de = fmaf(ad, (float)j, bd * kr), ce = fmaf(ac, (float)j, bc * kr);
