@@ -165,8 +165,12 @@ def timed_steps(fn, steps, warmup, flush, barrier):
     return [a.elapsed_time(b) for a, b in evs]
 
 
+_CPU_INPUTS = {}
+
+
 def run_cpu_sample(kind_wanted="reference"):
-    """Time the CPU implementation of the projection workload on a bounded sample of poses.
+    """Time the CPU implementation of the projection workload on a bounded sample: as many of
+    the 10,000 poses as take about 10 s, or several passes over all of them on a fast host.
     Returns (slices/s, kind, cores, sample description)."""
     import oracle
     # all host cores this process may use (torch.distributed.run exports OMP_NUM_THREADS=1)
@@ -174,8 +178,9 @@ def run_cpu_sample(kind_wanted="reference"):
         torch.set_num_threads(max(1, len(os.sched_getaffinity(0))))
     except (AttributeError, RuntimeError):
         pass
-    gen = torch.Generator().manual_seed(1)
-    rec, rot, shifts = make_projection_inputs("cpu", seed=1)
+    if "proj" not in _CPU_INPUTS:
+        _CPU_INPUTS["proj"] = make_projection_inputs("cpu", seed=1)
+    rec, rot, shifts = _CPU_INPUTS["proj"]
     if kind_wanted == "reference" and oracle.reference_available():
         ops, kind, cores = oracle.reference_ops(), "reference", torch.get_num_threads()
         f = ops.project_3d_to_2d_forw
@@ -183,7 +188,6 @@ def run_cpu_sample(kind_wanted="reference"):
         from oracle import port
         kind, cores = "port", 1
         f = port.project_3d_to_2d_forw
-    del gen
 
     def run(n):
         t0 = time.perf_counter()
@@ -191,9 +195,14 @@ def run_cpu_sample(kind_wanted="reference"):
         return time.perf_counter() - t0
     probe = 64 if kind == "reference" else 8
     dt = run(probe)                                   # also the warm-up
-    n = int(min(PROJ["P"], max(probe, probe * 12.0 / max(dt, 1e-3))))   # ~12 s of CPU work
+    n = int(min(PROJ["P"], max(probe, probe * 10.0 / max(dt, 1e-3))))   # ~10 s of CPU work
     dt = run(n)
-    return n / dt, kind, cores, f"{n} of the {PROJ['P']} poses of the projection workload, one call, {dt:.1f} s wall"
+    passes = 1
+    while n == PROJ["P"] and dt * passes < 8.0 and passes < 6:          # fast host: more passes
+        dt = (dt * passes + run(n)) / (passes + 1)
+        passes += 1
+    return (n / dt, kind, cores,
+            f"{n} of the {PROJ['P']} poses of the projection workload, {passes} call(s) of {dt:.1f} s wall each")
 
 
 def reference_arm(args):
