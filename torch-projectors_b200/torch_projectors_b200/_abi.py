@@ -97,17 +97,26 @@ def _p(t: Optional[torch.Tensor]) -> int:
     return 0 if t is None else t.data_ptr()
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _call(name: str, anchor: torch.Tensor, *args) -> None:
     """Invoke an entry point (its _f64 variant for double precision tensors) on the current
-    stream of anchor's device."""
+    stream of anchor's device.  This is the per-call hot path of small problems, so it avoids
+    Python-level context managers and stream objects where it can."""
     if anchor.dtype in (torch.complex128, torch.float64):
         name += "_f64"
     if not anchor.is_cuda:
         raise RuntimeError(f"{name}: tensors must be on a CUDA device (there is no CPU path)")
-    lib = load()
-    with torch.cuda.device(anchor.device):
-        stream = torch.cuda.current_stream(anchor.device).cuda_stream
-        rc = getattr(lib, name)(*args, stream)
+    lib = _lib if _lib is not None else load()
+    fn = getattr(lib, name)
+    index = anchor.device.index
+    if torch.cuda.current_device() == index:
+        stream = _raw_stream(index) if _raw_stream is not None else torch.cuda.current_stream(index).cuda_stream
+        rc = fn(*args, stream)
+    else:
+        with torch.cuda.device(index):
+            rc = fn(*args, torch.cuda.current_stream(index).cuda_stream)
     if rc != 0:
         msg = lib.b200proj_last_error().decode("utf-8", "replace")
         raise RuntimeError(f"{name}: {msg} (code {rc})")
