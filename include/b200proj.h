@@ -72,7 +72,25 @@ int b200proj_project_3d_to_2d_forw(const float* rec, int64_t B, int64_t R,
                                    const float* rot, int64_t B_rot,
                                    const float* shifts, int64_t B_shift,
                                    int64_t P, int64_t N, int interpolation, double oversampling,
-                                   double fourier_radius_cutoff, float* out, void* stream);
+                                   double fourier_radius_cutoff, float* out,
+                                   const int32_t* pose_order, void* stream);
+
+/* ---- processing order of the slices (3D operators that read a volume) -------------------
+ * No counterpart in the reference.  The three volume-reading 3D entry points
+ * (project_3d_to_2d_forw, project_3d_to_2d_back, backproject_2d_to_3d_back) take an optional
+ * `pose_order`: int32 [B*P] on the device, a permutation of the slice indices b*P + p; block
+ * k of the launch then handles slice pose_order[k].  Outputs stay where they belong (slice
+ * b*P + p is written at index b*P + p) and their values do not depend on the order; only the
+ * set of slices in flight at one time changes.  NULL = natural order.  An entry outside
+ * [0, B*P) makes its blocks idle (that slice is then never written).
+ * b200proj_pose_order_3d fills such an array from the rotations so that slices with nearby
+ * planes run together; worthwhile once one batch item's volume no longer fits L2 (about
+ * 100 MB), where it turns most DRAM reads of the volume into L2 hits, and harmless below.
+ * rot is [B_rot, P, 3, 3] with B_rot 1 or B, exactly as given to the operator. */
+int b200proj_pose_order_3d(const float* rot, int64_t B, int64_t B_rot, int64_t P,
+                           int32_t* order, void* stream);
+int b200proj_pose_order_3d_f64(const double* rot, int64_t B, int64_t B_rot, int64_t P,
+                               int32_t* order, void* stream);
 
 /* ---- backward of forward projection ----------------------------------------------------
  * grad_rec [B,(R,)R,Rh] is zero-filled here and accumulated with atomics.
@@ -94,7 +112,7 @@ int b200proj_project_3d_to_2d_back(const float* grad_proj, const float* rec, int
                                    int64_t P, int64_t N, int interpolation, double oversampling,
                                    double fourier_radius_cutoff,
                                    float* grad_rec, float* grad_rot, float* grad_shifts,
-                                   void* stream);
+                                   const int32_t* pose_order, void* stream);
 
 /* ---- back-projection (scatter) ---------------------------------------------------------
  * data_rec [B,(R,)R,Rh] complex and, when weights != NULL, weight_rec (same shape, float)
@@ -181,7 +199,7 @@ int b200proj_backproject_2d_to_3d_back(const float* grad_data_rec, const float* 
                                        int64_t P, int64_t N, int interpolation,
                                        double oversampling, double fourier_radius_cutoff,
                                        float* grad_proj, float* grad_weights, float* grad_rot,
-                                       float* grad_shifts, void* stream);
+                                       float* grad_shifts, const int32_t* pose_order, void* stream);
 
 
 /* ---- complex128 / float64 variants ------------------------------------------------------
@@ -201,7 +219,8 @@ int b200proj_project_3d_to_2d_forw_f64(const double* rec, int64_t B, int64_t R,
                                    const double* rot, int64_t B_rot,
                                    const double* shifts, int64_t B_shift,
                                    int64_t P, int64_t N, int interpolation, double oversampling,
-                                   double fourier_radius_cutoff, double* out, void* stream);
+                                   double fourier_radius_cutoff, double* out,
+                                   const int32_t* pose_order, void* stream);
 int b200proj_project_2d_back_f64(const double* grad_proj, const double* rec, int64_t B, int64_t R,
                              const double* rot, int64_t B_rot,
                              const double* shifts, int64_t B_shift,
@@ -214,7 +233,7 @@ int b200proj_project_3d_to_2d_back_f64(const double* grad_proj, const double* re
                                    int64_t P, int64_t N, int interpolation, double oversampling,
                                    double fourier_radius_cutoff,
                                    double* grad_rec, double* grad_rot, double* grad_shifts,
-                                   void* stream);
+                                   const int32_t* pose_order, void* stream);
 int b200proj_backproject_2d_forw_f64(const double* proj, const double* weights, int64_t B, int64_t R,
                                  const double* rot, int64_t B_rot,
                                  const double* shifts, int64_t B_shift,
@@ -244,7 +263,7 @@ int b200proj_backproject_2d_to_3d_back_f64(const double* grad_data_rec, const do
                                        int64_t P, int64_t N, int interpolation,
                                        double oversampling, double fourier_radius_cutoff,
                                        double* grad_proj, double* grad_weights, double* grad_rot,
-                                       double* grad_shifts, void* stream);
+                                       double* grad_shifts, const int32_t* pose_order, void* stream);
 
 #ifdef __cplusplus
 }

@@ -46,7 +46,7 @@ def _forw(lib, **over):
     a.update(over)
     return lib.b200proj_project_3d_to_2d_forw(a["rec"], a["B"], a["R"], a["rot"], a["B_rot"], a["shifts"],
                                               a["B_shift"], a["P"], a["N"], a["interp"], a["os"],
-                                              a["cutoff"], a["out"], a["stream"])
+                                              a["cutoff"], a["out"], 0, a["stream"])
 
 
 @pytest.mark.parametrize("over,fragment", [
@@ -75,6 +75,13 @@ def test_backprojection_checks_volume_size_rule():
     assert "does not match" in lib.b200proj_last_error().decode()
     rc = lib.b200proj_backproject_2d_to_3d_forw(1, 1, 1, 16, 1, 1, 0, 0, 1, 8, 0, 2.0, 4.0, 1, 0, 0, 0, 0, 0)
     assert rc == -1 and "given together" in lib.b200proj_last_error().decode()
+
+
+def test_pose_order_argument_errors_need_no_gpu():
+    lib = _abi.load()
+    assert lib.b200proj_pose_order_3d(0, 1, 1, 4, 1, 0) == -1 and "NULL" in lib.b200proj_last_error().decode()
+    assert lib.b200proj_pose_order_3d(1, 2, 3, 4, 1, 0) == -1 and "rotations must be 1 or same" in lib.b200proj_last_error().decode()
+    assert lib.b200proj_pose_order_3d(1, 1, 1, 0, 1, 0) == 0      # no poses: nothing to do
 
 
 def test_workspace_query_needs_no_gpu():

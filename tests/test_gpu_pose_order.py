@@ -1,0 +1,92 @@
+"""The optional processing order of the slices (3D operators that read a volume): the order
+the library derives from the rotations is a permutation that keeps neighbouring planes
+together, and results do not depend on the order at all."""
+import pytest
+import torch
+
+from cases import TOL_ATOMIC, random_rotations_3d, rel_err
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def tp(cuda_device):
+    import torch_projectors_b200
+    return torch_projectors_b200
+
+
+def _normals(rot):
+    n = rot[..., :, 2]
+    return torch.where(n[..., 2:3] < 0, -n, n)
+
+
+@pytest.mark.parametrize("B,B_rot,dtype", [(1, 1, torch.float32), (3, 3, torch.float32), (3, 1, torch.float32),
+                                           (2, 2, torch.float64)])
+def test_order_is_a_permutation_per_batch_item_and_groups_nearby_planes(tp, B, B_rot, dtype):
+    P = 3000
+    gen = torch.Generator().manual_seed(5)
+    rot = random_rotations_3d(B_rot * P, gen).reshape(B_rot, P, 3, 3).to("cuda", dtype)
+    order = torch.full((B * P,), -7, dtype=torch.int32, device="cuda")
+    tp._abi.pose_order_3d(rot, B, P, order)
+    order = order.cpu().long().reshape(B, P)
+    for b in range(B):
+        assert torch.equal(order[b].sort().values, torch.arange(b * P, (b + 1) * P))
+        n = _normals(rot[b if B_rot > 1 else 0].float().cpu())
+        walk = n[order[b] - b * P]
+        # |cos| of the angle between the planes of consecutive slices: ~0.5 on average for random
+        # order, close to 1 when neighbours in the order are neighbours on the sphere
+        near = (walk[1:] * walk[:-1]).sum(-1).abs().mean().item()
+        rand = (n[1:] * n[:-1]).sum(-1).abs().mean().item()
+        assert near > 0.97 and rand < 0.6, (near, rand)
+
+
+@pytest.mark.parametrize("interp", ["linear", "cubic"])
+def test_results_do_not_depend_on_the_processing_order(tp, interp, monkeypatch):
+    from torch_projectors_b200 import ops
+    B, P, N, R = 2, 70, 16, 32
+    gen = torch.Generator().manual_seed(11)
+    rec = torch.randn(B, R, R, R // 2 + 1, dtype=torch.complex64, generator=gen).cuda()
+    rot = random_rotations_3d(B * P, gen).reshape(B, P, 3, 3).cuda()
+    sh = ((torch.rand(B, P, 2, generator=gen) * 2 - 1) * 3).cuda()
+    gp = torch.randn(B, P, N, N // 2 + 1, dtype=torch.complex64, generator=gen).cuda()
+    gw = torch.randn(B, R, R, R // 2 + 1, generator=gen).cuda()
+    wts = torch.rand(B, P, N, N // 2 + 1, generator=gen).cuda()
+    t = torch.ops.torch_projectors_b200
+
+    def run():
+        r = rot.clone().requires_grad_(True)
+        s = sh.clone().requires_grad_(True)
+        return (t.project_3d_to_2d_forw(rec, r, s, [N, N], interp, 2.0, None),
+                *t.project_3d_to_2d_back(gp, rec, r, s, interp, 2.0, None),
+                *t.backproject_2d_to_3d_back(rec, gw, gp, wts, r, s, interp, 2.0, None))
+
+    monkeypatch.setattr(ops, "POSE_ORDER_MIN_BYTES", 1 << 60)
+    natural = run()
+    monkeypatch.setattr(ops, "POSE_ORDER_MIN_BYTES", 0)
+    monkeypatch.setattr(ops, "POSE_ORDER_MIN_POSES", 1)
+    seen = []
+    real = tp._abi.pose_order_3d
+    monkeypatch.setattr(tp._abi, "pose_order_3d", lambda *a: (seen.append(1), real(*a))[1])
+    ordered = run()
+    assert len(seen) == 3                     # all three operators took the ordered path
+    # gathers write each slice on its own: bit-identical; atomically accumulated outputs agree
+    # to rounding (their summation order is not fixed in either run)
+    for k in (0, 4, 5):                       # projections, grad_projections, grad_weights
+        assert torch.equal(natural[k], ordered[k]), k
+    for k in (1, 2, 3, 6, 7):
+        assert rel_err(ordered[k], natural[k]) < TOL_ATOMIC * 0.1, k
+
+
+def test_entries_outside_the_range_leave_their_slice_unwritten(tp):
+    P, N, R = 6, 8, 16
+    gen = torch.Generator().manual_seed(3)
+    rec = torch.randn(1, R, R, R // 2 + 1, dtype=torch.complex64, generator=gen).cuda()
+    rot = random_rotations_3d(P, gen).reshape(1, P, 3, 3).cuda()
+    want = torch.ops.torch_projectors_b200.project_3d_to_2d_forw(rec, rot, None, [N, N], "linear", 2.0, None)
+    out = torch.full_like(want, 123.0)
+    order = torch.tensor([5, 4, -1, 2, 1000, 0], dtype=torch.int32, device="cuda")
+    tp._abi.project_forw(3, rec, rot, None, P, N, tp._abi.LINEAR, 2.0, N / 2.0, out, order)
+    for p in (5, 4, 2, 0):
+        assert torch.equal(out[0, p], want[0, p])
+    for p in (1, 3):
+        assert (out[0, p] == 123.0).all()

@@ -79,6 +79,7 @@ int prepare(Launch& L, int dim, int64_t B, int64_t R, int64_t B_rot, const void*
     g.phase_scale = -2.0 * M_PI / (double)(float)N;
     g.shift_scale = -2.0 * M_PI / (double)N;
     g.vol_elems = vol;
+    g.order = nullptr;
 
     if (B * P > INT_MAX / 2) return fail(B200PROJ_ERR_LIMIT, "B*P = %lld slices exceed the grid limit; split the poses into chunks", (long long)(B * P));
     g.BP = (int)(B * P);
@@ -127,10 +128,11 @@ SlabPlan slab_plan(int64_t R, bool has_weights) {
 template <int DIM, typename Real>
 int project_forw(const Real* rec, int64_t B, int64_t R, const Real* rot, int64_t B_rot,
                  const Real* shifts, int64_t B_shift, int64_t P, int64_t N, int interpolation,
-                 double os, double cutoff, Real* out, void* stream) {
+                 double os, double cutoff, Real* out, const int32_t* pose_order, void* stream) {
     Launch L;
     if (int rc = prepare(L, DIM, B, R, B_rot, rot, shifts, B_shift, P, N, interpolation, os, cutoff)) return rc;
     if (rec == nullptr || out == nullptr) return fail(B200PROJ_ERR_ARGUMENT, "reconstruction / output pointer is NULL");
+    L.g.order = pose_order;
     if (P == 0) return B200PROJ_OK;
     cudaStream_t s = (cudaStream_t)stream;
     const C2<Real>* v = (const C2<Real>*)rec;
@@ -160,9 +162,10 @@ template <int DIM, typename Real>
 int project_back(const Real* grad_proj, const Real* rec, int64_t B, int64_t R, const Real* rot,
                  int64_t B_rot, const Real* shifts, int64_t B_shift, int64_t P, int64_t N,
                  int interpolation, double os, double cutoff, Real* grad_rec, Real* grad_rot,
-                 Real* grad_shifts, void* stream) {
+                 Real* grad_shifts, const int32_t* pose_order, void* stream) {
     Launch L;
     if (int rc = prepare(L, DIM, B, R, B_rot, rot, shifts, B_shift, P, N, interpolation, os, cutoff)) return rc;
+    L.g.order = pose_order;
     if (grad_proj == nullptr || rec == nullptr || grad_rec == nullptr)
         return fail(B200PROJ_ERR_ARGUMENT, "grad_projections / reconstruction / grad_reconstruction pointer is NULL");
     if (grad_shifts != nullptr && shifts == nullptr)
@@ -266,9 +269,10 @@ int backproject_back(const Real* grad_data_rec, const Real* grad_weight_rec, con
                      int64_t B, int64_t R, const Real* rot, int64_t B_rot, const Real* shifts,
                      int64_t B_shift, int64_t P, int64_t N, int interpolation, double os,
                      double cutoff, Real* grad_proj, Real* grad_weights, Real* grad_rot,
-                     Real* grad_shifts, void* stream) {
+                     Real* grad_shifts, const int32_t* pose_order, void* stream) {
     Launch L;
     if (int rc = prepare(L, DIM, B, R, B_rot, rot, shifts, B_shift, P, N, interpolation, os, cutoff)) return rc;
+    L.g.order = pose_order;
     if (grad_data_rec == nullptr || grad_proj == nullptr)
         return fail(B200PROJ_ERR_ARGUMENT, "grad_data_rec / grad_projections pointer is NULL");
     if ((grad_rot != nullptr || grad_shifts != nullptr) && proj == nullptr)
@@ -291,6 +295,17 @@ int backproject_back(const Real* grad_data_rec, const Real* grad_weight_rec, con
     return check_launch("backproject_back launch");
 }
 
+template <typename Real>
+int pose_order_3d(const Real* rot, int64_t B, int64_t B_rot, int64_t P, int32_t* order, void* stream) {
+    g_error[0] = 0;
+    if (rot == nullptr || order == nullptr) return fail(B200PROJ_ERR_ARGUMENT, "rotations / order pointer is NULL");
+    if (B < 1 || P < 0) return fail(B200PROJ_ERR_ARGUMENT, "batch size must be >= 1 and pose count >= 0 (B=%lld, P=%lld)", (long long)B, (long long)P);
+    if (B_rot != 1 && B_rot != B) return fail(B200PROJ_ERR_ARGUMENT, "Batch size of rotations must be 1 or same as reconstruction (B_rot=%lld, B=%lld)", (long long)B_rot, (long long)B);
+    if (B * P > INT_MAX / 2 || B > 65535 * 32768ll) return fail(B200PROJ_ERR_LIMIT, "B*P = %lld slices exceed the grid limit; split the poses into chunks", (long long)(B * P));
+    if (P == 0) return B200PROJ_OK;
+    pose_order_kernel<<<(unsigned)B, kOrderBins, 0, (cudaStream_t)stream>>>(rot, B_rot == 1 ? 0ll : (long long)P * 9, (int)P, order);
+    return check_launch("pose_order launch");
+}
 
 // ---- built-in scratch of the allocation-free back-projection entry point -----------------
 // The array lives in every GPU context that loads this library, from load until exit.
@@ -350,13 +365,13 @@ int b200proj_project_2d_forw(const float* rec, int64_t B, int64_t R, const float
                              const float* shifts, int64_t B_shift, int64_t P, int64_t N,
                              int interpolation, double oversampling, double cutoff, float* out,
                              void* stream) {
-    return project_forw<2>(rec, B, R, rot, B_rot, shifts, B_shift, P, N, interpolation, oversampling, cutoff, out, stream);
+    return project_forw<2>(rec, B, R, rot, B_rot, shifts, B_shift, P, N, interpolation, oversampling, cutoff, out, nullptr, stream);
 }
 int b200proj_project_3d_to_2d_forw(const float* rec, int64_t B, int64_t R, const float* rot,
                                    int64_t B_rot, const float* shifts, int64_t B_shift, int64_t P,
                                    int64_t N, int interpolation, double oversampling, double cutoff,
-                                   float* out, void* stream) {
-    return project_forw<3>(rec, B, R, rot, B_rot, shifts, B_shift, P, N, interpolation, oversampling, cutoff, out, stream);
+                                   float* out, const int32_t* pose_order, void* stream) {
+    return project_forw<3>(rec, B, R, rot, B_rot, shifts, B_shift, P, N, interpolation, oversampling, cutoff, out, pose_order, stream);
 }
 
 int b200proj_project_2d_back(const float* grad_proj, const float* rec, int64_t B, int64_t R,
@@ -364,14 +379,15 @@ int b200proj_project_2d_back(const float* grad_proj, const float* rec, int64_t B
                              int64_t P, int64_t N, int interpolation, double oversampling,
                              double cutoff, float* grad_rec, float* grad_rot, float* grad_shifts,
                              void* stream) {
-    return project_back<2>(grad_proj, rec, B, R, rot, B_rot, shifts, B_shift, P, N, interpolation, oversampling, cutoff, grad_rec, grad_rot, grad_shifts, stream);
+    return project_back<2>(grad_proj, rec, B, R, rot, B_rot, shifts, B_shift, P, N, interpolation, oversampling, cutoff, grad_rec, grad_rot, grad_shifts, nullptr, stream);
 }
 int b200proj_project_3d_to_2d_back(const float* grad_proj, const float* rec, int64_t B, int64_t R,
                                    const float* rot, int64_t B_rot, const float* shifts,
                                    int64_t B_shift, int64_t P, int64_t N, int interpolation,
                                    double oversampling, double cutoff, float* grad_rec,
-                                   float* grad_rot, float* grad_shifts, void* stream) {
-    return project_back<3>(grad_proj, rec, B, R, rot, B_rot, shifts, B_shift, P, N, interpolation, oversampling, cutoff, grad_rec, grad_rot, grad_shifts, stream);
+                                   float* grad_rot, float* grad_shifts, const int32_t* pose_order,
+                                   void* stream) {
+    return project_back<3>(grad_proj, rec, B, R, rot, B_rot, shifts, B_shift, P, N, interpolation, oversampling, cutoff, grad_rec, grad_rot, grad_shifts, pose_order, stream);
 }
 
 int b200proj_backproject_2d_forw(const float* proj, const float* weights, int64_t B, int64_t R,
@@ -395,7 +411,7 @@ int b200proj_backproject_2d_back(const float* grad_data_rec, const float* grad_w
                                  int64_t N, int interpolation, double oversampling, double cutoff,
                                  float* grad_proj, float* grad_weights, float* grad_rot,
                                  float* grad_shifts, void* stream) {
-    return backproject_back<2>(grad_data_rec, grad_weight_rec, proj, B, R, rot, B_rot, shifts, B_shift, P, N, interpolation, oversampling, cutoff, grad_proj, grad_weights, grad_rot, grad_shifts, stream);
+    return backproject_back<2>(grad_data_rec, grad_weight_rec, proj, B, R, rot, B_rot, shifts, B_shift, P, N, interpolation, oversampling, cutoff, grad_proj, grad_weights, grad_rot, grad_shifts, nullptr, stream);
 }
 int b200proj_backproject_2d_to_3d_back(const float* grad_data_rec, const float* grad_weight_rec,
                                        const float* proj, int64_t B, int64_t R, const float* rot,
@@ -403,8 +419,8 @@ int b200proj_backproject_2d_to_3d_back(const float* grad_data_rec, const float* 
                                        int64_t P, int64_t N, int interpolation,
                                        double oversampling, double cutoff, float* grad_proj,
                                        float* grad_weights, float* grad_rot, float* grad_shifts,
-                                       void* stream) {
-    return backproject_back<3>(grad_data_rec, grad_weight_rec, proj, B, R, rot, B_rot, shifts, B_shift, P, N, interpolation, oversampling, cutoff, grad_proj, grad_weights, grad_rot, grad_shifts, stream);
+                                       const int32_t* pose_order, void* stream) {
+    return backproject_back<3>(grad_data_rec, grad_weight_rec, proj, B, R, rot, B_rot, shifts, B_shift, P, N, interpolation, oversampling, cutoff, grad_proj, grad_weights, grad_rot, grad_shifts, pose_order, stream);
 }
 
 // ---- complex128 / float64 variants (same kernels instantiated for double) ----------------
@@ -412,13 +428,13 @@ int b200proj_project_2d_forw_f64(const double* rec, int64_t B, int64_t R, const 
                              const double* shifts, int64_t B_shift, int64_t P, int64_t N,
                              int interpolation, double oversampling, double cutoff, double* out,
                              void* stream) {
-    return project_forw<2>(rec, B, R, rot, B_rot, shifts, B_shift, P, N, interpolation, oversampling, cutoff, out, stream);
+    return project_forw<2>(rec, B, R, rot, B_rot, shifts, B_shift, P, N, interpolation, oversampling, cutoff, out, nullptr, stream);
 }
 int b200proj_project_3d_to_2d_forw_f64(const double* rec, int64_t B, int64_t R, const double* rot,
                                    int64_t B_rot, const double* shifts, int64_t B_shift, int64_t P,
                                    int64_t N, int interpolation, double oversampling, double cutoff,
-                                   double* out, void* stream) {
-    return project_forw<3>(rec, B, R, rot, B_rot, shifts, B_shift, P, N, interpolation, oversampling, cutoff, out, stream);
+                                   double* out, const int32_t* pose_order, void* stream) {
+    return project_forw<3>(rec, B, R, rot, B_rot, shifts, B_shift, P, N, interpolation, oversampling, cutoff, out, pose_order, stream);
 }
 
 int b200proj_project_2d_back_f64(const double* grad_proj, const double* rec, int64_t B, int64_t R,
@@ -426,14 +442,15 @@ int b200proj_project_2d_back_f64(const double* grad_proj, const double* rec, int
                              int64_t P, int64_t N, int interpolation, double oversampling,
                              double cutoff, double* grad_rec, double* grad_rot, double* grad_shifts,
                              void* stream) {
-    return project_back<2>(grad_proj, rec, B, R, rot, B_rot, shifts, B_shift, P, N, interpolation, oversampling, cutoff, grad_rec, grad_rot, grad_shifts, stream);
+    return project_back<2>(grad_proj, rec, B, R, rot, B_rot, shifts, B_shift, P, N, interpolation, oversampling, cutoff, grad_rec, grad_rot, grad_shifts, nullptr, stream);
 }
 int b200proj_project_3d_to_2d_back_f64(const double* grad_proj, const double* rec, int64_t B, int64_t R,
                                    const double* rot, int64_t B_rot, const double* shifts,
                                    int64_t B_shift, int64_t P, int64_t N, int interpolation,
                                    double oversampling, double cutoff, double* grad_rec,
-                                   double* grad_rot, double* grad_shifts, void* stream) {
-    return project_back<3>(grad_proj, rec, B, R, rot, B_rot, shifts, B_shift, P, N, interpolation, oversampling, cutoff, grad_rec, grad_rot, grad_shifts, stream);
+                                   double* grad_rot, double* grad_shifts, const int32_t* pose_order,
+                                   void* stream) {
+    return project_back<3>(grad_proj, rec, B, R, rot, B_rot, shifts, B_shift, P, N, interpolation, oversampling, cutoff, grad_rec, grad_rot, grad_shifts, pose_order, stream);
 }
 
 int b200proj_backproject_2d_forw_f64(const double* proj, const double* weights, int64_t B, int64_t R,
@@ -457,7 +474,7 @@ int b200proj_backproject_2d_back_f64(const double* grad_data_rec, const double* 
                                  int64_t N, int interpolation, double oversampling, double cutoff,
                                  double* grad_proj, double* grad_weights, double* grad_rot,
                                  double* grad_shifts, void* stream) {
-    return backproject_back<2>(grad_data_rec, grad_weight_rec, proj, B, R, rot, B_rot, shifts, B_shift, P, N, interpolation, oversampling, cutoff, grad_proj, grad_weights, grad_rot, grad_shifts, stream);
+    return backproject_back<2>(grad_data_rec, grad_weight_rec, proj, B, R, rot, B_rot, shifts, B_shift, P, N, interpolation, oversampling, cutoff, grad_proj, grad_weights, grad_rot, grad_shifts, nullptr, stream);
 }
 int b200proj_backproject_2d_to_3d_back_f64(const double* grad_data_rec, const double* grad_weight_rec,
                                        const double* proj, int64_t B, int64_t R, const double* rot,
@@ -465,8 +482,15 @@ int b200proj_backproject_2d_to_3d_back_f64(const double* grad_data_rec, const do
                                        int64_t P, int64_t N, int interpolation,
                                        double oversampling, double cutoff, double* grad_proj,
                                        double* grad_weights, double* grad_rot, double* grad_shifts,
-                                       void* stream) {
-    return backproject_back<3>(grad_data_rec, grad_weight_rec, proj, B, R, rot, B_rot, shifts, B_shift, P, N, interpolation, oversampling, cutoff, grad_proj, grad_weights, grad_rot, grad_shifts, stream);
+                                       const int32_t* pose_order, void* stream) {
+    return backproject_back<3>(grad_data_rec, grad_weight_rec, proj, B, R, rot, B_rot, shifts, B_shift, P, N, interpolation, oversampling, cutoff, grad_proj, grad_weights, grad_rot, grad_shifts, pose_order, stream);
+}
+
+int b200proj_pose_order_3d(const float* rot, int64_t B, int64_t B_rot, int64_t P, int32_t* order, void* stream) {
+    return pose_order_3d(rot, B, B_rot, P, order, stream);
+}
+int b200proj_pose_order_3d_f64(const double* rot, int64_t B, int64_t B_rot, int64_t P, int32_t* order, void* stream) {
+    return pose_order_3d(rot, B, B_rot, P, order, stream);
 }
 
 int b200proj_backproject_2d_to_3d_forw_noalloc(const float* proj, const float* weights, int64_t B,

@@ -72,6 +72,8 @@ struct SliceGeom {
     double phase_scale;     // -2*pi / float(N)
     double shift_scale;     // -2*pi / N   (d phase / d shift per unit frequency)
     long long vol_elems;    // voxels per batch item
+    const int* order;       // optional processing order: block k handles slice order[k] (a permutation of
+                            // [0, BP)); nullptr = natural order.  Changes which blocks run together, not results.
 };
 
 template <typename R>

@@ -26,7 +26,11 @@ constexpr int kGridYBits = 15;
 
 __device__ __forceinline__ BlockWork block_work(const SliceGeom& g) {
     BlockWork w;
-    const int bp = (int)blockIdx.y + ((int)blockIdx.z << kGridYBits);
+    int bp = (int)blockIdx.y + ((int)blockIdx.z << kGridYBits);
+    // an entry outside [0, BP) (a malformed order) makes the block idle instead of reading out of bounds
+    if (g.order != nullptr && bp < g.BP) bp = __ldg(g.order + bp);
+    const bool slice_ok = (unsigned)bp < (unsigned)g.BP;
+    if (!slice_ok) bp = 0;
     if (g.P_is_all) {            // one batch item: the usual case
         w.b = 0;
         w.p = bp;
@@ -35,7 +39,7 @@ __device__ __forceinline__ BlockWork block_work(const SliceGeom& g) {
         w.p = bp - w.b * g.P;
     }
     tile_pixel(g, (int)blockIdx.x, w.i, w.j);
-    w.in_image = w.i < g.N && w.j < g.Nh && bp < g.BP;
+    w.in_image = w.i < g.N && w.j < g.Nh && slice_ok;
     w.pix = ((size_t)bp * (size_t)g.N + (size_t)w.i) * (size_t)g.Nh + (size_t)w.j;
     return w;
 }
@@ -434,6 +438,75 @@ backproject_back_kernel(const C2<R>* __restrict__ grad_data_rec,
         if (write_w) __stcs(grad_weights + w.pix, 0.f);
     }
     if (NEED_ROT || NEED_SHIFT) pose_grad_flush<DIM>(g, acc, grad_rot, grad_shift, w.b, w.p);
+}
+
+// ---- processing order of the slices of a 3D operator --------------------------------------
+// Slices whose planes lie close together read (nearly) the same voxels.  When the volume is
+// larger than L2, running them one after the other turns most of those reads into L2 hits,
+// which random pose order does not.  The key is the slice normal (third column of the
+// rotation matrix, flipped into the upper hemisphere: n and -n span the same plane), mapped
+// to the unit disc by an equal-area projection and quantised to a 32 x 32 grid walked in
+// Morton order.  One block per batch item counting-sorts its P poses by that key: a histogram
+// in shared memory, an exclusive scan, then each pose takes the next free place of its bin.
+// The order inside a bin depends on thread timing; results of the operators do not depend on
+// the processing order at all.
+constexpr int kOrderBits = 5;
+constexpr int kOrderBins = 1 << (2 * kOrderBits);
+
+template <typename R>
+__device__ __forceinline__ int pose_order_key(const R* __restrict__ rm) {
+    float nx = (float)__ldg(rm + 2), ny = (float)__ldg(rm + 5), nz = (float)__ldg(rm + 8);
+    if (nz < 0.f) { nx = -nx; ny = -ny; nz = -nz; }
+    const float s = rsqrtf(fmaxf(1.f + nz, 1e-6f));          // |(nx, ny)| * s <= 1 on the hemisphere
+    const float q = (float)(1 << kOrderBits);
+    // min/max also send a NaN to a valid cell
+    const int x = (int)fminf(fmaxf((nx * s * 0.5f + 0.5f) * q, 0.f), q - 1.f);
+    const int y = (int)fminf(fmaxf((ny * s * 0.5f + 0.5f) * q, 0.f), q - 1.f);
+    int key = 0;
+#pragma unroll
+    for (int k = 0; k < kOrderBits; ++k) key |= ((x >> k) & 1) << (2 * k) | ((y >> k) & 1) << (2 * k + 1);
+    return key;
+}
+
+template <typename R>
+__global__ void __launch_bounds__(kOrderBins)
+pose_order_kernel(const R* __restrict__ rot, long long rot_stride_b, int P, int* __restrict__ order) {
+    __shared__ int bins[kOrderBins];
+    __shared__ int warp_sum[kOrderBins / 32];
+    const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+    const R* rm = rot + (size_t)blockIdx.x * (size_t)rot_stride_b;
+    const int base = (int)blockIdx.x * P;
+    bins[t] = 0;
+    __syncthreads();
+    for (int p = t; p < P; p += kOrderBins) atomicAdd(&bins[pose_order_key(rm + (size_t)p * 9)], 1);
+    __syncthreads();
+    // exclusive scan of the 1024 counts: inside each warp, then over the 32 warp totals
+    const int count = bins[t];
+    int incl = count;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        const int up = __shfl_up_sync(0xffffffffu, incl, d);
+        if (lane >= d) incl += up;
+    }
+    if (lane == 31) warp_sum[warp] = incl;
+    __syncthreads();
+    if (warp == 0) {
+        const int total = warp_sum[lane];
+        int w = total;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const int up = __shfl_up_sync(0xffffffffu, w, d);
+            if (lane >= d) w += up;
+        }
+        warp_sum[lane] = w - total;
+    }
+    __syncthreads();
+    bins[t] = warp_sum[warp] + incl - count;
+    __syncthreads();
+    for (int p = t; p < P; p += kOrderBins) {
+        const int pos = atomicAdd(&bins[pose_order_key(rm + (size_t)p * 9)], 1);
+        order[base + pos] = base + p;
+    }
 }
 
 }  // namespace b200proj

@@ -25,14 +25,15 @@ _i64, _dbl, _int, _ptr = C.c_int64, C.c_double, C.c_int, C.c_void_p
 _COMMON = [_i64, _i64, _ptr, _i64, _ptr, _i64, _i64, _i64, _int, _dbl, _dbl]  # B,R,rot,B_rot,shifts,B_shift,P,N,interp,os,cutoff
 SIGNATURES = {
     "b200proj_project_2d_forw": [_ptr] + _COMMON + [_ptr, _ptr],
-    "b200proj_project_3d_to_2d_forw": [_ptr] + _COMMON + [_ptr, _ptr],
+    "b200proj_project_3d_to_2d_forw": [_ptr] + _COMMON + [_ptr, _ptr, _ptr],
     "b200proj_project_2d_back": [_ptr, _ptr] + _COMMON + [_ptr, _ptr, _ptr, _ptr],
-    "b200proj_project_3d_to_2d_back": [_ptr, _ptr] + _COMMON + [_ptr, _ptr, _ptr, _ptr],
+    "b200proj_project_3d_to_2d_back": [_ptr, _ptr] + _COMMON + [_ptr, _ptr, _ptr, _ptr, _ptr],
     "b200proj_backproject_2d_forw": [_ptr, _ptr] + _COMMON + [_ptr, _ptr, _int, _ptr, C.c_size_t, _ptr],
     "b200proj_backproject_2d_to_3d_forw": [_ptr, _ptr] + _COMMON + [_ptr, _ptr, _int, _ptr, C.c_size_t, _ptr],
     "b200proj_backproject_2d_to_3d_forw_noalloc": [_ptr, _ptr] + _COMMON + [_ptr, _ptr, _int, _ptr],
     "b200proj_backproject_2d_back": [_ptr, _ptr, _ptr] + _COMMON + [_ptr, _ptr, _ptr, _ptr, _ptr],
-    "b200proj_backproject_2d_to_3d_back": [_ptr, _ptr, _ptr] + _COMMON + [_ptr, _ptr, _ptr, _ptr, _ptr],
+    "b200proj_backproject_2d_to_3d_back": [_ptr, _ptr, _ptr] + _COMMON + [_ptr, _ptr, _ptr, _ptr, _ptr, _ptr],
+    "b200proj_pose_order_3d": [_ptr, _i64, _i64, _i64, _ptr, _ptr],
 }
 # complex128 / float64 variants: same argument lists (pointers are void* here)
 SIGNATURES.update({name + "_f64": sig for name, sig in list(SIGNATURES.items()) if not name.endswith("_noalloc")})
@@ -128,18 +129,30 @@ def _geom(B, R, rot, shifts, P, N, interp, oversampling, cutoff):
             float(oversampling), float(cutoff))
 
 
-def project_forw(dim, rec, rot, shifts, P, N, interp, oversampling, cutoff, out):
+def pose_order_3d(rot, B, P, order):
+    """Fill order (int32 [B*P], CUDA) with a processing order of the slices that keeps slices
+    with nearby planes together (b200proj_pose_order_3d)."""
+    _call("b200proj_pose_order_3d", rot, _p(rot), int(B), int(rot.shape[0]), int(P), _p(order))
+
+
+def _order_arg(dim, order):
+    """Trailing pose_order argument: the 3D entry points take it, the 2D ones do not."""
+    return (_p(order),) if dim == 3 else ()
+
+
+def project_forw(dim, rec, rot, shifts, P, N, interp, oversampling, cutoff, out, order=None):
     name = "b200proj_project_2d_forw" if dim == 2 else "b200proj_project_3d_to_2d_forw"
     B, R = rec.shape[0], rec.shape[-2]
-    _call(name, rec, _p(rec), *_geom(B, R, rot, shifts, P, N, interp, oversampling, cutoff), _p(out))
+    _call(name, rec, _p(rec), *_geom(B, R, rot, shifts, P, N, interp, oversampling, cutoff), _p(out),
+          *_order_arg(dim, order))
 
 
 def project_back(dim, grad_proj, rec, rot, shifts, P, N, interp, oversampling, cutoff,
-                 grad_rec, grad_rot, grad_shifts):
+                 grad_rec, grad_rot, grad_shifts, order=None):
     name = "b200proj_project_2d_back" if dim == 2 else "b200proj_project_3d_to_2d_back"
     B, R = rec.shape[0], rec.shape[-2]
     _call(name, rec, _p(grad_proj), _p(rec), *_geom(B, R, rot, shifts, P, N, interp, oversampling, cutoff),
-          _p(grad_rec), _p(grad_rot), _p(grad_shifts))
+          _p(grad_rec), _p(grad_rot), _p(grad_shifts), *_order_arg(dim, order))
 
 
 def backproject_forw(dim, proj, weights, rot, shifts, interp, oversampling, cutoff,
@@ -169,10 +182,10 @@ def backproject_2d_to_3d_forw_noalloc(proj, weights, rot, shifts, interp, oversa
 
 
 def backproject_back(dim, grad_data_rec, grad_weight_rec, proj, rot, shifts, interp, oversampling,
-                     cutoff, grad_proj, grad_weights, grad_rot, grad_shifts):
+                     cutoff, grad_proj, grad_weights, grad_rot, grad_shifts, order=None):
     name = "b200proj_backproject_2d_back" if dim == 2 else "b200proj_backproject_2d_to_3d_back"
     B, P, N = proj.shape[0], proj.shape[1], proj.shape[2]
     R = grad_data_rec.shape[-2]
     _call(name, proj, _p(grad_data_rec), _p(grad_weight_rec), _p(proj),
           *_geom(B, R, rot, shifts, P, N, interp, oversampling, cutoff),
-          _p(grad_proj), _p(grad_weights), _p(grad_rot), _p(grad_shifts))
+          _p(grad_proj), _p(grad_weights), _p(grad_rot), _p(grad_shifts), *_order_arg(dim, order))

@@ -99,6 +99,25 @@ def _backproject_workspace(dim, B, R, P, N, interp, weights, device):
     return torch.empty(n, dtype=torch.uint8, device=device) if n else None
 
 
+# Volumes (one batch item) at least this large get a locality-preserving processing order of
+# their slices; below it the whole volume stays in the 126 MB L2 and the order changes nothing.
+POSE_ORDER_MIN_BYTES = 96 << 20
+POSE_ORDER_MIN_POSES = 64
+
+
+def _pose_order(dim, vol: torch.Tensor, B: int, P: int, rot: torch.Tensor):
+    """int32 [B*P] processing order for the volume-reading 3D operators (slices with nearby
+    planes run together, so that a volume larger than L2 is read from DRAM far less often), or
+    None when it would not pay.  Outputs do not depend on it."""
+    if dim != 3 or P < POSE_ORDER_MIN_POSES:
+        return None
+    if vol[0].numel() * vol.element_size() < POSE_ORDER_MIN_BYTES:
+        return None
+    order = torch.empty(B * P, dtype=torch.int32, device=rot.device)
+    _abi.pose_order_3d(rot, B, P, order)
+    return order
+
+
 def _cutoff(fourier_radius_cutoff: Optional[float], N: int) -> float:
     # default: Nyquist radius of the projection (reference: projection_3d_to_2d_kernels.cu:892)
     return float(fourier_radius_cutoff) if fourier_radius_cutoff is not None else N / 2.0
@@ -127,7 +146,8 @@ def _project_forw_impl(dim, reconstruction, rotations, shifts, output_shape, int
     rec = reconstruction.contiguous()
     out = torch.empty((B, P, N, N // 2 + 1), dtype=rec.dtype, device=rec.device)
     if out.numel():
-        _abi.project_forw(dim, rec, rot, sh, P, N, interp, oversampling, _cutoff(fourier_radius_cutoff, N), out)
+        _abi.project_forw(dim, rec, rot, sh, P, N, interp, oversampling, _cutoff(fourier_radius_cutoff, N), out,
+                          _pose_order(dim, rec, B, P, rot))
     return out
 
 
@@ -159,7 +179,8 @@ def _project_back_impl(dim, grad_projections, reconstruction, rotations, shifts,
         grad_rec.zero_()
     else:
         _abi.project_back(dim, gp, rec, rot, sh, P, N, interp, oversampling,
-                          _cutoff(fourier_radius_cutoff, N), grad_rec, grad_rot, grad_sh)
+                          _cutoff(fourier_radius_cutoff, N), grad_rec, grad_rot, grad_sh,
+                          _pose_order(dim, rec, B, P, rot))
     empty = lambda: torch.empty((0,), dtype=rot.dtype, device=dev)  # noqa: E731
     return grad_rec, (grad_rot if need_rot else empty()), (grad_sh if need_shift else empty())
 
@@ -238,7 +259,8 @@ def _backproject_back_impl(dim, grad_data_rec, grad_weight_rec, projections, wei
     grad_sh = torch.empty(sh.shape, dtype=sh.dtype, device=dev) if need_shift else None
     if proj.numel():
         _abi.backproject_back(dim, gd, grad_weight_rec, proj, rot, sh, interp, oversampling,
-                              _cutoff(fourier_radius_cutoff, N), grad_proj, grad_w, grad_rot, grad_sh)
+                              _cutoff(fourier_radius_cutoff, N), grad_proj, grad_w, grad_rot, grad_sh,
+                              _pose_order(dim, gd, B, P, rot))
     empty = lambda: torch.empty((0,), dtype=rot.dtype, device=dev)  # noqa: E731
     return (grad_proj, (grad_w if grad_w is not None else empty()),
             (grad_rot if need_rot else empty()), (grad_sh if need_shift else empty()))
