@@ -665,6 +665,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--skip-cpu", action="store_true", help="omit the CPU-baseline leg")
     ap.add_argument("--skip-backproject", action="store_true")
+    ap.add_argument("--natural-order", action="store_true",
+                    help="process slices in the order given (switch the plane-locality order of beyond-L2 volumes off), for comparisons")
     ap.add_argument("--profile-case", choices=["project", "backproject", "project_back", "backproject_slab", "autograd_step"], default=None,
                     help="run a few launches of one kernel on a reduced pose count (for ncu captures); prints no bench line")
     ap.add_argument("--profile-poses", type=int, default=2048)
@@ -674,6 +676,9 @@ def main():
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
 
+    if args.natural_order and args.impl != "reference":
+        import torch_projectors_b200.ops as _ops
+        _ops.POSE_ORDER_MIN_BYTES = 1 << 62
     if args.profile_case:
         profile_case(args)
         return
