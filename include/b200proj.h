@@ -178,6 +178,28 @@ int b200proj_backproject_2d_to_3d_forw_noalloc(const float* proj, const float* w
                                                float* data_rec, float* weight_rec, int accumulate,
                                                void* stream);
 
+/* ---- streaming back-projection into a persistent accumulator ----------------------------
+ * No counterpart in the reference (its callers sum the volumes of separate calls:
+ * tests/3d/back/test_performance_back_2d_to_3d.py:357-369).  For reconstructions fed chunk by
+ * chunk: the caller owns an accumulator of b200proj_accumulator_bytes(B, R) bytes -- one
+ * 16-byte (re, im, weight, 0) slot per voxel of [B,R,R,Rh], 16-byte aligned, zero-filled once
+ * by the caller (cudaMemsetAsync) -- and every b200proj_backproject_2d_to_3d_accumulate call
+ * ADDS its slices into it with one vector reduction per tap (half the reductions of separate
+ * data and weight volumes), choosing the slab-ordered kernel by itself when the accumulator
+ * exceeds L2.  Nothing is zero-filled or folded per call.  weights are required.
+ * b200proj_accumulator_fold writes (accumulate = 0) or adds (accumulate = 1) the sums into
+ * the API's data [B,R,R,Rh] complex / weight [B,R,R,Rh] float volumes; the accumulator is
+ * left unchanged. */
+size_t b200proj_accumulator_bytes(int64_t B, int64_t R);
+int b200proj_backproject_2d_to_3d_accumulate(const float* proj, const float* weights, int64_t B,
+                                             int64_t R, const float* rot, int64_t B_rot,
+                                             const float* shifts, int64_t B_shift,
+                                             int64_t P, int64_t N, int interpolation,
+                                             double oversampling, double fourier_radius_cutoff,
+                                             void* accumulator, void* stream);
+int b200proj_accumulator_fold(const void* accumulator, int64_t B, int64_t R, float* data_rec,
+                              float* weight_rec, int accumulate, void* stream);
+
 /* ---- backward of back-projection (gather) ----------------------------------------------
  * grad_proj [B,P,N,Nh] complex is fully written.  grad_weights [B,P,N,Nh] float is written
  * only when grad_weight_rec and grad_weights are both non-NULL (always tri/bi-linear).

@@ -54,3 +54,12 @@ def test_box400_backprojection_subset_against_oracle(tp):
     # accumulate a second time: exactly twice the volumes (streaming use of the sharded path)
     tp.backproject_2d_to_3d_accumulate_(data, wrec, proj.cuda(), rot.cuda(), weights.cuda(), shifts.cuda(), oversampling=2.0)
     assert rel_err(data, 2 * d_want) <= TOL_ATOMIC
+    # and the same slices through the persistent interleaved accumulator (slabs of 16-byte voxels,
+    # the path the sharded workload runs), two chunks folded once
+    vols = tp.sharding.PartialVolumes(1, 800, "cuda")
+    for lo, hi in ((0, 10), (10, P)):
+        vols.add_(proj[:, lo:hi].cuda(), rot[:, lo:hi].cuda(), weights[:, lo:hi].cuda(), shifts[:, lo:hi].cuda(),
+                  interpolation="linear", oversampling=2.0)
+    vols.flush()
+    assert rel_err(vols.data, d_want) <= TOL_ATOMIC
+    assert rel_err(vols.weights, w_want) <= TOL_ATOMIC

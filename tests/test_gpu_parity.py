@@ -312,6 +312,40 @@ def test_host_streaming_wrappers_match_device_calls(tp):
     assert rel_err(vols.data, d_want) <= TOL_ATOMIC and rel_err(vols.weights, w_want) <= TOL_ATOMIC
 
 
+@pytest.mark.parametrize("interp", ["linear", "cubic"])
+def test_persistent_accumulator_matches_oracle_and_partial_volumes_use_it(tp, interp):
+    from oracle import port
+    case = Case("accum", 3, interp, 2, 12, 16, 32, 2.0, None, 2, 2, weights=True, seed=77)
+    t = make_inputs(case)
+    c = lambda x: x.cuda()  # noqa: E731
+    dw, ww = port.backproject_2d_to_3d_forw(t["proj"], t["weights"], t["rot"], t["shifts"], interp, 2.0)
+    acc = tp.new_backprojection_accumulator(2, 32, "cuda")
+    for lo, hi in ((0, 5), (5, 12)):
+        tp.backproject_2d_to_3d_accumulate_interleaved_(acc, c(t["proj"])[:, lo:hi], c(t["rot"])[:, lo:hi], c(t["weights"])[:, lo:hi],
+                                                        c(t["shifts"])[:, lo:hi], interpolation=interp, oversampling=2.0)
+    d, w = tp.fold_backprojection_accumulator(acc)
+    assert rel_err(d, dw) <= TOL_ATOMIC and rel_err(w, ww) <= TOL_ATOMIC
+    # folding again with accumulate adds the same sums once more; the accumulator is unchanged
+    tp.fold_backprojection_accumulator(acc, d, w, accumulate=True)
+    assert rel_err(d, 2 * dw) <= TOL_ATOMIC and rel_err(w, 2 * ww) <= TOL_ATOMIC
+    assert acc[..., 3].abs().max().item() == 0.0          # the padding lane stays zero
+    # PartialVolumes: chunks through the accumulator, complete after flush()
+    vols = tp.sharding.PartialVolumes(2, 32, "cuda")
+    for lo, hi in ((0, 7), (7, 12)):
+        vols.add_(c(t["proj"])[:, lo:hi], c(t["rot"])[:, lo:hi], c(t["weights"])[:, lo:hi], c(t["shifts"])[:, lo:hi],
+                  interpolation=interp, oversampling=2.0)
+    assert vols._pending and vols.data.abs().max().item() == 0.0
+    vols.flush()
+    assert not vols._pending and rel_err(vols.data, dw) <= TOL_ATOMIC and rel_err(vols.weights, ww) <= TOL_ATOMIC
+    vols.flush()                                         # nothing pending: a no-op
+    assert rel_err(vols.data, dw) <= TOL_ATOMIC
+    # errors: weights are required, shapes are checked
+    with pytest.raises(RuntimeError, match="needs weights"):
+        tp.backproject_2d_to_3d_accumulate_interleaved_(acc, c(t["proj"]), c(t["rot"]), None, oversampling=2.0)
+    with pytest.raises(RuntimeError, match="accumulator must be"):
+        tp.backproject_2d_to_3d_accumulate_interleaved_(acc[:1], c(t["proj"]), c(t["rot"]), c(t["weights"]), oversampling=2.0)
+
+
 _SLAB_SCRIPT = r"""
 import sys, torch
 sys.path[:0] = [{root!r}, {root!r} + "/tests", {root!r} + "/torch-projectors_b200"]
@@ -331,6 +365,14 @@ for interp, weights in (("linear", True), ("cubic", True), ("linear", False)):
     tp.backproject_2d_to_3d_accumulate_(d, w if weights else None, c(t["proj"]), c(t["rot"]), c(t["weights"]), c(t["shifts"]),
                                         interpolation=interp, oversampling=2.0)
     assert rel_err(d, 2 * dw) <= TOL_ATOMIC
+    if weights:
+        # persistent interleaved accumulator: two chunks added, folded once (slabs of 16-byte voxels)
+        acc = tp.new_backprojection_accumulator(2, 40, "cuda")
+        for lo, hi in ((0, 4), (4, 9)):
+            tp.backproject_2d_to_3d_accumulate_interleaved_(acc, c(t["proj"])[:, lo:hi], c(t["rot"])[:, lo:hi], c(t["weights"])[:, lo:hi],
+                                                            c(t["shifts"])[:, lo:hi], interpolation=interp, oversampling=2.0)
+        da, wa = tp.fold_backprojection_accumulator(acc)
+        assert rel_err(da, dw) <= TOL_ATOMIC and rel_err(wa, ww) <= TOL_ATOMIC, (interp, rel_err(da, dw), rel_err(wa, ww))
 print("SLAB-OK")
 """
 

@@ -113,12 +113,13 @@ int zero_async(void* p, size_t bytes, cudaStream_t s) {
 // one batch item exceed `min_mb` are processed in slabs of at most `slab_mb` MB of planes.
 // Tunable for experiments through B200PROJ_SLAB_MB / B200PROJ_SLAB_MIN_MB (read once).
 struct SlabPlan { int slabs, planes; };
-SlabPlan slab_plan(int64_t R, bool has_weights) {
+SlabPlan slab_plan(int64_t R, bool has_weights, bool interleaved = false) {
     static const double slab_mb = [] { const char* e = getenv("B200PROJ_SLAB_MB"); return e ? atof(e) : 64.0; }();
     static const double min_mb = [] { const char* e = getenv("B200PROJ_SLAB_MIN_MB"); return e ? atof(e) : 160.0; }();
-    const double plane_bytes = (double)R * (double)(R / 2 + 1) * (has_weights ? 12.0 : 8.0);
+    const double plane_bytes = (double)R * (double)(R / 2 + 1) * (interleaved ? 16.0 : has_weights ? 12.0 : 8.0);
     if (slab_mb <= 0.0 || plane_bytes * (double)R <= min_mb * 1e6) return {1, (int)R};
-    int planes = (int)(slab_mb * 1e6 / plane_bytes);
+    // 16-byte voxels: fewer, larger reductions per plane leave room for 1.25x the bytes (measured)
+    int planes = (int)(slab_mb * (interleaved ? 1.25 : 1.0) * 1e6 / plane_bytes);
     if (planes < 1) planes = 1;
     const int slabs = (int)((R + planes - 1) / planes);
     return {slabs, planes};
@@ -230,7 +231,7 @@ int backproject_forw(const Real* proj, const Real* weights, int64_t B, int64_t R
         if (plan.slabs > 1) {
             const dim3 grid((unsigned)(B * P), (unsigned)plan.slabs, 1);
 #define B200PROJ_SL(C, W) \
-    backproject_slab_kernel<C, W><<<grid, kBlockThreads, 0, s>>>(p, weights, rot, shifts, d, weight_rec, L.g, plan.planes)
+    backproject_slab_kernel<C, W><<<grid, kBlockThreads, 0, s>>>(p, weights, rot, shifts, d, weight_rec, nullptr, L.g, plan.planes)
             if (cubic && hw) B200PROJ_SL(true, true);
             else if (cubic) B200PROJ_SL(true, false);
             else if (hw) B200PROJ_SL(false, true);
@@ -293,6 +294,40 @@ int backproject_back(const Real* grad_data_rec, const Real* grad_weight_rec, con
     else
         launch_backproject_back<DIM, false>(L, s, (const C2<Real>*)grad_data_rec, grad_weight_rec, (const C2<Real>*)proj, rot, shifts, (C2<Real>*)grad_proj, grad_weights, grad_rot, grad_shifts);
     return check_launch("backproject_back launch");
+}
+
+// Weighted 3D back-projection that ADDS into a persistent interleaved accumulator (16-byte
+// (re, im, w, 0) voxels): one v4 reduction per tap, nothing zero-filled or folded per call.
+int backproject_accumulate(const float* proj, const float* weights, int64_t B, int64_t R, const float* rot,
+                           int64_t B_rot, const float* shifts, int64_t B_shift, int64_t P, int64_t N,
+                           int interpolation, double os, double cutoff, void* accumulator, void* stream) {
+    Launch L;
+    if (int rc = prepare(L, 3, B, R, B_rot, rot, shifts, B_shift, P, N, interpolation, os, cutoff)) return rc;
+    if (proj == nullptr || weights == nullptr || accumulator == nullptr)
+        return fail(B200PROJ_ERR_ARGUMENT, "projections, weights and accumulator are all required");
+    if ((reinterpret_cast<uintptr_t>(accumulator) & 15u) != 0)
+        return fail(B200PROJ_ERR_ARGUMENT, "accumulator must be 16-byte aligned");
+    if (R != b200proj_rec_boxsize(N, os))
+        return fail(B200PROJ_ERR_ARGUMENT, "reconstruction boxsize %lld does not match ceil(N*oversampling) rounded up to even = %lld",
+                    (long long)R, (long long)b200proj_rec_boxsize(N, os));
+    if (P == 0) return B200PROJ_OK;
+    cudaStream_t s = (cudaStream_t)stream;
+    float4* acc = (float4*)accumulator;
+    const bool cubic = interpolation == B200PROJ_CUBIC;
+    const SlabPlan plan = slab_plan(R, true, true);
+    if (plan.slabs > 1) {
+        const dim3 grid((unsigned)(B * P), (unsigned)plan.slabs, 1);
+        if (cubic)
+            backproject_slab_kernel<true, true, true><<<grid, kBlockThreads, 0, s>>>((const float2*)proj, weights, rot, shifts, nullptr, nullptr, acc, L.g, plan.planes);
+        else
+            backproject_slab_kernel<false, true, true><<<grid, kBlockThreads, 0, s>>>((const float2*)proj, weights, rot, shifts, nullptr, nullptr, acc, L.g, plan.planes);
+        return check_launch("backproject_accumulate (slab-ordered) launch");
+    }
+    if (cubic)
+        backproject_forw_interleaved_kernel<3, true><<<L.grid, kBlockThreads, 0, s>>>((const float2*)proj, weights, rot, shifts, acc, L.g);
+    else
+        backproject_forw_interleaved_kernel<3, false><<<L.grid, kBlockThreads, 0, s>>>((const float2*)proj, weights, rot, shifts, acc, L.g);
+    return check_launch("backproject_accumulate launch");
 }
 
 template <typename Real>
@@ -484,6 +519,32 @@ int b200proj_backproject_2d_to_3d_back_f64(const double* grad_data_rec, const do
                                        double* grad_weights, double* grad_rot, double* grad_shifts,
                                        const int32_t* pose_order, void* stream) {
     return backproject_back<3>(grad_data_rec, grad_weight_rec, proj, B, R, rot, B_rot, shifts, B_shift, P, N, interpolation, oversampling, cutoff, grad_proj, grad_weights, grad_rot, grad_shifts, pose_order, stream);
+}
+
+int b200proj_backproject_2d_to_3d_accumulate(const float* proj, const float* weights, int64_t B,
+                                             int64_t R, const float* rot, int64_t B_rot,
+                                             const float* shifts, int64_t B_shift, int64_t P,
+                                             int64_t N, int interpolation, double oversampling,
+                                             double cutoff, void* accumulator, void* stream) {
+    return backproject_accumulate(proj, weights, B, R, rot, B_rot, shifts, B_shift, P, N, interpolation, oversampling, cutoff, accumulator, stream);
+}
+
+size_t b200proj_accumulator_bytes(int64_t B, int64_t R) {
+    if (B < 1 || R < 2) return 0;
+    return (size_t)B * (size_t)R * (size_t)R * (size_t)(R / 2 + 1) * sizeof(float4);
+}
+
+int b200proj_accumulator_fold(const void* accumulator, int64_t B, int64_t R, float* data_rec,
+                              float* weight_rec, int accumulate, void* stream) {
+    g_error[0] = 0;
+    if (accumulator == nullptr || data_rec == nullptr || weight_rec == nullptr)
+        return fail(B200PROJ_ERR_ARGUMENT, "accumulator, data_reconstruction and weight_reconstruction are all required");
+    if (B < 1 || R < 2 || (R % 2) != 0) return fail(B200PROJ_ERR_ARGUMENT, "batch size must be >= 1 and the boxsize even (B=%lld, R=%lld)", (long long)B, (long long)R);
+    const size_t n = (size_t)B * (size_t)R * (size_t)R * (size_t)(R / 2 + 1);
+    const size_t blocks = (n + 255) / 256;
+    fold_interleaved_kernel<<<(unsigned)(blocks < 148 * 16 ? blocks : 148 * 16), 256, 0, (cudaStream_t)stream>>>(
+        (const float4*)accumulator, (float2*)data_rec, weight_rec, n, accumulate != 0);
+    return check_launch("fold_interleaved launch");
 }
 
 int b200proj_pose_order_3d(const float* rot, int64_t B, int64_t B_rot, int64_t P, int32_t* order, void* stream) {

@@ -266,12 +266,14 @@ __device__ __forceinline__ void clip_run(float a, float b, float lo, float hi, f
     jb = fminf(jb, fmaxf(x0, x1));
 }
 
-template <bool CUBIC, bool WEIGHTS>
+// INTERLEAVED: reductions go to a 16-byte-per-voxel (re, im, w, 0) accumulator `accum` (one v4
+// reduction per tap) instead of data_rec / weight_rec.
+template <bool CUBIC, bool WEIGHTS, bool INTERLEAVED = false>
 __global__ void __launch_bounds__(kBlockThreads)
 backproject_slab_kernel(const float2* __restrict__ proj, const float* __restrict__ weights,
                         const float* __restrict__ rot, const float* __restrict__ shifts,
                         float2* __restrict__ data_rec, float* __restrict__ weight_rec,
-                        const SliceGeom g, int slab_planes) {
+                        float4* __restrict__ accum, const SliceGeom g, int slab_planes) {
     constexpr int T = CUBIC ? 4 : 2;
     constexpr unsigned kFull = 0xffffffffu;
     constexpr float kEps = 0.05f;                    // slack of the linear estimates below
@@ -291,8 +293,9 @@ backproject_slab_kernel(const float2* __restrict__ proj, const float* __restrict
     const float c_direct_min = -(float)(T / 2) - kEps;
     const float c_mirror_max = (float)(T / 2 - 1) + kEps;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    float2* data_b = data_rec + (size_t)b * g.vol_elems;
-    float* wrec_b = WEIGHTS ? weight_rec + (size_t)b * g.vol_elems : nullptr;
+    float2* data_b = INTERLEAVED ? nullptr : data_rec + (size_t)b * g.vol_elems;
+    float* wrec_b = (WEIGHTS && !INTERLEAVED) ? weight_rec + (size_t)b * g.vol_elems : nullptr;
+    float4* accum_b = INTERLEAVED ? accum + (size_t)b * g.vol_elems : nullptr;
     const float cut = sqrtf(g.cutoff_sq);
     // rows are dealt to the warps round-robin (row = n * 8 + warp), so that whichever rows a
     // slab's strip crosses, all warps of the block share them
@@ -388,7 +391,7 @@ backproject_slab_kernel(const float2* __restrict__ proj, const float* __restrict
                 }
                 if (WEIGHTS) wv = __ldcs(weights + pix);
             }
-            scatter_coop<3, CUBIC, WEIGHTS, true, false, true>(g, data_b, wrec_b, nullptr, px, active, v, wv, z_lo, z_hi);
+            scatter_coop<3, CUBIC, WEIGHTS, true, INTERLEAVED, true>(g, data_b, wrec_b, accum_b, px, active, v, wv, z_lo, z_hi);
         }
     }
 }

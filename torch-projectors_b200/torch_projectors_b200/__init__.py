@@ -17,6 +17,9 @@ from . import ops  # noqa: E402  (registers the raw operators)
 from .ops import (  # noqa: E402
     backproject_2d_forw,
     backproject_2d_to_3d_accumulate_,
+    backproject_2d_to_3d_accumulate_interleaved_,
+    fold_backprojection_accumulator,
+    new_backprojection_accumulator,
     backproject_2d_to_3d_back,
     backproject_2d_to_3d_forw,
     project_2d_back,
@@ -34,6 +37,7 @@ __version__ = "0.1.0"
 __all__ = [
     "project_2d_forw", "project_2d_back", "project_3d_to_2d_forw", "project_3d_to_2d_back",
     "backproject_2d_forw", "backproject_2d_to_3d_forw", "backproject_2d_to_3d_back",
-    "backproject_2d_to_3d_accumulate_", "sharding", "streaming", "prep",
+    "backproject_2d_to_3d_accumulate_", "backproject_2d_to_3d_accumulate_interleaved_",
+    "new_backprojection_accumulator", "fold_backprojection_accumulator", "sharding", "streaming", "prep",
     "project_3d_to_2d_to_host", "backproject_2d_to_3d_from_host",
 ]

@@ -37,8 +37,11 @@ SIGNATURES = {
 }
 # complex128 / float64 variants: same argument lists (pointers are void* here)
 SIGNATURES.update({name + "_f64": sig for name, sig in list(SIGNATURES.items()) if not name.endswith("_noalloc")})
+# fp32-only entry points of the persistent interleaved accumulator
+SIGNATURES["b200proj_backproject_2d_to_3d_accumulate"] = [_ptr, _ptr] + _COMMON + [_ptr, _ptr]
+SIGNATURES["b200proj_accumulator_fold"] = [_ptr, _i64, _i64, _ptr, _ptr, _int, _ptr]
 EXPORTS = list(SIGNATURES) + ["b200proj_version", "b200proj_last_error", "b200proj_rec_boxsize",
-                                "b200proj_backproject_workspace_bytes"]
+                                "b200proj_backproject_workspace_bytes", "b200proj_accumulator_bytes"]
 
 _lib: Optional[C.CDLL] = None
 
@@ -78,6 +81,8 @@ def load() -> C.CDLL:
     lib.b200proj_rec_boxsize.argtypes = [_i64, _dbl]
     lib.b200proj_backproject_workspace_bytes.restype = C.c_size_t
     lib.b200proj_backproject_workspace_bytes.argtypes = [_int, _i64, _i64, _i64, _i64, _int, _int]
+    lib.b200proj_accumulator_bytes.restype = C.c_size_t
+    lib.b200proj_accumulator_bytes.argtypes = [_i64, _i64]
     _lib = lib
     return lib
 
@@ -179,6 +184,23 @@ def backproject_2d_to_3d_forw_noalloc(proj, weights, rot, shifts, interp, oversa
     _call("b200proj_backproject_2d_to_3d_forw_noalloc", proj, _p(proj), _p(weights),
           *_geom(B, R, rot, shifts, P, N, interp, oversampling, cutoff),
           _p(data_rec), _p(weight_rec), int(bool(accumulate)))
+
+
+def accumulator_bytes(B: int, R: int) -> int:
+    return int(load().b200proj_accumulator_bytes(int(B), int(R)))
+
+
+def backproject_accumulate(proj, weights, rot, shifts, interp, oversampling, cutoff, R, accumulator):
+    """Add the slices into the persistent interleaved accumulator (a zero-initialised CUDA tensor
+    of accumulator_bytes(B, R) bytes); see b200proj_backproject_2d_to_3d_accumulate."""
+    B, P, N = proj.shape[0], proj.shape[1], proj.shape[2]
+    _call("b200proj_backproject_2d_to_3d_accumulate", proj, _p(proj), _p(weights),
+          *_geom(B, R, rot, shifts, P, N, interp, oversampling, cutoff), _p(accumulator))
+
+
+def accumulator_fold(accumulator, B, R, data_rec, weight_rec, accumulate):
+    _call("b200proj_accumulator_fold", data_rec, _p(accumulator), int(B), int(R), _p(data_rec), _p(weight_rec),
+          int(bool(accumulate)))
 
 
 def backproject_back(dim, grad_data_rec, grad_weight_rec, proj, rot, shifts, interp, oversampling,

@@ -452,6 +452,70 @@ def backproject_2d_to_3d_accumulate_(data_rec: torch.Tensor, weight_rec: Optiona
                           _backproject_workspace(3, B, R, P, N, interp, weights, projections.device))
 
 
+def new_backprojection_accumulator(batch: int, box: int, device) -> torch.Tensor:
+    """Zero-filled persistent accumulator for ``backproject_2d_to_3d_accumulate_interleaved_``:
+    float32 [batch, box, box, box//2+1, 4], one 16-byte (re, im, weight, 0) slot per voxel."""
+    _check(box >= 2 and box % 2 == 0, f"reconstruction boxsize {box} must be even")
+    assert _abi.accumulator_bytes(batch, box) == batch * box * box * (box // 2 + 1) * 16
+    return torch.zeros((batch, box, box, box // 2 + 1, 4), dtype=torch.float32, device=device)
+
+
+def backproject_2d_to_3d_accumulate_interleaved_(accumulator: torch.Tensor, projections: torch.Tensor,
+                                                 rotations: torch.Tensor, weights: torch.Tensor,
+                                                 shifts: Optional[torch.Tensor] = None,
+                                                 interpolation: str = "linear", oversampling: float = 1.0,
+                                                 fourier_radius_cutoff: Optional[float] = None) -> None:
+    """Streaming weighted back-projection (no autograd) that adds a chunk of slices into a
+    persistent interleaved accumulator (``new_backprojection_accumulator``): data and weight of
+    a tap leave as ONE vector reduction, nothing is zero-filled or folded per chunk, and
+    volumes beyond L2 take the slab-ordered kernel.  ``fold_backprojection_accumulator``
+    turns the sums into the usual data / weight volumes.  complex64 / float32 only.  Not in the
+    reference API."""
+    _validate_projections(projections, weights)
+    _check(weights is not None, "the interleaved accumulator needs weights")
+    if projections.dim() == 4 and rotations.dim() == 3:
+        rotations = rotations.unsqueeze(0)
+    if shifts is not None and shifts.dim() == 2:
+        shifts = shifts.unsqueeze(0)
+    _check(projections.is_cuda and weights.is_cuda, "projections and weights must be on a CUDA device")
+    _check(projections.dtype == torch.complex64 and weights.dtype == torch.float32,
+           "the interleaved accumulator holds float32 sums: projections must be complex64 and weights float32")
+    B, P_p, N, _ = projections.shape
+    interp = _interp_code(interpolation)
+    P, rot, sh = _check_pose_inputs(3, "projections", B, rotations, shifts, projections)
+    _check(P == P_p, "Number of poses in rotations must match projections")
+    R = _abi.rec_boxsize(N, oversampling)
+    want = (B, R, R, R // 2 + 1, 4)
+    _check(tuple(accumulator.shape) == want and accumulator.dtype == torch.float32 and accumulator.is_contiguous()
+           and accumulator.device == projections.device, f"accumulator must be a contiguous float32 tensor of shape {want}")
+    if P == 0:
+        return
+    _abi.backproject_accumulate(projections.contiguous(), weights.contiguous(), rot, sh, interp, oversampling,
+                                _cutoff(fourier_radius_cutoff, N), R, accumulator)
+
+
+def fold_backprojection_accumulator(accumulator: torch.Tensor, data_rec: Optional[torch.Tensor] = None,
+                                    weight_rec: Optional[torch.Tensor] = None, accumulate: bool = False):
+    """(data_rec, weight_rec) = the sums held by the accumulator, written into (or, with
+    ``accumulate=True``, added to) the given volumes; fresh ones are made when none are given.
+    The accumulator itself is left unchanged."""
+    _check(accumulator.is_cuda and accumulator.dtype == torch.float32 and accumulator.dim() == 5
+           and accumulator.size(-1) == 4 and accumulator.is_contiguous(), "accumulator must come from new_backprojection_accumulator")
+    shape = tuple(accumulator.shape[:-1])
+    B, R = shape[0], shape[1]
+    if data_rec is None:
+        _check(not accumulate, "accumulate=True needs existing volumes")
+        data_rec = torch.empty(shape, dtype=torch.complex64, device=accumulator.device)
+    if weight_rec is None:
+        _check(not accumulate, "accumulate=True needs existing volumes")
+        weight_rec = torch.empty(shape, dtype=torch.float32, device=accumulator.device)
+    for t, dt, what in ((data_rec, torch.complex64, "data_rec"), (weight_rec, torch.float32, "weight_rec")):
+        _check(tuple(t.shape) == shape and t.dtype == dt and t.is_contiguous() and t.device == accumulator.device,
+               f"{what} must be a contiguous {dt} tensor of shape {shape}")
+    _abi.accumulator_fold(accumulator, B, R, data_rec, weight_rec, accumulate)
+    return data_rec, weight_rec
+
+
 # ---------------------------------------------------------------------------------------
 # autograd glue (reference: torch_projectors/ops.py:300-514)
 # ---------------------------------------------------------------------------------------

@@ -78,7 +78,12 @@ def project_3d_to_2d_sharded(reconstruction: torch.Tensor, rotations: torch.Tens
 
 class PartialVolumes:
     """Data (complex64) and weight (float32) volumes of one rank, adjacent in one float32
-    buffer: [ data.re/im interleaved | weights ], so one collective reduces both."""
+    buffer: [ data.re/im interleaved | weights ], so one collective reduces both.
+
+    ``add_`` accumulates a chunk of slices.  On a CUDA device, weighted slices go through a
+    persistent interleaved accumulator (16-byte (re, im, weight, 0) voxels, one vector reduction
+    per tap, nothing zero-filled or folded per chunk); ``flush`` folds it into ``data`` /
+    ``weights``, which are therefore complete only after ``flush()`` (``reduce`` calls it)."""
 
     def __init__(self, batch: int, box: int, device, with_weights: bool = True):
         self.shape = (batch, box, box, box // 2 + 1)
@@ -86,10 +91,36 @@ class PartialVolumes:
         self.flat = torch.zeros(n * (3 if with_weights else 2), dtype=torch.float32, device=device)
         self.data = torch.view_as_complex(self.flat[: 2 * n].view(*self.shape, 2))
         self.weights = self.flat[2 * n:].view(self.shape) if with_weights else None
+        self._accum = None          # interleaved accumulator, made on first use
+        self._pending = False       # sums in _accum not yet folded into data / weights
+
+    def add_(self, projections: torch.Tensor, rotations: torch.Tensor,
+             weights: Optional[torch.Tensor] = None, shifts: Optional[torch.Tensor] = None, *,
+             interpolation: str = "linear", oversampling: float = 1.0,
+             fourier_radius_cutoff: Optional[float] = None) -> None:
+        """Back-project one chunk of device-resident slices [B, P, N, Nh] into these volumes."""
+        from . import ops
+        kw = dict(interpolation=interpolation, oversampling=oversampling, fourier_radius_cutoff=fourier_radius_cutoff)
+        if weights is not None and self.weights is not None and projections.dtype == torch.complex64:
+            if self._accum is None:
+                self._accum = ops.new_backprojection_accumulator(self.shape[0], self.shape[1], self.flat.device)
+            ops.backproject_2d_to_3d_accumulate_interleaved_(self._accum, projections, rotations, weights, shifts, **kw)
+            self._pending = True
+        else:
+            ops.backproject_2d_to_3d_accumulate_(self.data, self.weights, projections, rotations, weights, shifts, **kw)
+
+    def flush(self) -> None:
+        """Fold the interleaved accumulator (if it holds anything) into data / weights."""
+        if self._pending:
+            from . import ops
+            ops.fold_backprojection_accumulator(self._accum, self.data, self.weights, accumulate=True)
+            self._accum.zero_()
+            self._pending = False
 
     def reduce(self, dst: Optional[int] = 0, group=None) -> None:
         """Sum the partial volumes over ranks: onto rank `dst`, or onto every rank when
-        dst is None.  No-op outside an initialised process group."""
+        dst is None.  Outside an initialised process group only the pending sums are folded."""
+        self.flush()
         _, world = _world(group)
         if world == 1:
             return
@@ -111,10 +142,10 @@ def backproject_2d_to_3d_sharded(projections: torch.Tensor, rotations: torch.Ten
     """Back-project this rank's LOCAL slices [B, P_local, N, Nh] into its partial volumes
     in chunks of `chunk` poses, then (``reduce=True``) combine the ranks' partial volumes
     with one reduce.  Pass ``into=`` to keep accumulating into existing partial volumes
-    over several calls and ``reduce=False`` to postpone the collective to the last call.
+    over several calls and ``reduce=False`` to postpone the collective to the last call
+    (the volumes are complete after ``reduce()`` or ``flush()``).
     """
-    if accumulate_fn is None:
-        from .ops import backproject_2d_to_3d_accumulate_ as accumulate_fn
+    use_add = accumulate_fn is None           # the package's own CUDA path
     if rec_boxsize_fn is None:
         from ._abi import rec_boxsize as rec_boxsize_fn
     if projections.dim() != 4:
@@ -130,11 +161,14 @@ def backproject_2d_to_3d_sharded(projections: torch.Tensor, rotations: torch.Ten
                               with_weights=weights is not None)
     for lo in range(0, P, max(1, chunk)):
         hi = min(P, lo + chunk)
-        accumulate_fn(vols.data, vols.weights, projections[:, lo:hi], rotations[:, lo:hi],
+        chunk_args = (projections[:, lo:hi], rotations[:, lo:hi],
                       weights[:, lo:hi] if weights is not None else None,
-                      shifts[:, lo:hi] if shifts is not None else None,
-                      interpolation=interpolation, oversampling=oversampling,
-                      fourier_radius_cutoff=fourier_radius_cutoff)
+                      shifts[:, lo:hi] if shifts is not None else None)
+        kw = dict(interpolation=interpolation, oversampling=oversampling, fourier_radius_cutoff=fourier_radius_cutoff)
+        if use_add:
+            vols.add_(*chunk_args, **kw)
+        else:
+            accumulate_fn(vols.data, vols.weights, *chunk_args, **kw)
     if reduce:
         vols.reduce(dst=dst, group=group)
     return vols

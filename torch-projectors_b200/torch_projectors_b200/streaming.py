@@ -116,13 +116,13 @@ def backproject_2d_to_3d_from_host(projections: torch.Tensor, rotations: torch.T
             if k + 1 < len(spans):
                 staged = stage(spans[k + 1])
             main.wait_event(ev)
-            ops.backproject_2d_to_3d_accumulate_(vols.data, vols.weights, p, rot[:, lo:hi], w,
-                                                 sh[:, lo:hi] if sh is not None else None,
-                                                 interpolation=interpolation, oversampling=oversampling,
-                                                 fourier_radius_cutoff=fourier_radius_cutoff)
+            vols.add_(p, rot[:, lo:hi], w, sh[:, lo:hi] if sh is not None else None,
+                      interpolation=interpolation, oversampling=oversampling,
+                      fourier_radius_cutoff=fourier_radius_cutoff)
             p.record_stream(main)
             if w is not None:
                 w.record_stream(main)
+        vols.flush()
     return vols
 
 
