@@ -258,6 +258,18 @@ def profile_case(args):
         torch.cuda.synchronize()
         print(f"profile case autograd_step: {P} poses of 256x256 on a box-512 volume, 2 forward + 2 backward launches done")
         return
+    if args.profile_case == "project_2d":
+        # paper-protocol 2D case: 8 box-256 images, P poses each, linear, oversampling 1, shifts
+        from cases import random_rotations_2d
+        gen = torch.Generator(device=dev).manual_seed(7)
+        rec2 = torch.complex(torch.randn(8, 256, 129, generator=gen, device=dev), torch.randn(8, 256, 129, generator=gen, device=dev))
+        rot2 = random_rotations_2d(8 * P, torch.Generator().manual_seed(7)).reshape(8, P, 2, 2).to(dev)
+        sh2 = torch.randn(8, P, 2, generator=gen, device=dev) * 5.0
+        for _ in range(2):
+            tp.project_2d_forw(rec2, rot2, sh2, output_shape=(256, 256), interpolation="linear")
+        torch.cuda.synchronize()
+        print(f"profile case project_2d: 8 x {P} poses of 256x256, linear, 2 launches done")
+        return
     if args.profile_case == "backproject_slab":
         # 256x256 slices into box-512 volumes (808 MB > L2): the slab-ordered kernel
         gen = torch.Generator(device=dev).manual_seed(5)
@@ -672,7 +684,7 @@ def main():
     ap.add_argument("--skip-backproject", action="store_true")
     ap.add_argument("--natural-order", action="store_true",
                     help="process slices in the order given (switch the plane-locality order of beyond-L2 volumes off), for comparisons")
-    ap.add_argument("--profile-case", choices=["project", "backproject", "project_back", "backproject_slab", "autograd_step"], default=None,
+    ap.add_argument("--profile-case", choices=["project", "backproject", "project_back", "backproject_slab", "autograd_step", "project_2d"], default=None,
                     help="run a few launches of one kernel on a reduced pose count (for ncu captures); prints no bench line")
     ap.add_argument("--profile-poses", type=int, default=2048)
     ap.add_argument("--workload", choices=["default", "autograd_step", "sharded_backproject", "ops_table", "reference_cuda", "paper_matrix"], default="default",
