@@ -78,11 +78,12 @@ int b200proj_project_3d_to_2d_forw(const float* rec, int64_t B, int64_t R,
 /* ---- processing order of the slices (3D operators that read a volume) -------------------
  * No counterpart in the reference.  The three volume-reading 3D entry points
  * (project_3d_to_2d_forw, project_3d_to_2d_back, backproject_2d_to_3d_back) take an optional
- * `pose_order`: int32 [B*P] on the device, a permutation of the slice indices b*P + p; block
- * k of the launch then handles slice pose_order[k].  Outputs stay where they belong (slice
+ * `pose_order`: int32 [B*P] on the device, a permutation of the slice indices b*P + p that
+ * keeps every batch item's slices inside its own range [b*P, (b+1)*P); block k of the launch
+ * then handles slice pose_order[k].  Outputs stay where they belong (slice
  * b*P + p is written at index b*P + p) and their values do not depend on the order; only the
- * set of slices in flight at one time changes.  NULL = natural order.  An entry outside
- * [0, B*P) makes its blocks idle (that slice is then never written).
+ * set of slices in flight at one time changes.  NULL = natural order.  An entry outside its
+ * batch item's range makes its blocks idle (that slice is then never written).
  * b200proj_pose_order_3d fills such an array from the rotations so that slices with nearby
  * planes run together; worthwhile once one batch item's volume no longer fits L2 (about
  * 100 MB), where it turns most DRAM reads of the volume into L2 hits, and harmless below.

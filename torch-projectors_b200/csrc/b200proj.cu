@@ -83,14 +83,24 @@ int prepare(Launch& L, int dim, int64_t B, int64_t R, int64_t B_rot, const void*
 
     if (B * P > INT_MAX / 2) return fail(B200PROJ_ERR_LIMIT, "B*P = %lld slices exceed the grid limit; split the poses into chunks", (long long)(B * P));
     g.BP = (int)(B * P);
-    g.P_is_all = (B == 1);
+    g.slice_pixels = (int)(N * Nh);
+    g.os_f = (float)oversampling;
+    g.os_is_float = ((double)g.os_f == oversampling);
     g.sparse_samples = oversampling >= 1.5;
     // exact for tile < 2^16 whenever tiles_j <= 2^16 (the numbers of tiles per slice are far below)
     g.tiles_j_magic = g.tiles_j == 1 ? 0u : (unsigned)(((1ull << 32) + (unsigned long long)g.tiles_j - 1) / (unsigned long long)g.tiles_j);
-    // x = tile, (y, z) = slice index split as y + 32768 * z (see block_work)
-    const int64_t bp = B * P;
-    const unsigned gy = (unsigned)(bp < 32768 ? (bp > 0 ? bp : 1) : 32768);
-    const unsigned gz = (unsigned)((bp + 32767) / 32768 > 0 ? (bp + 32767) / 32768 : 1);
+    // x = tile, (y, z) = the slice (see block_work for the three decodings)
+    unsigned gy, gz;
+    if (B > 1 && P >= 1 && P <= 32768 && B <= 65535) {
+        g.decode = 1;
+        gy = (unsigned)P;
+        gz = (unsigned)B;
+    } else {
+        g.decode = (B == 1) ? 0 : 2;
+        const int64_t bp = B * P;
+        gy = (unsigned)(bp < 32768 ? (bp > 0 ? bp : 1) : 32768);
+        gz = (unsigned)((bp + 32767) / 32768 > 0 ? (bp + 32767) / 32768 : 1);
+    }
     L.grid = dim3((unsigned)(g.tiles_j * g.tiles_i), gy, gz);
     L.B = B; L.P = P;
     L.rec_count = (size_t)B * (size_t)vol;

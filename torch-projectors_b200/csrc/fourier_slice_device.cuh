@@ -59,7 +59,11 @@ struct SliceGeom {
     int R, Rh, half;        // volume box, stored width R/2+1, R/2
     int P;                  // poses per batch item
     int BP;                 // B * P, slices of the call
-    int P_is_all;           // B == 1
+    int decode;             // how (blockIdx.y, blockIdx.z) name a slice: 0 = one batch item, p = y + 32768*z;
+                            // 1 = b = z, p = y; 2 = b*P + p = y + 32768*z (needs a division)
+    int slice_pixels;       // N * Nh
+    int os_is_float;        // the oversampling factor is exactly representable in float
+    float os_f;
     int sparse_samples;     // oversampling >= 1.5
     unsigned tiles_j_magic; // ceil(2^32 / tiles_j): tile / tiles_j == __umulhi(tile, magic) for tile < 2^16
     int tiles_j, tiles_i;   // block tiles per slice
@@ -108,8 +112,14 @@ __device__ __forceinline__ bool pixel_setup(const SliceGeom& g, const R* __restr
     px.kc = (R)j;
     const R rad = add_rn(mul_rn(px.kr, px.kr), mul_rn(px.kc, px.kc));
     if (rad > cutoff_sq_of(g, rad)) return false;
-    px.sc = (R)((double)px.kc * g.os);
-    px.sr = (R)((double)px.kr * g.os);
+    if (sizeof(R) == 4 && g.os_is_float) {
+        // the exact product of two floats rounds to the same float from double or in one fp32 multiply
+        px.sc = mul_rn(px.kc, (R)g.os_f);
+        px.sr = mul_rn(px.kr, (R)g.os_f);
+    } else {
+        px.sc = (R)((double)px.kc * g.os);
+        px.sr = (R)((double)px.kr * g.os);
+    }
     if (DIM == 3) {
         px.c = add_rn(mul_rn(__ldg(rm + 0), px.sc), mul_rn(__ldg(rm + 1), px.sr));
         px.r = add_rn(mul_rn(__ldg(rm + 3), px.sc), mul_rn(__ldg(rm + 4), px.sr));
@@ -123,14 +133,16 @@ __device__ __forceinline__ bool pixel_setup(const SliceGeom& g, const R* __restr
 }
 
 // sin and cos of a phase of tens of radians.  fp32: the phase (already rounded to float as the
-// reference rounds it) is reduced to [-pi, pi] exactly in double, then evaluated with the
-// hardware approximations, whose absolute error there (< 5e-7) is below the fp32 noise of the
-// interpolated value it multiplies; this replaces ~40 instructions of sincosf's full-range
-// path by ~10.  fp64: the accurate library routine.
+// reference rounds it) is reduced to about [-pi, pi] with a two-constant Cody-Waite step in
+// fp32 (2*pi = 6.28125 + 1.9353072e-3: the first product is exact for |k| < 2^16, so the
+// reduced argument is good to ~1e-7), then evaluated with the hardware approximations, whose
+// absolute error there (< 5e-7) is below the fp32 noise of the interpolated value it
+// multiplies; this replaces ~40 instructions of sincosf's full-range path by 6.  fp64: the
+// accurate library routine.
 __device__ __forceinline__ void phase_sincos(float ph, float* sn, float* cs) {
-    const double x = (double)ph;
-    const double k = rint(x * 0.15915494309189535);                 // 1 / (2*pi)
-    const float r = (float)fma(k, -6.283185307179586, x);
+    const float k = rintf(ph * 0.15915494309189535f);               // 1 / (2*pi)
+    float r = fmaf(k, -6.28125f, ph);
+    r = fmaf(k, -1.9353071795864769e-3f, r);
     *sn = __sinf(r);
     *cs = __cosf(r);
 }

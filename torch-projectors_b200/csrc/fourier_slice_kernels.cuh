@@ -20,27 +20,50 @@ struct BlockWork {
     size_t pix;     // element offset of (b, p, i, j) in a [B, P, N, Nh] tensor
 };
 
-// Grid: x = tile of the slice, (y, z) = slice index b*P + p split as y + 32768*z (so that no
-// integer division is needed to decode a block and any number of slices fits the grid limits).
+// Grid: x = tile of the slice, (y, z) = the slice.  Three decodings keep integer division out
+// of the common cases (every thread decodes its block): one batch item: p = y + 32768*z;
+// several batch items of at most 32768 poses: b = z, p = y; otherwise the flat slice index
+// b*P + p = y + 32768*z is divided by P.
 constexpr int kGridYBits = 15;
 
+template <bool WIDE_PIX = false>
 __device__ __forceinline__ BlockWork block_work(const SliceGeom& g) {
     BlockWork w;
-    int bp = (int)blockIdx.y + ((int)blockIdx.z << kGridYBits);
-    // an entry outside [0, BP) (a malformed order) makes the block idle instead of reading out of bounds
-    if (g.order != nullptr && bp < g.BP) bp = __ldg(g.order + bp);
-    const bool slice_ok = (unsigned)bp < (unsigned)g.BP;
-    if (!slice_ok) bp = 0;
-    if (g.P_is_all) {            // one batch item: the usual case
-        w.b = 0;
-        w.p = bp;
+    const int y = (int)blockIdx.y, z = (int)blockIdx.z;
+    int b, p;
+    if (g.decode == 0) {
+        b = 0;
+        p = y + (z << kGridYBits);
+    } else if (g.decode == 1) {
+        b = z;
+        p = y;
     } else {
-        w.b = bp / g.P;
-        w.p = bp - w.b * g.P;
+        const int bp = y + (z << kGridYBits);
+        b = bp / g.P;
+        p = bp - b * g.P;
     }
+    int k = b * g.P + p;
+    bool slice_ok = p < g.P && k < g.BP;
+    if (g.order != nullptr && slice_ok) {
+        // block k handles slice order[k], which lies in the same batch item; any other entry
+        // (a malformed order) makes the block idle instead of reading out of bounds
+        p = __ldg(g.order + k) - b * g.P;
+        slice_ok = (unsigned)p < (unsigned)g.P;
+    }
+    if (!slice_ok) b = p = 0;
+    w.b = b;
+    w.p = p;
     tile_pixel(g, (int)blockIdx.x, w.i, w.j);
     w.in_image = w.i < g.N && w.j < g.Nh && slice_ok;
-    w.pix = ((size_t)bp * (size_t)g.N + (size_t)w.i) * (size_t)g.Nh + (size_t)w.j;
+    // WIDE_PIX: the same offset as one 64-bit expression per thread.  It costs the cubic 3D
+    // forward kernel 9 registers (57 instead of 48) and that is its purpose: the kernel is bound
+    // by the L1TEX data pipe and runs slower with five resident blocks per SM than with four
+    // (measured 4.44 vs 4.09 ms per 10,000 poses of the box-256 workload; a larger L1 carve-out,
+    // taller blocks and plane-sorted slices did not change that).
+    if (WIDE_PIX)
+        w.pix = ((size_t)(b * g.P + p) * (size_t)g.N + (size_t)w.i) * (size_t)g.Nh + (size_t)w.j;
+    else    // block-uniform slice base (64-bit) + 32-bit offset inside the slice
+        w.pix = (size_t)(b * g.P + p) * (size_t)g.slice_pixels + (size_t)(w.i * g.Nh + w.j);
     return w;
 }
 
@@ -59,7 +82,7 @@ template <int DIM, bool CUBIC, typename R>
 __global__ void __launch_bounds__(kBlockThreads)
 project_forw_kernel(const C2<R>* __restrict__ rec, const R* __restrict__ rot,
                     const R* __restrict__ shifts, C2<R>* __restrict__ out, const SliceGeom g) {
-    const BlockWork w = block_work(g);
+    const BlockWork w = block_work<CUBIC && DIM == 3>(g);
     PixelT<R> px;
     px.c = px.r = px.d = 0.f;
     const bool valid = w.in_image && pixel_setup<DIM>(g, pose_rot<DIM>(g, rot, w.b, w.p), w.i, w.j, px);
