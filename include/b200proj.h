@@ -201,6 +201,24 @@ int b200proj_backproject_2d_to_3d_accumulate(const float* proj, const float* wei
 int b200proj_accumulator_fold(const void* accumulator, int64_t B, int64_t R, float* data_rec,
                               float* weight_rec, int accumulate, void* stream);
 
+/* ---- the steps either side of the operators ----------------------------------------------
+ * No raw-operator counterpart in the reference, which does them with torch calls in its README
+ * and test utilities (README.md:96-160, tests/test_utils.py:174-293).
+ * b200proj_pad_fftshift: `batch` real arrays of box n (dims = 2: [n,n]; 3: [n,n,n]) -> box m
+ * (even, >= n), zero-padded by lo = (m-n)/2 in front of every axis and rolled so that the
+ * real-space centre lands on index 0 -- the array whose real FFT (norm 'forward') is the
+ * reconstruction the projection operators read.  b200proj_ifftshift_crop is its adjoint /
+ * inverse: box m -> the centred box n of an inverse-transformed reconstruction.  One pass each
+ * (every output element written once). */
+int b200proj_pad_fftshift(const float* real, int64_t batch, int dims, int64_t n, int64_t m,
+                          float* out, void* stream);
+int b200proj_ifftshift_crop(const float* full, int64_t batch, int dims, int64_t m, int64_t n,
+                            float* out, void* stream);
+int b200proj_pad_fftshift_f64(const double* real, int64_t batch, int dims, int64_t n, int64_t m,
+                              double* out, void* stream);
+int b200proj_ifftshift_crop_f64(const double* full, int64_t batch, int dims, int64_t m, int64_t n,
+                                double* out, void* stream);
+
 /* ---- backward of back-projection (gather) ----------------------------------------------
  * grad_proj [B,P,N,Nh] complex is fully written.  grad_weights [B,P,N,Nh] float is written
  * only when grad_weight_rec and grad_weights are both non-NULL (always tri/bi-linear).

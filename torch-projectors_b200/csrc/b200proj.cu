@@ -340,6 +340,32 @@ int backproject_accumulate(const float* proj, const float* weights, int64_t B, i
     return check_launch("backproject_accumulate launch");
 }
 
+// pad + fftshift (pad != 0) or ifftshift + crop (pad == 0) of `batch` real arrays with `dims` axes.
+template <typename Real>
+int pad_shift(const Real* in, int64_t batch, int dims, int64_t n, int64_t m, int pad, Real* out, void* stream) {
+    g_error[0] = 0;
+    if (in == nullptr || out == nullptr) return fail(B200PROJ_ERR_ARGUMENT, "input / output pointer is NULL");
+    if (dims != 2 && dims != 3) return fail(B200PROJ_ERR_ARGUMENT, "dims must be 2 or 3");
+    if (batch < 1 || n < 1 || m < n || (m % 2) != 0)
+        return fail(B200PROJ_ERR_ARGUMENT, "need batch >= 1, 1 <= n <= m and an even padded box (batch=%lld, n=%lld, m=%lld)", (long long)batch, (long long)n, (long long)m);
+    const int64_t out_box = pad ? m : n;
+    if (m > 8192 || batch * (dims == 3 ? out_box : 1) > 65535 * 32768ll || out_box > 65535)
+        return fail(B200PROJ_ERR_LIMIT, "box %lld / batch %lld beyond what one launch indexes", (long long)m, (long long)batch);
+    const int64_t gz = batch * (dims == 3 ? out_box : 1);
+    if (gz > 65535) return fail(B200PROJ_ERR_LIMIT, "batch * box = %lld exceeds the grid limit; split the batch", (long long)gz);
+    const dim3 grid((unsigned)((out_box + 255) / 256), (unsigned)out_box, (unsigned)gz);
+    cudaStream_t s = (cudaStream_t)stream;
+    const int lo = (int)((m - n) / 2);
+    if (dims == 3) {
+        if (pad) pad_shift_kernel<3, true><<<grid, 256, 0, s>>>(in, out, (int)n, (int)m, lo, (long long)batch);
+        else pad_shift_kernel<3, false><<<grid, 256, 0, s>>>(in, out, (int)n, (int)m, lo, (long long)batch);
+    } else {
+        if (pad) pad_shift_kernel<2, true><<<grid, 256, 0, s>>>(in, out, (int)n, (int)m, lo, (long long)batch);
+        else pad_shift_kernel<2, false><<<grid, 256, 0, s>>>(in, out, (int)n, (int)m, lo, (long long)batch);
+    }
+    return check_launch("pad_shift launch");
+}
+
 template <typename Real>
 int pose_order_3d(const Real* rot, int64_t B, int64_t B_rot, int64_t P, int32_t* order, void* stream) {
     g_error[0] = 0;
@@ -555,6 +581,19 @@ int b200proj_accumulator_fold(const void* accumulator, int64_t B, int64_t R, flo
     fold_interleaved_kernel<<<(unsigned)(blocks < 148 * 16 ? blocks : 148 * 16), 256, 0, (cudaStream_t)stream>>>(
         (const float4*)accumulator, (float2*)data_rec, weight_rec, n, accumulate != 0);
     return check_launch("fold_interleaved launch");
+}
+
+int b200proj_pad_fftshift(const float* real, int64_t batch, int dims, int64_t n, int64_t m, float* out, void* stream) {
+    return pad_shift(real, batch, dims, n, m, 1, out, stream);
+}
+int b200proj_pad_fftshift_f64(const double* real, int64_t batch, int dims, int64_t n, int64_t m, double* out, void* stream) {
+    return pad_shift(real, batch, dims, n, m, 1, out, stream);
+}
+int b200proj_ifftshift_crop(const float* full, int64_t batch, int dims, int64_t m, int64_t n, float* out, void* stream) {
+    return pad_shift(full, batch, dims, n, m, 0, out, stream);
+}
+int b200proj_ifftshift_crop_f64(const double* full, int64_t batch, int dims, int64_t m, int64_t n, double* out, void* stream) {
+    return pad_shift(full, batch, dims, n, m, 0, out, stream);
 }
 
 int b200proj_pose_order_3d(const float* rot, int64_t B, int64_t B_rot, int64_t P, int32_t* order, void* stream) {

@@ -535,4 +535,37 @@ pose_order_kernel(const R* __restrict__ rot, long long rot_stride_b, int P, int*
     }
 }
 
+// ---- the steps either side of the operators: pad + fftshift, ifftshift + crop ----------------
+// Real-space image / volume (box n) <-> zero-padded, origin-at-index-0 array (box m >= n, both
+// even or n odd is fine; lo = (m - n) / 2) that cuFFT transforms.  One pass each instead of
+// pad -> roll (two extra passes over the padded array).
+//   pad:   out[i...] = in[s(i0), s(i1)(, s(i2))],  s(i) = (i + m/2) mod m - lo,  0 outside [0, n)
+//   crop:  out[j...] = in[t(j0), t(j1)(, t(j2))],  t(j) = (j + lo + m/2) mod m
+// The two are adjoint to each other, which is what autograd needs.
+// Grid: x covers the innermost axis, y the middle axis, z = batch * (outer axis or 1).
+template <int DIMS, bool PAD, typename R>
+__global__ void __launch_bounds__(256)
+pad_shift_kernel(const R* __restrict__ in, R* __restrict__ out, int n, int m, int lo, long long batch) {
+    const int out_box = PAD ? m : n, in_box = PAD ? n : m;
+    const int i2 = (int)(blockIdx.x * blockDim.x + threadIdx.x);
+    const int i1 = (int)blockIdx.y;
+    const int zi = (int)blockIdx.z;
+    const int b = DIMS == 3 ? zi / out_box : zi;
+    const int i0 = DIMS == 3 ? zi - b * out_box : 0;
+    if (i2 >= out_box || b >= batch) return;
+    const int half = m / 2;
+    auto src = [&](int i) {
+        if (PAD) { int s = i + half; if (s >= m) s -= m; return s - lo; }
+        int t = i + lo + half; if (t >= m) t -= m; return t;
+    };
+    const int s2 = src(i2), s1 = src(i1), s0 = DIMS == 3 ? src(i0) : 0;
+    const size_t o = ((size_t)((long long)b * (DIMS == 3 ? out_box : 1) + i0) * out_box + i1) * out_box + i2;
+    R v = 0;
+    if (!PAD || ((unsigned)s2 < (unsigned)n && (unsigned)s1 < (unsigned)n && (unsigned)s0 < (unsigned)n)) {
+        const size_t k = ((size_t)((long long)b * (DIMS == 3 ? in_box : 1) + s0) * in_box + s1) * in_box + s2;
+        v = PAD ? __ldg(in + k) : __ldcs(in + k);
+    }
+    out[o] = v;
+}
+
 }  // namespace b200proj

@@ -34,6 +34,8 @@ SIGNATURES = {
     "b200proj_backproject_2d_back": [_ptr, _ptr, _ptr] + _COMMON + [_ptr, _ptr, _ptr, _ptr, _ptr],
     "b200proj_backproject_2d_to_3d_back": [_ptr, _ptr, _ptr] + _COMMON + [_ptr, _ptr, _ptr, _ptr, _ptr, _ptr],
     "b200proj_pose_order_3d": [_ptr, _i64, _i64, _i64, _ptr, _ptr],
+    "b200proj_pad_fftshift": [_ptr, _i64, _int, _i64, _i64, _ptr, _ptr],
+    "b200proj_ifftshift_crop": [_ptr, _i64, _int, _i64, _i64, _ptr, _ptr],
 }
 # complex128 / float64 variants: same argument lists (pointers are void* here)
 SIGNATURES.update({name + "_f64": sig for name, sig in list(SIGNATURES.items()) if not name.endswith("_noalloc")})
@@ -184,6 +186,14 @@ def backproject_2d_to_3d_forw_noalloc(proj, weights, rot, shifts, interp, oversa
     _call("b200proj_backproject_2d_to_3d_forw_noalloc", proj, _p(proj), _p(weights),
           *_geom(B, R, rot, shifts, P, N, interp, oversampling, cutoff),
           _p(data_rec), _p(weight_rec), int(bool(accumulate)))
+
+
+def pad_fftshift(real, batch, dims, n, m, out):
+    _call("b200proj_pad_fftshift", real, _p(real), int(batch), int(dims), int(n), int(m), _p(out))
+
+
+def ifftshift_crop(full, batch, dims, m, n, out):
+    _call("b200proj_ifftshift_crop", full, _p(full), int(batch), int(dims), int(m), int(n), _p(out))
 
 
 def accumulator_bytes(B: int, R: int) -> int:
