@@ -200,6 +200,11 @@ int b200proj_backproject_2d_to_3d_accumulate(const float* proj, const float* wei
                                              void* accumulator, void* stream);
 int b200proj_accumulator_fold(const void* accumulator, int64_t B, int64_t R, float* data_rec,
                               float* weight_rec, int accumulate, void* stream);
+/* The same for voxels [first_voxel, first_voxel + voxel_count) only (all three pointers are the
+ * bases of the whole volumes), so that a caller can fold range by range and hand each finished
+ * range to a collective while the next one is folded. */
+int b200proj_accumulator_fold_range(const void* accumulator, int64_t first_voxel, int64_t voxel_count,
+                                    float* data_rec, float* weight_rec, int accumulate, void* stream);
 
 /* ---- the steps either side of the operators ----------------------------------------------
  * No raw-operator counterpart in the reference, which does them with torch calls in its README

@@ -98,3 +98,27 @@ def test_no_alloc_entry_reports_its_limit_without_a_device():
     assert rc == -2 and "built-in scratch" in lib.b200proj_last_error().decode()
     rc = lib.b200proj_backproject_2d_to_3d_forw_noalloc(1, 0, 1, 64, 1, 1, 0, 0, 1, 32, 0, 2.0, 16.0, 1, 1, 0, 0)
     assert rc == -1 and "required" in lib.b200proj_last_error().decode()
+
+
+def test_accumulator_and_prep_entries_validate_without_a_device():
+    lib = _abi.load()
+    assert _abi.accumulator_bytes(1, 800) == 800 * 800 * 401 * 16
+    assert _abi.accumulator_bytes(0, 800) == 0
+    err = lambda: lib.b200proj_last_error().decode()  # noqa: E731
+    # accumulate: weights and accumulator are required, alignment and the size rule are checked
+    acc = lib.b200proj_backproject_2d_to_3d_accumulate
+    assert acc(1, 0, 1, 16, 1, 1, 0, 0, 1, 8, 0, 2.0, 4.0, 16, 0) == -1 and "required" in err()
+    assert acc(1, 1, 1, 16, 1, 1, 0, 0, 1, 8, 0, 2.0, 4.0, 8, 0) == -1 and "16-byte aligned" in err()
+    assert acc(1, 1, 1, 10, 1, 1, 0, 0, 1, 8, 0, 2.0, 4.0, 16, 0) == -1 and "does not match" in err()
+    assert acc(1, 1, 1, 16, 1, 1, 0, 0, 0, 8, 0, 2.0, 4.0, 16, 0) == 0            # no poses: nothing to launch
+    fold = lib.b200proj_accumulator_fold
+    assert fold(0, 1, 16, 1, 1, 0, 0) == -1 and "required" in err()
+    assert fold(1, 1, 15, 1, 1, 0, 0) == -1 and "even" in err()
+    # pad + fftshift / ifftshift + crop
+    pad = lib.b200proj_pad_fftshift
+    assert pad(0, 1, 3, 8, 16, 1, 0) == -1 and "NULL" in err()
+    assert pad(1, 1, 4, 8, 16, 1, 0) == -1 and "dims" in err()
+    assert pad(1, 1, 3, 8, 15, 1, 0) == -1 and "even padded box" in err()
+    assert pad(1, 1, 3, 20, 16, 1, 0) == -1 and "n <= m" in err()
+    assert pad(1, 200, 3, 256, 512, 1, 0) == -2 and "split the batch" in err()
+    assert lib.b200proj_ifftshift_crop(1, 1, 2, 16, 20, 1, 0) == -1

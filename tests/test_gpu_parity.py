@@ -339,6 +339,18 @@ def test_persistent_accumulator_matches_oracle_and_partial_volumes_use_it(tp, in
     assert not vols._pending and rel_err(vols.data, dw) <= TOL_ATOMIC and rel_err(vols.weights, ww) <= TOL_ATOMIC
     vols.flush()                                         # nothing pending: a no-op
     assert rel_err(vols.data, dw) <= TOL_ATOMIC
+    # folding range by range (as reduce() does to overlap the collective) gives the same volumes
+    parts = tp.sharding.PartialVolumes(2, 32, "cuda")
+    parts.add_(c(t["proj"]), c(t["rot"]), c(t["weights"]), c(t["shifts"]), interpolation=interp, oversampling=2.0)
+    seen = []
+    parts.flush(parts=3, after_part=lambda first, stop: seen.append((first, stop)))
+    n = parts.data.numel()
+    assert len(seen) == 3 and seen[0][0] == 0 and seen[-1][1] == n and all(a[1] == b[0] for a, b in zip(seen, seen[1:]))
+    assert rel_err(parts.data, dw) <= TOL_ATOMIC and rel_err(parts.weights, ww) <= TOL_ATOMIC
+    parts.reduce()                                       # one process: nothing pending, nothing to reduce
+    assert rel_err(parts.data, dw) <= TOL_ATOMIC
+    half = tp.fold_backprojection_accumulator(acc, voxel_range=(0, n // 2))[0]
+    assert rel_err(half.flatten()[: n // 2], dw.flatten()[: n // 2]) <= TOL_ATOMIC
     # errors: weights are required, shapes are checked
     with pytest.raises(RuntimeError, match="needs weights"):
         tp.backproject_2d_to_3d_accumulate_interleaved_(acc, c(t["proj"]), c(t["rot"]), None, oversampling=2.0)

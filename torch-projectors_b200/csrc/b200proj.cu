@@ -353,16 +353,20 @@ int pad_shift(const Real* in, int64_t batch, int dims, int64_t n, int64_t m, int
         return fail(B200PROJ_ERR_LIMIT, "box %lld / batch %lld beyond what one launch indexes", (long long)m, (long long)batch);
     const int64_t gz = batch * (dims == 3 ? out_box : 1);
     if (gz > 65535) return fail(B200PROJ_ERR_LIMIT, "batch * box = %lld exceeds the grid limit; split the batch", (long long)gz);
-    const dim3 grid((unsigned)((out_box + 255) / 256), (unsigned)out_box, (unsigned)gz);
+    const dim3 grid((unsigned)((out_box + 255) / 256), (unsigned)((out_box + 3) / 4), (unsigned)gz), block(64, 4, 1);
     cudaStream_t s = (cudaStream_t)stream;
     const int lo = (int)((m - n) / 2);
+    // 16-byte stores when every output row starts on a 16-byte boundary
+    const bool vec = (out_box % 4) == 0 && (reinterpret_cast<uintptr_t>(out) & 15u) == 0;
+#define B200PROJ_PS(D, P, V) pad_shift_kernel<D, P, V><<<grid, block, 0, s>>>(in, out, (int)n, (int)m, lo, (int)batch)
     if (dims == 3) {
-        if (pad) pad_shift_kernel<3, true><<<grid, 256, 0, s>>>(in, out, (int)n, (int)m, lo, (long long)batch);
-        else pad_shift_kernel<3, false><<<grid, 256, 0, s>>>(in, out, (int)n, (int)m, lo, (long long)batch);
+        if (pad) { if (vec) B200PROJ_PS(3, true, true); else B200PROJ_PS(3, true, false); }
+        else     { if (vec) B200PROJ_PS(3, false, true); else B200PROJ_PS(3, false, false); }
     } else {
-        if (pad) pad_shift_kernel<2, true><<<grid, 256, 0, s>>>(in, out, (int)n, (int)m, lo, (long long)batch);
-        else pad_shift_kernel<2, false><<<grid, 256, 0, s>>>(in, out, (int)n, (int)m, lo, (long long)batch);
+        if (pad) { if (vec) B200PROJ_PS(2, true, true); else B200PROJ_PS(2, true, false); }
+        else     { if (vec) B200PROJ_PS(2, false, true); else B200PROJ_PS(2, false, false); }
     }
+#undef B200PROJ_PS
     return check_launch("pad_shift launch");
 }
 
@@ -570,17 +574,24 @@ size_t b200proj_accumulator_bytes(int64_t B, int64_t R) {
     return (size_t)B * (size_t)R * (size_t)R * (size_t)(R / 2 + 1) * sizeof(float4);
 }
 
-int b200proj_accumulator_fold(const void* accumulator, int64_t B, int64_t R, float* data_rec,
-                              float* weight_rec, int accumulate, void* stream) {
+int b200proj_accumulator_fold_range(const void* accumulator, int64_t first_voxel, int64_t voxel_count,
+                                    float* data_rec, float* weight_rec, int accumulate, void* stream) {
     g_error[0] = 0;
     if (accumulator == nullptr || data_rec == nullptr || weight_rec == nullptr)
         return fail(B200PROJ_ERR_ARGUMENT, "accumulator, data_reconstruction and weight_reconstruction are all required");
-    if (B < 1 || R < 2 || (R % 2) != 0) return fail(B200PROJ_ERR_ARGUMENT, "batch size must be >= 1 and the boxsize even (B=%lld, R=%lld)", (long long)B, (long long)R);
-    const size_t n = (size_t)B * (size_t)R * (size_t)R * (size_t)(R / 2 + 1);
+    if (first_voxel < 0 || voxel_count < 0) return fail(B200PROJ_ERR_ARGUMENT, "voxel range must be non-negative (first=%lld, count=%lld)", (long long)first_voxel, (long long)voxel_count);
+    if (voxel_count == 0) return B200PROJ_OK;
+    const size_t n = (size_t)voxel_count;
     const size_t blocks = (n + 255) / 256;
     fold_interleaved_kernel<<<(unsigned)(blocks < 148 * 16 ? blocks : 148 * 16), 256, 0, (cudaStream_t)stream>>>(
-        (const float4*)accumulator, (float2*)data_rec, weight_rec, n, accumulate != 0);
+        (const float4*)accumulator + first_voxel, (float2*)data_rec + first_voxel, weight_rec + first_voxel, n, accumulate != 0);
     return check_launch("fold_interleaved launch");
+}
+
+int b200proj_accumulator_fold(const void* accumulator, int64_t B, int64_t R, float* data_rec,
+                              float* weight_rec, int accumulate, void* stream) {
+    if (B < 1 || R < 2 || (R % 2) != 0) return fail(B200PROJ_ERR_ARGUMENT, "batch size must be >= 1 and the boxsize even (B=%lld, R=%lld)", (long long)B, (long long)R);
+    return b200proj_accumulator_fold_range(accumulator, 0, B * R * R * (R / 2 + 1), data_rec, weight_rec, accumulate, stream);
 }
 
 int b200proj_pad_fftshift(const float* real, int64_t batch, int dims, int64_t n, int64_t m, float* out, void* stream) {

@@ -542,30 +542,51 @@ pose_order_kernel(const R* __restrict__ rot, long long rot_stride_b, int P, int*
 //   pad:   out[i...] = in[s(i0), s(i1)(, s(i2))],  s(i) = (i + m/2) mod m - lo,  0 outside [0, n)
 //   crop:  out[j...] = in[t(j0), t(j1)(, t(j2))],  t(j) = (j + lo + m/2) mod m
 // The two are adjoint to each other, which is what autograd needs.
+// Block = 64 x 4 threads: a thread produces 4 consecutive elements of one row (one 16-byte
+// store when VEC: the output rows are then 16-byte aligned), a block 256 elements of 4 rows.
 // Grid: x covers the innermost axis, y the middle axis, z = batch * (outer axis or 1).
-template <int DIMS, bool PAD, typename R>
+__device__ __forceinline__ void store4(float* p, const float (&v)[4]) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+}
+__device__ __forceinline__ void store4(double* p, const double (&v)[4]) {
+    *reinterpret_cast<double2*>(p) = make_double2(v[0], v[1]);
+    *reinterpret_cast<double2*>(p + 2) = make_double2(v[2], v[3]);
+}
+
+template <int DIMS, bool PAD, bool VEC, typename R>
 __global__ void __launch_bounds__(256)
-pad_shift_kernel(const R* __restrict__ in, R* __restrict__ out, int n, int m, int lo, long long batch) {
+pad_shift_kernel(const R* __restrict__ in, R* __restrict__ out, int n, int m, int lo, int batch) {
     const int out_box = PAD ? m : n, in_box = PAD ? n : m;
-    const int i2 = (int)(blockIdx.x * blockDim.x + threadIdx.x);
-    const int i1 = (int)blockIdx.y;
+    const int j0 = (int)(blockIdx.x * 64 + threadIdx.x) * 4;
+    const int i1 = (int)(blockIdx.y * 4 + threadIdx.y);
     const int zi = (int)blockIdx.z;
     const int b = DIMS == 3 ? zi / out_box : zi;
     const int i0 = DIMS == 3 ? zi - b * out_box : 0;
-    if (i2 >= out_box || b >= batch) return;
+    if (j0 >= out_box || i1 >= out_box || b >= batch) return;
     const int half = m / 2;
     auto src = [&](int i) {
         if (PAD) { int s = i + half; if (s >= m) s -= m; return s - lo; }
         int t = i + lo + half; if (t >= m) t -= m; return t;
     };
-    const int s2 = src(i2), s1 = src(i1), s0 = DIMS == 3 ? src(i0) : 0;
-    const size_t o = ((size_t)((long long)b * (DIMS == 3 ? out_box : 1) + i0) * out_box + i1) * out_box + i2;
-    R v = 0;
-    if (!PAD || ((unsigned)s2 < (unsigned)n && (unsigned)s1 < (unsigned)n && (unsigned)s0 < (unsigned)n)) {
-        const size_t k = ((size_t)((long long)b * (DIMS == 3 ? in_box : 1) + s0) * in_box + s1) * in_box + s2;
-        v = PAD ? __ldg(in + k) : __ldcs(in + k);
+    const int s1 = src(i1), s0 = DIMS == 3 ? src(i0) : 0;
+    const bool row_ok = !PAD || ((unsigned)s1 < (unsigned)n && (unsigned)s0 < (unsigned)n);
+    const size_t in_row = ((size_t)((long long)b * (DIMS == 3 ? in_box : 1) + s0) * in_box + s1) * in_box;
+    const size_t o = ((size_t)((long long)b * (DIMS == 3 ? out_box : 1) + i0) * out_box + i1) * out_box + j0;
+    R v[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        v[q] = 0;
+        const int s2 = src(j0 + q);
+        if (row_ok && j0 + q < out_box && (!PAD || (unsigned)s2 < (unsigned)n))
+            v[q] = PAD ? __ldg(in + in_row + s2) : __ldcs(in + in_row + s2);
     }
-    out[o] = v;
+    if (VEC) {
+        store4(out + o, v);
+    } else {
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+            if (j0 + q < out_box) out[o + q] = v[q];
+    }
 }
 
 }  // namespace b200proj

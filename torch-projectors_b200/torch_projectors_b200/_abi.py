@@ -42,6 +42,7 @@ SIGNATURES.update({name + "_f64": sig for name, sig in list(SIGNATURES.items()) 
 # fp32-only entry points of the persistent interleaved accumulator
 SIGNATURES["b200proj_backproject_2d_to_3d_accumulate"] = [_ptr, _ptr] + _COMMON + [_ptr, _ptr]
 SIGNATURES["b200proj_accumulator_fold"] = [_ptr, _i64, _i64, _ptr, _ptr, _int, _ptr]
+SIGNATURES["b200proj_accumulator_fold_range"] = [_ptr, _i64, _i64, _ptr, _ptr, _int, _ptr]
 EXPORTS = list(SIGNATURES) + ["b200proj_version", "b200proj_last_error", "b200proj_rec_boxsize",
                                 "b200proj_backproject_workspace_bytes", "b200proj_accumulator_bytes"]
 
@@ -208,9 +209,13 @@ def backproject_accumulate(proj, weights, rot, shifts, interp, oversampling, cut
           *_geom(B, R, rot, shifts, P, N, interp, oversampling, cutoff), _p(accumulator))
 
 
-def accumulator_fold(accumulator, B, R, data_rec, weight_rec, accumulate):
-    _call("b200proj_accumulator_fold", data_rec, _p(accumulator), int(B), int(R), _p(data_rec), _p(weight_rec),
-          int(bool(accumulate)))
+def accumulator_fold(accumulator, B, R, data_rec, weight_rec, accumulate, voxel_range=None):
+    if voxel_range is None:
+        _call("b200proj_accumulator_fold", data_rec, _p(accumulator), int(B), int(R), _p(data_rec), _p(weight_rec),
+              int(bool(accumulate)))
+    else:
+        _call("b200proj_accumulator_fold_range", data_rec, _p(accumulator), int(voxel_range[0]),
+              int(voxel_range[1] - voxel_range[0]), _p(data_rec), _p(weight_rec), int(bool(accumulate)))
 
 
 def backproject_back(dim, grad_data_rec, grad_weight_rec, proj, rot, shifts, interp, oversampling,

@@ -495,10 +495,12 @@ def backproject_2d_to_3d_accumulate_interleaved_(accumulator: torch.Tensor, proj
 
 
 def fold_backprojection_accumulator(accumulator: torch.Tensor, data_rec: Optional[torch.Tensor] = None,
-                                    weight_rec: Optional[torch.Tensor] = None, accumulate: bool = False):
+                                    weight_rec: Optional[torch.Tensor] = None, accumulate: bool = False,
+                                    voxel_range: Optional[tuple] = None):
     """(data_rec, weight_rec) = the sums held by the accumulator, written into (or, with
     ``accumulate=True``, added to) the given volumes; fresh ones are made when none are given.
-    The accumulator itself is left unchanged."""
+    ``voxel_range=(first, stop)`` folds only that range of the flattened volumes (the rest of the
+    outputs is left as it is).  The accumulator itself is left unchanged."""
     _check(accumulator.is_cuda and accumulator.dtype == torch.float32 and accumulator.dim() == 5
            and accumulator.size(-1) == 4 and accumulator.is_contiguous(), "accumulator must come from new_backprojection_accumulator")
     shape = tuple(accumulator.shape[:-1])
@@ -512,7 +514,11 @@ def fold_backprojection_accumulator(accumulator: torch.Tensor, data_rec: Optiona
     for t, dt, what in ((data_rec, torch.complex64, "data_rec"), (weight_rec, torch.float32, "weight_rec")):
         _check(tuple(t.shape) == shape and t.dtype == dt and t.is_contiguous() and t.device == accumulator.device,
                f"{what} must be a contiguous {dt} tensor of shape {shape}")
-    _abi.accumulator_fold(accumulator, B, R, data_rec, weight_rec, accumulate)
+    if voxel_range is not None:
+        first, stop = int(voxel_range[0]), int(voxel_range[1])
+        _check(0 <= first <= stop <= data_rec.numel(), f"voxel_range {voxel_range} outside the volume of {data_rec.numel()} voxels")
+        voxel_range = (first, stop)
+    _abi.accumulator_fold(accumulator, B, R, data_rec, weight_rec, accumulate, voxel_range)
     return data_rec, weight_rec
 
 

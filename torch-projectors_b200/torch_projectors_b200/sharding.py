@@ -109,25 +109,52 @@ class PartialVolumes:
         else:
             ops.backproject_2d_to_3d_accumulate_(self.data, self.weights, projections, rotations, weights, shifts, **kw)
 
-    def flush(self) -> None:
-        """Fold the interleaved accumulator (if it holds anything) into data / weights."""
+    def _ranges(self, parts: int):
+        n = self.data.numel()
+        step = -(-n // max(1, parts))
+        return [(lo, min(n, lo + step)) for lo in range(0, n, step)]
+
+    def flush(self, parts: int = 1, after_part: Optional[Callable] = None) -> None:
+        """Fold the interleaved accumulator (if it holds anything) into data / weights, in
+        `parts` ranges of voxels; ``after_part(first, stop)`` is called once a range is folded
+        (or, with nothing pending, once per range right away)."""
+        from . import ops
+        for first, stop in self._ranges(parts):
+            if self._pending:
+                ops.fold_backprojection_accumulator(self._accum, self.data, self.weights, accumulate=True,
+                                                    voxel_range=(first, stop))
+            if after_part is not None:
+                after_part(first, stop)
         if self._pending:
-            from . import ops
-            ops.fold_backprojection_accumulator(self._accum, self.data, self.weights, accumulate=True)
             self._accum.zero_()
             self._pending = False
 
-    def reduce(self, dst: Optional[int] = 0, group=None) -> None:
-        """Sum the partial volumes over ranks: onto rank `dst`, or onto every rank when
-        dst is None.  Outside an initialised process group only the pending sums are folded."""
-        self.flush()
+    def reduce(self, dst: Optional[int] = 0, group=None, parts: int = 4) -> None:
+        """Sum the partial volumes over ranks: onto rank `dst`, or onto every rank when dst is
+        None.  The volumes are handled in `parts` ranges: the collective of a range (data and
+        weights of the same voxels) starts on the communication stream as soon as that range is
+        folded, while the next range is folded on the compute stream.  Outside an initialised
+        process group only the pending sums are folded."""
         _, world = _world(group)
         if world == 1:
+            self.flush()
             return
-        if dst is None:
-            dist.all_reduce(self.flat, op=dist.ReduceOp.SUM, group=group)
-        else:
-            dist.reduce(self.flat, dst=dst, op=dist.ReduceOp.SUM, group=group)
+        n = self.data.numel()
+        works = []
+
+        def start(first: int, stop: int) -> None:
+            pieces = [self.flat[2 * first: 2 * stop]]
+            if self.weights is not None:
+                pieces.append(self.flat[2 * n + first: 2 * n + stop])
+            for piece in pieces:
+                if dst is None:
+                    works.append(dist.all_reduce(piece, op=dist.ReduceOp.SUM, group=group, async_op=True))
+                else:
+                    works.append(dist.reduce(piece, dst=dst, op=dist.ReduceOp.SUM, group=group, async_op=True))
+
+        self.flush(parts=parts if self._pending else 1, after_part=start)
+        for w in works:
+            w.wait()
 
 
 def backproject_2d_to_3d_sharded(projections: torch.Tensor, rotations: torch.Tensor,
