@@ -63,3 +63,39 @@ def test_box400_backprojection_subset_against_oracle(tp):
     vols.flush()
     assert rel_err(vols.data, d_want) <= TOL_ATOMIC
     assert rel_err(vols.weights, w_want) <= TOL_ATOMIC
+
+
+def test_offsets_beyond_2_to_the_30_in_a_box_1400_volume(tp):
+    """Maximum-size edge: a 1400^3 half-volume has 1.37e9 voxels (11 GB), so flat offsets use
+    the top of the 31-bit range.  Known answers instead of an oracle: with a quarter turn about x
+    (pixel (kr, kc) samples column 20*kc, row 0, plane 20*kr at oversampling 20) a single voxel
+    in the last planes is read by exactly one pixel, and a single pixel is back-projected onto
+    exactly that voxel."""
+    R, N, os_ = 1400, 70, 20.0
+    free, _ = torch.cuda.mem_get_info()
+    if free < 40 * (1 << 30):
+        pytest.skip("needs 40 GB of free device memory")
+    rot = torch.tensor([[1.0, 0.0, 0.0], [0.0, 0.0, -1.0], [0.0, 1.0, 0.0]], device="cuda").view(1, 1, 3, 3)
+    rec = torch.zeros(1, R, R, R // 2 + 1, dtype=torch.complex64, device="cuda")
+    # plane -100 (index R-100), row 0, column 60  <-  pixel kr = -5 (row N-5), kc = 3
+    rec[0, R - 100, 0, 60] = 2.0 - 3.0j
+    flat = ((R - 100) * R + 0) * (R // 2 + 1) + 60
+    assert flat > 1 << 30
+    for interp in ("linear", "cubic"):
+        out = tp.project_3d_to_2d_forw(rec, rot, output_shape=(N, N), interpolation=interp, oversampling=os_)
+        assert out[0, 0, N - 5, 3] == 2.0 - 3.0j
+        assert out.abs().sum().item() == pytest.approx(abs(2.0 - 3.0j), rel=1e-6)       # nothing else is non-zero
+    grad = torch.zeros(1, 1, N, N // 2 + 1, dtype=torch.complex64, device="cuda")
+    grad[0, 0, N - 5, 3] = 1.0 + 0.5j
+    grad_rec = tp.project_3d_to_2d_back(grad, rec, rot, interpolation="linear", oversampling=os_)
+    assert grad_rec[0, R - 100, 0, 60] == 1.0 + 0.5j and grad_rec.abs().sum().item() == pytest.approx(abs(1.0 + 0.5j), rel=1e-6)
+    del grad_rec, rec
+    # back-projection of that one pixel (slab-ordered: 16.5 GB of data + weight volumes)
+    proj = torch.zeros(1, 1, N, N // 2 + 1, dtype=torch.complex64, device="cuda")
+    proj[0, 0, N - 5, 3] = 4.0 + 1.0j
+    wts = torch.zeros(1, 1, N, N // 2 + 1, device="cuda")
+    wts[0, 0, N - 5, 3] = 0.25
+    data, wrec = tp.backproject_2d_to_3d_forw(proj, rot, weights=wts, interpolation="linear", oversampling=os_)
+    assert data.shape == (1, R, R, R // 2 + 1)
+    assert data[0, R - 100, 0, 60] == 4.0 + 1.0j and wrec[0, R - 100, 0, 60] == 0.25
+    assert data.abs().sum().item() == pytest.approx(abs(4.0 + 1.0j), rel=1e-6) and wrec.sum().item() == pytest.approx(0.25, rel=1e-6)
