@@ -270,12 +270,22 @@ def profile_case(args):
         torch.cuda.synchronize()
         print(f"profile case project_2d: 8 x {P} poses of 256x256, linear, 2 launches done")
         return
-    if args.profile_case == "backproject_slab":
+    if args.profile_case in ("backproject_slab", "accumulate_slab"):
         # 256x256 slices into box-512 volumes (808 MB > L2): the slab-ordered kernel
         gen = torch.Generator(device=dev).manual_seed(5)
         proj = torch.complex(torch.randn(1, P, 256, 129, generator=gen, device=dev), torch.randn(1, P, 256, 129, generator=gen, device=dev))
         weights = torch.rand(1, P, 256, 129, generator=gen, device=dev)
         brot = uniform_rotations(P, torch.Generator().manual_seed(5), dev)
+        if args.profile_case == "accumulate_slab":
+            # the streaming path of the sharded workload: persistent interleaved accumulator
+            from torch_projectors_b200 import sharding
+            vols = sharding.PartialVolumes(1, 512, dev)
+            for _ in range(2):
+                vols.add_(proj, brot, weights, interpolation="linear", oversampling=2.0)
+            vols.flush()
+            torch.cuda.synchronize()
+            print(f"profile case accumulate_slab: {P} slices of 256x256 into the box-512 accumulator, 2 launches + fold done")
+            return
         for _ in range(2):
             tp.backproject_2d_to_3d_forw(proj, brot, weights=weights, interpolation="linear", oversampling=2.0)
         torch.cuda.synchronize()
@@ -681,7 +691,7 @@ def main():
     ap.add_argument("--skip-backproject", action="store_true")
     ap.add_argument("--natural-order", action="store_true",
                     help="process slices in the order given (switch the plane-locality order of beyond-L2 volumes off), for comparisons")
-    ap.add_argument("--profile-case", choices=["project", "backproject", "project_back", "backproject_slab", "autograd_step", "project_2d"], default=None,
+    ap.add_argument("--profile-case", choices=["project", "backproject", "project_back", "backproject_slab", "accumulate_slab", "autograd_step", "project_2d"], default=None,
                     help="run a few launches of one kernel on a reduced pose count (for ncu captures); prints no bench line")
     ap.add_argument("--profile-poses", type=int, default=2048)
     ap.add_argument("--workload", choices=["default", "autograd_step", "sharded_backproject", "ops_table", "reference_cuda", "paper_matrix"], default="default",
