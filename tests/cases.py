@@ -152,3 +152,23 @@ MEDIUM_CASES = [
     Case("2d_lin_private_noweights", 2, "linear", 1, 80, 12, 24, 2.0, 4.5, 1, 0, weights=False, seed=25),
     Case("2d_lin_private_overreach", 2, "linear", 1, 66, 16, 16, 1.5, None, 1, 1, seed=26),
 ]
+
+
+def random_case(k: int) -> Case:
+    """Seeded random small configuration: every combination of the optional arguments, odd
+    oversampling factors, cutoffs from tight to beyond the corners, boxes that leave the volume."""
+    import random
+    rnd = random.Random(1000 + k)
+    dim = rnd.choice([2, 3])
+    interp = rnd.choice(["linear", "cubic"])
+    B = rnd.choice([1, 1, 2, 3])
+    P = rnd.choice([1, 2, 5, 9])
+    N = rnd.choice([2, 4, 6, 10, 14, 18])
+    os_ = rnd.choice([1.0, 1.25, 1.3, 1.5, 2.0, 2.5, 3.0])
+    R = math.ceil(N * os_)
+    R += R % 2                                   # the box back-projection produces (projection accepts any even box)
+    cutoff = rnd.choice([None, None, 1.0, N / 4, N / 2 - 0.5, float(N)])
+    B_rot = rnd.choice([1, B])
+    B_shift = rnd.choice([0, 1, B])
+    return Case(f"random{k}", dim, interp, B, P, N, R, os_, cutoff, B_rot, B_shift, weights=rnd.random() < 0.7,
+                shift_range=rnd.choice([0.5, 3.0]), seed=2000 + k, special_poses=rnd.random() < 0.5)

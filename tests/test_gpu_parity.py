@@ -4,13 +4,14 @@ oracle and with the golden vectors made by the reference's own CPU operators.
 Tolerances (global-normalised max error, see cases.rel_err): 1e-5 for forward projection,
 1e-4 for atomically accumulated back-projection and for all gradients."""
 import glob
+import math
 from pathlib import Path
 
 import pytest
 import torch
 
 from cases import (Case, MEDIUM_CASES, SMALL_CASES, TOL_ATOMIC, TOL_FORWARD, hermitian_dc_column_,
-                   make_inputs, make_rotations, rel_err)
+                   make_inputs, make_rotations, random_case, rel_err)
 from runners import load_golden, run_case, tolerance_for
 
 pytestmark = pytest.mark.gpu
@@ -483,3 +484,10 @@ def test_operators_can_be_captured_in_a_cuda_graph(tp):
         want_d, want_w = tp.backproject_2d_forw(want, rot, weights=wts, shifts=sh, **kw)
         assert torch.equal(g_out, want)
         assert rel_err(g_data, want_d) <= TOL_ATOMIC and rel_err(g_w, want_w) <= TOL_ATOMIC
+
+
+@pytest.mark.parametrize("k", range(48))
+def test_randomised_configurations_match_the_oracle(tp, k):
+    case = random_case(k)
+    t = make_inputs(case)
+    _compare(run_case("cuda", case, t), run_case("port", case, t))

@@ -10,7 +10,7 @@ import torch
 
 import oracle
 from oracle import port
-from cases import SMALL_CASES, make_inputs, rel_err
+from cases import SMALL_CASES, make_inputs, random_case, rel_err
 from runners import load_golden, run_case
 
 GOLDEN = sorted(glob.glob(str(Path(__file__).parent / "golden" / "*.npz")))
@@ -43,6 +43,22 @@ def test_port_matches_reference_ops(case):
     for k in want:
         assert got[k].shape == want[k].shape, k
         assert rel_err(got[k], want[k]) <= PIN_TOL, (k, rel_err(got[k], want[k]))
+
+
+@pytest.mark.skipif(not oracle.reference_available(), reason="oracle/_ref not built")
+@pytest.mark.parametrize("k", range(48))
+def test_port_matches_reference_ops_on_randomised_configurations(k):
+    """48 seeded random small configurations (odd oversampling factors, tight to unbounded
+    cutoffs, every combination of optional arguments and batch broadcasting): the same cases the
+    GPU parity test runs against this oracle."""
+    case = random_case(k)
+    t = make_inputs(case)
+    want = run_case("reference", case, t)
+    got = run_case("port", case, t)
+    assert set(got) == set(want)
+    for key in want:
+        assert got[key].shape == want[key].shape, key
+        assert rel_err(got[key], want[key]) <= PIN_TOL * 2, (case, key, rel_err(got[key], want[key]))
 
 
 @pytest.mark.skipif(not oracle.reference_available(), reason="oracle/_ref not built")
