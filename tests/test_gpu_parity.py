@@ -491,3 +491,15 @@ def test_randomised_configurations_match_the_oracle(tp, k):
     case = random_case(k)
     t = make_inputs(case)
     _compare(run_case("cuda", case, t), run_case("port", case, t))
+
+
+@pytest.mark.parametrize("k", range(0, 48, 3))
+def test_randomised_configurations_in_double_precision(tp, k):
+    case = random_case(k)
+    t = make_inputs(case, cdtype=torch.complex128)
+    got = run_case("cuda", case, t)
+    want = run_case("port", case, t)
+    assert set(got) == set(want)
+    for key in want:
+        assert got[key].dtype == want[key].dtype and got[key].shape == want[key].shape, key
+        assert rel_err(got[key], want[key]) <= F64_TOL, (case, key, rel_err(got[key], want[key]))
