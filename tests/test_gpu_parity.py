@@ -503,3 +503,48 @@ def test_randomised_configurations_in_double_precision(tp, k):
     for key in want:
         assert got[key].dtype == want[key].dtype and got[key].shape == want[key].shape, key
         assert rel_err(got[key], want[key]) <= F64_TOL, (case, key, rel_err(got[key], want[key]))
+
+
+def test_calls_from_several_threads_on_their_own_streams(tp):
+    """The library keeps no shared mutable state between calls (its error text is per thread):
+    four host threads, each on its own stream, run forward and backward passes at once and get
+    the single-threaded results."""
+    import threading
+    case = Case("threads", 3, "cubic", 1, 12, 16, 32, 2.0, None, 1, 1, seed=61)
+    t = {k: (v.cuda() if v is not None else None) for k, v in make_inputs(case).items()}
+    ops = torch.ops.torch_projectors_b200
+
+    def work():
+        rot = t["rot"].clone().requires_grad_(True)
+        sh = t["shifts"].clone().requires_grad_(True)
+        fwd = ops.project_3d_to_2d_forw(t["rec"], rot, sh, [16, 16], "cubic", 2.0, None)
+        back = ops.project_3d_to_2d_back(t["proj"], t["rec"], rot, sh, "cubic", 2.0, None)
+        bp = ops.backproject_2d_to_3d_forw(t["proj"], t["weights"], rot, sh, "cubic", 2.0, None)
+        return [fwd, *back, *bp]
+
+    want = work()
+    torch.cuda.synchronize()
+    results, errors = {}, []
+
+    def runner(i):
+        try:
+            stream = torch.cuda.Stream()
+            stream.wait_stream(torch.cuda.default_stream())
+            with torch.cuda.stream(stream):
+                for _ in range(5):
+                    out = work()
+                stream.synchronize()
+            results[i] = out
+        except Exception as e:  # noqa: BLE001
+            errors.append(e)
+
+    threads = [threading.Thread(target=runner, args=(i,)) for i in range(4)]
+    for th in threads:
+        th.start()
+    for th in threads:
+        th.join()
+    assert not errors, errors
+    for i in range(4):
+        assert torch.equal(results[i][0], want[0])                       # gathers are deterministic
+        for got, ref in zip(results[i][1:], want[1:]):
+            assert rel_err(got, ref) <= TOL_ATOMIC * 0.1
