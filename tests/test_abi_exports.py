@@ -122,3 +122,17 @@ def test_accumulator_and_prep_entries_validate_without_a_device():
     assert pad(1, 1, 3, 20, 16, 1, 0) == -1 and "n <= m" in err()
     assert pad(1, 200, 3, 256, 512, 1, 0) == -2 and "split the batch" in err()
     assert lib.b200proj_ifftshift_crop(1, 1, 2, 16, 20, 1, 0) == -1
+
+
+def test_header_is_plain_c(tmp_path):
+    """The boundary is a C ABI: the header compiles as C99 with no torch, CUDA or C++ in sight."""
+    import shutil
+    import subprocess
+    gcc = shutil.which("gcc")
+    if gcc is None:
+        pytest.skip("no gcc on this machine")
+    src = tmp_path / "use_header.c"
+    src.write_text('#include "b200proj.h"\nint use(void) { return b200proj_version() + B200PROJ_CUBIC + B200PROJ_ERR_LIMIT; }\n')
+    r = subprocess.run([gcc, "-std=c99", "-Wall", "-Wextra", "-pedantic", "-Werror", "-fsyntax-only", f"-I{HEADER.parent}", str(src)],
+                       capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
