@@ -333,7 +333,7 @@ def _dist_setup():
 
 
 def autograd_step_workload(args):
-    """BASELINE config 4: forward + MSE loss + backward, all three gradients; every rank runs
+    """Autograd-step workload (box-512 volume, 4,096 poses): forward + MSE loss + backward, all three gradients; every rank runs
     the same step on its own replica (weak scaling, no collective)."""
     import torch_projectors_b200 as tp
     dist, rank, world, local_rank, dev = _dist_setup()
@@ -407,7 +407,7 @@ def autograd_step_workload(args):
 
 
 def sharded_backprojection_workload(args):
-    """BASELINE config 5: 200,000 box-400 slices split over the ranks (strong scaling), generated
+    """Sharded back-projection workload: 200,000 box-400 slices split over the ranks (strong scaling), generated
     on the device per rank seed in chunks of 8192 outside the timed region; CUDA events around the
     accumulate calls only, plus the final NCCL reduce of the partial volumes."""
     import torch_projectors_b200 as tp
@@ -492,7 +492,7 @@ def sharded_backprojection_workload(args):
 
 def ops_table_workload(args):
     """Device-resident timing of all eight raw operators (slices/s each), linear and cubic, at the
-    sizes of BASELINE configs 1-3: 2D ops on a 128x128 reference (64 px padded 2x), 64x64 output;
+    sizes of the three small benchmark workloads: 2D ops on a 128x128 reference (64 px padded 2x), 64x64 output;
     3D ops on the box-256 volume, 128x128 slices.  One JSON object, one entry per operator."""
     import torch_projectors_b200 as tp
     dist, rank, world, local_rank, dev = _dist_setup()

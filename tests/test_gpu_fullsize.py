@@ -1,4 +1,4 @@
-"""Parity at the full volume sizes of the large BASELINE configurations, on subsets of poses
+"""Parity at the full volume sizes of the two large benchmark workloads, on subsets of poses
 small enough for the CPU oracle: the box-512 volume of the autograd-step workload (cubic,
 forward and all gradients) and the box-400 -> 800^3 back-projection of the sharded workload
 (the slab-ordered kernel with its real slab count)."""
