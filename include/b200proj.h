@@ -58,6 +58,17 @@ const char* b200proj_last_error(void);
  * replaces: csrc/cuda/3d/backprojection_2d_to_3d_kernels.cu:1039-1041 */
 int64_t b200proj_rec_boxsize(int64_t N, double oversampling);
 
+/* Test hook (host only, launches nothing): the result of one of the kernels' index helpers, which
+ * are compiled for host and device from the same source, for a signed voxel coordinate.
+ * which: 0 gather column (linear), 1 gather column (cubic), 2 gather row/plane (linear),
+ * 3 gather row/plane (cubic), 4 scatter column, 5 scatter row/plane.  Gathers clamp (result is
+ * always a valid index), scatters return -1 for a dropped tap.  For the column helpers
+ * *mirrored_out tells whether the Friedel mate is addressed; the row/plane helpers take that flag
+ * as mirrored_in.  Exists so that a CPU test can feed INT_MIN / INT_MAX (what a sample position
+ * beyond +-2^31 saturates to) without running such poses on a GPU.
+ * No counterpart in the reference (its CPU code indexes in int64, csrc/cpu/common/fftw_sampling.h:96-137). */
+int b200proj_debug_index(int which, int R, int coordinate, int mirrored_in, int* mirrored_out);
+
 /* ---- forward projection (gather) -------------------------------------------------------
  * out[b,p,i,j] = interp(rec[b], R_p * os * (j, freq(i)[, 0])) * exp(-2 pi i k.s / N);
  * every stored pixel is written (0 outside the cutoff), so `out` needs no pre-fill.

@@ -57,6 +57,8 @@ int prepare(Launch& L, int dim, int64_t B, int64_t R, int64_t B_rot, const void*
     if (!(oversampling > 0.0) || !std::isfinite(oversampling))
         return fail(B200PROJ_ERR_ARGUMENT, "oversampling must be a positive finite number");
     if (std::isnan(cutoff)) return fail(B200PROJ_ERR_ARGUMENT, "fourier_radius_cutoff is NaN");
+    if ((double)N * oversampling > 1073741824.0)
+        return fail(B200PROJ_ERR_LIMIT, "N * oversampling = %g puts sample coordinates beyond 2^30", (double)N * oversampling);
 
     const int64_t Nh = N / 2 + 1, Rh = R / 2 + 1;
     const int64_t vol = (dim == 3 ? R : 1) * R * Rh;
@@ -434,6 +436,24 @@ size_t b200proj_backproject_workspace_bytes(int dim, int64_t B, int64_t R, int64
 int64_t b200proj_rec_boxsize(int64_t N, double oversampling) {
     const int64_t raw = (int64_t)std::ceil((double)N * oversampling);
     return raw + (raw % 2);
+}
+
+int b200proj_debug_index(int which, int R, int coordinate, int mirrored_in, int* mirrored_out) {
+    SliceGeom g{};
+    g.R = R; g.Rh = R / 2 + 1; g.half = R / 2;
+    bool m = mirrored_in != 0;
+    int r = INT_MIN;
+    switch (which) {
+        case 0: r = gather_col<false>(g, coordinate, m); break;
+        case 1: r = gather_col<true>(g, coordinate, m); break;
+        case 2: r = gather_line<false>(g, coordinate, m); break;
+        case 3: r = gather_line<true>(g, coordinate, m); break;
+        case 4: r = scatter_col(g, coordinate, m); break;
+        case 5: r = scatter_line(g, coordinate, m); break;
+        default: break;
+    }
+    if (mirrored_out != nullptr) *mirrored_out = m ? 1 : 0;
+    return r;
 }
 
 int b200proj_project_2d_forw(const float* rec, int64_t B, int64_t R, const float* rot, int64_t B_rot,

@@ -9,8 +9,9 @@
 //    rounded once, the rotation is separately rounded fp32 multiplies and adds (no FMA),
 //    so floor() and the fractional parts agree bit for bit with the CPU result;
 //  * the phase of the shift ramp is float(double(float(kr*s0 + kc*s1)) * (-2*pi/N))
-//    (csrc/cpu/common/projection_utils.h:82-94), reduced to [-pi, pi] exactly in double and
-//    then evaluated with the hardware sin/cos (fp32) or the library sincos (fp64);
+//    (csrc/cpu/common/projection_utils.h:82-94); fp32: reduced to about [-pi, pi] by a
+//    two-constant Cody-Waite step in fp32 and evaluated with the hardware sin/cos
+//    (see phase_sincos); fp64: the library sincos;
 //  * tap sums are re-associated (separable form); that moves results by ~1e-7 relative.
 #pragma once
 
@@ -221,24 +222,29 @@ __device__ __forceinline__ void axis_weights(R x, AxisWeights<R, T>& a) {
 // reference: csrc/cpu/common/fftw_sampling.h:96-137 and, for cubic, the pre-clamp of
 // csrc/cpu/common/interpolation_kernels.h:331-342.
 
+// Integer min / max usable from host code too (the index helpers below are also compiled for
+// the host, where a unit test feeds them INT_MIN / INT_MAX).
+__host__ __device__ __forceinline__ int imin(int a, int b) { return a < b ? a : b; }
+__host__ __device__ __forceinline__ int imax(int a, int b) { return a > b ? a : b; }
+
 // Column index of signed column c; `mirrored` tells whether the Friedel mate is read.
+// The column is clamped to [-(Rh-1), Rh-1] BEFORE the mirror: for in-range and moderately
+// out-of-range columns that equals "mirror, then clamp to Rh-1" (linear) and the cubic
+// pre-clamp, and it keeps a saturated coordinate (INT_MIN from a sample position at or below
+// -2^31, whose negation is INT_MIN again) from becoming a negative index.
 template <bool CUBIC>
-__device__ __forceinline__ int gather_col(const SliceGeom& g, int c, bool& mirrored) {
-    if (CUBIC) {
-        if (c >= g.Rh) c = g.Rh - 1;
-        if (c <= -g.Rh) c = -(g.Rh - 1);
-    }
+__host__ __device__ __forceinline__ int gather_col(const SliceGeom& g, int c, bool& mirrored) {
+    c = imax(-(g.Rh - 1), imin(c, g.Rh - 1));
     mirrored = c < 0;
-    c = mirrored ? -c : c;
-    return min(c, g.Rh - 1);
+    return mirrored ? -c : c;
 }
 
 // Row / plane index of signed coordinate r, for a tap that is (not) mirrored.
 template <bool CUBIC>
-__device__ __forceinline__ int gather_line(const SliceGeom& g, int r, bool mirrored) {
-    if (CUBIC) r = max(-g.half + 1, min(r, g.half));
-    if (mirrored) r = -r;
-    r = min(g.half, max(r, -g.half + 1));
+__host__ __device__ __forceinline__ int gather_line(const SliceGeom& g, int r, bool mirrored) {
+    if (CUBIC) r = imax(-g.half + 1, imin(r, g.half));
+    if (mirrored) r = -r;                          // INT_MIN stays INT_MIN, which the clamp below catches
+    r = imin(g.half, imax(r, -g.half + 1));
     return r < 0 ? r + g.R : r;
 }
 
@@ -471,10 +477,19 @@ __device__ __forceinline__ void interpolate_any(const SliceGeom& g, const C2<R>*
 // reference: csrc/cpu/common/projection_utils.h:414-493.
 
 // Index of signed row / plane coordinate r for a (non-)mirrored tap, or -1 when dropped.
-__device__ __forceinline__ int scatter_line(const SliceGeom& g, int r, bool mirrored) {
-    if (mirrored) r = -r;
+__host__ __device__ __forceinline__ int scatter_line(const SliceGeom& g, int r, bool mirrored) {
+    if (mirrored) r = -r;                          // INT_MIN stays INT_MIN, which the range test drops
     if (r > g.half || r < -g.half + 1) return -1;
     return r < 0 ? r + g.R : r;
+}
+
+// Stored column of signed column c (Friedel mirror for c < 0; `mirrored` says so), or -1 when
+// the tap is dropped.  The range test comes BEFORE the negation: a sample position at or below
+// -2^31 saturates to INT_MIN, which negation leaves negative.
+__host__ __device__ __forceinline__ int scatter_col(const SliceGeom& g, int c, bool& mirrored) {
+    mirrored = c < 0;
+    if (c <= -g.Rh || c >= g.Rh) return -1;
+    return mirrored ? -c : c;
 }
 
 __device__ __forceinline__ void red_add_v2(float2* addr, float a, float b) {
@@ -546,9 +561,9 @@ __device__ __forceinline__ void scatter_coop(const SliceGeom& g, C2<R>* __restri
         } else {
             wc = q ? fc : 1.f - fc;
         }
-        const bool m = c < 0;
-        c = m ? -c : c;
-        if (c >= g.Rh || wc == 0.f) continue;
+        bool m;
+        c = scatter_col(g, c, m);
+        if (c < 0 || wc == 0.f) continue;
         const R sgn = m ? -1.f : 1.f;
         AxisWeights<R, T> ar, ad;
         axis_weights<T, false>(pr, ar);
@@ -619,13 +634,12 @@ __device__ __forceinline__ R gather_weight_grad(const SliceGeom& g, const R* __r
             R ri = 0.f;
 #pragma unroll
             for (int j = 0; j < 2; ++j) {
-                int c = ac.base + j;
-                const bool m = c < 0;
-                c = m ? -c : c;
+                bool m;
+                const int c = scatter_col(g, ac.base + j, m);
                 R q = 0.f;
                 const int rl = scatter_line(g, ar.base + i, m);
                 const int dl = (DIM == 3) ? scatter_line(g, ad.base + k, m) : 0;
-                if (c < g.Rh && rl >= 0 && dl >= 0) q = __ldg(wv + (dl * plane_stride + rl * g.Rh + c));
+                if (c >= 0 && rl >= 0 && dl >= 0) q = __ldg(wv + (dl * plane_stride + rl * g.Rh + c));
                 ri = rfma(ac.w[j], q, ri);
             }
             pk = rfma(ar.w[i], ri, pk);
