@@ -54,8 +54,20 @@ BACK_BYTES_PER_SLICE = 128 * 65 * 8 + 128 * 65 * 4 + 44 + 2 * (256 * 256 * 129 *
 # DRAM traffic per slice of the dominant kernels (dram__bytes_read.sum + dram__bytes_write.sum) from
 # ncu captures of a smaller launch of the same kernels, scaled by the slices a launch processes
 # (traffic grows in proportion to the slices: the volumes are touched the same way by every slice).
-PROJ_TRAFFIC_PER_SLICE = (48.83e6 + 105.61e6) / 2048      # profiles/project_forw_3d_cubic_box256_2048poses.md
-BACK_TRAFFIC_PER_SLICE = (512.2e6 + 1344.1e6) / 4096      # profiles/backproject_forw_3d_linear_box256_4096slices.md
+PROJ_TRAFFIC_PER_SLICE = (48.7e6 + 105.3e6) / 2048        # profiles/project_forw_3d_cubic_box256_2048poses.md (current kernel)
+BACK_TRAFFIC_PER_SLICE = (497.0e6 + 1301.0e6) / 4096      # profiles/backproject_forw_3d_linear_box256_4096slices.md (lane-pair kernel)
+# The ceilings the kernels actually sit on (from the same summaries): share of the L1TEX data pipe
+# the cubic gather keeps busy.
+PROJ_L1TEX_DATA_PIPE_FRAC = 0.889
+
+
+def reduction_ceiling(taps, ms, pattern):
+    """The ceiling that binds the scatter kernels: reductions retired per second against the rate a
+    microbenchmark of the same access pattern reaches on an L2-resident buffer."""
+    rate = taps / (ms * 1e-3) / 1e9
+    return {"bound": "L2 reduction rate", "achieved": rate, "peak": RED_CEILING_GTAPS[pattern], "unit": "G taps/s",
+            "frac": rate / RED_CEILING_GTAPS[pattern], "pattern": pattern,
+            "peak_source": "python bench.py --workload red_ceiling (profiles/red_ceiling_b200.md)"}
 
 
 def measured_peak_gbs():
@@ -106,12 +118,18 @@ class ClockSampler:
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index):
-        self.index, self.lines, self.proc = index, [], None
+        # nvidia-smi numbers physical GPUs and ignores CUDA_VISIBLE_DEVICES: name the device by its
+        # own UUID so that the sampled GPU is the one the kernels run on
+        self.lines, self.proc = [], None
+        try:
+            self.gpu = "GPU-" + str(torch.cuda.get_device_properties(index).uuid)
+        except Exception:  # noqa: BLE001
+            self.gpu = str(index)
 
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "25"],
+                ["nvidia-smi", f"--id={self.gpu}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "25"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=lambda: self.lines.extend(self.proc.stdout), daemon=True).start()
         except OSError:
@@ -119,7 +137,7 @@ class ClockSampler:
 
     def stop(self):
         if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"], "gpu": self.gpu}
         time.sleep(0.15)
         self.proc.terminate()
         try:
@@ -140,7 +158,7 @@ class ClockSampler:
                 if v.lower().startswith("active"):
                     reasons.add(name)
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(smax) if smax else None,
-                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
+                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons), "gpu": self.gpu}
 
 
 def timed_steps(fn, steps, warmup, flush, barrier):
@@ -168,16 +186,32 @@ def timed_steps(fn, steps, warmup, flush, barrier):
 _CPU_INPUTS = {}
 
 
+def set_all_threads():
+    """All host cores this process may use (torch.distributed.run exports OMP_NUM_THREADS=1)."""
+    try:
+        torch.set_num_threads(max(1, len(os.sched_getaffinity(0))))
+    except (AttributeError, RuntimeError):
+        pass
+    return torch.get_num_threads()
+
+
+def cpu_model():
+    try:
+        for ln in open("/proc/cpuinfo"):
+            if ln.lower().startswith("model name"):
+                return ln.split(":", 1)[1].strip()
+    except OSError:
+        pass
+    import platform
+    return platform.processor() or platform.machine()
+
+
 def run_cpu_sample(kind_wanted="reference"):
     """Time the CPU implementation of the projection workload on a bounded sample: as many of
     the 10,000 poses as take about 10 s, or several passes over all of them on a fast host.
     Returns (slices/s, kind, cores, sample description)."""
     import oracle
-    # all host cores this process may use (torch.distributed.run exports OMP_NUM_THREADS=1)
-    try:
-        torch.set_num_threads(max(1, len(os.sched_getaffinity(0))))
-    except (AttributeError, RuntimeError):
-        pass
+    set_all_threads()
     if "proj" not in _CPU_INPUTS:
         _CPU_INPUTS["proj"] = make_projection_inputs("cpu", seed=1)
     rec, rot, shifts = _CPU_INPUTS["proj"]
@@ -205,6 +239,40 @@ def run_cpu_sample(kind_wanted="reference"):
             f"{n} of the {PROJ['P']} poses of the projection workload, {passes} call(s) of {dt:.1f} s wall each")
 
 
+def _cpu_checker():
+    """(operators, kind): the reference's CPU operators where built, else the C restatement."""
+    import oracle
+    if oracle.reference_available():
+        set_all_threads()
+        return oracle.reference_ops(), "reference"
+    from oracle import port
+    return port, "port"
+
+
+def check_projection_parity(out, rec, rot, shifts, n=64):
+    """n poses of the last timed step's output (the first, the last and seeded random ones)
+    against the CPU reference on the same inputs; runs after the timed region."""
+    from cases import rel_err
+    ops, kind = _cpu_checker()
+    P = rot.shape[1]
+    g = torch.Generator().manual_seed(99)
+    pick = torch.unique(torch.cat([torch.tensor([0, P - 1]), torch.randint(0, P, (n - 2,), generator=g)]))
+    want = ops.project_3d_to_2d_forw(rec.cpu(), rot[:, pick.to(rot.device)].cpu().contiguous(), shifts[:, pick.to(rot.device)].cpu().contiguous(),
+                                     [PROJ["N"], PROJ["N"]], PROJ["interp"], PROJ["os"], PROJ["cutoff"])
+    return {"poses": int(pick.numel()), "against": kind, "max_rel_err": rel_err(out[:, pick.to(out.device)], want), "tol": 1e-5}
+
+
+def check_backprojection_parity(tp, proj, weights, rot, shifts, dev, n=64):
+    """The first n slices of the timed workload back-projected alone by the same entry point
+    (workspace included) against the CPU reference; runs after the timed region."""
+    from cases import rel_err
+    ops, kind = _cpu_checker()
+    sub = [x[:, :n].contiguous() for x in (proj, weights, rot, shifts)]
+    d, w = tp.backproject_2d_to_3d_forw(sub[0], sub[2], weights=sub[1], shifts=sub[3], interpolation=BACK["interp"], oversampling=BACK["os"])
+    d_want, w_want = ops.backproject_2d_to_3d_forw(sub[0].cpu(), sub[1].cpu(), sub[2].cpu(), sub[3].cpu(), BACK["interp"], BACK["os"], None)
+    return {"slices": n, "against": kind, "max_rel_err_data": rel_err(d, d_want), "max_rel_err_weights": rel_err(w, w_want), "tol": 1e-4}
+
+
 def reference_arm(args):
     """Time the reference's CPU operators; rank 0 only."""
     rank = int(os.environ.get("RANK", "0"))
@@ -227,7 +295,7 @@ def reference_arm(args):
         "ms_per_step": 1e3 * PROJ["P"] / value, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
         "config": {"workload": PROJ["name"], "device": "host CPU", "note": "each step is a bounded sample of the poses; ms_per_step is extrapolated to all 10000"},
-        "cpu_baseline": {"value": value, "unit": "slices/s", "cores": cores, "kind": kind, "sample": sample},
+        "cpu_baseline": {"value": value, "unit": "slices/s", "cores": cores, "cpu_model": cpu_model(), "kind": kind, "sample": sample},
         "e2e": {"value": value, "unit": "slices/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -315,6 +383,12 @@ SHARD = dict(name="sharded backproject_2d_to_3d_forw: 200000 slices of 400x400 +
 # read once, gradient volume zero-filled and written): 4.32 GB = 1.055 MB per slice
 STEP_BYTES_PER_SLICE = (2 * 512 * 512 * 257 * 8 + 2 * 4096 * 256 * 129 * 8 + 2 * 512 * 512 * 257 * 8) / 4096
 SHARD_BYTES_PER_SLICE = 400 * 201 * 8 + 400 * 201 * 4 + 44
+SHARD_PIXELS_PER_SLICE = 62_814          # pixels inside the default cutoff of a 400x201 slice that are scattered
+BACK_PIXELS_PER_SLICE = 6_426            # the same for a 128x65 slice
+# Reduction ceilings measured by `bench.py --workload red_ceiling` on B200 (L2-resident buffer,
+# 10^9 reductions per second).
+RED_CEILING_GTAPS = {"one random 16-byte slot per lane": 221.0, "lane pairs on adjacent 16-byte slots": 254.0,
+                     "lane pairs sharing a 32-byte sector": 300.0, "four lanes on four adjacent 8-byte voxels": 489.0}
 
 
 def _dist_setup():
@@ -328,7 +402,9 @@ def _dist_setup():
     dev = torch.device("cuda", local_rank)
     if world > 1 and not dist.is_initialized():
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=dev)
+        opts = dist.ProcessGroupNCCL.Options()
+        opts.is_high_priority_stream = True      # the reduce of finished slabs overlaps the scatter of later ones
+        dist.init_process_group("nccl", device_id=dev, pg_options=opts)
     return dist, rank, world, local_rank, dev
 
 
@@ -406,29 +482,49 @@ def autograd_step_workload(args):
         dist.destroy_process_group()
 
 
-def sharded_backprojection_workload(args):
-    """Sharded back-projection workload: 200,000 box-400 slices split over the ranks (strong scaling), generated
-    on the device per rank seed in chunks of 8192 outside the timed region; CUDA events around the
-    accumulate calls only, plus the final NCCL reduce of the partial volumes."""
+def run_sharded_backprojection(dist, rank, world, local_rank, dev, total, overlap_tail=True, check_slices=0):
+    """Sharded back-projection workload: `total` box-400 slices split over the ranks (strong scaling),
+    generated on the device per rank seed in chunks of 8192 outside the timed region; CUDA events
+    around the accumulate calls, then the final stage: the rank's last chunk(s), scattered slab by
+    slab while finished slabs are folded and reduced onto rank 0 (NCCL) on a second stream.
+    Returns the result dict (meaningful on rank 0)."""
     import torch_projectors_b200 as tp
     from torch_projectors_b200 import sharding
-    dist, rank, world, local_rank, dev = _dist_setup()
-    total = args.total_slices or SHARD["P_total"]
     lo, hi = sharding.pose_range(total, rank, world)
     N, Nh = SHARD["N"], SHARD["N"] // 2 + 1
     R = tp._abi.rec_boxsize(N, 2.0)
+    kw = dict(interpolation="linear", oversampling=2.0)
     vols = sharding.PartialVolumes(1, R, dev, with_weights=True)
+    vols.timing = True
     gen = torch.Generator(device=dev).manual_seed(900 + rank)
     cgen = torch.Generator().manual_seed(900 + rank)
     # untimed warm-up: the first launch of a kernel pays for loading it (tens of ms when eight
-    # processes do so at once); a few slices into the volumes, which are then cleared again
+    # processes do so at once), and the first collective for its set-up; a few slices through both
+    # stages, then the volumes are cleared again
     wp = torch.complex(torch.randn(1, 64, N, Nh, generator=gen, device=dev), torch.randn(1, 64, N, Nh, generator=gen, device=dev))
+    wrot = uniform_rotations(64, cgen, dev)
     for _ in range(3):
-        vols.add_(wp, uniform_rotations(64, cgen, dev), wp.real.abs().contiguous(), None, interpolation="linear", oversampling=2.0)
-    vols.flush()
+        vols.add_(wp, wrot, wp.real.abs().contiguous(), None, **kw)
+    vols.add_(wp, wrot, wp.real.abs().contiguous(), None, final=True, **kw)
+    vols.reduce(dst=0)
     vols.flat.zero_()
+    vols._flat_zero = True
+    vols._accumulator()                  # clears the accumulator now, outside the timed region
     del wp
-    op_ms = 0.0
+
+    def make_chunk(n):
+        proj = torch.complex(torch.randn(1, n, N, Nh, generator=gen, device=dev), torch.randn(1, n, N, Nh, generator=gen, device=dev))
+        weights = torch.rand(1, n, N, Nh, generator=gen, device=dev)
+        rot = uniform_rotations(n, cgen, dev)
+        shifts = ((torch.rand(1, n, 2, generator=cgen) * 2 - 1) * SHARD["shift"]).to(dev)
+        return proj, weights, rot, shifts
+
+    spans = [(c0, min(hi, c0 + SHARD["chunk"])) for c0 in range(lo, hi, SHARD["chunk"])]
+    n_final = 1
+    if overlap_tail and len(spans) >= 2 and spans[-1][1] - spans[-1][0] < SHARD["chunk"] // 2:
+        n_final = 2                        # a short last chunk joins the one before it
+    if not overlap_tail:
+        n_final = 0
     chunk_ms = []
     sampler = ClockSampler(local_rank)
     sampler.start()
@@ -436,56 +532,96 @@ def sharded_backprojection_workload(args):
         dist.barrier()
     torch.cuda.synchronize()
     launches = 0
-    for c0 in range(lo, hi, SHARD["chunk"]):
-        n = min(SHARD["chunk"], hi - c0)
-        proj = torch.complex(torch.randn(1, n, N, Nh, generator=gen, device=dev), torch.randn(1, n, N, Nh, generator=gen, device=dev))
-        weights = torch.rand(1, n, N, Nh, generator=gen, device=dev)
-        rot = uniform_rotations(n, cgen, dev)
-        shifts = ((torch.rand(1, n, 2, generator=cgen) * 2 - 1) * SHARD["shift"]).to(dev)
+    for c0, c1 in spans[: len(spans) - n_final]:
+        proj, weights, rot, shifts = make_chunk(c1 - c0)
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
-        vols.add_(proj, rot, weights, shifts, interpolation="linear", oversampling=2.0)
+        vols.add_(proj, rot, weights, shifts, **kw)
         b.record()
         torch.cuda.synchronize()
-        op_ms += a.elapsed_time(b)
         chunk_ms.append(a.elapsed_time(b))
         launches += 1
         del proj, weights
-    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    # the final stage's slices: generated chunk by chunk like the others, then handed over as one tensor
+    final = None
+    if n_final:
+        parts = [make_chunk(c1 - c0) for c0, c1 in spans[len(spans) - n_final:]]
+        final = tuple(torch.cat([p[k] for p in parts], dim=1) for k in range(4)) if len(parts) > 1 else parts[0]
+        del parts
+    torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     a.record()
-    # fold the interleaved accumulator into the data / weight volumes and reduce them onto rank 0:
-    # range by range, the collective of a folded range overlapping the fold of the next
+    if final is not None:
+        vols.add_(final[0], final[2], final[1], final[3], final=True, **kw)
     vols.reduce(dst=0)
     b.record()
     torch.cuda.synchronize()
-    reduce_ms = a.elapsed_time(b)
     clocks = sampler.stop()
-    t = torch.tensor([op_ms, reduce_ms], dtype=torch.float64, device=dev)
-    rank_ms = [op_ms]
+    final_ms = a.elapsed_time(b)
+    # the part of the final stage after its last scatter launch has finished: fold + reduce left exposed
+    tail_ms = vols.last_scatter_done.elapsed_time(b) if (final is not None and vols.last_scatter_done is not None) else final_ms
+    launches += (vols.slab_groups if final is not None else 0) + 1
+    scatter_ms = sum(chunk_ms) + (final_ms - tail_ms)
+    t = torch.tensor([scatter_ms + tail_ms, scatter_ms, tail_ms], dtype=torch.float64, device=dev)
+    rank_ms = [scatter_ms]
     if world > 1:
         gathered = [torch.zeros_like(t) for _ in range(world)]
         dist.all_gather(gathered, t)
-        rank_ms = [float(x[0]) for x in gathered]
+        rank_ms = [float(x[1]) for x in gathered]
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    op_ms, reduce_ms = float(t[0]), float(t[1])
-    total_ms = op_ms + reduce_ms
+    total_ms, scatter_ms, tail_ms = float(t[0]), float(t[1]), float(t[2])
     peak, peak_kind = measured_peak_gbs()
-    per_rank = (hi - lo)
-    achieved = (SHARD_BYTES_PER_SLICE * per_rank + 2 * vols.flat.numel() * 4) / (op_ms * 1e-3) / 1e9
+    per_rank = hi - lo
+    achieved = (SHARD_BYTES_PER_SLICE * per_rank + 2 * vols.flat.numel() * 4) / (total_ms * 1e-3) / 1e9
+    taps = per_rank * SHARD_PIXELS_PER_SLICE * 8
+    parity = None
+    if rank == 0 and check_slices and final is not None:
+        parity = check_sharded_parity(final, check_slices, dev)
+    return {
+        "metric": "Fourier slices/sec (sharded backproject_2d_to_3d_forw, box 400 -> 800, 2x oversampling)",
+        "value": total / (total_ms * 1e-3), "unit": "slices/s", "n_gpus": world, "steps": 1, "warmup": 3,
+        "ms_per_step": total_ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": SHARD["name"], "total_slices": total, "slices_per_rank": per_rank,
+                   "final_stage_slices": (final[0].shape[1] if final is not None else 0),
+                   "timing": "per rank: sum of CUDA-event times of the accumulate calls + the final stage (last chunks scattered slab by slab, "
+                             "finished slabs folded and reduced on a second stream meanwhile), max over ranks; chunk generation excluded",
+                   "l2": "each 8192-slice chunk (7.9 GB) and the 3.1 GB volumes exceed L2"},
+        "scatter_ms": scatter_ms, "fold_and_reduce_ms": tail_ms, "scatter_ms_per_rank": rank_ms, "chunk_ms_rank0": chunk_ms,
+        "final_stage_ms_rank0": final_ms,
+        "roofline": {"bound": "hbm", "kernel": "backproject_slab_kernel<linear,weights,interleaved> (+ fold_interleaved_kernel, NCCL reduce)",
+                     "achieved": achieved, "peak": peak, "peak_source": peak_kind, "unit": "GB/s", "frac": achieved / peak,
+                     "traffic": None, "launch_ms": total_ms,
+                     "secondary": reduction_ceiling(taps, scatter_ms, "lane pairs on adjacent 16-byte slots")},
+        "parity_check": parity,
+        "gpu_launches": launches, "clocks": clocks}
+
+
+def check_sharded_parity(final, n, dev):
+    """The first n slices of the final stage once more, alone, through the same slab-by-slab path,
+    against the CPU reference on the same slices (outside every timed region)."""
+    from cases import rel_err
+    from torch_projectors_b200 import sharding
+    import torch_projectors_b200 as tp
+    proj, weights, rot, shifts = (x[:, :n].contiguous() for x in final)
+    R = tp._abi.rec_boxsize(SHARD["N"], 2.0)
+    vols = sharding.PartialVolumes(1, R, dev, with_weights=True)
+    vols.add_(proj, rot, weights, shifts, interpolation="linear", oversampling=2.0, final=True)
+    vols.flush()
+    torch.cuda.synchronize()
+    ops, kind = _cpu_checker()
+    d_want, w_want = ops.backproject_2d_to_3d_forw(proj.cpu(), weights.cpu(), rot.cpu(), shifts.cpu(), "linear", 2.0, None)
+    return {"slices": n, "against": kind, "max_rel_err_data": rel_err(vols.data, d_want),
+            "max_rel_err_weights": rel_err(vols.weights, w_want), "tol": 1e-4}
+
+
+def sharded_backprojection_workload(args):
+    dist, rank, world, local_rank, dev = _dist_setup()
+    res = run_sharded_backprojection(dist, rank, world, local_rank, dev, args.total_slices or SHARD["P_total"],
+                                     overlap_tail=not args.no_overlap_tail, check_slices=0 if args.skip_cpu else 32)
     if rank == 0:
-        print(json.dumps({
-            "metric": "Fourier slices/sec (sharded backproject_2d_to_3d_forw, box 400 -> 800, 2x oversampling)",
-            "value": total / (total_ms * 1e-3), "unit": "slices/s", "n_gpus": world, "steps": 1, "warmup": 3,
-            "ms_per_step": total_ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": SHARD["name"], "total_slices": total, "slices_per_rank": per_rank,
-                       "timing": "sum of CUDA-event times of the accumulate calls (max over ranks) + final fold of the accumulator pipelined with the NCCL reduce; chunk generation excluded",
-                       "l2": "each 8192-slice chunk (7.9 GB) and the 3.1 GB volumes exceed L2"},
-            "scatter_ms": op_ms, "fold_and_reduce_ms": reduce_ms, "scatter_ms_per_rank": rank_ms, "chunk_ms_rank0": chunk_ms,
-            "roofline": {"bound": "hbm", "kernel": "backproject_slab_kernel<linear,weights,interleaved> + fold", "achieved": achieved, "peak": peak,
-                         "peak_source": peak_kind, "unit": "GB/s", "frac": achieved / peak, "traffic": None, "launch_ms": op_ms},
-            "gpu_launches": launches, "clocks": clocks}), flush=True)
+        print(json.dumps(res), flush=True)
     if world > 1:
         dist.destroy_process_group()
 
@@ -697,6 +833,8 @@ def main():
     ap.add_argument("--workload", choices=["default", "autograd_step", "sharded_backproject", "ops_table", "reference_cuda", "paper_matrix"], default="default",
                     help="default: projection (+ back-projection) headline line; the other two print their own line")
     ap.add_argument("--total-slices", type=int, default=0, help="sharded_backproject: total slices over all ranks (default 200000)")
+    ap.add_argument("--no-overlap-tail", action="store_true", help="sharded_backproject: fold and reduce after the last chunk instead of overlapping them with it")
+    ap.add_argument("--skip-sharded", action="store_true", help="default workload: leave the sharded box-400 back-projection out (quick runs)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
 
@@ -769,7 +907,14 @@ def main():
     roofline = {"bound": "hbm", "kernel": "project_forw_kernel<3,cubic>", "achieved": achieved, "peak": peak,
                 "peak_source": peak_kind, "unit": "GB/s", "frac": achieved / peak,
                 "traffic": (PROJ_TRAFFIC_PER_SLICE * PROJ["P"]) if PROJ_TRAFFIC_PER_SLICE else None,
-                "algorithmic_bytes_per_launch": PROJ_BYTES_PER_SLICE * PROJ["P"], "launch_ms": kernel_ms}
+                "algorithmic_bytes_per_launch": PROJ_BYTES_PER_SLICE * PROJ["P"], "launch_ms": kernel_ms,
+                "secondary": {"bound": "L1TEX data pipe (64 taps x 8 B per pixel, volume L2-resident)",
+                              "frac": PROJ_L1TEX_DATA_PIPE_FRAC, "unit": "l1tex__data_pipe_lsu_wavefronts, fraction of peak",
+                              "gather_taps_per_s": 6490 * 64 * PROJ["P"] / (kernel_ms * 1e-3),
+                              "peak_source": "ncu capture, profiles/project_forw_3d_cubic_box256_2048poses.md"}}
+    parity = None
+    if rank == 0 and not args.skip_cpu:
+        parity = check_projection_parity(out_holder["out"], rec, rot, shifts)
 
     # ---- projection end to end: pinned host inputs in, projections back to the host ----
     h_rec = rec.cpu().pin_memory()
@@ -804,6 +949,8 @@ def main():
         ws_bytes = tp._abi.backproject_workspace_bytes(3, 1, R, BACK["P"], BACK["N"], tp._abi.LINEAR, True)
         workspace = torch.empty(ws_bytes, dtype=torch.uint8, device=dev) if ws_bytes else None
         scatter_ev = []
+        back_kernel_name = ("memset(workspace) + backproject_forw_interleaved_kernel<3,linear> + fold_interleaved_kernel" if workspace is not None
+                            else "memset(volumes) + backproject_forw_kernel<3,linear,weights>")
 
         def back_step():
             # zero-fill + scatter (one library call), then the cross-rank reduce when N > 1
@@ -822,19 +969,31 @@ def main():
         back = {"metric": "Fourier slices/sec (backproject_2d_to_3d_forw, box 256, 2x oversampling)",
                 "value": world * BACK["P"] / (bms_per_step * 1e-3), "unit": "slices/s", "ms_per_step": bms_per_step,
                 "config": {"workload": BACK["name"], "collective": "NCCL reduce of data+weight partial volumes to rank 0" if world > 1 else "none"},
-                "roofline": {"bound": "hbm", "kernel": "memset + backproject_forw_kernel<3,linear,weights>", "achieved": bach,
+                "roofline": {"bound": "hbm", "kernel": back_kernel_name, "achieved": bach,
                              "peak": peak, "peak_source": peak_kind, "unit": "GB/s", "frac": bach / peak,
                              "traffic": (BACK_TRAFFIC_PER_SLICE * BACK["P"]) if BACK_TRAFFIC_PER_SLICE else None,
-                             "algorithmic_bytes_per_launch": BACK_BYTES_PER_SLICE * BACK["P"], "launch_ms": scat}}
+                             "algorithmic_bytes_per_launch": BACK_BYTES_PER_SLICE * BACK["P"], "launch_ms": scat,
+                             "secondary": reduction_ceiling(BACK["P"] * BACK_PIXELS_PER_SLICE * 8, scat,
+                                                            "lane pairs on adjacent 16-byte slots" if workspace is not None else "lane pairs sharing a 32-byte sector")}}
+        if rank == 0 and not args.skip_cpu:
+            back["parity_check"] = check_backprojection_parity(tp, proj, weights, brot, bshifts, dev)
         launches += (args.steps + args.warmup) * (2 if workspace is not None else 1)     # scatter (+ fold)
         del proj, weights
+        torch.cuda.empty_cache()
+
+    # ---- sharded back-projection (box 400 -> 800, strong scaling over the ranks) ---------
+    sharded = None
+    if not args.skip_sharded:
+        sharded = run_sharded_backprojection(dist, rank, world, local_rank, dev, args.total_slices or SHARD["P_total"],
+                                             check_slices=0 if args.skip_cpu else 32)
+        launches += sharded["gpu_launches"]
         torch.cuda.empty_cache()
 
     # ---- CPU baseline (rank 0, single-GPU runs only) ------------------------------------
     cpu = None
     if rank == 0 and world == 1 and not args.skip_cpu:
         v, kind, cores, sample = run_cpu_sample("reference")
-        cpu = {"value": v, "unit": "slices/s", "cores": cores, "kind": kind, "sample": sample}
+        cpu = {"value": v, "unit": "slices/s", "cores": cores, "cpu_model": cpu_model(), "kind": kind, "sample": sample}
 
     if rank == 0:
         line = {
@@ -845,7 +1004,7 @@ def main():
             "config": {"workload": PROJ["name"], "poses_per_gpu": PROJ["P"], "parallelism": f"poses sharded over {world} GPU(s), volume replicated",
                        "l2": "flushed before every step (256 MiB memset outside the timed events)"},
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches, "clocks": clocks,
-            "backproject": back,
+            "parity_check": parity, "backproject": back, "sharded_backproject": sharded,
         }
         print(json.dumps(line), flush=True)
     if world > 1:

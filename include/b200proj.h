@@ -50,6 +50,11 @@ extern "C" {
 /* Library version (major*10000 + minor*100 + patch). */
 int b200proj_version(void);
 
+/* Hash of the sources (this header and the kernel files) the library was built from, as the
+ * build script passed it in; "" for a build that did not.  A binding compares it with the hash
+ * of the sources it was written against and refuses a library built from other ones. */
+const char* b200proj_source_stamp(void);
+
 /* Message of the calling thread's last failing call ("" if none). */
 const char* b200proj_last_error(void);
 
@@ -216,6 +221,31 @@ int b200proj_accumulator_fold(const void* accumulator, int64_t B, int64_t R, flo
  * range to a collective while the next one is folded. */
 int b200proj_accumulator_fold_range(const void* accumulator, int64_t first_voxel, int64_t voxel_count,
                                     float* data_rec, float* weight_rec, int accumulate, void* stream);
+
+/* Slab by slab.  An accumulator larger than L2 is filled by slab-ordered passes: the planes of
+ * the volume (signed coordinate z = -R/2+1 .. R/2, stored at index z < 0 ? z + R : z) are cut
+ * into `slabs` runs of `planes_per_slab` consecutive z, and a pass issues only the reductions
+ * that land in its own slab.  b200proj_accumulator_slab_plan reports the cut (slabs = 1: the
+ * accumulator is small enough to be scattered in one pass).
+ * b200proj_backproject_2d_to_3d_accumulate_slabs does the work of
+ * b200proj_backproject_2d_to_3d_accumulate for slabs [slab_first, slab_first + slab_count) only:
+ * calling it for every slab once, in any order and grouping, adds exactly what the one-call form
+ * adds.  Once a slab's pass has run for the caller's last slices, the voxels
+ * b200proj_accumulator_slab_voxels reports for it (at most two ranges per batch item, relative to
+ * the batch item's first voxel: planes with negative and with non-negative coordinates) are
+ * final, so they can be folded (b200proj_accumulator_fold_range) and handed to a collective on
+ * another stream while later slabs are still being scattered.  This is how the reduce of
+ * multi-GPU partial volumes is overlapped with the tail of the scatter. */
+int b200proj_accumulator_slab_plan(int64_t R, int32_t* slabs, int32_t* planes_per_slab);
+int b200proj_backproject_2d_to_3d_accumulate_slabs(const float* proj, const float* weights, int64_t B,
+                                                   int64_t R, const float* rot, int64_t B_rot,
+                                                   const float* shifts, int64_t B_shift,
+                                                   int64_t P, int64_t N, int interpolation,
+                                                   double oversampling, double fourier_radius_cutoff,
+                                                   void* accumulator, int slab_first, int slab_count,
+                                                   void* stream);
+int b200proj_accumulator_slab_voxels(int64_t R, int slab_first, int slab_count,
+                                     int64_t first_voxel[2], int64_t voxel_count[2]);
 
 /* ---- the steps either side of the operators ----------------------------------------------
  * No raw-operator counterpart in the reference, which does them with torch calls in its README

@@ -24,6 +24,21 @@ def _ops_for(backend: str):
     raise ValueError(backend)
 
 
+def cpu_checker():
+    """(operators, kind) of the strongest CPU checker present: the reference's own CPU operators
+    (multi-threaded; oracle/_ref, where built) or else the C restatement of them."""
+    import oracle
+    if oracle.reference_available():
+        try:
+            import os
+            torch.set_num_threads(max(1, len(os.sched_getaffinity(0))))
+        except (AttributeError, RuntimeError):
+            pass
+        return oracle.reference_ops(), "reference"
+    from oracle import port
+    return port, "port"
+
+
 def run_case(backend: str, case: Case, t: dict, which=("fwd", "pb", "bp", "bb")) -> dict:
     ops = _ops_for(backend)
     d = "2d" if case.dim == 2 else "3d_to_2d"

@@ -208,27 +208,46 @@ def _cfg2_inputs(P, seed=2):
 
 
 def test_full_size_projection_config(tp):
-    """Box-256 2x-oversampled volume, 128x128 output, cubic, cutoff 64 (the headline
-    projection workload): a subset of poses against the oracle, plus linearity."""
-    from oracle import port
-    P = 512
+    """Box-256 2x-oversampled volume, 10,000 poses, 128x128 output, cubic, cutoff 64 (the headline
+    projection workload at its full pose count): the first, the last and 256 random poses against
+    the CPU reference, plus linearity in the volume."""
+    from runners import cpu_checker
+    ops, _ = cpu_checker()
+    P = 10_000
     rec, rot, shifts = _cfg2_inputs(P)
     kw = dict(output_shape=(128, 128), interpolation="cubic", oversampling=2.0, fourier_radius_cutoff=64.0)
     out = tp.project_3d_to_2d_forw(rec.cuda(), rot.cuda(), shifts.cuda(), **kw)
-    pick = torch.tensor([0, 1, 17, 255, 511])
-    want = port.project_3d_to_2d_forw(rec, rot[:, pick], shifts[:, pick], [128, 128], "cubic", 2.0, 64.0)
+    pick = torch.unique(torch.cat([torch.tensor([0, P - 1]), torch.randint(0, P, (256,), generator=torch.Generator().manual_seed(8))]))
+    want = ops.project_3d_to_2d_forw(rec, rot[:, pick].contiguous(), shifts[:, pick].contiguous(), [128, 128], "cubic", 2.0, 64.0)
     assert rel_err(out[:, pick.cuda()], want) <= TOL_FORWARD
-    # linearity in the volume: P(a*x + y) = a*P(x) + P(y)
+    # linearity in the volume on a subset of the poses: P(a*x + y) = a*P(x) + P(y)
+    sub = slice(0, 512)
     rec2 = torch.roll(rec, 3, dims=1).cuda()
-    lhs = tp.project_3d_to_2d_forw(2.5 * rec.cuda() + rec2, rot.cuda(), shifts.cuda(), **kw)
-    rhs = 2.5 * out + tp.project_3d_to_2d_forw(rec2, rot.cuda(), shifts.cuda(), **kw)
+    lhs = tp.project_3d_to_2d_forw(2.5 * rec.cuda() + rec2, rot[:, sub].cuda(), shifts[:, sub].cuda(), **kw)
+    rhs = 2.5 * out[:, sub] + tp.project_3d_to_2d_forw(rec2, rot[:, sub].cuda(), shifts[:, sub].cuda(), **kw)
     assert rel_err(lhs, rhs) <= TOL_FORWARD
+
+
+def test_medium_case_directly_against_the_reference_operators(tp):
+    """No restatement in between: the CUDA operators against the reference's own CPU operators
+    (oracle/_ref, compiled from its sources) on a medium case, all eight operators."""
+    import oracle
+    if not oracle.reference_available():
+        pytest.skip("oracle/_ref is not built on this machine")
+    case = Case("direct_ref", 3, "cubic", 2, 12, 32, 64, 2.0, 14.0, 2, 2, shift_range=5.0, seed=31, special_poses=True)
+    t = make_inputs(case)
+    got = run_case("cuda", case, t)
+    want = run_case("reference", case, t)
+    assert set(got) == set(want)
+    for key in want:
+        assert rel_err(got[key], want[key]) <= tolerance_for(key), key
 
 
 def test_full_size_backprojection_config(tp):
     """128x128 slices into a box-256 volume, linear, with weights (the headline
-    back-projection workload): a subset against the oracle, chunk additivity, linearity."""
-    from oracle import port
+    back-projection workload): 512 slices against the CPU reference, chunk additivity, linearity."""
+    from runners import cpu_checker
+    ops, _ = cpu_checker()
     P = 2048
     gen = torch.Generator().manual_seed(3)
     proj = torch.complex(torch.randn(1, P, 128, 65, generator=gen), torch.randn(1, P, 128, 65, generator=gen))
@@ -239,9 +258,10 @@ def test_full_size_backprojection_config(tp):
     c = lambda x: x.cuda()  # noqa: E731
     d_all, w_all = tp.backproject_2d_to_3d_forw(c(proj), c(rot), weights=c(weights), shifts=c(shifts), oversampling=2.0)
     assert d_all.shape == (1, 256, 256, 129) and w_all.shape == (1, 256, 256, 129)
-    n = 48
+    n = 512
     d_sub, w_sub = tp.backproject_2d_to_3d_forw(c(proj[:, :n]), c(rot[:, :n]), weights=c(weights[:, :n]), shifts=c(shifts[:, :n]), oversampling=2.0)
-    d_want, w_want = port.backproject_2d_to_3d_forw(proj[:, :n], weights[:, :n], rot[:, :n], shifts[:, :n], "linear", 2.0)
+    d_want, w_want = ops.backproject_2d_to_3d_forw(proj[:, :n].contiguous(), weights[:, :n].contiguous(), rot[:, :n].contiguous(),
+                                                   shifts[:, :n].contiguous(), "linear", 2.0, None)
     assert rel_err(d_sub, d_want) <= TOL_ATOMIC and rel_err(w_sub, w_want) <= TOL_ATOMIC
     d_rest, w_rest = tp.backproject_2d_to_3d_forw(c(proj[:, n:]), c(rot[:, n:]), weights=c(weights[:, n:]), shifts=c(shifts[:, n:]), oversampling=2.0)
     assert rel_err(d_sub + d_rest, d_all) <= TOL_ATOMIC and rel_err(w_sub + w_rest, w_all) <= TOL_ATOMIC

@@ -166,6 +166,51 @@ def test_sharded_pipeline_on_two_gloo_ranks(tmp_path):
     assert all((tmp_path / f"ok{r}").exists() for r in range(world))
 
 
+def _gloo_failure_worker(rank, world, port, tmp):
+    import datetime
+    import time
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    sys.path[:0] = [str(ROOT), str(ROOT / "tests"), str(ROOT / "torch-projectors_b200")]
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=10))
+    vols = sharding.PartialVolumes(1, 8, "cpu", with_weights=True)
+    vols.data += 1.0
+    dist.barrier()
+    if rank == 1:
+        # this rank fails on the host before the collective (an exception in its own work) and leaves
+        try:
+            raise RuntimeError("injected failure before reduce")
+        except RuntimeError:
+            Path(tmp, "rank1_failed").write_text("left before reduce")
+            return
+    t0 = time.time()
+    try:
+        vols.reduce(dst=0)
+        outcome = "no error"
+    except Exception as e:  # noqa: BLE001
+        outcome = f"error {type(e).__name__}"
+    Path(tmp, "rank0_outcome").write_text(f"{outcome}|{time.time() - t0:.1f}")
+
+
+def test_reduce_ends_with_an_error_when_a_rank_left_before_it(tmp_path):
+    """Failure on the host, no GPU involved: rank 1 raises in its own work and never joins the
+    reduce of the partial volumes; rank 0 must come back from reduce() with an error within the
+    process group's timeout instead of waiting for ever."""
+    world = 2
+    ctx = mp.spawn(_gloo_failure_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=False)
+    deadline = 90
+    import time
+    t0 = time.time()
+    while not ctx.join(timeout=1.0) and time.time() - t0 < deadline:
+        pass
+    for proc in ctx.processes:
+        if proc.is_alive():
+            proc.terminate()
+    assert (tmp_path / "rank1_failed").exists()
+    outcome, seconds = (tmp_path / "rank0_outcome").read_text().split("|")
+    assert outcome.startswith("error"), outcome
+    assert float(seconds) < 60.0
+
+
 def test_sharding_without_process_group_is_single_rank():
     calls = []
 

@@ -123,18 +123,30 @@ int zero_async(void* p, size_t bytes, cudaStream_t s) {
 
 // Slab plan of the slab-ordered 3D back-projection: volumes whose data (+ weight) planes of
 // one batch item exceed `min_mb` are processed in slabs of at most `slab_mb` MB of planes.
-// Tunable for experiments through B200PROJ_SLAB_MB / B200PROJ_SLAB_MIN_MB (read once).
+// Tunable for experiments through B200PROJ_SLAB_MB / B200PROJ_SLAB_MIN_MB (12- and 8-byte voxels)
+// and B200PROJ_SLAB_MIN_MB_INTERLEAVED (16-byte voxels), read once.
 struct SlabPlan { int slabs, planes; };
 SlabPlan slab_plan(int64_t R, bool has_weights, bool interleaved = false) {
     static const double slab_mb = [] { const char* e = getenv("B200PROJ_SLAB_MB"); return e ? atof(e) : 64.0; }();
     static const double min_mb = [] { const char* e = getenv("B200PROJ_SLAB_MIN_MB"); return e ? atof(e) : 160.0; }();
+    static const double min_mb_i = [] { const char* e = getenv("B200PROJ_SLAB_MIN_MB_INTERLEAVED"); return e ? atof(e) : min_mb; }();
     const double plane_bytes = (double)R * (double)(R / 2 + 1) * (interleaved ? 16.0 : has_weights ? 12.0 : 8.0);
-    if (slab_mb <= 0.0 || plane_bytes * (double)R <= min_mb * 1e6) return {1, (int)R};
+    if (slab_mb <= 0.0 || plane_bytes * (double)R <= (interleaved ? min_mb_i : min_mb) * 1e6) return {1, (int)R};
     // 16-byte voxels: fewer, larger reductions per plane leave room for 1.25x the bytes (measured)
     int planes = (int)(slab_mb * (interleaved ? 1.25 : 1.0) * 1e6 / plane_bytes);
     if (planes < 1) planes = 1;
     const int slabs = (int)((R + planes - 1) / planes);
     return {slabs, planes};
+}
+
+// Launch the slab-ordered kernel into an interleaved accumulator for slabs [first, first + count).
+void launch_slab_interleaved(const Launch& L, cudaStream_t s, bool cubic, const float* proj, const float* weights,
+                             const float* rot, const float* shifts, float4* acc, const SlabPlan& plan, int first, int count) {
+    const dim3 grid((unsigned)(L.B * L.P), (unsigned)count, 1);
+    if (cubic)
+        backproject_slab_kernel<true, true, true><<<grid, kBlockThreads, 0, s>>>((const float2*)proj, weights, rot, shifts, nullptr, nullptr, acc, L.g, plan.planes, first);
+    else
+        backproject_slab_kernel<false, true, true><<<grid, kBlockThreads, 0, s>>>((const float2*)proj, weights, rot, shifts, nullptr, nullptr, acc, L.g, plan.planes, first);
 }
 
 // ---- operator bodies, templated on the dimensionality and the real type (float | double) ------------------------------------
@@ -220,7 +232,10 @@ int backproject_forw(const Real* proj, const Real* weights, int64_t B, int64_t R
         (reinterpret_cast<uintptr_t>(workspace) & 15u) == 0) {
         if (int rc = zero_async(workspace, ws_need, s)) return rc;
         float4* acc = (float4*)workspace;
-        if (cubic)
+        const SlabPlan plan_i = (DIM == 3) ? slab_plan(R, true, true) : SlabPlan{1, (int)R};
+        if (DIM == 3 && plan_i.slabs > 1)      // the 16-byte volume itself is beyond L2: slab-ordered passes
+            launch_slab_interleaved(L, s, cubic, (const float*)proj, (const float*)weights, (const float*)rot, (const float*)shifts, acc, plan_i, 0, plan_i.slabs);
+        else if (cubic)
             backproject_forw_interleaved_kernel<DIM, true><<<L.grid, kBlockThreads, 0, s>>>((const C2<Real>*)proj, weights, rot, shifts, acc, L.g);
         else
             backproject_forw_interleaved_kernel<DIM, false><<<L.grid, kBlockThreads, 0, s>>>((const C2<Real>*)proj, weights, rot, shifts, acc, L.g);
@@ -243,7 +258,7 @@ int backproject_forw(const Real* proj, const Real* weights, int64_t B, int64_t R
         if (plan.slabs > 1) {
             const dim3 grid((unsigned)(B * P), (unsigned)plan.slabs, 1);
 #define B200PROJ_SL(C, W) \
-    backproject_slab_kernel<C, W><<<grid, kBlockThreads, 0, s>>>(p, weights, rot, shifts, d, weight_rec, nullptr, L.g, plan.planes)
+    backproject_slab_kernel<C, W><<<grid, kBlockThreads, 0, s>>>(p, weights, rot, shifts, d, weight_rec, nullptr, L.g, plan.planes, 0)
             if (cubic && hw) B200PROJ_SL(true, true);
             else if (cubic) B200PROJ_SL(true, false);
             else if (hw) B200PROJ_SL(false, true);
@@ -312,7 +327,8 @@ int backproject_back(const Real* grad_data_rec, const Real* grad_weight_rec, con
 // (re, im, w, 0) voxels): one v4 reduction per tap, nothing zero-filled or folded per call.
 int backproject_accumulate(const float* proj, const float* weights, int64_t B, int64_t R, const float* rot,
                            int64_t B_rot, const float* shifts, int64_t B_shift, int64_t P, int64_t N,
-                           int interpolation, double os, double cutoff, void* accumulator, void* stream) {
+                           int interpolation, double os, double cutoff, void* accumulator,
+                           int slab_first, int slab_count, void* stream) {
     Launch L;
     if (int rc = prepare(L, 3, B, R, B_rot, rot, shifts, B_shift, P, N, interpolation, os, cutoff)) return rc;
     if (proj == nullptr || weights == nullptr || accumulator == nullptr)
@@ -322,17 +338,16 @@ int backproject_accumulate(const float* proj, const float* weights, int64_t B, i
     if (R != b200proj_rec_boxsize(N, os))
         return fail(B200PROJ_ERR_ARGUMENT, "reconstruction boxsize %lld does not match ceil(N*oversampling) rounded up to even = %lld",
                     (long long)R, (long long)b200proj_rec_boxsize(N, os));
+    const SlabPlan plan = slab_plan(R, true, true);
+    if (slab_count < 0) { slab_first = 0; slab_count = plan.slabs; }         // all slabs
+    if (slab_first < 0 || slab_count < 1 || slab_first + slab_count > plan.slabs)
+        return fail(B200PROJ_ERR_ARGUMENT, "slabs [%d, %d) outside the plan of %d slabs", slab_first, slab_first + slab_count, plan.slabs);
     if (P == 0) return B200PROJ_OK;
     cudaStream_t s = (cudaStream_t)stream;
     float4* acc = (float4*)accumulator;
     const bool cubic = interpolation == B200PROJ_CUBIC;
-    const SlabPlan plan = slab_plan(R, true, true);
     if (plan.slabs > 1) {
-        const dim3 grid((unsigned)(B * P), (unsigned)plan.slabs, 1);
-        if (cubic)
-            backproject_slab_kernel<true, true, true><<<grid, kBlockThreads, 0, s>>>((const float2*)proj, weights, rot, shifts, nullptr, nullptr, acc, L.g, plan.planes);
-        else
-            backproject_slab_kernel<false, true, true><<<grid, kBlockThreads, 0, s>>>((const float2*)proj, weights, rot, shifts, nullptr, nullptr, acc, L.g, plan.planes);
+        launch_slab_interleaved(L, s, cubic, proj, weights, rot, shifts, acc, plan, slab_first, slab_count);
         return check_launch("backproject_accumulate (slab-ordered) launch");
     }
     if (cubic)
@@ -417,7 +432,12 @@ int noalloc_scratch(float4** out) {
 
 extern "C" {
 
-int b200proj_version(void) { return 100; }
+int b200proj_version(void) { return 200; }
+
+#ifndef B200PROJ_SOURCE_STAMP
+#define B200PROJ_SOURCE_STAMP ""
+#endif
+const char* b200proj_source_stamp(void) { return B200PROJ_SOURCE_STAMP; }
 
 const char* b200proj_last_error(void) { return g_error; }
 
@@ -586,7 +606,47 @@ int b200proj_backproject_2d_to_3d_accumulate(const float* proj, const float* wei
                                              const float* shifts, int64_t B_shift, int64_t P,
                                              int64_t N, int interpolation, double oversampling,
                                              double cutoff, void* accumulator, void* stream) {
-    return backproject_accumulate(proj, weights, B, R, rot, B_rot, shifts, B_shift, P, N, interpolation, oversampling, cutoff, accumulator, stream);
+    return backproject_accumulate(proj, weights, B, R, rot, B_rot, shifts, B_shift, P, N, interpolation, oversampling, cutoff, accumulator, 0, -1, stream);
+}
+
+int b200proj_backproject_2d_to_3d_accumulate_slabs(const float* proj, const float* weights, int64_t B,
+                                                   int64_t R, const float* rot, int64_t B_rot,
+                                                   const float* shifts, int64_t B_shift, int64_t P,
+                                                   int64_t N, int interpolation, double oversampling,
+                                                   double cutoff, void* accumulator, int slab_first,
+                                                   int slab_count, void* stream) {
+    if (slab_count < 0) return fail(B200PROJ_ERR_ARGUMENT, "slab_count must be >= 1");
+    return backproject_accumulate(proj, weights, B, R, rot, B_rot, shifts, B_shift, P, N, interpolation, oversampling, cutoff, accumulator, slab_first, slab_count, stream);
+}
+
+int b200proj_accumulator_slab_plan(int64_t R, int32_t* slabs, int32_t* planes_per_slab) {
+    g_error[0] = 0;
+    if (R < 2 || (R % 2) != 0 || slabs == nullptr || planes_per_slab == nullptr)
+        return fail(B200PROJ_ERR_ARGUMENT, "need an even boxsize >= 2 and two output pointers");
+    const SlabPlan plan = slab_plan(R, true, true);
+    *slabs = plan.slabs;
+    *planes_per_slab = plan.planes;
+    return B200PROJ_OK;
+}
+
+int b200proj_accumulator_slab_voxels(int64_t R, int slab_first, int slab_count, int64_t first_voxel[2], int64_t voxel_count[2]) {
+    g_error[0] = 0;
+    if (R < 2 || (R % 2) != 0 || first_voxel == nullptr || voxel_count == nullptr)
+        return fail(B200PROJ_ERR_ARGUMENT, "need an even boxsize >= 2 and two output arrays");
+    const SlabPlan plan = slab_plan(R, true, true);
+    if (slab_first < 0 || slab_count < 1 || slab_first + slab_count > plan.slabs)
+        return fail(B200PROJ_ERR_ARGUMENT, "slabs [%d, %d) outside the plan of %d slabs", slab_first, slab_first + slab_count, plan.slabs);
+    // signed plane coordinates [z_a, z_b) of the slabs; plane z is stored at index z < 0 ? z + R : z
+    const int64_t half = R / 2, plane = R * (R / 2 + 1);
+    const int64_t z_a = -half + 1 + (int64_t)slab_first * plan.planes;
+    int64_t z_b = z_a + (int64_t)slab_count * plan.planes;
+    if (z_b > half + 1) z_b = half + 1;
+    const int64_t neg_b = z_b < 0 ? z_b : 0, pos_a = z_a > 0 ? z_a : 0;
+    first_voxel[0] = (z_a < neg_b) ? (z_a + R) * plane : 0;            // planes with negative coordinates
+    voxel_count[0] = (z_a < neg_b) ? (neg_b - z_a) * plane : 0;
+    first_voxel[1] = (pos_a < z_b) ? pos_a * plane : 0;                // planes with coordinates >= 0
+    voxel_count[1] = (pos_a < z_b) ? (z_b - pos_a) * plane : 0;
+    return B200PROJ_OK;
 }
 
 size_t b200proj_accumulator_bytes(int64_t B, int64_t R) {

@@ -193,6 +193,23 @@ __device__ __forceinline__ void cubic_dweights(R f, R (&dw)[4]) {
     dw[3] = (1.5f * f - 1.0f) * f;
 }
 
+// One of those weights / derivatives (tap K = 0..3), for code that wants them one at a time
+// instead of holding all four in registers.
+template <int K, typename R>
+__device__ __forceinline__ R cubic_weight_k(R f) {
+    if (K == 0) return ((-0.5f * f + 1.0f) * f - 0.5f) * f;
+    if (K == 1) return (1.5f * f - 2.5f) * f * f + 1.0f;
+    if (K == 2) return ((-1.5f * f + 2.0f) * f + 0.5f) * f;
+    return (0.5f * f - 0.5f) * f * f;
+}
+template <int K, typename R>
+__device__ __forceinline__ R cubic_dweight_k(R f) {
+    if (K == 0) return (-1.5f * f + 2.0f) * f - 0.5f;
+    if (K == 1) return (4.5f * f - 5.0f) * f;
+    if (K == 2) return (-4.5f * f + 4.0f) * f + 0.5f;
+    return (1.5f * f - 1.0f) * f;
+}
+
 // Per-axis interpolation weights: T = 2 (linear: taps at floor, floor+1) or
 // T = 4 (cubic: taps at floor-1 .. floor+2).  base = index of the first tap.
 template <typename R, int T>
@@ -328,6 +345,88 @@ __device__ __forceinline__ void interpolate_lane(const SliceGeom& g, const C2<R>
     }
 }
 
+// One lane's share of a cooperative gather: column tap q of every footprint row of the pixel at
+// (pc, pr, pd).  Returns the lane's column weight and its derivative (wc, dwc), whether the
+// column is a Friedel mate (m: its values are conjugates), and the sums over the footprint's rows
+// and planes of the column's voxels: A (value weights), Bq (row-derivative weights), Dq
+// (plane-derivative weights).
+template <int DIM, bool CUBIC, bool WITH_DERIV, typename R>
+__device__ __forceinline__ void coop_column_sums(const SliceGeom& g, const C2<R>* __restrict__ vol,
+                                                 R pc, R pr, R pd, int q, R& wc, R& dwc, bool& m,
+                                                 C2<R>& A, C2<R>& Bq, C2<R>& Dq) {
+    constexpr int T = CUBIC ? 4 : 2;
+    constexpr int TD = (DIM == 3) ? T : 1;
+    const int plane_stride = g.R * g.Rh;
+    AxisWeights<R, T> ar;
+    axis_weights<T, WITH_DERIV>(pr, ar);
+    // plane weights are formed one at a time inside the loop below (each is used once)
+    const R fld = (DIM == 3) ? rfloor(pd) : (R)0;
+    const R fd = pd - fld;
+    const int dbase = (int)fld - (CUBIC ? 1 : 0);
+    // this lane's column tap
+    const R flc = rfloor(pc);
+    const R fc = pc - flc;
+    const int cbase = CUBIC ? (int)flc - 1 : (int)flc;
+    const int col = gather_col<CUBIC>(g, cbase + q, m);
+    dwc = 0.f;
+    if constexpr (CUBIC) {
+        R w4[4];
+        cubic_weights(fc, w4);
+        wc = q == 0 ? w4[0] : q == 1 ? w4[1] : q == 2 ? w4[2] : w4[3];
+        if (WITH_DERIV) {
+            R d4[4];
+            cubic_dweights(fc, d4);
+            dwc = q == 0 ? d4[0] : q == 1 ? d4[1] : q == 2 ? d4[2] : d4[3];
+        }
+    } else {
+        wc = q ? fc : 1.f - fc;
+        dwc = q ? 1.f : -1.f;
+    }
+    int rowcol[T];
+#pragma unroll
+    for (int i = 0; i < T; ++i) rowcol[i] = gather_line<CUBIC>(g, ar.base + i, m) * g.Rh + col;
+
+    A = make2<R>(0.f, 0.f);
+    Bq = A;
+    Dq = A;
+#pragma unroll
+    for (int k = 0; k < TD; ++k) {
+        const C2<R>* __restrict__ pl = vol + ((DIM == 3) ? gather_line<CUBIC>(g, dbase + k, m) * plane_stride : 0);
+        C2<R> rs = make2<R>(0.f, 0.f), rds = rs;
+#pragma unroll
+        for (int i = 0; i < T; ++i) {
+            const C2<R> v = __ldg(pl + rowcol[i]);
+            rs.x = rfma(ar.w[i], v.x, rs.x);
+            rs.y = rfma(ar.w[i], v.y, rs.y);
+            if (WITH_DERIV) {
+                rds.x = rfma(ar.dw[i], v.x, rds.x);
+                rds.y = rfma(ar.dw[i], v.y, rds.y);
+            }
+        }
+        R wd = 1.f, dwd = 0.f;
+        if (DIM == 3) {
+            if constexpr (CUBIC) {
+                wd = k == 0 ? cubic_weight_k<0>(fd) : k == 1 ? cubic_weight_k<1>(fd) : k == 2 ? cubic_weight_k<2>(fd) : cubic_weight_k<3>(fd);
+                if (WITH_DERIV)
+                    dwd = k == 0 ? cubic_dweight_k<0>(fd) : k == 1 ? cubic_dweight_k<1>(fd) : k == 2 ? cubic_dweight_k<2>(fd) : cubic_dweight_k<3>(fd);
+            } else {
+                wd = k ? fd : 1.f - fd;
+                dwd = k ? 1.f : -1.f;
+            }
+        }
+        A.x = rfma(wd, rs.x, A.x);
+        A.y = rfma(wd, rs.y, A.y);
+        if (WITH_DERIV) {
+            Bq.x = rfma(wd, rds.x, Bq.x);
+            Bq.y = rfma(wd, rds.y, Bq.y);
+            if (DIM == 3) {
+                Dq.x = rfma(dwd, rs.x, Dq.x);
+                Dq.y = rfma(dwd, rs.y, Dq.y);
+            }
+        }
+    }
+}
+
 // Cooperative separable interpolation of a complex half-volume, optionally with the spatial
 // derivatives (d/dc, d/dr, d/dd).  The T lanes of a group (T = 2 linear, 4 cubic; groups
 // are aligned runs of lanes, whose pixels are T consecutive columns of one slice row) work
@@ -346,11 +445,9 @@ __device__ __forceinline__ void interpolate_coop(const SliceGeom& g, const C2<R>
                                                  const PixelT<R>& px, bool valid_own, C2<R>& val,
                                                  C2<R>& g_c, C2<R>& g_r, C2<R>& g_d) {
     constexpr int T = CUBIC ? 4 : 2;
-    constexpr int TD = (DIM == 3) ? T : 1;
     constexpr unsigned kFull = 0xffffffffu;
     const int lane = threadIdx.x & 31;
     const int q = lane & (T - 1);
-    const int plane_stride = g.R * g.Rh;
     val = make2<R>(0.f, 0.f);
     g_c = g_r = g_d = val;
 
@@ -366,63 +463,10 @@ __device__ __forceinline__ void interpolate_coop(const SliceGeom& g, const C2<R>
 
         C2<R> cv = make2<R>(0.f, 0.f), cgc = cv, cgr = cv, cgd = cv;
         if (valid) {
-            AxisWeights<R, T> ar, ad;
-            axis_weights<T, WITH_DERIV>(pr, ar);
-            if (DIM == 3) axis_weights<T, WITH_DERIV>(pd, ad);
-            // this lane's column tap
-            const R flc = rfloor(pc);
-            const R fc = pc - flc;
-            const int cbase = CUBIC ? (int)flc - 1 : (int)flc;
+            R wc, dwc;
             bool m;
-            const int col = gather_col<CUBIC>(g, cbase + q, m);
-            R wc, dwc = 0.f;
-            if constexpr (CUBIC) {
-                R w4[4];
-                cubic_weights(fc, w4);
-                wc = q == 0 ? w4[0] : q == 1 ? w4[1] : q == 2 ? w4[2] : w4[3];
-                if (WITH_DERIV) {
-                    R d4[4];
-                    cubic_dweights(fc, d4);
-                    dwc = q == 0 ? d4[0] : q == 1 ? d4[1] : q == 2 ? d4[2] : d4[3];
-                }
-            } else {
-                wc = q ? fc : 1.f - fc;
-                dwc = q ? 1.f : -1.f;
-            }
-            int rowcol[T], plane[TD];
-#pragma unroll
-            for (int i = 0; i < T; ++i) rowcol[i] = gather_line<CUBIC>(g, ar.base + i, m) * g.Rh + col;
-#pragma unroll
-            for (int k = 0; k < TD; ++k)
-                plane[k] = (DIM == 3) ? gather_line<CUBIC>(g, ad.base + k, m) * plane_stride : 0;
-
-            C2<R> A = make2<R>(0.f, 0.f), Bq = A, Dq = A;
-#pragma unroll
-            for (int k = 0; k < TD; ++k) {
-                const C2<R>* __restrict__ pl = vol + plane[k];
-                C2<R> rs = make2<R>(0.f, 0.f), rds = rs;
-#pragma unroll
-                for (int i = 0; i < T; ++i) {
-                    const C2<R> v = __ldg(pl + rowcol[i]);
-                    rs.x = rfma(ar.w[i], v.x, rs.x);
-                    rs.y = rfma(ar.w[i], v.y, rs.y);
-                    if (WITH_DERIV) {
-                        rds.x = rfma(ar.dw[i], v.x, rds.x);
-                        rds.y = rfma(ar.dw[i], v.y, rds.y);
-                    }
-                }
-                const R wd = (DIM == 3) ? ad.w[k] : 1.f;
-                A.x = rfma(wd, rs.x, A.x);
-                A.y = rfma(wd, rs.y, A.y);
-                if (WITH_DERIV) {
-                    Bq.x = rfma(wd, rds.x, Bq.x);
-                    Bq.y = rfma(wd, rds.y, Bq.y);
-                    if (DIM == 3) {
-                        Dq.x = rfma(ad.dw[k], rs.x, Dq.x);
-                        Dq.y = rfma(ad.dw[k], rs.y, Dq.y);
-                    }
-                }
-            }
+            C2<R> A, Bq, Dq;
+            coop_column_sums<DIM, CUBIC, WITH_DERIV>(g, vol, pc, pr, pd, q, wc, dwc, m, A, Bq, Dq);
             const R sg = m ? -1.f : 1.f;          // a mirrored column holds conjugated values
             cv = make2<R>(wc * A.x, sg * wc * A.y);
             if (WITH_DERIV) {
@@ -451,6 +495,73 @@ __device__ __forceinline__ void interpolate_coop(const SliceGeom& g, const C2<R>
             g_c = cgc;
             g_r = cgr;
             g_d = cgd;
+        }
+    }
+}
+
+// What the backward of the forward projection needs from the gather, as real scalars: with
+// u = grad * conj(phase) of a pixel and the interpolated value v and its derivatives there,
+//   dots[0..2] = Re(u * conj(dv/dc)), Re(u * conj(dv/dr)), Re(u * conj(dv/dd))   (rotation gradient)
+//   dots[3]    = Im(u * conj(v))                                                  (shift gradient)
+// All four are linear in the gathered voxels, so in the cooperative form every lane of a group
+// dots ITS column's partial sums with the pixel's u (sent along with the position) and the group
+// adds four scalars instead of eight complex components; only four registers per pixel outlive
+// the gather.  MUST be called by all 32 lanes of the warp.
+template <int DIM, bool CUBIC, bool NEED_ROT, typename R>
+__device__ __forceinline__ void gather_pose_dots(const SliceGeom& g, const C2<R>* __restrict__ vol,
+                                                 const PixelT<R>& px, bool valid_own, C2<R> u_own,
+                                                 R (&dots)[4]) {
+    constexpr int T = CUBIC ? 4 : 2;
+    constexpr unsigned kFull = 0xffffffffu;
+#pragma unroll
+    for (int v = 0; v < 4; ++v) dots[v] = 0.f;
+    if (!(CUBIC || (DIM == 3 && g.sparse_samples))) {            // warp-uniform: one lane per pixel
+        if (valid_own) {
+            C2<R> val, gc, gr, gd;
+            interpolate_lane<DIM, CUBIC, NEED_ROT>(g, vol, px, val, gc, gr, gd);
+            if (NEED_ROT) {
+                dots[0] = u_own.x * gc.x + u_own.y * gc.y;
+                dots[1] = u_own.x * gr.x + u_own.y * gr.y;
+                if (DIM == 3) dots[2] = u_own.x * gd.x + u_own.y * gd.y;
+            }
+            dots[3] = u_own.y * val.x - u_own.x * val.y;
+        }
+        return;
+    }
+    const int lane = threadIdx.x & 31;
+    const int q = lane & (T - 1);
+#pragma unroll 1
+    for (int s = 0; s < T; ++s) {
+        const int src = (lane & ~(T - 1)) | s;
+        const R pc = __shfl_sync(kFull, px.c, src);
+        const R pr = __shfl_sync(kFull, px.r, src);
+        const R pd = (DIM == 3) ? __shfl_sync(kFull, px.d, src) : 0.f;
+        const R ux = __shfl_sync(kFull, u_own.x, src);
+        const R uy = __shfl_sync(kFull, u_own.y, src);
+        const bool valid = __shfl_sync(kFull, (int)valid_own, src) != 0;
+        R part[4] = {0.f, 0.f, 0.f, 0.f};
+        if (valid) {
+            R wc, dwc;
+            bool m;
+            C2<R> A, Bq, Dq;
+            coop_column_sums<DIM, CUBIC, NEED_ROT>(g, vol, pc, pr, pd, q, wc, dwc, m, A, Bq, Dq);
+            const R uys = m ? -uy : uy;                      // a mirrored column holds conjugated values
+            if (NEED_ROT) {
+                part[0] = dwc * (ux * A.x + uys * A.y);
+                part[1] = wc * (ux * Bq.x + uys * Bq.y);
+                if (DIM == 3) part[2] = wc * (ux * Dq.x + uys * Dq.y);
+            }
+            part[3] = wc * (uy * A.x - (m ? -ux : ux) * A.y);
+        }
+#pragma unroll
+        for (int o = 1; o < T; o <<= 1) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v)
+                if ((v < 3 && NEED_ROT && (v < 2 || DIM == 3)) || v == 3) part[v] += __shfl_xor_sync(kFull, part[v], o);
+        }
+        if (q == s) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) dots[v] = part[v];
         }
     }
 }
@@ -525,8 +636,10 @@ __device__ __forceinline__ void red_add_v4(float4* addr, float a, float b, float
 // and weight of a tap go out as ONE red.global.add.v4.f32; otherwise vol (complex) and, when
 // WEIGHTS, wvol (R) are reduced into directly (v2 + scalar reduction).
 // MUST be called by all 32 lanes of the warp; lanes without a pixel pass valid_own = false.
-// SLAB: only taps whose signed plane coordinate (after the mirror) lies in [z_lo, z_hi) are
-// written; used by the slab-ordered back-projection, where each pass owns a range of planes.
+// SLAB: only reductions that LAND in planes with signed coordinate in [z_lo, z_hi) are issued
+// (a tap by the plane it lands in after the mirror, the Friedel duplicate of a c == 0 tap by the
+// plane of its partner), so a pass of the slab-ordered back-projection writes nothing outside the
+// planes it owns and, over all passes, every reduction is issued exactly once.
 template <int DIM, bool CUBIC, bool WEIGHTS, bool WITH_DUP, bool INTERLEAVED, bool SLAB = false, typename R>
 __device__ __forceinline__ void scatter_coop(const SliceGeom& g, C2<R>* __restrict__ vol,
                                              NoDeduce<R>* __restrict__ wvol, float4* __restrict__ vol4,
@@ -572,10 +685,14 @@ __device__ __forceinline__ void scatter_coop(const SliceGeom& g, C2<R>* __restri
         for (int k = 0; k < TD; ++k) {
             int dl = 0;
             R wd = 1.f;
+            bool tap_here = true, dup_here = true;      // SLAB: which of the two land in [z_lo, z_hi)
             if (DIM == 3) {
                 if (SLAB) {
                     const int sd = m ? -(ad.base + k) : ad.base + k;
-                    if (sd < z_lo || sd >= z_hi) continue;
+                    tap_here = sd >= z_lo && sd < z_hi;
+                    const int sp = (sd == g.half) ? sd : -sd;      // plane R/2 is its own partner
+                    dup_here = WITH_DUP && c == 0 && sp >= z_lo && sp < z_hi;
+                    if (!tap_here && !dup_here) continue;
                 }
                 dl = scatter_line(g, ad.base + k, m);
                 wd = ad.w[k];
@@ -590,13 +707,15 @@ __device__ __forceinline__ void scatter_coop(const SliceGeom& g, C2<R>* __restri
                 const int off = dl * plane_stride + rl * g.Rh + c;
                 const R re = vx * w, im = vy * w * sgn;
                 const R fw = WEIGHTS ? wval * rabs(w) : 0.f;
-                if (INTERLEAVED) {
-                    red_add_v4(vol4 + off, re, im, fw, 0.f);
-                } else {
-                    red_add_v2(vol + off, re, im);
-                    if (WEIGHTS) red_add(wvol + off, fw);
+                if (!SLAB || tap_here) {
+                    if (INTERLEAVED) {
+                        red_add_v4(vol4 + off, re, im, fw, 0.f);
+                    } else {
+                        red_add_v2(vol + off, re, im);
+                        if (WEIGHTS) red_add(wvol + off, fw);
+                    }
                 }
-                if (WITH_DUP && c == 0) {
+                if (WITH_DUP && c == 0 && (!SLAB || dup_here)) {
                     // Friedel partner (-d, -r, 0); skipped when it is the same voxel
                     const int rl2 = (rl == 0) ? 0 : g.R - rl;
                     const int dl2 = (DIM == 3) ? ((dl == 0) ? 0 : g.R - dl) : 0;

@@ -14,6 +14,10 @@
 
 namespace b200proj {
 
+#ifndef PB_MIN_BLOCKS
+#define PB_MIN_BLOCKS 4
+#endif
+
 struct BlockWork {
     int b, p, i, j;
     bool in_image;
@@ -146,7 +150,7 @@ __device__ __forceinline__ void pose_grad_flush(const SliceGeom& g, R (&acc)[2 *
 // ---- backward of forward projection -----------------------------------------------------
 // reference semantics: csrc/cpu/3d/projection_3d_to_2d_kernels.cpp:283-396
 template <int DIM, bool CUBIC, bool NEED_ROT, bool NEED_SHIFT, typename R>
-__global__ void __launch_bounds__(kBlockThreads)
+__global__ void __launch_bounds__(kBlockThreads, (DIM == 3 && CUBIC && NEED_ROT && sizeof(R) == 4) ? PB_MIN_BLOCKS : 1)
 project_back_kernel(const C2<R>* __restrict__ grad_proj, const C2<R>* __restrict__ rec,
                     const R* __restrict__ rot, const R* __restrict__ shifts,
                     C2<R>* __restrict__ grad_rec, R* __restrict__ grad_rot,
@@ -160,29 +164,44 @@ project_back_kernel(const C2<R>* __restrict__ grad_proj, const C2<R>* __restrict
     const bool active = w.in_image &&
                         pixel_setup<DIM>(g, pose_rot<DIM>(g, rot, w.b, w.p), w.i, w.j, px) &&
                         !(w.j == 0 && w.i >= g.N / 2);
-    C2<R> val = make2<R>(0.f, 0.f), gc = val, gr = val, gd = val;
-    if (NEED_ROT || NEED_SHIFT)      // cooperative gather: every lane of the warp takes part
-        interpolate_any<DIM, CUBIC, NEED_ROT>(g, rec + (size_t)w.b * g.vol_elems, px, active, val, gc, gr, gd);
-    C2<R> orig = make2<R>(0.f, 0.f), u = orig, ph = make2<R>(1.f, 0.f);
+    C2<R> u = make2<R>(0.f, 0.f);
     if (active) {
-        orig = __ldcs(grad_proj + w.pix);
-        u = orig;
+        u = __ldcs(grad_proj + w.pix);
         if (g.has_shift) {
             const R* s = pose_shift(g, shifts, w.b, w.p);
-            ph = phase_ramp(g, px, __ldg(s), __ldg(s + 1));
-            u = cmul_conj(orig, ph);
+            u = cmul_conj(u, phase_ramp(g, px, __ldg(s), __ldg(s + 1)));
         }
+    }
+    if (NEED_ROT || NEED_SHIFT) {
+        // Pose gradients first, so that nothing but the pixel's position and `u` stays live across
+        // the scatter below.  The gather returns the four real scalars they are made of (see
+        // gather_pose_dots); every lane of the warp takes part in it.
+        R dots[4];
+        gather_pose_dots<DIM, CUBIC, NEED_ROT>(g, rec + (size_t)w.b * g.vol_elems, px, active, u, dots);
+        if (active) {
+            // the pixel's frequencies are formed again from (i, j) rather than kept in registers
+            // across the gather (the empty asm keeps the compiler from reusing the earlier values)
+            int i2 = w.i, j2 = w.j;
+            asm volatile("" : "+r"(i2), "+r"(j2));
+            const R kr = (R)((i2 <= g.N / 2) ? i2 : i2 - g.N), kc = (R)j2;
+            if (NEED_ROT) {
+                const R sc = (R)((double)kc * g.os), sr = (R)((double)kr * g.os);
+#pragma unroll
+                for (int a = 0; a < DIM; ++a) {
+                    acc[2 * a + 0] = dots[a] * sc;
+                    acc[2 * a + 1] = dots[a] * sr;
+                }
+            }
+            if (NEED_SHIFT) {
+                acc[2 * DIM + 0] = (R)(g.shift_scale * (double)kr) * dots[3];
+                acc[2 * DIM + 1] = (R)(g.shift_scale * (double)kc) * dots[3];
+            }
+        }
+        pose_grad_flush<DIM>(g, acc, grad_rot, grad_shift, w.b, w.p);
     }
     // cooperative scatter: every lane of the warp takes part
     scatter_coop<DIM, CUBIC, false, false, false>(g, grad_rec + (size_t)w.b * g.vol_elems, nullptr, nullptr,
                                                   px, active, u, 0.f);
-    if (active) {
-        if (NEED_ROT || NEED_SHIFT) {
-            const C2<R> mod = g.has_shift ? cmul(val, ph) : val;
-            pose_grad_terms<DIM, NEED_ROT, NEED_SHIFT>(g, px, u, orig, mod, gc, gr, gd, acc);
-        }
-    }
-    if (NEED_ROT || NEED_SHIFT) pose_grad_flush<DIM>(g, acc, grad_rot, grad_shift, w.b, w.p);
 }
 
 // ---- back-projection --------------------------------------------------------------------
@@ -275,7 +294,13 @@ fold_interleaved_kernel(const float4* __restrict__ accum, float2* __restrict__ d
 // (d and c are linear in the column j; one run for direct taps, one for Friedel-mirrored
 // taps, which land at -d and exist where c < 0); the runs are computed from linear estimates
 // with a small slack, candidates pass a one-FMA prefilter, and each tap is then tested
-// exactly (scatter_coop<SLAB>), so every tap is written by exactly one slab pass.
+// exactly (scatter_coop<SLAB>), so every tap is written by exactly one slab pass.  A pass writes
+// only into the planes of its own slab: the Friedel duplicate of a tap on the c == 0 plane,
+// which lands in the mirrored plane, is issued by the pass that owns THAT plane (pixels with a
+// tap on column 0 are therefore candidates of the mirrored run as well).  So the planes of a
+// slab are final as soon as its pass has run for every slice, which lets a caller fold and
+// reduce a finished slab while later slabs are still being scattered (`slab_first` +
+// gridDim.y select the slabs of a launch).
 // One block = one slice x one slab; its 8 warps take the rows round-robin and each prepares 32
 // of its rows at a time, one per lane.
 // Restrict the column run [ja, jb] to the columns where a*j + b lies in [lo, hi].
@@ -296,13 +321,13 @@ __global__ void __launch_bounds__(kBlockThreads)
 backproject_slab_kernel(const float2* __restrict__ proj, const float* __restrict__ weights,
                         const float* __restrict__ rot, const float* __restrict__ shifts,
                         float2* __restrict__ data_rec, float* __restrict__ weight_rec,
-                        float4* __restrict__ accum, const SliceGeom g, int slab_planes) {
+                        float4* __restrict__ accum, const SliceGeom g, int slab_planes, int slab_first) {
     constexpr int T = CUBIC ? 4 : 2;
     constexpr unsigned kFull = 0xffffffffu;
     constexpr float kEps = 0.05f;                    // slack of the linear estimates below
     const int bp = blockIdx.x;
     const int b = bp / g.P, p = bp - b * g.P;
-    const int z_lo = -g.half + 1 + (int)blockIdx.y * slab_planes;
+    const int z_lo = -g.half + 1 + ((int)blockIdx.y + slab_first) * slab_planes;
     const int z_hi = min(z_lo + slab_planes, g.half + 1);
     const float* rm = pose_rot<3>(g, rot, b, p);
     // linear estimates of the sample position along a row: d ~ ad*j + bd*kr, c ~ ac*j + bc*kr
@@ -310,11 +335,12 @@ backproject_slab_kernel(const float2* __restrict__ proj, const float* __restrict
     const float ac = osf * __ldg(rm + 0), bc = osf * __ldg(rm + 1);
     const float ad = osf * __ldg(rm + 6), bd = osf * __ldg(rm + 7);
     // taps of a pixel use planes floor(d)-T/2+1 .. floor(d)+T/2 (mirrored taps their negatives)
-    // and columns floor(c)-T/2+1 .. floor(c)+T/2; direct taps need a column >= 0, mirrored < 0
+    // and columns floor(c)-T/2+1 .. floor(c)+T/2; direct taps need a column >= 0, mirrored taps a
+    // column < 0, and the duplicate of a column-0 tap (which lands in the mirrored plane) a column == 0
     const float band_lo = (float)z_lo - (float)(T / 2) - kEps;
     const float band_hi = (float)z_hi + (float)(T / 2 - 1) + kEps;
     const float c_direct_min = -(float)(T / 2) - kEps;
-    const float c_mirror_max = (float)(T / 2 - 1) + kEps;
+    const float c_mirror_max = (float)(T / 2) + kEps;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     float2* data_b = INTERLEAVED ? nullptr : data_rec + (size_t)b * g.vol_elems;
     float* wrec_b = (WEIGHTS && !INTERLEAVED) ? weight_rec + (size_t)b * g.vol_elems : nullptr;
@@ -399,7 +425,7 @@ backproject_slab_kernel(const float2* __restrict__ proj, const float* __restrict
                 const int pd = (int)floorf(px.d) - (CUBIC ? 1 : 0);
                 const int pc = (int)floorf(px.c) - (CUBIC ? 1 : 0);
                 const bool direct = pc + T - 1 >= 0 && pd < z_hi && pd + T > z_lo;
-                const bool mirror = pc < 0 && -(pd + T - 1) < z_hi && -pd >= z_lo;
+                const bool mirror = pc <= 0 && -(pd + T - 1) < z_hi && -pd >= z_lo;
                 active = direct || mirror;
             }
             if (!__any_sync(kFull, active)) continue;

@@ -43,8 +43,11 @@ SIGNATURES.update({name + "_f64": sig for name, sig in list(SIGNATURES.items()) 
 SIGNATURES["b200proj_backproject_2d_to_3d_accumulate"] = [_ptr, _ptr] + _COMMON + [_ptr, _ptr]
 SIGNATURES["b200proj_accumulator_fold"] = [_ptr, _i64, _i64, _ptr, _ptr, _int, _ptr]
 SIGNATURES["b200proj_accumulator_fold_range"] = [_ptr, _i64, _i64, _ptr, _ptr, _int, _ptr]
+SIGNATURES["b200proj_backproject_2d_to_3d_accumulate_slabs"] = [_ptr, _ptr] + _COMMON + [_ptr, _int, _int, _ptr]
 EXPORTS = list(SIGNATURES) + ["b200proj_version", "b200proj_last_error", "b200proj_rec_boxsize",
-                                "b200proj_backproject_workspace_bytes", "b200proj_accumulator_bytes"]
+                                "b200proj_backproject_workspace_bytes", "b200proj_accumulator_bytes",
+                                "b200proj_source_stamp", "b200proj_accumulator_slab_plan",
+                                "b200proj_accumulator_slab_voxels", "b200proj_debug_index"]
 
 _lib: Optional[C.CDLL] = None
 
@@ -54,24 +57,30 @@ def library_path():
 
 
 def load() -> C.CDLL:
-    """Load (building first if the file is absent or older than its sources) the CUDA library; raises ImportError
-    when that is impossible.  Never substitutes another implementation."""
+    """Load the CUDA library, building it first when it is absent or was built from other sources
+    than the ones beside it; raises ImportError when it cannot be built or when the file that
+    loads reports other sources than it should.  Never substitutes another implementation."""
     global _lib
     if _lib is not None:
         return _lib
     path = _build.LIB_PATH
-    if _build.needs_build():          # missing, or older than its sources
+    if _build.needs_build():
         try:
             _build.build()
         except Exception as e:  # noqa: BLE001
-            if not path.exists():
-                raise ImportError(
-                    f"torch_projectors_b200: {path} is not built and building it failed ({e}); "
-                    "run `python -m torch_projectors_b200.build` on a machine with nvcc") from e
+            raise ImportError(
+                f"torch_projectors_b200: {path} is missing or stale and building it failed ({e}); "
+                "run `python -m torch_projectors_b200.build` on a machine with nvcc") from e
     try:
         lib = C.CDLL(str(path))
     except OSError as e:
         raise ImportError(f"torch_projectors_b200: cannot load {path}: {e}") from e
+    lib.b200proj_source_stamp.restype = C.c_char_p
+    lib.b200proj_source_stamp.argtypes = []
+    built_from = (lib.b200proj_source_stamp() or b"").decode()
+    if built_from != _build.source_stamp():
+        raise ImportError(f"torch_projectors_b200: {path} was built from other sources (stamp {built_from!r}, "
+                          f"expected {_build.source_stamp()!r}); run `python -m torch_projectors_b200.build --force`")
     for name, argtypes in SIGNATURES.items():
         fn = getattr(lib, name)
         fn.argtypes = argtypes
@@ -86,6 +95,10 @@ def load() -> C.CDLL:
     lib.b200proj_backproject_workspace_bytes.argtypes = [_int, _i64, _i64, _i64, _i64, _int, _int]
     lib.b200proj_accumulator_bytes.restype = C.c_size_t
     lib.b200proj_accumulator_bytes.argtypes = [_i64, _i64]
+    lib.b200proj_accumulator_slab_plan.restype = _int
+    lib.b200proj_accumulator_slab_plan.argtypes = [_i64, C.POINTER(C.c_int32), C.POINTER(C.c_int32)]
+    lib.b200proj_accumulator_slab_voxels.restype = _int
+    lib.b200proj_accumulator_slab_voxels.argtypes = [_i64, _int, _int, C.POINTER(_i64), C.POINTER(_i64)]
     _lib = lib
     return lib
 
@@ -207,6 +220,36 @@ def backproject_accumulate(proj, weights, rot, shifts, interp, oversampling, cut
     B, P, N = proj.shape[0], proj.shape[1], proj.shape[2]
     _call("b200proj_backproject_2d_to_3d_accumulate", proj, _p(proj), _p(weights),
           *_geom(B, R, rot, shifts, P, N, interp, oversampling, cutoff), _p(accumulator))
+
+
+def backproject_accumulate_slabs(proj, weights, rot, shifts, interp, oversampling, cutoff, R, accumulator,
+                                 slab_first, slab_count):
+    """The same for slabs [slab_first, slab_first + slab_count) of the accumulator's slab plan only."""
+    B, P, N = proj.shape[0], proj.shape[1], proj.shape[2]
+    _call("b200proj_backproject_2d_to_3d_accumulate_slabs", proj, _p(proj), _p(weights),
+          *_geom(B, R, rot, shifts, P, N, interp, oversampling, cutoff), _p(accumulator), int(slab_first), int(slab_count))
+
+
+def _host_call(fn, *args) -> None:
+    rc = fn(*args)
+    if rc != 0:
+        raise RuntimeError(f"{fn.__name__}: {load().b200proj_last_error().decode('utf-8', 'replace')} (code {rc})")
+
+
+def accumulator_slab_plan(R: int):
+    """(slabs, planes per slab) of the slab-ordered passes that fill an accumulator of box R;
+    slabs == 1 when it is small enough for one pass."""
+    slabs, planes = C.c_int32(0), C.c_int32(0)
+    _host_call(load().b200proj_accumulator_slab_plan, int(R), C.byref(slabs), C.byref(planes))
+    return slabs.value, planes.value
+
+
+def accumulator_slab_voxels(R: int, slab_first: int, slab_count: int):
+    """[(first, stop), ...] voxel ranges (relative to a batch item's first voxel) that slabs
+    [slab_first, slab_first + slab_count) own: at most two, in ascending order."""
+    first, count = (_i64 * 2)(), (_i64 * 2)()
+    _host_call(load().b200proj_accumulator_slab_voxels, int(R), int(slab_first), int(slab_count), first, count)
+    return sorted((int(f), int(f + n)) for f, n in zip(first, count) if n > 0)
 
 
 def accumulator_fold(accumulator, B, R, data_rec, weight_rec, accumulate, voxel_range=None):

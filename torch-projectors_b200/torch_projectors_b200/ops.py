@@ -460,17 +460,14 @@ def new_backprojection_accumulator(batch: int, box: int, device) -> torch.Tensor
     return torch.zeros((batch, box, box, box // 2 + 1, 4), dtype=torch.float32, device=device)
 
 
-def backproject_2d_to_3d_accumulate_interleaved_(accumulator: torch.Tensor, projections: torch.Tensor,
-                                                 rotations: torch.Tensor, weights: torch.Tensor,
-                                                 shifts: Optional[torch.Tensor] = None,
-                                                 interpolation: str = "linear", oversampling: float = 1.0,
-                                                 fourier_radius_cutoff: Optional[float] = None) -> None:
-    """Streaming weighted back-projection (no autograd) that adds a chunk of slices into a
-    persistent interleaved accumulator (``new_backprojection_accumulator``): data and weight of
-    a tap leave as ONE vector reduction, nothing is zero-filled or folded per chunk, and
-    volumes beyond L2 take the slab-ordered kernel.  ``fold_backprojection_accumulator``
-    turns the sums into the usual data / weight volumes.  complex64 / float32 only.  Not in the
-    reference API."""
+def prepare_accumulate_interleaved(accumulator: torch.Tensor, projections: torch.Tensor,
+                                   rotations: torch.Tensor, weights: torch.Tensor,
+                                   shifts: Optional[torch.Tensor] = None,
+                                   interpolation: str = "linear", oversampling: float = 1.0,
+                                   fourier_radius_cutoff: Optional[float] = None):
+    """Validate one chunk for the interleaved accumulator and return the positional arguments of
+    ``_abi.backproject_accumulate`` / ``_abi.backproject_accumulate_slabs`` (contiguous tensors
+    included, so holding the tuple keeps them alive), or None for an empty chunk."""
     _validate_projections(projections, weights)
     _check(weights is not None, "the interleaved accumulator needs weights")
     if projections.dim() == 4 and rotations.dim() == 3:
@@ -489,9 +486,26 @@ def backproject_2d_to_3d_accumulate_interleaved_(accumulator: torch.Tensor, proj
     _check(tuple(accumulator.shape) == want and accumulator.dtype == torch.float32 and accumulator.is_contiguous()
            and accumulator.device == projections.device, f"accumulator must be a contiguous float32 tensor of shape {want}")
     if P == 0:
-        return
-    _abi.backproject_accumulate(projections.contiguous(), weights.contiguous(), rot, sh, interp, oversampling,
-                                _cutoff(fourier_radius_cutoff, N), R, accumulator)
+        return None
+    return (projections.contiguous(), weights.contiguous(), rot, sh, interp, oversampling,
+            _cutoff(fourier_radius_cutoff, N), R, accumulator)
+
+
+def backproject_2d_to_3d_accumulate_interleaved_(accumulator: torch.Tensor, projections: torch.Tensor,
+                                                 rotations: torch.Tensor, weights: torch.Tensor,
+                                                 shifts: Optional[torch.Tensor] = None,
+                                                 interpolation: str = "linear", oversampling: float = 1.0,
+                                                 fourier_radius_cutoff: Optional[float] = None) -> None:
+    """Streaming weighted back-projection (no autograd) that adds a chunk of slices into a
+    persistent interleaved accumulator (``new_backprojection_accumulator``): data and weight of
+    a tap leave as ONE vector reduction, nothing is zero-filled or folded per chunk, and
+    volumes beyond L2 take the slab-ordered kernel.  ``fold_backprojection_accumulator``
+    turns the sums into the usual data / weight volumes.  complex64 / float32 only.  Not in the
+    reference API."""
+    call = prepare_accumulate_interleaved(accumulator, projections, rotations, weights, shifts,
+                                          interpolation, oversampling, fourier_radius_cutoff)
+    if call is not None:
+        _abi.backproject_accumulate(*call)
 
 
 def fold_backprojection_accumulator(accumulator: torch.Tensor, data_rec: Optional[torch.Tensor] = None,
