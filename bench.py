@@ -840,7 +840,7 @@ def main():
 
     if args.natural_order and args.impl != "reference":
         import torch_projectors_b200.ops as _ops
-        _ops.POSE_ORDER_MIN_BYTES = 1 << 62
+        _ops.set_pose_order_thresholds(1 << 62, 64)
     if args.profile_case:
         profile_case(args)
         return

@@ -29,14 +29,10 @@ def test_autograd_step_volume_size_subset_against_reference(tp):
     d_rec = rec.cuda().requires_grad_(True)
     d_rot = rot.cuda().requires_grad_(True)
     d_sh = shifts.cuda().requires_grad_(True)
-    import torch_projectors_b200.ops as _ops
-    keep = _ops.POSE_ORDER_MIN_POSES
-    _ops.POSE_ORDER_MIN_POSES = 1          # the plane-locality order of the full workload, on 32 poses
-    try:
-        out = tp.project_3d_to_2d_forw(d_rec, d_rot, d_sh, output_shape=(N, N), interpolation="cubic", oversampling=2.0)
-        out.backward(g.cuda())
-    finally:
-        _ops.POSE_ORDER_MIN_POSES = keep
+    # with the plane-locality order the full workload uses (32 poses are below the threshold at which it is derived unasked)
+    out = tp.project_3d_to_2d_forw(d_rec, d_rot, d_sh, output_shape=(N, N), interpolation="cubic", oversampling=2.0,
+                                   pose_order=tp.plane_locality_order(d_rot.detach()))
+    out.backward(g.cuda())
     want = ops.project_3d_to_2d_forw(rec, rot, shifts, [N, N], "cubic", 2.0, None)
     assert rel_err(out, want) <= TOL_FORWARD
     w_rec, w_rot, w_sh = ops.project_3d_to_2d_back(g, rec, rot.clone().requires_grad_(True), shifts.clone().requires_grad_(True),

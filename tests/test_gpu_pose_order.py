@@ -41,7 +41,7 @@ def test_order_is_a_permutation_per_batch_item_and_groups_nearby_planes(tp, B, B
 
 
 @pytest.mark.parametrize("interp", ["linear", "cubic"])
-def test_results_do_not_depend_on_the_processing_order(tp, interp, monkeypatch):
+def test_results_do_not_depend_on_the_processing_order(tp, interp):
     from torch_projectors_b200 import ops
     B, P, N, R = 2, 70, 16, 32
     gen = torch.Generator().manual_seed(11)
@@ -60,15 +60,25 @@ def test_results_do_not_depend_on_the_processing_order(tp, interp, monkeypatch):
                 *t.project_3d_to_2d_back(gp, rec, r, s, interp, 2.0, None),
                 *t.backproject_2d_to_3d_back(rec, gw, gp, wts, r, s, interp, 2.0, None))
 
-    monkeypatch.setattr(ops, "POSE_ORDER_MIN_BYTES", 1 << 60)
-    natural = run()
-    monkeypatch.setattr(ops, "POSE_ORDER_MIN_BYTES", 0)
-    monkeypatch.setattr(ops, "POSE_ORDER_MIN_POSES", 1)
-    seen = []
-    real = tp._abi.pose_order_3d
-    monkeypatch.setattr(tp._abi, "pose_order_3d", lambda *a: (seen.append(1), real(*a))[1])
-    ordered = run()
-    assert len(seen) == 3                     # all three operators took the ordered path
+    try:
+        ops.set_pose_order_thresholds(1 << 60, 64)
+        natural = run()
+        ops.set_pose_order_thresholds(0, 1)              # every call derives an order
+        ordered = run()
+    finally:
+        ops.set_pose_order_thresholds()
+    # the same through the *_ordered operators with one order computed up front and reused
+    order = ops.plane_locality_order(rot, B)
+    assert order.dtype == torch.int32 and order.numel() == B * P
+    r = rot.clone().requires_grad_(True)
+    s = sh.clone().requires_grad_(True)
+    reused = (t.project_3d_to_2d_forw_ordered(rec, r, s, [N, N], interp, 2.0, None, order),
+              *t.project_3d_to_2d_back_ordered(gp, rec, r, s, interp, 2.0, None, order),
+              *t.backproject_2d_to_3d_back_ordered(rec, gw, gp, wts, r, s, interp, 2.0, None, order))
+    for k in (0, 4, 5):
+        assert torch.equal(natural[k], reused[k]), k
+    for k in (1, 2, 3, 6, 7):
+        assert rel_err(reused[k], natural[k]) < TOL_ATOMIC * 0.1, k
     # gathers write each slice on its own: bit-identical; atomically accumulated outputs agree
     # to rounding (their summation order is not fixed in either run)
     for k in (0, 4, 5):                       # projections, grad_projections, grad_weights
@@ -90,3 +100,38 @@ def test_entries_outside_the_range_leave_their_slice_unwritten(tp):
         assert torch.equal(out[0, p], want[0, p])
     for p in (1, 3):
         assert (out[0, p] == 123.0).all()
+
+
+def test_public_api_keeps_one_order_for_forward_and_backward(tp):
+    """pose_order= of the public function: an order computed once is used by the forward pass and
+    saved for the backward pass; None derives one per call; False keeps the given order.  All give
+    the same projections (bit for bit) and gradients (to rounding)."""
+    from torch_projectors_b200 import ops
+    P, N, R = 80, 16, 32
+    gen = torch.Generator().manual_seed(12)
+    rec = torch.randn(1, R, R, R // 2 + 1, dtype=torch.complex64, generator=gen).cuda()
+    rot = random_rotations_3d(P, gen).reshape(1, P, 3, 3).cuda()
+    sh = ((torch.rand(1, P, 2, generator=gen) * 2 - 1) * 3).cuda()
+    g = torch.randn(1, P, N, N // 2 + 1, dtype=torch.complex64, generator=gen).cuda()
+    order = tp.plane_locality_order(rot)
+    assert torch.equal(order.sort().values.cpu(), torch.arange(P, dtype=torch.int32))
+    results = {}
+    try:
+        ops.set_pose_order_thresholds(0, 1)
+        for name, arg in (("given", order), ("auto", None), ("natural", False)):
+            v = rec.clone().requires_grad_(True)
+            r = rot.clone().requires_grad_(True)
+            s = sh.clone().requires_grad_(True)
+            out = tp.project_3d_to_2d_forw(v, r, s, output_shape=(N, N), interpolation="cubic", oversampling=2.0, pose_order=arg)
+            out.backward(g)
+            results[name] = (out.detach(), v.grad, r.grad, s.grad)
+    finally:
+        ops.set_pose_order_thresholds()
+    for name in ("auto", "natural"):
+        assert torch.equal(results[name][0], results["given"][0])
+        for a, b in zip(results[name][1:], results["given"][1:]):
+            assert rel_err(a, b) < TOL_ATOMIC * 0.1
+    # without gradients the call goes straight to the raw operator and gives the same projections
+    with torch.no_grad():
+        plain = tp.project_3d_to_2d_forw(rec, rot, sh, output_shape=(N, N), interpolation="cubic", oversampling=2.0, pose_order=order)
+    assert torch.equal(plain, results["given"][0])

@@ -83,6 +83,64 @@ def test_public_names_match_the_reference_api():
 
 
 # ---- pose sharding ------------------------------------------------------------------------
+# ---- the C++ operator layer, as far as it goes without a GPU -----------------------------------
+REFERENCE_SCHEMAS = {
+    "project_forw": "(Tensor reconstruction, Tensor rotations, Tensor? shifts, int[] output_shape, str interpolation, float oversampling, float? fourier_radius_cutoff) -> Tensor",
+    "project_back": "(Tensor grad_projections, Tensor reconstruction, Tensor rotations, Tensor? shifts, str interpolation, float oversampling, float? fourier_radius_cutoff) -> (Tensor, Tensor, Tensor)",
+    "backproject_forw": "(Tensor projections, Tensor? weights, Tensor rotations, Tensor? shifts, str interpolation, float oversampling, float? fourier_radius_cutoff) -> (Tensor, Tensor)",
+    "backproject_back": "(Tensor grad_data_rec, Tensor? grad_weight_rec, Tensor projections, Tensor? weights, Tensor rotations, Tensor? shifts, str interpolation, float oversampling, float? fourier_radius_cutoff) -> (Tensor, Tensor, Tensor, Tensor)",
+}
+
+
+def test_operators_are_defined_in_cpp_with_the_reference_schemas():
+    """The eight raw operators come from the compiled C++ library (not from Python registrations)
+    and carry the reference's schema strings (csrc/torch_projectors.cpp:23-36 there)."""
+    import torch_projectors_b200  # noqa: F401
+    from torch_projectors_b200 import build
+    assert build.BINDING_PATH.exists()
+    ops = torch.ops.torch_projectors_b200
+    for name, kind in (("project_2d_forw", "project_forw"), ("project_3d_to_2d_forw", "project_forw"),
+                       ("project_2d_back", "project_back"), ("project_3d_to_2d_back", "project_back"),
+                       ("backproject_2d_forw", "backproject_forw"), ("backproject_2d_to_3d_forw", "backproject_forw"),
+                       ("backproject_2d_back", "backproject_back"), ("backproject_2d_to_3d_back", "backproject_back")):
+        schema = str(getattr(ops, name).default._schema)
+        assert schema == f"torch_projectors_b200::{name}{REFERENCE_SCHEMAS[kind]}", schema
+        assert torch._C._dispatch_has_kernel_for_dispatch_key(f"torch_projectors_b200::{name}", "CUDA")
+        assert not torch._C._dispatch_has_kernel_for_dispatch_key(f"torch_projectors_b200::{name}", "CPU")
+
+
+def test_cpu_tensors_are_rejected_by_the_dispatcher():
+    import torch_projectors_b200 as tp
+    rec = torch.zeros(1, 8, 5, dtype=torch.complex64)
+    rot = torch.eye(2).view(1, 1, 2, 2)
+    with pytest.raises(NotImplementedError, match="CPU"):
+        tp.project_2d_forw(rec, rot)
+    with pytest.raises(NotImplementedError, match="CPU"):
+        tp.backproject_2d_forw(torch.zeros(1, 1, 8, 5, dtype=torch.complex64), rot)
+
+
+def test_meta_implementations_give_the_output_shapes():
+    """Shape-only implementations (Meta key): what tracing the operators needs."""
+    import torch_projectors_b200  # noqa: F401
+    ops = torch.ops.torch_projectors_b200
+    m = dict(device="meta")
+    rec = torch.empty(2, 16, 16, 9, dtype=torch.complex64, **m)
+    rot = torch.empty(1, 5, 3, 3, **m).requires_grad_(True)
+    sh = torch.empty(2, 5, 2, **m)
+    assert ops.project_3d_to_2d_forw(rec, rot, sh, [8, 8], "cubic", 2.0, None).shape == (2, 5, 8, 5)
+    g = torch.empty(2, 5, 8, 5, dtype=torch.complex64, **m)
+    gr, grot, gsh = ops.project_3d_to_2d_back(g, rec, rot, sh, "cubic", 2.0, None)
+    assert gr.shape == rec.shape and grot.shape == rot.shape and gsh.shape == (0,)
+    w = torch.empty(2, 5, 8, 5, **m)
+    d, wr = ops.backproject_2d_to_3d_forw(g, w, rot, sh, "linear", 2.0, None)
+    assert d.shape == (2, 16, 16, 9) and wr.shape == (2, 16, 16, 9) and d.dtype == torch.complex64 and wr.dtype == torch.float32
+    d2, w2 = ops.backproject_2d_forw(g, None, torch.empty(1, 5, 2, 2, **m), None, "linear", 1.5, None)
+    assert d2.shape == (2, 12, 7) and w2.shape == (0,)
+    gp, gw, grot, gsh = ops.backproject_2d_to_3d_back(d, wr, g, w, rot, sh, "linear", 2.0, None)
+    assert gp.shape == g.shape and gw.shape == w.shape and grot.shape == rot.shape and gsh.shape == (0,)
+    assert ops.plane_locality_order(rot, 2).shape == (10,)
+
+
 @pytest.mark.parametrize("P,world", [(10, 1), (10, 2), (10, 3), (7, 8), (0, 4), (200000, 8)])
 def test_pose_range_partitions_exactly(P, world):
     spans = [sharding.pose_range(P, r, world) for r in range(world)]

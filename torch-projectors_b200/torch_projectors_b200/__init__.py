@@ -2,8 +2,8 @@
 API of warpem/torch-projectors.
 
 Importing the package loads ``libb200proj.so`` (hand-written CUDA kernels behind a C ABI,
-``include/b200proj.h``) and registers the eight raw operators under
-``torch.ops.torch_projectors_b200`` for CUDA tensors.  There is no CPU, MPS or Triton
+``include/b200proj.h``) and ``_C.so`` (the C++ operator layer over it, ``csrc/torch_binding.cpp``),
+which defines the eight raw operators under ``torch.ops.torch_projectors_b200`` for CUDA tensors.  There is no CPU, MPS or Triton
 path: if the library cannot be loaded the import fails, and CPU tensors are rejected by
 the dispatcher.
 
@@ -20,6 +20,8 @@ from .ops import (  # noqa: E402
     backproject_2d_to_3d_accumulate_interleaved_,
     fold_backprojection_accumulator,
     new_backprojection_accumulator,
+    plane_locality_order,
+    set_pose_order_thresholds,
     backproject_2d_to_3d_back,
     backproject_2d_to_3d_forw,
     project_2d_back,
@@ -38,6 +40,7 @@ __all__ = [
     "project_2d_forw", "project_2d_back", "project_3d_to_2d_forw", "project_3d_to_2d_back",
     "backproject_2d_forw", "backproject_2d_to_3d_forw", "backproject_2d_to_3d_back",
     "backproject_2d_to_3d_accumulate_", "backproject_2d_to_3d_accumulate_interleaved_",
-    "new_backprojection_accumulator", "fold_backprojection_accumulator", "sharding", "streaming", "prep",
+    "new_backprojection_accumulator", "fold_backprojection_accumulator", "plane_locality_order",
+    "set_pose_order_thresholds", "sharding", "streaming", "prep",
     "project_3d_to_2d_to_host", "backproject_2d_to_3d_from_host",
 ]

@@ -1,41 +1,51 @@
-"""Public API, autograd glue and raw-operator registration.
+"""Public API and autograd glue over the C++ operator layer.
 
 The seven public functions and the eight raw operators keep the names, argument lists,
 defaults and error behaviour of warpem/torch-projectors (``torch_projectors/ops.py`` and
 ``csrc/torch_projectors.cpp:23-36`` in the reference) so that user code switches by
-changing the import.  The raw operators are registered under the op namespace
-``torch_projectors_b200`` for the CUDA dispatch key only: calling them with CPU (or MPS)
-tensors raises from the dispatcher -- there is no CPU fallback.  complex128 / float64
-inputs, which the reference's CUDA wrappers silently route through its CPU kernels
-(``csrc/cuda/3d/projection_3d_to_2d_kernels.cu:902-918``), run on the GPU here (the same
-kernels instantiated for double); mixed precisions raise ``RuntimeError``.
+changing the import.  The raw operators are defined and implemented in C++
+(``csrc/torch_binding.cpp``, built into ``_C.so``: ``TORCH_LIBRARY`` with the reference's schema
+strings, ``TORCH_LIBRARY_IMPL`` for the CUDA key, shape-only Meta implementations) under the op
+namespace ``torch_projectors_b200``; each calls one entry point of the C ABI
+(``include/b200proj.h``).  Calling them with CPU (or MPS) tensors raises from the dispatcher --
+there is no CPU fallback.  complex128 / float64 inputs, which the reference's CUDA wrappers
+silently route through its CPU kernels (``csrc/cuda/3d/projection_3d_to_2d_kernels.cu:902-918``),
+run on the GPU here (the same kernels instantiated for double); mixed precisions raise
+``RuntimeError``.
+
+As in the reference, autograd lives in Python (four ``autograd.Function``s).  Calls that cannot
+need a gradient (no input requires one, or gradients are switched off) go straight to the raw
+operator, which keeps small problems from paying for the autograd machinery.
 """
 from __future__ import annotations
 
-from typing import Optional
+from typing import Optional, Union
 
 import torch
 
 from . import _abi
+from . import build as _build
 
 NAMESPACE = "torch_projectors_b200"
 
-# ---------------------------------------------------------------------------------------
-# raw operators (schemas verbatim from the reference: csrc/torch_projectors.cpp:23-36)
-# ---------------------------------------------------------------------------------------
-_lib = torch.library.Library(NAMESPACE, "DEF")
-_PROJECT_FORW = "(Tensor reconstruction, Tensor rotations, Tensor? shifts, int[] output_shape, str interpolation, float oversampling, float? fourier_radius_cutoff) -> Tensor"
-_PROJECT_BACK = "(Tensor grad_projections, Tensor reconstruction, Tensor rotations, Tensor? shifts, str interpolation, float oversampling, float? fourier_radius_cutoff) -> (Tensor, Tensor, Tensor)"
-_BACKPROJECT_FORW = "(Tensor projections, Tensor? weights, Tensor rotations, Tensor? shifts, str interpolation, float oversampling, float? fourier_radius_cutoff) -> (Tensor, Tensor)"
-_BACKPROJECT_BACK = "(Tensor grad_data_rec, Tensor? grad_weight_rec, Tensor projections, Tensor? weights, Tensor rotations, Tensor? shifts, str interpolation, float oversampling, float? fourier_radius_cutoff) -> (Tensor, Tensor, Tensor, Tensor)"
-_lib.define("project_2d_forw" + _PROJECT_FORW)
-_lib.define("project_2d_back" + _PROJECT_BACK)
-_lib.define("backproject_2d_forw" + _BACKPROJECT_FORW)
-_lib.define("backproject_2d_back" + _BACKPROJECT_BACK)
-_lib.define("project_3d_to_2d_forw" + _PROJECT_FORW)
-_lib.define("project_3d_to_2d_back" + _PROJECT_BACK)
-_lib.define("backproject_2d_to_3d_forw" + _BACKPROJECT_FORW)
-_lib.define("backproject_2d_to_3d_back" + _BACKPROJECT_BACK)
+
+def _load_operator_library():
+    """Load ``_C.so`` (building it first when absent or stale); ImportError when impossible."""
+    path = _build.BINDING_PATH
+    if _build.binding_needs_build():
+        try:
+            _build.build_binding()
+        except Exception as e:  # noqa: BLE001
+            raise ImportError(f"torch_projectors_b200: {path} is missing or stale and building it failed ({e}); "
+                              "run `python -m torch_projectors_b200.build` on a machine with g++ and nvcc") from e
+    try:
+        torch.ops.load_library(str(path))
+    except OSError as e:
+        raise ImportError(f"torch_projectors_b200: cannot load {path}: {e}") from e
+
+
+_load_operator_library()
+_ops = getattr(torch.ops, NAMESPACE)
 
 
 def _check(cond: bool, msg: str) -> None:
@@ -100,189 +110,58 @@ def _backproject_workspace(dim, B, R, P, N, interp, weights, device):
 
 
 # Volumes (one batch item) at least this large get a locality-preserving processing order of
-# their slices; below it the whole volume stays in the 126 MB L2 and the order changes nothing.
+# their slices when the caller gives none; below it the whole volume stays in the 126 MB L2 and
+# the order changes nothing.  Change them with set_pose_order_thresholds (the C++ layer holds a copy).
 POSE_ORDER_MIN_BYTES = 96 << 20
 POSE_ORDER_MIN_POSES = 64
 
 
-def _pose_order(dim, vol: torch.Tensor, B: int, P: int, rot: torch.Tensor):
-    """int32 [B*P] processing order for the volume-reading 3D operators (slices with nearby
-    planes run together, so that a volume larger than L2 is read from DRAM far less often), or
-    None when it would not pay.  Outputs do not depend on it."""
-    if dim != 3 or P < POSE_ORDER_MIN_POSES:
-        return None
-    if vol[0].numel() * vol.element_size() < POSE_ORDER_MIN_BYTES:
-        return None
-    order = torch.empty(B * P, dtype=torch.int32, device=rot.device)
-    _abi.pose_order_3d(rot, B, P, order)
-    return order
+def set_pose_order_thresholds(min_volume_bytes: int = 96 << 20, min_poses: int = 64) -> None:
+    """When the 3D operators that read a volume derive a processing order of the slices by
+    themselves: volumes of at least `min_volume_bytes` per batch item and at least `min_poses` poses."""
+    global POSE_ORDER_MIN_BYTES, POSE_ORDER_MIN_POSES
+    POSE_ORDER_MIN_BYTES, POSE_ORDER_MIN_POSES = int(min_volume_bytes), int(min_poses)
+    _ops._set_pose_order_thresholds(POSE_ORDER_MIN_BYTES, POSE_ORDER_MIN_POSES)
+
+
+def plane_locality_order(rotations: torch.Tensor, batch: int = 1) -> torch.Tensor:
+    """int32 [batch * P] processing order of the slices of a 3D operator that reads a volume:
+    slices whose planes lie close together come one after the other, so that a volume larger than
+    L2 is read from DRAM far less often.  Results of the operators do not depend on it.  Compute it
+    once per set of rotations and pass it as ``pose_order=`` to ``project_3d_to_2d_forw`` (its
+    backward reuses it) for as many iterations as the rotations stay (roughly) the same.
+    rotations: [B_rot, P, 3, 3] (or [P, 3, 3]) on the device."""
+    if rotations.dim() == 3:
+        rotations = rotations.unsqueeze(0)
+    return _ops.plane_locality_order(rotations.detach(), int(batch))
+
+
+_NATURAL = {}
+
+
+def _natural_order(device) -> torch.Tensor:
+    """The empty int32 tensor that tells the operators to keep the given order of the slices."""
+    t = _NATURAL.get(device)
+    if t is None:
+        t = _NATURAL[device] = torch.empty(0, dtype=torch.int32, device=device)
+    return t
+
+
+def _resolve_order(pose_order, vol: torch.Tensor, rotations: torch.Tensor) -> torch.Tensor:
+    """pose_order argument of the public 3D functions -> the tensor handed to the operators (and
+    kept for the backward pass): a given order as it is, ``False`` = natural order, ``None`` = made
+    here when the volume is large enough for it to matter."""
+    if isinstance(pose_order, torch.Tensor):
+        return pose_order
+    if pose_order is None and rotations.size(1) >= POSE_ORDER_MIN_POSES and \
+            vol[0].numel() * vol.element_size() >= POSE_ORDER_MIN_BYTES and vol.is_cuda:
+        return _ops.plane_locality_order(rotations.detach(), vol.size(0))
+    return _natural_order(vol.device)
 
 
 def _cutoff(fourier_radius_cutoff: Optional[float], N: int) -> float:
     # default: Nyquist radius of the projection (reference: projection_3d_to_2d_kernels.cu:892)
     return float(fourier_radius_cutoff) if fourier_radius_cutoff is not None else N / 2.0
-
-
-def _rec_dims_ok(dim: int, rec: torch.Tensor) -> None:
-    _check(rec.dim() == dim + 1, f"Reconstruction must have {dim + 1} dimensions")
-    R, Rh = rec.size(-2), rec.size(-1)
-    _check(R % 2 == 0 and Rh == R // 2 + 1, f"Reconstruction must be rfft-shaped with an even box (got {tuple(rec.shape)})")
-    if dim == 3:
-        _check(rec.size(1) == R, "Reconstruction volume must be cubic (depth == height)")
-
-
-def _project_forw_impl(dim, reconstruction, rotations, shifts, output_shape, interpolation,
-                       oversampling, fourier_radius_cutoff):
-    _check(reconstruction.is_cuda, "Input reconstruction must be on CUDA device")
-    _check(reconstruction.is_complex(), "Reconstruction must be a complex tensor")
-    interp = _interp_code(interpolation)
-    _rec_dims_ok(dim, reconstruction)
-    _check_fp32("reconstruction", reconstruction, True)
-    B = reconstruction.size(0)
-    P, rot, sh = _check_pose_inputs(dim, "reconstruction", B, rotations, shifts, reconstruction)
-    _check(len(output_shape) >= 1, "output_shape must have at least one element")
-    N = int(output_shape[0])          # only element 0 is used, as in the reference
-    _check(N >= 2 and N % 2 == 0, f"Output boxsize {N} must be even")
-    rec = reconstruction.contiguous()
-    out = torch.empty((B, P, N, N // 2 + 1), dtype=rec.dtype, device=rec.device)
-    if out.numel():
-        _abi.project_forw(dim, rec, rot, sh, P, N, interp, oversampling, _cutoff(fourier_radius_cutoff, N), out,
-                          _pose_order(dim, rec, B, P, rot))
-    return out
-
-
-def _project_back_impl(dim, grad_projections, reconstruction, rotations, shifts, interpolation,
-                       oversampling, fourier_radius_cutoff):
-    _check(grad_projections.is_cuda, "Input grad_projections must be on CUDA device")
-    _check(reconstruction.is_cuda, "Input reconstruction must be on CUDA device")
-    _check(grad_projections.is_complex(), "Projections must be a complex tensor")
-    _check(reconstruction.is_complex(), "Reconstruction must be a complex tensor")
-    interp = _interp_code(interpolation)
-    _check(grad_projections.dim() == 4, "Projections must be a 4D tensor (B, P, H, W/2+1)")
-    _rec_dims_ok(dim, reconstruction)
-    _check_fp32("reconstruction", reconstruction, True)
-    _check_fp32("grad_projections", grad_projections, True, reconstruction)
-    B, P_g, N, Nh = grad_projections.shape
-    _check(N % 2 == 0 and Nh == N // 2 + 1, "grad_projections must be rfft-shaped with an even box")
-    _check(reconstruction.size(0) == B, "Batch size of grad_projections must match reconstruction")
-    P, rot, sh = _check_pose_inputs(dim, "reconstruction", B, rotations, shifts, reconstruction)
-    _check(P == P_g, "Number of poses in rotations must match grad_projections")
-    need_rot = rotations.requires_grad
-    need_shift = shifts is not None and shifts.requires_grad
-    gp = grad_projections.contiguous()
-    rec = reconstruction.contiguous()
-    dev = rec.device
-    grad_rec = torch.empty_like(rec)                      # zero-filled by the library call
-    grad_rot = torch.empty(rot.shape, dtype=rot.dtype, device=dev) if need_rot else None
-    grad_sh = torch.empty(sh.shape, dtype=sh.dtype, device=dev) if need_shift else None
-    if P == 0:                      # nothing to launch: pointers of empty tensors are NULL
-        grad_rec.zero_()
-    else:
-        _abi.project_back(dim, gp, rec, rot, sh, P, N, interp, oversampling,
-                          _cutoff(fourier_radius_cutoff, N), grad_rec, grad_rot, grad_sh,
-                          _pose_order(dim, rec, B, P, rot))
-    empty = lambda: torch.empty((0,), dtype=rot.dtype, device=dev)  # noqa: E731
-    return grad_rec, (grad_rot if need_rot else empty()), (grad_sh if need_shift else empty())
-
-
-def _backproject_forw_impl(dim, projections, weights, rotations, shifts, interpolation,
-                           oversampling, fourier_radius_cutoff):
-    _check(projections.is_cuda, "Input projections must be on CUDA device")
-    _check(projections.is_complex(), "Projections must be a complex tensor")
-    interp = _interp_code(interpolation)
-    _check(projections.dim() == 4, "Projections must be (B, P, height, width/2+1)")
-    _check_fp32("projections", projections, True)
-    B, P_p, N, Nh = projections.shape
-    _check(N % 2 == 0 and Nh == N // 2 + 1, "projections must be rfft-shaped with an even box")
-    if weights is not None:
-        _check(weights.is_cuda, "Weights must be on CUDA device")
-        _check(weights.is_floating_point(), "Weights must be a real-valued tensor")
-        _check(weights.dim() == 4, "Weights must be (B, P, height, width/2+1)")
-        _check(weights.shape == projections.shape, "Weights and projections must have the same shape")
-        _check_fp32("weights", weights, False, projections)
-        weights = weights.contiguous()
-    P, rot, sh = _check_pose_inputs(dim, "projections", B, rotations, shifts, projections)
-    _check(P == P_p, "Number of poses in rotations must match projections")
-    proj = projections.contiguous()
-    dev = proj.device
-    R = _abi.rec_boxsize(N, oversampling)
-    shape = (B, R, R, R // 2 + 1) if dim == 3 else (B, R, R // 2 + 1)
-    data_rec = torch.empty(shape, dtype=proj.dtype, device=dev)          # zero-filled by the call
-    weight_rec = torch.empty(shape, dtype=_REAL_OF[proj.dtype], device=dev) if weights is not None else None
-    if P == 0:                      # nothing to launch: pointers of empty tensors are NULL
-        data_rec.zero_()
-        if weight_rec is not None:
-            weight_rec.zero_()
-    else:
-        _abi.backproject_forw(dim, proj, weights, rot, sh, interp, oversampling,
-                              _cutoff(fourier_radius_cutoff, N), data_rec, weight_rec, False,
-                              _backproject_workspace(dim, B, R, P, N, interp, weights, dev))
-    if weight_rec is None:
-        weight_rec = torch.empty((0,), dtype=rot.dtype, device=dev)
-    return data_rec, weight_rec
-
-
-def _backproject_back_impl(dim, grad_data_rec, grad_weight_rec, projections, weights, rotations,
-                           shifts, interpolation, oversampling, fourier_radius_cutoff):
-    _check(grad_data_rec.is_cuda, "Input grad_data_rec must be on CUDA device")
-    _check(projections.is_cuda, "Input projections must be on CUDA device")
-    _check(grad_data_rec.is_complex(), "grad_data_rec must be a complex tensor")
-    _check(projections.is_complex(), "projections must be a complex tensor")
-    interp = _interp_code(interpolation)
-    _check(grad_data_rec.dim() == dim + 1, "grad_data_rec must be (B, D, H, W/2+1)" if dim == 3 else "grad_data_rec must be (B, H, W/2+1)")
-    _check(projections.dim() == 4, "projections must be a 4D tensor (B, P, boxsize, boxsize/2+1)")
-    _check_fp32("projections", projections, True)
-    _check_fp32("grad_data_rec", grad_data_rec, True, projections)
-    B, P_p, N, Nh = projections.shape
-    if grad_weight_rec is not None:
-        _check(grad_weight_rec.is_cuda, "grad_weight_rec must be on CUDA device")
-        _check(grad_weight_rec.is_floating_point(), "grad_weight_rec must be a real-valued tensor")
-        _check(grad_weight_rec.shape == grad_data_rec.shape, "grad_weight_rec and grad_data_rec must have same shape")
-        _check_fp32("grad_weight_rec", grad_weight_rec, False, projections)
-        grad_weight_rec = grad_weight_rec.contiguous()
-    R = _abi.rec_boxsize(N, oversampling)
-    want = (B, R, R, R // 2 + 1) if dim == 3 else (B, R, R // 2 + 1)
-    _check(tuple(grad_data_rec.shape) == want, "grad_data_rec shape must match expected reconstruction size")
-    if weights is not None:
-        _check(weights.is_cuda, "weights must be on CUDA device")
-        _check_fp32("weights", weights, False, projections)
-    P, rot, sh = _check_pose_inputs(dim, "projections", B, rotations, shifts, projections)
-    _check(P == P_p, "Number of poses in rotations must match projections")
-    need_rot = rotations.requires_grad
-    need_shift = shifts is not None and shifts.requires_grad
-    gd = grad_data_rec.contiguous()
-    proj = projections.contiguous()
-    dev = proj.device
-    grad_proj = torch.empty_like(proj)
-    grad_w = torch.empty(proj.shape, dtype=_REAL_OF[proj.dtype], device=dev) if weights is not None else None
-    grad_rot = torch.empty(rot.shape, dtype=rot.dtype, device=dev) if need_rot else None
-    grad_sh = torch.empty(sh.shape, dtype=sh.dtype, device=dev) if need_shift else None
-    if proj.numel():
-        _abi.backproject_back(dim, gd, grad_weight_rec, proj, rot, sh, interp, oversampling,
-                              _cutoff(fourier_radius_cutoff, N), grad_proj, grad_w, grad_rot, grad_sh,
-                              _pose_order(dim, gd, B, P, rot))
-    empty = lambda: torch.empty((0,), dtype=rot.dtype, device=dev)  # noqa: E731
-    return (grad_proj, (grad_w if grad_w is not None else empty()),
-            (grad_rot if need_rot else empty()), (grad_sh if need_shift else empty()))
-
-
-def _register(name, dim, impl):
-    def cuda_impl(*args):
-        return impl(dim, *args)
-    cuda_impl.__name__ = f"{name}_cuda"
-    _lib.impl(name, cuda_impl, "CUDA")
-
-
-_register("project_2d_forw", 2, _project_forw_impl)
-_register("project_2d_back", 2, _project_back_impl)
-_register("backproject_2d_forw", 2, _backproject_forw_impl)
-_register("backproject_2d_back", 2, _backproject_back_impl)
-_register("project_3d_to_2d_forw", 3, _project_forw_impl)
-_register("project_3d_to_2d_back", 3, _project_back_impl)
-_register("backproject_2d_to_3d_forw", 3, _backproject_forw_impl)
-_register("backproject_2d_to_3d_back", 3, _backproject_back_impl)
-
-_ops = getattr(torch.ops, NAMESPACE)
 
 
 # ---------------------------------------------------------------------------------------
@@ -320,6 +199,10 @@ def _validate_projections(projections, weights) -> None:
             raise ValueError("Weights must be real-valued (floating point)")
 
 
+def _wants_grad(*tensors) -> bool:
+    return torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in tensors)
+
+
 def project_2d_forw(reconstruction: torch.Tensor, rotations: torch.Tensor,
                     shifts: Optional[torch.Tensor] = None,
                     output_shape: Optional[tuple[int, ...]] = None,
@@ -331,6 +214,10 @@ def project_2d_forw(reconstruction: torch.Tensor, rotations: torch.Tensor,
         raise ValueError("Reconstruction must have at least 2 dimensions")
     _validate_rec_box(reconstruction.shape[-2], reconstruction.shape[-1])
     output_shape = _validate_output_shape(output_shape, reconstruction.shape[-2])
+    if not _wants_grad(reconstruction, rotations, shifts):
+        reconstruction, rotations, shifts = _canon_project(2, reconstruction, rotations, shifts)
+        return _ops.project_2d_forw(reconstruction, rotations, shifts, output_shape, interpolation,
+                                    oversampling, fourier_radius_cutoff)
     return _Project2D.apply(reconstruction, rotations, shifts, output_shape, interpolation,
                             oversampling, fourier_radius_cutoff)
 
@@ -355,6 +242,10 @@ def backproject_2d_forw(projections: torch.Tensor, rotations: torch.Tensor,
     real weights) into 2D rfft reconstructions.  Returns (data, weights); the second is an
     empty ``(0,)`` tensor without weights.  (reference: torch_projectors/ops.py:61-117)"""
     _validate_projections(projections, weights)
+    if not _wants_grad(projections, weights, rotations, shifts):
+        projections, weights, rotations, shifts = _canon_backproject(projections, weights, rotations, shifts)
+        return _ops.backproject_2d_forw(projections, weights, rotations, shifts, interpolation,
+                                        oversampling, fourier_radius_cutoff)
     return _Backproject2D.apply(projections, weights, rotations, shifts, interpolation,
                                 oversampling, fourier_radius_cutoff)
 
@@ -363,15 +254,30 @@ def project_3d_to_2d_forw(reconstruction: torch.Tensor, rotations: torch.Tensor,
                           shifts: Optional[torch.Tensor] = None,
                           output_shape: Optional[tuple[int, ...]] = None,
                           interpolation: str = "linear", oversampling: float = 1.0,
-                          fourier_radius_cutoff: Optional[float] = None) -> torch.Tensor:
+                          fourier_radius_cutoff: Optional[float] = None,
+                          pose_order: Union[torch.Tensor, bool, None] = None) -> torch.Tensor:
     """Sample P rotated central slices from 3D rfft volumes [B, D, H, W/2+1]
-    -> [B, P, H_out, W_out/2+1].  (reference: torch_projectors/ops.py:119-174)"""
+    -> [B, P, H_out, W_out/2+1].  (reference: torch_projectors/ops.py:119-174)
+
+    ``pose_order`` (not in the reference API) is the processing order of the slices
+    (``plane_locality_order``): None = derived here when the volume is larger than L2 and there are
+    enough poses, once per call and reused by the backward pass; a tensor = reused as given (compute
+    it once for a training loop over the same rotations); False = the order given.  Results do not
+    depend on it."""
     if reconstruction.dim() != 4:
         raise ValueError("Reconstruction must be a 4D tensor (B, D, H, W/2+1)")
     _validate_rec_box(reconstruction.shape[2], reconstruction.shape[3])
     output_shape = _validate_output_shape(output_shape, reconstruction.shape[2])
+    if not _wants_grad(reconstruction, rotations, shifts):
+        reconstruction, rotations, shifts = _canon_project(3, reconstruction, rotations, shifts)
+        if pose_order is None:        # the operator derives the order by the same thresholds
+            return _ops.project_3d_to_2d_forw(reconstruction, rotations, shifts, output_shape, interpolation,
+                                              oversampling, fourier_radius_cutoff)
+        return _ops.project_3d_to_2d_forw_ordered(reconstruction, rotations, shifts, output_shape, interpolation,
+                                                  oversampling, fourier_radius_cutoff,
+                                                  _resolve_order(pose_order, reconstruction, rotations))
     return _Project3DTo2D.apply(reconstruction, rotations, shifts, output_shape, interpolation,
-                                oversampling, fourier_radius_cutoff)
+                                oversampling, fourier_radius_cutoff, pose_order)
 
 
 def project_3d_to_2d_back(projections: torch.Tensor, reconstruction: torch.Tensor,
@@ -394,6 +300,10 @@ def backproject_2d_to_3d_forw(projections: torch.Tensor, rotations: torch.Tensor
     into cubic 3D rfft volumes of box ceil(N*oversampling) rounded up to even.
     (reference: torch_projectors/ops.py:208-264)"""
     _validate_projections(projections, weights)
+    if not _wants_grad(projections, weights, rotations, shifts):
+        projections, weights, rotations, shifts = _canon_backproject(projections, weights, rotations, shifts)
+        return _ops.backproject_2d_to_3d_forw(projections, weights, rotations, shifts, interpolation,
+                                              oversampling, fourier_radius_cutoff)
     return _Backproject2DTo3D.apply(projections, weights, rotations, shifts, interpolation,
                                     oversampling, fourier_radius_cutoff)
 
@@ -552,31 +462,33 @@ def _canon_poses(rotations, shifts):
     return rotations, shifts
 
 
-class _ProjectBase(torch.autograd.Function):
-    _rec_rank = 0          # rank of an un-batched reconstruction
-    _forw = None
-    _back = None
+def _canon_project(rec_rank: int, reconstruction, rotations, shifts):
+    """Ranks of the raw operators: [B, (R,) R, Rh], [B_rot, P, d, d], [B_s, P, 2]."""
+    if reconstruction.dim() == rec_rank:
+        reconstruction = reconstruction.unsqueeze(0)
+    rotations, shifts = _canon_poses(rotations, shifts)
+    if rotations.size(0) != reconstruction.size(0) and rotations.size(0) != 1:
+        raise ValueError("Batch size of rotations must be 1 or match reconstruction")
+    return reconstruction, rotations, shifts
 
-    @classmethod
-    def _run_forward(cls, ctx, reconstruction, rotations, shifts, output_shape, interpolation,
-                     oversampling, fourier_radius_cutoff):
-        if reconstruction.dim() == cls._rec_rank:
-            reconstruction = reconstruction.unsqueeze(0)
-        rotations, shifts = _canon_poses(rotations, shifts)
-        if rotations.size(0) != reconstruction.size(0) and rotations.size(0) != 1:
-            raise ValueError("Batch size of rotations must be 1 or match reconstruction")
-        projection = getattr(_ops, cls._forw)(reconstruction, rotations, shifts, output_shape,
-                                              interpolation, oversampling, fourier_radius_cutoff)
+
+class _Project2D(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, reconstruction, rotations, shifts, output_shape, interpolation, oversampling,
+                fourier_radius_cutoff):
+        reconstruction, rotations, shifts = _canon_project(2, reconstruction, rotations, shifts)
+        projection = _ops.project_2d_forw(reconstruction, rotations, shifts, output_shape, interpolation,
+                                          oversampling, fourier_radius_cutoff)
         ctx.save_for_backward(reconstruction, rotations, shifts)
         ctx.interpolation = interpolation
         ctx.oversampling = oversampling
         ctx.fourier_radius_cutoff = fourier_radius_cutoff
         return projection
 
-    @classmethod
-    def _run_backward(cls, ctx, grad_output):
+    @staticmethod
+    def backward(ctx, grad_output):
         reconstruction, rotations, shifts = ctx.saved_tensors
-        grad_reconstruction, grad_rotations, grad_shifts = getattr(_ops, cls._back)(
+        grad_reconstruction, grad_rotations, grad_shifts = _ops.project_2d_back(
             grad_output.contiguous(), reconstruction, rotations, shifts, ctx.interpolation,
             ctx.oversampling, ctx.fourier_radius_cutoff)
         if shifts is None:
@@ -584,44 +496,53 @@ class _ProjectBase(torch.autograd.Function):
         return grad_reconstruction, grad_rotations, grad_shifts, None, None, None, None
 
 
-class _Project2D(_ProjectBase):
-    _rec_rank, _forw, _back = 2, "project_2d_forw", "project_2d_back"
-
+class _Project3DTo2D(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, *args):
-        return _Project2D._run_forward(ctx, *args)
-
-    @staticmethod
-    def backward(ctx, grad_output):
-        return _Project2D._run_backward(ctx, grad_output)
-
-
-class _Project3DTo2D(_ProjectBase):
-    _rec_rank, _forw, _back = 3, "project_3d_to_2d_forw", "project_3d_to_2d_back"
-
-    @staticmethod
-    def forward(ctx, *args):
-        return _Project3DTo2D._run_forward(ctx, *args)
+    def forward(ctx, reconstruction, rotations, shifts, output_shape, interpolation, oversampling,
+                fourier_radius_cutoff, pose_order):
+        reconstruction, rotations, shifts = _canon_project(3, reconstruction, rotations, shifts)
+        # the processing order of the slices is settled once here and kept for the backward pass
+        order = _resolve_order(pose_order, reconstruction, rotations)
+        projection = _ops.project_3d_to_2d_forw_ordered(reconstruction, rotations, shifts, output_shape, interpolation,
+                                                        oversampling, fourier_radius_cutoff, order)
+        ctx.save_for_backward(reconstruction, rotations, shifts)
+        ctx.pose_order = order
+        ctx.interpolation = interpolation
+        ctx.oversampling = oversampling
+        ctx.fourier_radius_cutoff = fourier_radius_cutoff
+        return projection
 
     @staticmethod
     def backward(ctx, grad_output):
-        return _Project3DTo2D._run_backward(ctx, grad_output)
+        reconstruction, rotations, shifts = ctx.saved_tensors
+        grad_reconstruction, grad_rotations, grad_shifts = _ops.project_3d_to_2d_back_ordered(
+            grad_output.contiguous(), reconstruction, rotations, shifts, ctx.interpolation,
+            ctx.oversampling, ctx.fourier_radius_cutoff, ctx.pose_order)
+        if shifts is None:
+            grad_shifts = None
+        return grad_reconstruction, grad_rotations, grad_shifts, None, None, None, None, None
+
+
+def _canon_backproject(projections, weights, rotations, shifts):
+    if projections.dim() == 3:
+        projections = projections.unsqueeze(0)
+    rotations, shifts = _canon_poses(rotations, shifts)
+    if weights is not None and weights.dim() == 3:
+        weights = weights.unsqueeze(0)
+    if rotations.size(0) != projections.size(0) and rotations.size(0) != 1:
+        raise ValueError("Batch size of rotations must be 1 or match projections")
+    return projections, weights, rotations, shifts
 
 
 class _BackprojectBase(torch.autograd.Function):
     _forw = None
     _back = None
+    _ordered = False
 
     @classmethod
     def _run_forward(cls, ctx, projections, weights, rotations, shifts, interpolation,
                      oversampling, fourier_radius_cutoff):
-        if projections.dim() == 3:
-            projections = projections.unsqueeze(0)
-        rotations, shifts = _canon_poses(rotations, shifts)
-        if weights is not None and weights.dim() == 3:
-            weights = weights.unsqueeze(0)
-        if rotations.size(0) != projections.size(0) and rotations.size(0) != 1:
-            raise ValueError("Batch size of rotations must be 1 or match projections")
+        projections, weights, rotations, shifts = _canon_backproject(projections, weights, rotations, shifts)
         data_reconstruction, weight_reconstruction = getattr(_ops, cls._forw)(
             projections, weights, rotations, shifts, interpolation, oversampling, fourier_radius_cutoff)
         ctx.save_for_backward(projections, weights, rotations, shifts)
