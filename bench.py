@@ -817,6 +817,97 @@ def paper_matrix_workload(args):
                       "data": "synthetic", "dtype": "f32", "rows": rows}), flush=True)
 
 
+RED_PATTERNS = ["one random 16-byte slot per lane", "lane pairs on adjacent 16-byte slots", "lane pairs sharing a 32-byte sector",
+                "four lanes on four adjacent 8-byte voxels", "one random 8-byte voxel per lane", "lane pairs on adjacent 8-byte voxels"]
+
+
+def red_ceiling_workload(args):
+    """The rate at which red.global.add retires for the access patterns of the scatter kernels
+    (library probe, b200proj_reduction_rate_probe): on a 32 MiB buffer (L2-resident: the ceiling
+    the scatters are measured against) and on a 2 GiB buffer (what is left when the volume is far
+    beyond L2).  148 x 32 blocks of 256 lanes, 64 reductions per lane, CUDA events, median."""
+    import torch_projectors_b200 as tp
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    blocks, iters = 148 * 32, 64
+    taps = blocks * 256 * iters
+    rows = {}
+    sampler = ClockSampler(0)
+    sampler.start()
+    for label, nbytes in (("32 MiB (L2-resident)", 32 << 20), ("2 GiB (beyond L2)", 2 << 30)):
+        buf = torch.zeros(nbytes // 4, dtype=torch.float32, device=dev)
+        for pattern, name in enumerate(RED_PATTERNS):
+            ms = statistics.median(timed_steps(lambda: tp._abi.reduction_rate_probe(pattern, buf, blocks, iters),
+                                               max(args.steps, 5), args.warmup, lambda: None, lambda: None))
+            rows.setdefault(name, {})[label] = {"ms": ms, "g_taps_per_s": taps / (ms * 1e-3) / 1e9}
+        del buf
+        torch.cuda.empty_cache()
+    print(json.dumps({"metric": "red.global.add retired per second by access pattern (10^9 taps/s)", "data": "synthetic",
+                      "config": {"workload": f"{blocks} blocks x 256 lanes x {iters} reductions to pseudo-random places"},
+                      "rows": rows, "clocks": sampler.stop()}), flush=True)
+
+
+def latency_workload(args):
+    """Per-call cost of the smallest benchmark configuration (project_2d_forw, one 128x65 reference,
+    256 poses, 64x64 out, linear, oversampling 2): wall clock per call over a long back-to-back loop
+    (the device never idles) through the raw operator, through the public function, and replayed
+    from a CUDA graph of ten calls; next to it the reference's own CUDA operator when
+    oracle/_ref holds it."""
+    import oracle
+    import torch_projectors_b200 as tp
+    from cases import random_rotations_2d
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    gen = torch.Generator().manual_seed(11)
+    rec = torch.fft.rfft2(torch.fft.fftshift(torch.nn.functional.pad(torch.randn(64, 64, generator=gen), (32, 32, 32, 32))),
+                          norm="forward").to(torch.complex64).unsqueeze(0).to(dev)
+    rot = random_rotations_2d(256, gen).reshape(1, 256, 2, 2).to(dev)
+    sh = ((torch.rand(1, 256, 2, generator=gen) * 2 - 1) * 4).to(dev)
+    ops = torch.ops.torch_projectors_b200
+
+    def per_call_us(fn, n=3000):
+        for _ in range(200):
+            fn()
+        torch.cuda.synchronize()
+        best = None
+        for _ in range(5):
+            t0 = time.perf_counter()
+            for _ in range(n):
+                fn()
+            torch.cuda.synchronize()
+            dt = (time.perf_counter() - t0) / n * 1e6
+            best = dt if best is None else min(best, dt)
+        return best
+
+    rows = {"raw operator (torch.ops)": per_call_us(lambda: ops.project_2d_forw(rec, rot, sh, [64, 64], "linear", 2.0, None)),
+            "public function": per_call_us(lambda: tp.project_2d_forw(rec, rot, sh, output_shape=(64, 64), interpolation="linear", oversampling=2.0))}
+    r_g = rot.clone().requires_grad_(True)
+    rows["public function, rotations require grad (autograd.Function)"] = per_call_us(
+        lambda: tp.project_2d_forw(rec, r_g, sh, output_shape=(64, 64), interpolation="linear", oversampling=2.0))
+    graph = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        for _ in range(3):
+            ops.project_2d_forw(rec, rot, sh, [64, 64], "linear", 2.0, None)
+        torch.cuda.synchronize()
+        with torch.cuda.graph(graph, stream=side):
+            for _ in range(10):
+                out = ops.project_2d_forw(rec, rot, sh, [64, 64], "linear", 2.0, None)
+    rows["replayed from a CUDA graph of ten calls"] = per_call_us(graph.replay, n=500) / 10
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(1000):
+        graph.replay()
+    b.record()
+    torch.cuda.synchronize()
+    rows["device time per call (graph replays, CUDA events)"] = a.elapsed_time(b) / 10000 * 1e3
+    if oracle.reference_cuda_available():
+        ref = oracle.reference_cuda_ops()
+        rows["reference CUDA operator (torch.ops.torch_projectors)"] = per_call_us(lambda: ref.project_2d_forw(rec, rot, sh, [64, 64], "linear", 2.0, None))
+    print(json.dumps({"metric": "microseconds per call, project_2d_forw with 256 poses of 64x64 (back-to-back calls, wall clock)",
+                      "data": "synthetic", "rows": rows}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -830,7 +921,7 @@ def main():
     ap.add_argument("--profile-case", choices=["project", "backproject", "project_back", "backproject_slab", "accumulate_slab", "autograd_step", "project_2d"], default=None,
                     help="run a few launches of one kernel on a reduced pose count (for ncu captures); prints no bench line")
     ap.add_argument("--profile-poses", type=int, default=2048)
-    ap.add_argument("--workload", choices=["default", "autograd_step", "sharded_backproject", "ops_table", "reference_cuda", "paper_matrix"], default="default",
+    ap.add_argument("--workload", choices=["default", "autograd_step", "sharded_backproject", "ops_table", "reference_cuda", "paper_matrix", "red_ceiling", "latency"], default="default",
                     help="default: projection (+ back-projection) headline line; the other two print their own line")
     ap.add_argument("--total-slices", type=int, default=0, help="sharded_backproject: total slices over all ranks (default 200000)")
     ap.add_argument("--no-overlap-tail", action="store_true", help="sharded_backproject: fold and reduce after the last chunk instead of overlapping them with it")
@@ -846,6 +937,12 @@ def main():
         return
     if args.impl == "b200" and args.workload == "autograd_step":
         autograd_step_workload(args)
+        return
+    if args.impl == "b200" and args.workload == "red_ceiling":
+        red_ceiling_workload(args)
+        return
+    if args.impl == "b200" and args.workload == "latency":
+        latency_workload(args)
         return
     if args.impl == "b200" and args.workload == "paper_matrix":
         paper_matrix_workload(args)
@@ -932,11 +1029,26 @@ def main():
     h2d = h_rec.numel() * 8 + h_rot.numel() * 4 + h_sh.numel() * 4
     d2h = h_out.numel() * 8
     e2e = {"value": world * PROJ["P"] / (e2e_ms_per_step * 1e-3), "unit": "slices/s", "ms_per_step": e2e_ms_per_step,
-           "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}
+           "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+           "pcie_gbs": (h2d + d2h) / (e2e_ms_per_step * 1e-3) / 1e9}
+    # the same with packed output: only the pixels inside the cutoff leave the device
+    n_inside = tp._abi.cutoff_pack_index(PROJ["N"], PROJ["cutoff"], dev)[1]
+    h_packed = torch.empty((1, PROJ["P"], n_inside), dtype=torch.complex64).pin_memory()
+
+    def e2e_packed_step():
+        tp.project_3d_to_2d_to_host(h_rec, h_rot, h_sh, out=h_packed, chunk=1000, device=dev, packed=True, **kw)
+
+    p_ms = timed_steps(e2e_packed_step, max(3, args.steps // 2), 3, flush, barrier)
+    p_ms_per_step = max_over_ranks(sum(p_ms) / len(p_ms))
+    e2e_packed = {"value": world * PROJ["P"] / (p_ms_per_step * 1e-3), "unit": "slices/s", "ms_per_step": p_ms_per_step,
+                  "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": h_packed.numel() * 8,
+                  "pcie_gbs": (h2d + h_packed.numel() * 8) / (p_ms_per_step * 1e-3) / 1e9,
+                  "note": f"{n_inside} of {PROJ['N'] * (PROJ['N'] // 2 + 1)} pixels per slice lie inside the cutoff and are copied"}
+    del h_packed
     # kernels of this package launched so far: one per device-resident step, one per 1000-pose
     # chunk in every end-to-end step (warm-ups included)
     e2e_chunks = (PROJ["P"] + 999) // 1000
-    launches = args.steps + args.warmup + (len(e2e_ms) + 3) * e2e_chunks
+    launches = args.steps + args.warmup + (len(e2e_ms) + 3) * e2e_chunks + (len(p_ms) + 3) * e2e_chunks
     del h_out, out_holder
     torch.cuda.empty_cache()
 
@@ -1003,7 +1115,7 @@ def main():
             "dtype": "f32", "data": "synthetic",
             "config": {"workload": PROJ["name"], "poses_per_gpu": PROJ["P"], "parallelism": f"poses sharded over {world} GPU(s), volume replicated",
                        "l2": "flushed before every step (256 MiB memset outside the timed events)"},
-            "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches, "clocks": clocks,
+            "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "e2e_packed": e2e_packed, "gpu_launches": launches, "clocks": clocks,
             "parity_check": parity, "backproject": back, "sharded_backproject": sharded,
         }
         print(json.dumps(line), flush=True)

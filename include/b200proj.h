@@ -91,6 +91,24 @@ int b200proj_project_3d_to_2d_forw(const float* rec, int64_t B, int64_t R,
                                    double fourier_radius_cutoff, float* out,
                                    const int32_t* pose_order, void* stream);
 
+/* ---- forward projection with packed output ------------------------------------------------
+ * No counterpart in the reference.  For callers that move the projections off the device: only
+ * the pixels inside the cutoff are produced, side by side, out_packed [B, P, pack_count] complex
+ * (at cutoff N/2 that is 78 % of the stored pixels), so the zeros outside the cutoff never cross
+ * PCIe.  b200proj_cutoff_pack_index (host only, launches nothing) fills index [N * Nh] with the
+ * position of every pixel among the packed ones (-1 outside the cutoff), using the kernels' own
+ * cutoff test, and returns their number (index may be NULL to get the count alone; -1 on bad
+ * arguments).  The caller copies that table to the device once and passes it as pack_index; to
+ * unpack, scatter out_packed[.., index[q]] to pixel q.  float only. */
+int64_t b200proj_cutoff_pack_index(int64_t N, double fourier_radius_cutoff, int32_t* index);
+int b200proj_project_3d_to_2d_forw_packed(const float* rec, int64_t B, int64_t R,
+                                          const float* rot, int64_t B_rot,
+                                          const float* shifts, int64_t B_shift,
+                                          int64_t P, int64_t N, int interpolation, double oversampling,
+                                          double fourier_radius_cutoff, float* out_packed,
+                                          const int32_t* pack_index, int64_t pack_count,
+                                          const int32_t* pose_order, void* stream);
+
 /* ---- processing order of the slices (3D operators that read a volume) -------------------
  * No counterpart in the reference.  The three volume-reading 3D entry points
  * (project_3d_to_2d_forw, project_3d_to_2d_back, backproject_2d_to_3d_back) take an optional
@@ -222,6 +240,13 @@ int b200proj_accumulator_fold(const void* accumulator, int64_t B, int64_t R, flo
 int b200proj_accumulator_fold_range(const void* accumulator, int64_t first_voxel, int64_t voxel_count,
                                     float* data_rec, float* weight_rec, int accumulate, void* stream);
 
+/* The weighted-average reconstruction data / max(weight, eps) (the usual consumer of the two
+ * volumes: README.md:152-160 and paper/main.tex:72 of the reference) straight from the
+ * accumulator, for voxels [first_voxel, first_voxel + voxel_count): fold and division in one
+ * pass.  normalized is the base of a complex [B,R,R,Rh] volume; eps > 0. */
+int b200proj_accumulator_fold_normalized(const void* accumulator, int64_t first_voxel, int64_t voxel_count,
+                                         double eps, float* normalized, void* stream);
+
 /* Slab by slab.  An accumulator larger than L2 is filled by slab-ordered passes: the planes of
  * the volume (signed coordinate z = -R/2+1 .. R/2, stored at index z < 0 ? z + R : z) are cut
  * into `slabs` runs of `planes_per_slab` consecutive z, and a pass issues only the reductions
@@ -264,6 +289,19 @@ int b200proj_pad_fftshift_f64(const double* real, int64_t batch, int dims, int64
                               double* out, void* stream);
 int b200proj_ifftshift_crop_f64(const double* full, int64_t batch, int dims, int64_t m, int64_t n,
                                 double* out, void* stream);
+
+/* ---- reduction-rate probe (diagnostic) ------------------------------------------------------
+ * No counterpart in the reference.  The scatter kernels are bound by the rate at which the memory
+ * system retires red.global.add, not by HBM bandwidth; this probe measures that rate for their
+ * access patterns so that a benchmark can state it beside the kernels' own rate.  `blocks` blocks
+ * of 256 lanes each issue `iterations` reductions to pseudo-random places of `buffer`
+ * (buffer_bytes, 16-byte aligned; size it below L2 for the ceiling, far above for the DRAM rate):
+ *   0 one random 16-byte slot per lane (v4)      1 lane pairs on adjacent 16-byte slots (v4)
+ *   2 lane pairs sharing a 32-byte sector (v4)   3 four lanes on four adjacent 8-byte voxels (v2)
+ *   4 one random 8-byte voxel per lane (v2)      5 lane pairs on adjacent 8-byte voxels (v2)
+ * The buffer's contents are added to, not preserved. */
+int b200proj_reduction_rate_probe(int pattern, float* buffer, size_t buffer_bytes, int blocks,
+                                  int iterations, void* stream);
 
 /* ---- backward of back-projection (gather) ----------------------------------------------
  * grad_proj [B,P,N,Nh] complex is fully written.  grad_weights [B,P,N,Nh] float is written

@@ -1,0 +1,69 @@
+"""Additions around the operators: packed projections (only the pixels inside the cutoff), the
+weighted-average reconstruction straight from the accumulator, and the reduction-rate probe."""
+import pytest
+import torch
+
+from cases import Case, TOL_ATOMIC, make_inputs, rel_err
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def tp(cuda_device):
+    import torch_projectors_b200
+    return torch_projectors_b200
+
+
+@pytest.mark.parametrize("interp,cutoff", [("cubic", None), ("linear", 5.5), ("cubic", 100.0)])
+def test_packed_projection_holds_exactly_the_pixels_inside_the_cutoff(tp, interp, cutoff):
+    case = Case("packed", 3, interp, 2, 9, 16, 32, 2.0, cutoff, 2, 2, shift_range=3.0, seed=81)
+    t = {k: (v.cuda() if v is not None else None) for k, v in make_inputs(case).items()}
+    kw = dict(output_shape=(16, 16), interpolation=interp, oversampling=2.0, fourier_radius_cutoff=cutoff)
+    dense = tp.project_3d_to_2d_forw(t["rec"], t["rot"], t["shifts"], **kw)
+    packed, index = tp.project_3d_to_2d_forw_packed(t["rec"], t["rot"], t["shifts"], **kw)
+    # the table marks what the dense kernel leaves non-zero-able: kr^2 + kc^2 <= cutoff^2
+    kr = torch.where(torch.arange(16) <= 8, torch.arange(16), torch.arange(16) - 16).float()[:, None]
+    kc = torch.arange(9).float()[None, :]
+    inside = (kr * kr + kc * kc <= (cutoff if cutoff is not None else 8.0) ** 2).flatten()
+    assert torch.equal(index.cpu() >= 0, inside) and packed.shape == (2, 9, int(inside.sum()))
+    assert torch.equal(index.cpu()[inside], torch.arange(int(inside.sum()), dtype=torch.int32))
+    assert torch.equal(tp.unpack_projections(packed, index, 16), dense)          # bit for bit
+    assert dense.flatten(2)[:, :, ~inside.cuda()].abs().max().item() == 0.0 if (~inside).any() else True
+
+
+def test_packed_host_streaming_matches_the_dense_call(tp):
+    case = Case("packed_host", 3, "linear", 1, 37, 16, 32, 2.0, None, 1, 1, seed=82, special_poses=False)
+    t = make_inputs(case)
+    pin = lambda x: x.pin_memory()  # noqa: E731
+    out, index = tp.project_3d_to_2d_to_host(pin(t["rec"]), pin(t["rot"]), pin(t["shifts"]), chunk=8, output_shape=(16, 16),
+                                             interpolation="linear", oversampling=2.0, packed=True)
+    torch.cuda.current_stream().synchronize()
+    want = tp.project_3d_to_2d_forw(t["rec"].cuda(), t["rot"].cuda(), t["shifts"].cuda(), output_shape=(16, 16), oversampling=2.0)
+    assert not out.is_cuda and not index.is_cuda and out.shape[-1] == int((index >= 0).sum())
+    assert torch.equal(tp.unpack_projections(out, index, 16), want.cpu())
+
+
+def test_normalized_fold_equals_fold_then_divide(tp):
+    from oracle import port
+    case = Case("norm", 3, "linear", 2, 12, 16, 32, 2.0, None, 2, 2, weights=True, seed=83)
+    t = make_inputs(case)
+    c = lambda x: x.cuda()  # noqa: E731
+    acc = tp.new_backprojection_accumulator(2, 32, "cuda")
+    tp.backproject_2d_to_3d_accumulate_interleaved_(acc, c(t["proj"]), c(t["rot"]), c(t["weights"]), c(t["shifts"]), oversampling=2.0)
+    got = tp.fold_backprojection_accumulator_normalized(acc, eps=1e-2)
+    d, w = tp.fold_backprojection_accumulator(acc)
+    assert rel_err(got, tp.prep.normalize_by_weights(d, w, eps=1e-2)) <= 1e-6
+    dw, ww = port.backproject_2d_to_3d_forw(t["proj"], t["weights"], t["rot"], t["shifts"], "linear", 2.0)
+    assert rel_err(got, dw / torch.clamp(ww, min=1e-2)) <= TOL_ATOMIC
+    with pytest.raises(RuntimeError, match="eps must be positive"):
+        tp.fold_backprojection_accumulator_normalized(acc, eps=0.0)
+
+
+@pytest.mark.parametrize("pattern,per_tap", [(0, 3.0), (1, 3.0), (2, 3.0), (3, 2.0), (4, 2.0), (5, 2.0)])
+def test_reduction_rate_probe_issues_every_reduction(tp, pattern, per_tap):
+    buf = torch.zeros(1 << 18, dtype=torch.float32, device="cuda")           # 1 MiB
+    tp._abi.reduction_rate_probe(pattern, buf, blocks=8, iterations=5)
+    torch.cuda.synchronize()
+    assert buf.double().sum().item() == 8 * 256 * 5 * per_tap                 # every lane added 1.0 to 3 (v4) or 2 (v2) floats
+    with pytest.raises(RuntimeError, match="pattern must be"):
+        tp._abi.reduction_rate_probe(9, buf, blocks=1, iterations=1)

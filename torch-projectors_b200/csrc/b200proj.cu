@@ -82,6 +82,8 @@ int prepare(Launch& L, int dim, int64_t B, int64_t R, int64_t B_rot, const void*
     g.shift_scale = -2.0 * M_PI / (double)N;
     g.vol_elems = vol;
     g.order = nullptr;
+    g.pack_index = nullptr;
+    g.pack_count = 0;
 
     if (B * P > INT_MAX / 2) return fail(B200PROJ_ERR_LIMIT, "B*P = %lld slices exceed the grid limit; split the poses into chunks", (long long)(B * P));
     g.BP = (int)(B * P);
@@ -666,6 +668,82 @@ int b200proj_accumulator_fold_range(const void* accumulator, int64_t first_voxel
     fold_interleaved_kernel<<<(unsigned)(blocks < 148 * 16 ? blocks : 148 * 16), 256, 0, (cudaStream_t)stream>>>(
         (const float4*)accumulator + first_voxel, (float2*)data_rec + first_voxel, weight_rec + first_voxel, n, accumulate != 0);
     return check_launch("fold_interleaved launch");
+}
+
+int b200proj_accumulator_fold_normalized(const void* accumulator, int64_t first_voxel, int64_t voxel_count,
+                                         double eps, float* normalized, void* stream) {
+    g_error[0] = 0;
+    if (accumulator == nullptr || normalized == nullptr) return fail(B200PROJ_ERR_ARGUMENT, "accumulator and output are required");
+    if (first_voxel < 0 || voxel_count < 0) return fail(B200PROJ_ERR_ARGUMENT, "voxel range must be non-negative (first=%lld, count=%lld)", (long long)first_voxel, (long long)voxel_count);
+    if (!(eps > 0.0)) return fail(B200PROJ_ERR_ARGUMENT, "eps must be positive");
+    if (voxel_count == 0) return B200PROJ_OK;
+    const size_t n = (size_t)voxel_count;
+    const size_t blocks = (n + 255) / 256;
+    fold_normalized_kernel<<<(unsigned)(blocks < 148 * 16 ? blocks : 148 * 16), 256, 0, (cudaStream_t)stream>>>(
+        (const float4*)accumulator + first_voxel, (float2*)normalized + first_voxel, n, (float)eps);
+    return check_launch("fold_normalized launch");
+}
+
+int64_t b200proj_cutoff_pack_index(int64_t N, double cutoff, int32_t* index) {
+    g_error[0] = 0;
+    if (N < 2 || (N % 2) != 0 || N > 2048 || std::isnan(cutoff)) { fail(B200PROJ_ERR_ARGUMENT, "need an even projection boxsize in [2, 2048] and a cutoff"); return -1; }
+    // the kernels' own test (pixel_setup): kr*kr + kc*kc > float(cutoff)^2 in fp32 excludes a pixel
+    const float rc = (float)cutoff, cutoff_sq = rc * rc;
+    const int64_t Nh = N / 2 + 1;
+    int64_t count = 0;
+    for (int64_t i = 0; i < N; ++i) {
+        const float kr = (float)((i <= N / 2) ? i : i - N);
+        for (int64_t j = 0; j < Nh; ++j) {
+            const float kc = (float)j;
+            const bool inside = !(kr * kr + kc * kc > cutoff_sq);
+            if (index != nullptr) index[i * Nh + j] = inside ? (int32_t)count : -1;
+            count += inside ? 1 : 0;
+        }
+    }
+    return count;
+}
+
+int b200proj_project_3d_to_2d_forw_packed(const float* rec, int64_t B, int64_t R, const float* rot,
+                                          int64_t B_rot, const float* shifts, int64_t B_shift, int64_t P,
+                                          int64_t N, int interpolation, double oversampling, double cutoff,
+                                          float* out_packed, const int32_t* pack_index, int64_t pack_count,
+                                          const int32_t* pose_order, void* stream) {
+    Launch L;
+    if (int rc = prepare(L, 3, B, R, B_rot, rot, shifts, B_shift, P, N, interpolation, oversampling, cutoff)) return rc;
+    if (rec == nullptr || out_packed == nullptr || pack_index == nullptr)
+        return fail(B200PROJ_ERR_ARGUMENT, "reconstruction / output / pack_index pointer is NULL");
+    if (pack_count != b200proj_cutoff_pack_index(N, cutoff, nullptr))
+        return fail(B200PROJ_ERR_ARGUMENT, "pack_count %lld is not the number of pixels inside the cutoff (%lld)",
+                    (long long)pack_count, (long long)b200proj_cutoff_pack_index(N, cutoff, nullptr));
+    L.g.order = pose_order;
+    L.g.pack_index = pack_index;
+    L.g.pack_count = (int)pack_count;
+    if (P == 0 || pack_count == 0) return B200PROJ_OK;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (interpolation == B200PROJ_CUBIC)
+        project_forw_kernel<3, true, float, true><<<L.grid, kBlockThreads, 0, s>>>((const float2*)rec, rot, shifts, (float2*)out_packed, L.g);
+    else
+        project_forw_kernel<3, false, float, true><<<L.grid, kBlockThreads, 0, s>>>((const float2*)rec, rot, shifts, (float2*)out_packed, L.g);
+    return check_launch("project_forw (packed) launch");
+}
+
+int b200proj_reduction_rate_probe(int pattern, float* buffer, size_t buffer_bytes, int blocks, int iterations, void* stream) {
+    g_error[0] = 0;
+    if (buffer == nullptr || (reinterpret_cast<uintptr_t>(buffer) & 15u) != 0) return fail(B200PROJ_ERR_ARGUMENT, "buffer must be a 16-byte aligned device pointer");
+    if (pattern < 0 || pattern > 5 || blocks < 1 || iterations < 1) return fail(B200PROJ_ERR_ARGUMENT, "pattern must be 0..5, blocks and iterations >= 1");
+    const size_t unit = pattern <= 2 ? 16 : 8;
+    const size_t units = buffer_bytes / unit;
+    if (units < 16 || units > 0xffffffffull) return fail(B200PROJ_ERR_LIMIT, "buffer of %zu bytes holds too few or too many units", buffer_bytes);
+    cudaStream_t s = (cudaStream_t)stream;
+    switch (pattern) {
+        case 0: reduction_rate_kernel<0><<<blocks, 256, 0, s>>>(buffer, (unsigned)units, iterations); break;
+        case 1: reduction_rate_kernel<1><<<blocks, 256, 0, s>>>(buffer, (unsigned)units, iterations); break;
+        case 2: reduction_rate_kernel<2><<<blocks, 256, 0, s>>>(buffer, (unsigned)units, iterations); break;
+        case 3: reduction_rate_kernel<3><<<blocks, 256, 0, s>>>(buffer, (unsigned)units, iterations); break;
+        case 4: reduction_rate_kernel<4><<<blocks, 256, 0, s>>>(buffer, (unsigned)units, iterations); break;
+        default: reduction_rate_kernel<5><<<blocks, 256, 0, s>>>(buffer, (unsigned)units, iterations); break;
+    }
+    return check_launch("reduction_rate_probe launch");
 }
 
 int b200proj_accumulator_fold(const void* accumulator, int64_t B, int64_t R, float* data_rec,

@@ -82,7 +82,10 @@ __device__ __forceinline__ const R* pose_shift(const SliceGeom& g, const R* shif
 
 // ---- forward projection -----------------------------------------------------------------
 // reference semantics: csrc/cpu/3d/projection_3d_to_2d_kernels.cpp:155-207
-template <int DIM, bool CUBIC, typename R>
+// PACKED: only the pixels inside the cutoff are written, side by side ([B, P, pack_count]; the
+// position of a pixel comes from g.pack_index), for callers that copy the projections to the host
+// and do not want to move the zeros outside the cutoff over PCIe.
+template <int DIM, bool CUBIC, typename R, bool PACKED = false>
 __global__ void __launch_bounds__(kBlockThreads)
 project_forw_kernel(const C2<R>* __restrict__ rec, const R* __restrict__ rot,
                     const R* __restrict__ shifts, C2<R>* __restrict__ out, const SliceGeom g) {
@@ -100,7 +103,14 @@ project_forw_kernel(const C2<R>* __restrict__ rec, const R* __restrict__ rot,
     }
     // streaming store: the projections are written once and never re-read by this kernel,
     // keep the cache for the volume
-    __stcs(out + w.pix, v);
+    if constexpr (PACKED) {
+        if (valid) {
+            const int slot = __ldg(g.pack_index + (w.i * g.Nh + w.j));
+            if (slot >= 0) __stcs(out + ((size_t)(w.b * g.P + w.p) * (size_t)g.pack_count + (size_t)slot), v);
+        }
+    } else {
+        __stcs(out + w.pix, v);
+    }
 }
 
 // Pose-gradient terms shared by the two backward kernels.
@@ -279,6 +289,18 @@ fold_interleaved_kernel(const float4* __restrict__ accum, float2* __restrict__ d
         }
         data[k] = d;
         weight[k] = wv;
+    }
+}
+
+// out[k] = accum[k].xy / max(accum[k].z, eps): the weighted-average reconstruction straight from
+// the interleaved accumulator (the fold and the division by the weights in one pass).
+__global__ void __launch_bounds__(256)
+fold_normalized_kernel(const float4* __restrict__ accum, float2* __restrict__ out, size_t n, float eps) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t k = (size_t)blockIdx.x * blockDim.x + threadIdx.x; k < n; k += stride) {
+        const float4 a = __ldcs(accum + k);
+        const float inv = 1.0f / fmaxf(a.z, eps);
+        out[k] = make_float2(a.x * inv, a.y * inv);
     }
 }
 
@@ -558,6 +580,50 @@ pose_order_kernel(const R* __restrict__ rot, long long rot_stride_b, int P, int*
     for (int p = t; p < P; p += kOrderBins) {
         const int pos = atomicAdd(&bins[pose_order_key(rm + (size_t)p * 9)], 1);
         order[base + pos] = base + p;
+    }
+}
+
+// ---- reduction-rate probe -------------------------------------------------------------------
+// How many red.global.add the memory system retires per second for the access patterns of the
+// scatter kernels, on a buffer the caller sizes (L2-resident: the ceiling of the scatters; far
+// beyond L2: what they fall to when the volume does not fit).  Every lane issues `iters`
+// reductions to pseudo-random places:
+//   0  one random 16-byte slot per lane                      (red.v4)
+//   1  lane pairs on two adjacent 16-byte slots              (red.v4; the linear scatter into an interleaved volume)
+//   2  lane pairs on the two halves of one 32-byte sector    (red.v4)
+//   3  four lanes on four adjacent 8-byte voxels             (red.v2; the cubic scatter into a complex volume)
+//   4  one random 8-byte voxel per lane                      (red.v2)
+//   5  lane pairs on two adjacent 8-byte voxels              (red.v2; the linear scatter into a complex volume)
+__device__ __forceinline__ unsigned probe_hash(unsigned x) {
+    x ^= x >> 16; x *= 0x7feb352du; x ^= x >> 15; x *= 0x846ca68bu; x ^= x >> 16;
+    return x;
+}
+
+template <int PATTERN>
+__global__ void __launch_bounds__(256)
+reduction_rate_kernel(float* __restrict__ buf, unsigned units, int iters) {
+    // units: 16-byte slots (patterns 0-2) or 8-byte voxels (3-5) in the buffer
+    const unsigned t = blockIdx.x * blockDim.x + threadIdx.x;
+    for (int i = 0; i < iters; ++i) {
+        if (PATTERN == 0) {
+            const unsigned s = probe_hash(t * 977u + i * 7919u) % units;
+            red_add_v4(reinterpret_cast<float4*>(buf) + s, 1.f, 1.f, 1.f, 0.f);
+        } else if (PATTERN == 1) {
+            const unsigned s = probe_hash((t >> 1) * 977u + i * 7919u) % (units - 1) + (t & 1);
+            red_add_v4(reinterpret_cast<float4*>(buf) + s, 1.f, 1.f, 1.f, 0.f);
+        } else if (PATTERN == 2) {
+            const unsigned s = (probe_hash((t >> 1) * 977u + i * 7919u) % (units / 2)) * 2 + (t & 1);
+            red_add_v4(reinterpret_cast<float4*>(buf) + s, 1.f, 1.f, 1.f, 0.f);
+        } else if (PATTERN == 3) {
+            const unsigned s = probe_hash((t >> 2) * 977u + i * 7919u) % (units - 3) + (t & 3);
+            red_add_v2(reinterpret_cast<float2*>(buf) + s, 1.f, 1.f);
+        } else if (PATTERN == 4) {
+            const unsigned s = probe_hash(t * 977u + i * 7919u) % units;
+            red_add_v2(reinterpret_cast<float2*>(buf) + s, 1.f, 1.f);
+        } else {
+            const unsigned s = probe_hash((t >> 1) * 977u + i * 7919u) % (units - 1) + (t & 1);
+            red_add_v2(reinterpret_cast<float2*>(buf) + s, 1.f, 1.f);
+        }
     }
 }
 

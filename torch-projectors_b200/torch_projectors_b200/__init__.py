@@ -19,6 +19,9 @@ from .ops import (  # noqa: E402
     backproject_2d_to_3d_accumulate_,
     backproject_2d_to_3d_accumulate_interleaved_,
     fold_backprojection_accumulator,
+    fold_backprojection_accumulator_normalized,
+    project_3d_to_2d_forw_packed,
+    unpack_projections,
     new_backprojection_accumulator,
     plane_locality_order,
     set_pose_order_thresholds,
@@ -41,6 +44,7 @@ __all__ = [
     "backproject_2d_forw", "backproject_2d_to_3d_forw", "backproject_2d_to_3d_back",
     "backproject_2d_to_3d_accumulate_", "backproject_2d_to_3d_accumulate_interleaved_",
     "new_backprojection_accumulator", "fold_backprojection_accumulator", "plane_locality_order",
-    "set_pose_order_thresholds", "sharding", "streaming", "prep",
+    "set_pose_order_thresholds", "fold_backprojection_accumulator_normalized", "project_3d_to_2d_forw_packed",
+    "unpack_projections", "sharding", "streaming", "prep",
     "project_3d_to_2d_to_host", "backproject_2d_to_3d_from_host",
 ]

@@ -43,11 +43,14 @@ SIGNATURES.update({name + "_f64": sig for name, sig in list(SIGNATURES.items()) 
 SIGNATURES["b200proj_backproject_2d_to_3d_accumulate"] = [_ptr, _ptr] + _COMMON + [_ptr, _ptr]
 SIGNATURES["b200proj_accumulator_fold"] = [_ptr, _i64, _i64, _ptr, _ptr, _int, _ptr]
 SIGNATURES["b200proj_accumulator_fold_range"] = [_ptr, _i64, _i64, _ptr, _ptr, _int, _ptr]
+SIGNATURES["b200proj_accumulator_fold_normalized"] = [_ptr, _i64, _i64, _dbl, _ptr, _ptr]
+SIGNATURES["b200proj_project_3d_to_2d_forw_packed"] = [_ptr] + _COMMON + [_ptr, _ptr, _i64, _ptr, _ptr]
+SIGNATURES["b200proj_reduction_rate_probe"] = [_int, _ptr, C.c_size_t, _int, _int, _ptr]
 SIGNATURES["b200proj_backproject_2d_to_3d_accumulate_slabs"] = [_ptr, _ptr] + _COMMON + [_ptr, _int, _int, _ptr]
 EXPORTS = list(SIGNATURES) + ["b200proj_version", "b200proj_last_error", "b200proj_rec_boxsize",
                                 "b200proj_backproject_workspace_bytes", "b200proj_accumulator_bytes",
                                 "b200proj_source_stamp", "b200proj_accumulator_slab_plan",
-                                "b200proj_accumulator_slab_voxels", "b200proj_debug_index"]
+                                "b200proj_accumulator_slab_voxels", "b200proj_debug_index", "b200proj_cutoff_pack_index"]
 
 _lib: Optional[C.CDLL] = None
 
@@ -95,6 +98,8 @@ def load() -> C.CDLL:
     lib.b200proj_backproject_workspace_bytes.argtypes = [_int, _i64, _i64, _i64, _i64, _int, _int]
     lib.b200proj_accumulator_bytes.restype = C.c_size_t
     lib.b200proj_accumulator_bytes.argtypes = [_i64, _i64]
+    lib.b200proj_cutoff_pack_index.restype = _i64
+    lib.b200proj_cutoff_pack_index.argtypes = [_i64, _dbl, _ptr]
     lib.b200proj_accumulator_slab_plan.restype = _int
     lib.b200proj_accumulator_slab_plan.argtypes = [_i64, C.POINTER(C.c_int32), C.POINTER(C.c_int32)]
     lib.b200proj_accumulator_slab_voxels.restype = _int
@@ -269,3 +274,37 @@ def backproject_back(dim, grad_data_rec, grad_weight_rec, proj, rot, shifts, int
     _call(name, proj, _p(grad_data_rec), _p(grad_weight_rec), _p(proj),
           *_geom(B, R, rot, shifts, P, N, interp, oversampling, cutoff),
           _p(grad_proj), _p(grad_weights), _p(grad_rot), _p(grad_shifts), *_order_arg(dim, order))
+
+
+def accumulator_fold_normalized(accumulator, eps, normalized, voxel_range=None):
+    """normalized[k] = accumulator data[k] / max(accumulator weight[k], eps), for the whole
+    volume or for the flattened voxel range (first, stop)."""
+    first, stop = voxel_range if voxel_range is not None else (0, normalized.numel())
+    _call("b200proj_accumulator_fold_normalized", normalized, _p(accumulator), int(first), int(stop - first), float(eps), _p(normalized))
+
+
+_pack_tables = {}
+
+
+def cutoff_pack_index(N: int, cutoff: float, device):
+    """(index, count): int32 [N * Nh] device table with the position of every pixel among the
+    `count` pixels inside the cutoff (-1 outside), made by the library's own cutoff test; cached."""
+    key = (int(N), float(cutoff), str(device))
+    hit = _pack_tables.get(key)
+    if hit is None:
+        host = torch.empty(N * (N // 2 + 1), dtype=torch.int32)
+        count = int(load().b200proj_cutoff_pack_index(int(N), float(cutoff), host.data_ptr()))
+        if count < 0:
+            raise RuntimeError("b200proj_cutoff_pack_index: " + load().b200proj_last_error().decode("utf-8", "replace"))
+        hit = _pack_tables[key] = (host.to(device), count)
+    return hit
+
+
+def project_3d_to_2d_forw_packed(rec, rot, shifts, P, N, interp, oversampling, cutoff, out_packed, pack_index, pack_count, order=None):
+    B, R = rec.shape[0], rec.shape[-2]
+    _call("b200proj_project_3d_to_2d_forw_packed", rec, _p(rec), *_geom(B, R, rot, shifts, P, N, interp, oversampling, cutoff),
+          _p(out_packed), _p(pack_index), int(pack_count), _p(order))
+
+
+def reduction_rate_probe(pattern: int, buffer, blocks: int, iterations: int):
+    _call("b200proj_reduction_rate_probe", buffer, int(pattern), _p(buffer), buffer.numel() * buffer.element_size(), int(blocks), int(iterations))

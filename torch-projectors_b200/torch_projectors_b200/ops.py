@@ -446,6 +446,65 @@ def fold_backprojection_accumulator(accumulator: torch.Tensor, data_rec: Optiona
     return data_rec, weight_rec
 
 
+def fold_backprojection_accumulator_normalized(accumulator: torch.Tensor, eps: float = 1e-3,
+                                               out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The weighted-average reconstruction ``data / max(weight, eps)`` straight from the
+    accumulator (fold and division in one pass; the same values as
+    ``prep.normalize_by_weights(*fold_backprojection_accumulator(acc), eps)``).  For reconstructions
+    made on one GPU; partial volumes of several ranks have to be reduced before they are divided."""
+    _check(accumulator.is_cuda and accumulator.dtype == torch.float32 and accumulator.dim() == 5
+           and accumulator.size(-1) == 4 and accumulator.is_contiguous(), "accumulator must come from new_backprojection_accumulator")
+    _check(eps > 0, "eps must be positive")
+    shape = tuple(accumulator.shape[:-1])
+    if out is None:
+        out = torch.empty(shape, dtype=torch.complex64, device=accumulator.device)
+    _check(tuple(out.shape) == shape and out.dtype == torch.complex64 and out.is_contiguous() and out.device == accumulator.device,
+           f"out must be a contiguous complex64 tensor of shape {shape}")
+    if out.numel():
+        _abi.accumulator_fold_normalized(accumulator, eps, out)
+    return out
+
+
+def project_3d_to_2d_forw_packed(reconstruction: torch.Tensor, rotations: torch.Tensor,
+                                 shifts: Optional[torch.Tensor] = None, output_shape: Optional[tuple] = None,
+                                 interpolation: str = "linear", oversampling: float = 1.0,
+                                 fourier_radius_cutoff: Optional[float] = None,
+                                 pose_order: Union[torch.Tensor, bool, None] = None):
+    """``project_3d_to_2d_forw`` (no autograd, complex64) that produces only the pixels inside the
+    cutoff: returns (packed [B, P, n_inside] complex64, index [N * Nh] int32 with the position of
+    every pixel among the packed ones, -1 outside).  ``unpack_projections`` restores the dense
+    slices.  For results that leave the device: the zeros outside the cutoff are never moved."""
+    if reconstruction.dim() != 4:
+        raise ValueError("Reconstruction must be a 4D tensor (B, D, H, W/2+1)")
+    _validate_rec_box(reconstruction.shape[2], reconstruction.shape[3])
+    output_shape = _validate_output_shape(output_shape, reconstruction.shape[2])
+    reconstruction, rotations, shifts = _canon_project(3, reconstruction, rotations, shifts)
+    _check(reconstruction.is_cuda and reconstruction.dtype == torch.complex64, "the packed projection takes complex64 CUDA volumes")
+    interp = _interp_code(interpolation)
+    B, N = reconstruction.size(0), int(output_shape[0])
+    P, rot, sh = _check_pose_inputs(3, "reconstruction", B, rotations, shifts, reconstruction)
+    cutoff = _cutoff(fourier_radius_cutoff, N)
+    index, count = _abi.cutoff_pack_index(N, cutoff, reconstruction.device)
+    packed = torch.empty((B, P, count), dtype=torch.complex64, device=reconstruction.device)
+    if packed.numel():
+        rec = reconstruction.contiguous()
+        order = _resolve_order(pose_order, rec, rot)
+        _abi.project_3d_to_2d_forw_packed(rec, rot, sh, P, N, interp, oversampling, cutoff, packed, index, count,
+                                          order if order.numel() else None)
+    return packed, index
+
+
+def unpack_projections(packed: torch.Tensor, index: torch.Tensor, boxsize: int) -> torch.Tensor:
+    """Dense [B, P, N, N/2+1] slices (zeros outside the cutoff) from the output of
+    ``project_3d_to_2d_forw_packed``; works on host or device tensors."""
+    Nh = boxsize // 2 + 1
+    index = index.to(packed.device).long()
+    inside = index >= 0
+    dense = torch.zeros(packed.shape[:-1] + (boxsize * Nh,), dtype=packed.dtype, device=packed.device)
+    dense[..., inside] = packed[..., index[inside]]
+    return dense.view(packed.shape[:-1] + (boxsize, Nh))
+
+
 # ---------------------------------------------------------------------------------------
 # autograd glue (reference: torch_projectors/ops.py:300-514)
 # ---------------------------------------------------------------------------------------

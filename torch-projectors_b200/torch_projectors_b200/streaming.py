@@ -32,8 +32,12 @@ def project_3d_to_2d_to_host(reconstruction: torch.Tensor, rotations: torch.Tens
                              out: Optional[torch.Tensor] = None, chunk: int = 1024, device=None,
                              output_shape: Optional[Tuple[int, int]] = None,
                              interpolation: str = "linear", oversampling: float = 1.0,
-                             fourier_radius_cutoff: Optional[float] = None) -> torch.Tensor:
+                             fourier_radius_cutoff: Optional[float] = None, packed: bool = False):
     """``project_3d_to_2d_forw`` from host (or device) inputs to a HOST result.
+
+    ``packed=True``: only the pixels inside the cutoff are produced and copied (at the default
+    cutoff 78 % of the bytes): returns (out [B,P,n_inside] pinned host tensor, index [N*Nh] int32
+    host tensor); ``ops.unpack_projections(out, index, N)`` gives the dense slices.
 
     reconstruction [B,D,H,W/2+1], rotations [B_rot,P,3,3], shifts [B_s,P,2] may live on the
     host (ideally pinned) or on the device.  Projections are produced `chunk` poses at a time
@@ -55,20 +59,32 @@ def project_3d_to_2d_to_host(reconstruction: torch.Tensor, rotations: torch.Tens
         sh = shifts.to(dev, non_blocking=True) if shifts is not None else None
         B, P = rec.shape[0], rot.shape[1]
         N = int(output_shape[0]) if output_shape is not None else rec.shape[2]
+        index = None
+        shape = (B, P, N, N // 2 + 1)
+        if packed:
+            from . import _abi
+            index, count = _abi.cutoff_pack_index(N, fourier_radius_cutoff if fourier_radius_cutoff is not None else N / 2.0, dev)
+            shape = (B, P, count)
         if out is None:
-            out = torch.empty((B, P, N, N // 2 + 1), dtype=torch.complex64, pin_memory=True)
-        elif tuple(out.shape) != (B, P, N, N // 2 + 1) or out.dtype != torch.complex64 or out.is_cuda:
-            raise ValueError(f"out must be a host complex64 tensor of shape {(B, P, N, N // 2 + 1)}")
+            out = torch.empty(shape, dtype=torch.complex64, pin_memory=True)
+        elif tuple(out.shape) != shape or out.dtype != torch.complex64 or out.is_cuda:
+            raise ValueError(f"out must be a host complex64 tensor of shape {shape}")
+        kw = dict(output_shape=(N, N), interpolation=interpolation, oversampling=oversampling,
+                  fourier_radius_cutoff=fourier_radius_cutoff)
         for lo in range(0, P, max(1, chunk)):
             hi = min(P, lo + chunk)
-            part = ops.project_3d_to_2d_forw(rec, rot[:, lo:hi], sh[:, lo:hi] if sh is not None else None,
-                                             output_shape=(N, N), interpolation=interpolation,
-                                             oversampling=oversampling, fourier_radius_cutoff=fourier_radius_cutoff)
+            if packed:
+                part, _ = ops.project_3d_to_2d_forw_packed(rec, rot[:, lo:hi], sh[:, lo:hi] if sh is not None else None, **kw)
+            else:
+                with torch.no_grad():
+                    part = ops.project_3d_to_2d_forw(rec, rot[:, lo:hi], sh[:, lo:hi] if sh is not None else None, **kw)
             copy.wait_stream(main)
             with torch.cuda.stream(copy):
                 out[:, lo:hi].copy_(part, non_blocking=True)
             part.record_stream(copy)          # keep the chunk alive until its copy has run
         main.wait_stream(copy)
+    if packed:
+        return out, index.cpu()
     return out
 
 
