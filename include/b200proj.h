@@ -22,7 +22,9 @@
  *  - fourier_radius_cutoff is in projection frequency units; pixels with
  *    kr*kr + kc*kc > cutoff*cutoff are excluded.  Pass N/2.0 for the reference's default.
  *  - Calls are asynchronous on the given stream, allocate nothing and never synchronise.
- *    The device of the pointers must be current.
+ *    The device of the pointers must be current.  One exception: the FIRST call of
+ *    b200proj_backproject_2d_to_3d_forw_noalloc on a device looks up its built-in scratch, which
+ *    may load the library's device code and so block and reserve device memory (see there).
  *  - Return value: B200PROJ_OK or a negative error code; b200proj_last_error() gives the
  *    message of the calling thread's last failure.  Argument errors are detected before
  *    anything is launched.
@@ -199,8 +201,13 @@ size_t b200proj_backproject_workspace_bytes(int dim, int64_t B, int64_t R, int64
  *    B200PROJ_ERR_LIMIT before anything is launched.
  *  - The entry point calls no cudaMalloc, cudaFree or allocating library routine.
  *  - The first call on each device looks up the array's device address
- *    (cudaGetSymbolAddress, with that device current) and caches it; make that first call
- *    before any stream capture begins.
+ *    (cudaGetSymbolAddress, with that device current) and caches it.  With CUDA's lazy module
+ *    loading that lookup can be what loads the library's device code onto the GPU and reserves
+ *    the array, i.e. it may block and take device memory.  Make that first call at start-up
+ *    (a call with P = 0 does): before the phase in which allocation is forbidden and before any
+ *    stream capture begins.  Later calls only enqueue work.
+ *  - The cached address belongs to the device context that was current at the first call.  A
+ *    process that destroys it (cudaDeviceReset) must not call this entry point afterwards.
  *  - All calls on a device share the one array, which keeps the previous call's sums; each
  *    call clears the part it uses on its stream first.  Two calls that overlap on the GPU
  *    (different streams, or different host threads) race on the array: serialise them. */

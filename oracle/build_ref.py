@@ -59,7 +59,10 @@ SOURCES = [
 
 
 def default_reference() -> Path:
-    return Path(os.environ.get("TORCH_PROJECTORS_REFERENCE", "/root/reference"))
+    """The reference checkout: $TORCH_PROJECTORS_REFERENCE, else a folder named ``reference``
+    beside this repository (absent on machines that only use the prebuilt object)."""
+    env = os.environ.get("TORCH_PROJECTORS_REFERENCE")
+    return Path(env) if env else HERE.parent.parent / "reference"
 
 
 def build(reference: Path | None = None, force: bool = False, verbose: bool = True) -> Path | None:

@@ -42,6 +42,30 @@ def test_no_alloc_entry_matches_regular_entry_twice_in_a_row(cuda_device):
     assert rel_err(gd, 2 * wd) <= TOL_ATOMIC and rel_err(gw, 2 * ww) <= TOL_ATOMIC
 
 
+def test_no_alloc_entry_matches_the_cpu_oracle_and_takes_no_device_memory(cuda_device):
+    """Against the CPU oracle directly (not only against the regular entry point), and the property
+    the entry point exists for: once its first call on the device has been made, further calls
+    change neither the free device memory nor what torch's allocator holds."""
+    from oracle import port
+    from torch_projectors_b200 import _abi
+    case = Case("na4", 3, "linear", 1, 24, 32, 64, 2.0, None, 1, 1, shift_range=3.0, seed=64, special_poses=False)
+    cpu = make_inputs(case)
+    t = {k: (v.cuda() if v is not None else None) for k, v in cpu.items()}
+    d = torch.empty((1, 64, 64, 33), dtype=torch.complex64, device="cuda")
+    w = torch.empty((1, 64, 64, 33), dtype=torch.float32, device="cuda")
+    args = (t["proj"], t["weights"], t["rot"], t["shifts"], _abi.LINEAR, 2.0, 16.0, d, w, False)
+    _abi.backproject_2d_to_3d_forw_noalloc(*args)          # first call on the device: set-up happens here
+    torch.cuda.synchronize()
+    free0, held0, reserved0 = torch.cuda.mem_get_info()[0], torch.cuda.memory_allocated(), torch.cuda.memory_reserved()
+    for _ in range(5):
+        _abi.backproject_2d_to_3d_forw_noalloc(*args)
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info()[0] == free0
+    assert torch.cuda.memory_allocated() == held0 and torch.cuda.memory_reserved() == reserved0
+    d_want, w_want = port.backproject_2d_to_3d_forw(cpu["proj"], cpu["weights"], cpu["rot"], cpu["shifts"], "linear", 2.0)
+    assert rel_err(d, d_want) <= TOL_ATOMIC and rel_err(w, w_want) <= TOL_ATOMIC
+
+
 def test_no_alloc_entry_refuses_volumes_beyond_its_scratch(cuda_device):
     from torch_projectors_b200 import _abi
     case = Case("na3", 3, "linear", 1, 2, 34, 68, 2.0, None, 1, 1, seed=63)      # box 68 > box 64
