@@ -67,3 +67,41 @@ def test_reduction_rate_probe_issues_every_reduction(tp, pattern, per_tap):
     assert buf.double().sum().item() == 8 * 256 * 5 * per_tap                 # every lane added 1.0 to 3 (v4) or 2 (v2) floats
     with pytest.raises(RuntimeError, match="pattern must be"):
         tp._abi.reduction_rate_probe(9, buf, blocks=1, iterations=1)
+
+
+_ROWS_SCRIPT = r"""
+import sys, torch
+sys.path[:0] = [{root!r}, {root!r} + "/tests", {root!r} + "/torch-projectors_b200"]
+import torch_projectors_b200 as tp
+from cases import Case, make_inputs
+out = {{}}
+for k, (dim, B, P, N, R, os_, cutoff) in enumerate([(3, 1, 7, 34, 70, 2.0, None), (3, 2, 5, 16, 16, 1.0, 6.5), (2, 1, 9, 64, 128, 2.0, None),
+                                                     (2, 3, 4, 12, 12, 1.0, 4.5), (3, 1, 3, 48, 72, 1.5, None)]):
+    case = Case(f"rows{{k}}", dim, "linear", B, P, N, R, os_, cutoff, B, B, shift_range=3.0, seed=300 + k)
+    t = make_inputs(case)
+    f = tp.project_3d_to_2d_forw if dim == 3 else tp.project_2d_forw
+    out[k] = f(t["rec"].cuda(), t["rot"].cuda(), t["shifts"].cuda(), output_shape=(N, N), interpolation="linear",
+               oversampling=os_, fourier_radius_cutoff=cutoff).cpu()
+torch.save(out, {path!r})
+"""
+
+
+def test_two_pixels_per_lane_forward_kernel_is_bit_identical_to_the_one_pixel_kernel(tp, tmp_path):
+    """Linear forward projection runs a kernel in which every lane handles two pixels of one column
+    (terms that do not depend on the row are formed once).  Its arithmetic per pixel is unchanged, so
+    its outputs must equal, bit for bit, those of the one-pixel kernel (selected in a fresh process)."""
+    import os
+    import subprocess
+    import sys
+    from pathlib import Path
+    root = str(Path(__file__).resolve().parent.parent)
+    results = {}
+    for flag in ("1", "0"):
+        path = str(tmp_path / f"rows{flag}.pt")
+        env = dict(os.environ, B200PROJ_LINEAR_ROWS2=flag)
+        r = subprocess.run([sys.executable, "-c", _ROWS_SCRIPT.format(root=root, path=path)], env=env, capture_output=True, text=True, timeout=600)
+        assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+        results[flag] = torch.load(path)
+    assert results["1"].keys() == results["0"].keys()
+    for k in results["1"]:
+        assert torch.equal(results["1"][k], results["0"][k]), k

@@ -157,6 +157,13 @@ void launch_slab_interleaved(const Launch& L, cudaStream_t s, bool cubic, const 
         backproject_slab_kernel<false, true, true><<<grid, kBlockThreads, 0, s>>>((const float2*)proj, weights, rot, shifts, nullptr, nullptr, acc, L.g, plan.planes, first);
 }
 
+// Linear forward projection with two pixels per lane (project_forw_rows2_kernel); B200PROJ_LINEAR_ROWS2=0
+// selects the one-pixel kernel for comparisons (read once).
+bool linear_rows2() {
+    static const bool on = [] { const char* e = getenv("B200PROJ_LINEAR_ROWS2"); return e ? atoi(e) != 0 : true; }();
+    return on;
+}
+
 // ---- operator bodies, templated on the dimensionality and the real type (float | double) ------------------------------------
 template <int DIM, typename Real>
 int project_forw(const Real* rec, int64_t B, int64_t R, const Real* rot, int64_t B_rot,
@@ -170,10 +177,15 @@ int project_forw(const Real* rec, int64_t B, int64_t R, const Real* rot, int64_t
     cudaStream_t s = (cudaStream_t)stream;
     const C2<Real>* v = (const C2<Real>*)rec;
     C2<Real>* o = (C2<Real>*)out;
-    if (interpolation == B200PROJ_CUBIC)
+    if (interpolation == B200PROJ_CUBIC) {
         project_forw_kernel<DIM, true><<<L.grid, kBlockThreads, 0, s>>>(v, rot, shifts, o, L.g);
-    else
+    } else if (linear_rows2()) {
+        // linear: two pixels per lane, a block covers 16 columns x 32 rows
+        const dim3 grid((unsigned)(L.g.tiles_j * ((N + 2 * kTileI - 1) / (2 * kTileI))), L.grid.y, L.grid.z);
+        project_forw_rows2_kernel<DIM><<<grid, kBlockThreads, 0, s>>>(v, rot, shifts, o, L.g);
+    } else {
         project_forw_kernel<DIM, false><<<L.grid, kBlockThreads, 0, s>>>(v, rot, shifts, o, L.g);
+    }
     return check_launch("project_forw launch");
 }
 

@@ -113,6 +113,89 @@ project_forw_kernel(const C2<R>* __restrict__ rec, const R* __restrict__ rot,
     }
 }
 
+// Linear interpolation, two pixels per lane: the 4- and 8-tap gathers are bound by instruction
+// issue, and a good part of a pixel's instructions does not depend on its row (block decoding,
+// pose loads, the column's share of the rotated position and of the shift phase).  Here a block
+// covers 16 columns x 32 rows and every lane handles pixels (i, j) and (i + 16, j), forming those
+// terms once.  The arithmetic per pixel is that of project_forw_kernel, operation for operation,
+// so the outputs are bit-identical.
+template <int DIM, typename R>
+__global__ void __launch_bounds__(kBlockThreads)
+project_forw_rows2_kernel(const C2<R>* __restrict__ rec, const R* __restrict__ rot,
+                          const R* __restrict__ shifts, C2<R>* __restrict__ out, const SliceGeom g) {
+    // slice of this block (same decodings as block_work)
+    const int y = (int)blockIdx.y, z = (int)blockIdx.z;
+    int b, p;
+    if (g.decode == 0) { b = 0; p = y + (z << kGridYBits); }
+    else if (g.decode == 1) { b = z; p = y; }
+    else { const int bp = y + (z << kGridYBits); b = bp / g.P; p = bp - b * g.P; }
+    bool slice_ok = p < g.P && b * g.P + p < g.BP;
+    if (g.order != nullptr && slice_ok) {
+        p = __ldg(g.order + (b * g.P + p)) - b * g.P;
+        slice_ok = (unsigned)p < (unsigned)g.P;
+    }
+    if (!slice_ok) b = p = 0;
+    const int tile = (int)blockIdx.x;
+    const int ti = g.tiles_j == 1 ? tile : (int)__umulhi((unsigned)tile, g.tiles_j_magic);
+    const int tj = tile - ti * g.tiles_j;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int j = tj * kTileJ + (warp & 1) * 8 + (lane & 7);
+    const int i0 = ti * (2 * kTileI) + (warp >> 1) * 4 + (lane >> 3);
+    const bool col_ok = slice_ok && j < g.Nh;
+    const R* rm = pose_rot<DIM>(g, rot, b, p);
+    // column terms, formed once for both pixels
+    const R kc = (R)j;
+    const R kc2 = mul_rn(kc, kc);
+    const R sc = (sizeof(R) == 4 && g.os_is_float) ? mul_rn(kc, (R)g.os_f) : (R)((double)kc * g.os);
+    R m_c[3], m_r[3];
+    if (DIM == 3) {
+        m_c[0] = mul_rn(__ldg(rm + 0), sc); m_r[0] = __ldg(rm + 1);
+        m_c[1] = mul_rn(__ldg(rm + 3), sc); m_r[1] = __ldg(rm + 4);
+        m_c[2] = mul_rn(__ldg(rm + 6), sc); m_r[2] = __ldg(rm + 7);
+    } else {
+        m_c[0] = mul_rn(__ldg(rm + 0), sc); m_r[0] = __ldg(rm + 1);
+        m_c[1] = mul_rn(__ldg(rm + 2), sc); m_r[1] = __ldg(rm + 3);
+        m_c[2] = 0.f; m_r[2] = 0.f;
+    }
+    R s0 = 0.f, kc_s1 = 0.f;
+    if (g.has_shift) {
+        const R* s = pose_shift(g, shifts, b, p);
+        s0 = __ldg(s);
+        kc_s1 = mul_rn(kc, __ldg(s + 1));
+    }
+    const C2<R>* vol = rec + (size_t)b * g.vol_elems;
+    const size_t slice_base = (size_t)(b * g.P + p) * (size_t)g.slice_pixels;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int i = i0 + h * kTileI;
+        const bool in_image = col_ok && i < g.N;
+        PixelT<R> px;
+        px.c = px.r = px.d = 0.f;
+        px.kr = (R)((i <= g.N / 2) ? i : i - g.N);
+        px.kc = kc;
+        const R rad = add_rn(mul_rn(px.kr, px.kr), kc2);
+        const bool valid = in_image && !(rad > cutoff_sq_of(g, rad));
+        if (valid) {
+            px.sc = sc;
+            px.sr = (sizeof(R) == 4 && g.os_is_float) ? mul_rn(px.kr, (R)g.os_f) : (R)((double)px.kr * g.os);
+            px.c = add_rn(m_c[0], mul_rn(m_r[0], px.sr));
+            px.r = add_rn(m_c[1], mul_rn(m_r[1], px.sr));
+            if (DIM == 3) px.d = add_rn(m_c[2], mul_rn(m_r[2], px.sr));
+        }
+        C2<R> v, gc, gr, gd;
+        interpolate_any<DIM, false, false>(g, vol, px, valid, v, gc, gr, gd);      // all 32 lanes take part
+        if (!in_image) continue;
+        if (valid && g.has_shift) {
+            const R dot = add_rn(mul_rn(px.kr, s0), kc_s1);
+            const R ph = (R)((double)dot * g.phase_scale);
+            R sn, cs;
+            phase_sincos(ph, &sn, &cs);
+            v = cmul(v, make2<R>(cs, sn));
+        }
+        __stcs(out + (slice_base + (size_t)(i * g.Nh + j)), v);
+    }
+}
+
 // Pose-gradient terms shared by the two backward kernels.
 //   rotation:  dL/dR[a][m] += s_m * Re(u * conj(grad_a)),  a: (c, r, d) rows, s = (sc, sr, 0)
 //   shift:     dL/ds[n]    += q_n * (u.y * val.x - u.x * val.y),  q = -2*pi*k_n/N
