@@ -54,11 +54,15 @@ BACK_BYTES_PER_SLICE = 128 * 65 * 8 + 128 * 65 * 4 + 44 + 2 * (256 * 256 * 129 *
 # DRAM traffic per slice of the dominant kernels (dram__bytes_read.sum + dram__bytes_write.sum) from
 # ncu captures of a smaller launch of the same kernels, scaled by the slices a launch processes
 # (traffic grows in proportion to the slices: the volumes are touched the same way by every slice).
-PROJ_TRAFFIC_PER_SLICE = (48.7e6 + 105.3e6) / 2048        # profiles/project_forw_3d_cubic_box256_2048poses.md (current kernel)
-BACK_TRAFFIC_PER_SLICE = (497.0e6 + 1301.0e6) / 4096      # profiles/backproject_forw_3d_linear_box256_4096slices.md (lane-pair kernel)
+PROJ_TRAFFIC_PER_SLICE = (48.87e6 + 105.01e6) / 2048      # profiles/project_forw_3d_cubic_box256_2048poses.md (current kernel)
+# back-projection: two captures of the slab-ordered kernel (4,096 and 16,384 slices) give a part that grows with the
+# slices and a fixed part (the workspace); the fixed part also holds the zero-fill and the fold of the workspace
+# (profiles/backproject_forw_3d_linear_box256_4096slices.md)
+BACK_TRAFFIC_PER_SLICE = (2506.4e6 - 730.7e6) / (16384 - 4096)
+BACK_TRAFFIC_FIXED = (730.7e6 - 4096 * BACK_TRAFFIC_PER_SLICE) + 135.3e6 + (135.3e6 + 44.2e6)
 # The ceilings the kernels actually sit on (from the same summaries): share of the L1TEX data pipe
 # the cubic gather keeps busy.
-PROJ_L1TEX_DATA_PIPE_FRAC = 0.889
+PROJ_L1TEX_DATA_PIPE_FRAC = 0.909
 
 
 def reduction_ceiling(taps, ms, pattern):
@@ -387,8 +391,9 @@ SHARD_PIXELS_PER_SLICE = 62_814          # pixels inside the default cutoff of a
 BACK_PIXELS_PER_SLICE = 6_426            # the same for a 128x65 slice
 # Reduction ceilings measured by `bench.py --workload red_ceiling` on B200 (L2-resident buffer,
 # 10^9 reductions per second).
-RED_CEILING_GTAPS = {"one random 16-byte slot per lane": 221.0, "lane pairs on adjacent 16-byte slots": 254.0,
-                     "lane pairs sharing a 32-byte sector": 300.0, "four lanes on four adjacent 8-byte voxels": 489.0}
+RED_CEILING_GTAPS = {"one random 16-byte slot per lane": 222.5, "lane pairs on adjacent 16-byte slots": 255.6,
+                     "lane pairs sharing a 32-byte sector": 257.3, "four lanes on four adjacent 8-byte voxels": 497.0,
+                     "one random 8-byte voxel per lane": 222.5, "lane pairs on adjacent 8-byte voxels": 356.6}
 
 
 def _dist_setup():
@@ -1083,10 +1088,10 @@ def main():
                 "config": {"workload": BACK["name"], "collective": "NCCL reduce of data+weight partial volumes to rank 0" if world > 1 else "none"},
                 "roofline": {"bound": "hbm", "kernel": back_kernel_name, "achieved": bach,
                              "peak": peak, "peak_source": peak_kind, "unit": "GB/s", "frac": bach / peak,
-                             "traffic": (BACK_TRAFFIC_PER_SLICE * BACK["P"]) if BACK_TRAFFIC_PER_SLICE else None,
+                             "traffic": (BACK_TRAFFIC_FIXED + BACK_TRAFFIC_PER_SLICE * BACK["P"]) if workspace is not None else None,
                              "algorithmic_bytes_per_launch": BACK_BYTES_PER_SLICE * BACK["P"], "launch_ms": scat,
                              "secondary": reduction_ceiling(BACK["P"] * BACK_PIXELS_PER_SLICE * 8, scat,
-                                                            "lane pairs on adjacent 16-byte slots" if workspace is not None else "lane pairs sharing a 32-byte sector")}}
+                                                            "lane pairs on adjacent 16-byte slots" if workspace is not None else "lane pairs on adjacent 8-byte voxels")}}
         if rank == 0 and not args.skip_cpu:
             back["parity_check"] = check_backprojection_parity(tp, proj, weights, brot, bshifts, dev)
         launches += (args.steps + args.warmup) * (2 if workspace is not None else 1)     # scatter (+ fold)

@@ -124,21 +124,21 @@ int zero_async(void* p, size_t bytes, cudaStream_t s) {
 }
 
 // Slab plan of the slab-ordered 3D back-projection: volumes whose planes of one batch item
-// exceed a threshold are processed in slabs of at most `slab_mb` MB of planes.  Thresholds: 160 MB
-// for data (+ weight) volumes reduced into directly (8 or 12 bytes per voxel); 120 MB for
-// interleaved accumulators (16 bytes per voxel), where a volume just above L2 already loses its
-// sectors between hits (box 256: 135 MB, 4.4x the compulsory DRAM traffic in one pass) and two
-// slabs cost less than that -- except for the cubic scatter through a workspace, whose wider
-// footprints make the second visit of a pixel dearer (160 MB there, `relaxed`).
+// exceed 160 MB are processed in slabs of at most `slab_mb` MB of planes.  `eager` lowers the
+// threshold to 120 MB: an interleaved accumulator (16 bytes per voxel) just above L2 (box 256:
+// 135 MB) loses its sectors between hits when the samples are sparse (linear taps at oversampling
+// >= 1.5: 4.4x the compulsory DRAM traffic in one pass), and two slab passes then cost less than
+// that (11.2 -> 10.65 ms per 50,000 slices); with dense samples (oversampling 1) or cubic footprints
+// the second visit of the pixels costs more than the evictions (measured 6 % and 1.5 % slower).
 // Tunable for experiments through B200PROJ_SLAB_MB / B200PROJ_SLAB_MIN_MB /
-// B200PROJ_SLAB_MIN_MB_INTERLEAVED (read once).
+// B200PROJ_SLAB_MIN_MB_EAGER (read once).
 struct SlabPlan { int slabs, planes; };
-SlabPlan slab_plan(int64_t R, bool has_weights, bool interleaved = false, bool relaxed = false) {
+SlabPlan slab_plan(int64_t R, bool has_weights, bool interleaved = false, bool eager = false) {
     static const double slab_mb = [] { const char* e = getenv("B200PROJ_SLAB_MB"); return e ? atof(e) : 64.0; }();
     static const double min_mb = [] { const char* e = getenv("B200PROJ_SLAB_MIN_MB"); return e ? atof(e) : 160.0; }();
-    static const double min_mb_i = [] { const char* e = getenv("B200PROJ_SLAB_MIN_MB_INTERLEAVED"); return e ? atof(e) : 120.0; }();
+    static const double min_mb_e = [] { const char* e = getenv("B200PROJ_SLAB_MIN_MB_EAGER"); return e ? atof(e) : 120.0; }();
     const double plane_bytes = (double)R * (double)(R / 2 + 1) * (interleaved ? 16.0 : has_weights ? 12.0 : 8.0);
-    const double threshold = (interleaved && !relaxed) ? (min_mb_i < min_mb ? min_mb_i : min_mb) : min_mb;
+    const double threshold = (eager && min_mb_e < min_mb) ? min_mb_e : min_mb;
     if (slab_mb <= 0.0 || plane_bytes * (double)R <= threshold * 1e6) return {1, (int)R};
     // 16-byte voxels: fewer, larger reductions per plane leave room for 1.25x the bytes (measured)
     int planes = (int)(slab_mb * (interleaved ? 1.25 : 1.0) * 1e6 / plane_bytes);
@@ -252,7 +252,7 @@ int backproject_forw(const Real* proj, const Real* weights, int64_t B, int64_t R
         (reinterpret_cast<uintptr_t>(workspace) & 15u) == 0) {
         if (int rc = zero_async(workspace, ws_need, s)) return rc;
         float4* acc = (float4*)workspace;
-        const SlabPlan plan_i = (DIM == 3) ? slab_plan(R, true, true, /*relaxed=*/cubic) : SlabPlan{1, (int)R};
+        const SlabPlan plan_i = (DIM == 3) ? slab_plan(R, true, true, /*eager=*/!cubic && os >= 1.5) : SlabPlan{1, (int)R};
         if (DIM == 3 && plan_i.slabs > 1)      // the 16-byte volume itself is beyond L2: slab-ordered passes
             launch_slab_interleaved(L, s, cubic, (const float*)proj, (const float*)weights, (const float*)rot, (const float*)shifts, acc, plan_i, 0, plan_i.slabs);
         else if (cubic)
