@@ -210,96 +210,75 @@ def cpu_model():
     return platform.processor() or platform.machine()
 
 
-def run_cpu_sample(kind_wanted="reference"):
-    """Time the CPU implementation of the projection workload on a bounded sample: as many of
-    the 10,000 poses as take about 10 s, or several passes over all of them on a fast host.
-    Returns (slices/s, kind, cores, sample description)."""
+def _cpu_projector(kind_wanted="reference"):
+    """(callable(n_lo, n_hi) -> seconds, kind, cores) for the projection workload on the host."""
     import oracle
-    set_all_threads()
+    cores = set_all_threads()
     if "proj" not in _CPU_INPUTS:
         _CPU_INPUTS["proj"] = make_projection_inputs("cpu", seed=1)
     rec, rot, shifts = _CPU_INPUTS["proj"]
     if kind_wanted == "reference" and oracle.reference_available():
-        ops, kind, cores = oracle.reference_ops(), "reference", torch.get_num_threads()
-        f = ops.project_3d_to_2d_forw
+        kind = "reference"
+        f = oracle.reference_ops().project_3d_to_2d_forw
     else:
         from oracle import port
         kind, cores = "port", 1
         f = port.project_3d_to_2d_forw
 
-    def run(n):
+    def run(lo, hi):
         t0 = time.perf_counter()
-        f(rec, rot[:, :n].contiguous(), shifts[:, :n].contiguous(), [PROJ["N"], PROJ["N"]], PROJ["interp"], PROJ["os"], PROJ["cutoff"])
+        f(rec, rot[:, lo:hi].contiguous(), shifts[:, lo:hi].contiguous(), [PROJ["N"], PROJ["N"]], PROJ["interp"], PROJ["os"], PROJ["cutoff"])
         return time.perf_counter() - t0
+    return run, kind, cores
+
+
+def run_cpu_sample(kind_wanted="reference"):
+    """Time the CPU implementation of the projection workload on a bounded sample: as many of
+    the 10,000 poses as take about 10 s, or several passes over all of them on a fast host.
+    Returns (slices/s, kind, cores, sample description)."""
+    run, kind, cores = _cpu_projector(kind_wanted)
     probe = 64 if kind == "reference" else 8
-    dt = run(probe)                                   # also the warm-up
+    dt = run(0, probe)                                # also the warm-up
     n = int(min(PROJ["P"], max(probe, probe * 10.0 / max(dt, 1e-3))))   # ~10 s of CPU work
-    dt = run(n)
+    dt = run(0, n)
     passes = 1
     while n == PROJ["P"] and dt * passes < 8.0 and passes < 6:          # fast host: more passes
-        dt = (dt * passes + run(n)) / (passes + 1)
+        dt = (dt * passes + run(0, n)) / (passes + 1)
         passes += 1
     return (n / dt, kind, cores,
             f"{n} of the {PROJ['P']} poses of the projection workload, {passes} call(s) of {dt:.1f} s wall each")
 
 
-def _cpu_checker():
-    """(operators, kind): the reference's CPU operators where built, else the C restatement."""
-    import oracle
-    if oracle.reference_available():
-        set_all_threads()
-        return oracle.reference_ops(), "reference"
-    from oracle import port
-    return port, "port"
-
-
-def check_projection_parity(out, rec, rot, shifts, n=64):
-    """n poses of the last timed step's output (the first, the last and seeded random ones)
-    against the CPU reference on the same inputs; runs after the timed region."""
-    from cases import rel_err
-    ops, kind = _cpu_checker()
-    P = rot.shape[1]
-    g = torch.Generator().manual_seed(99)
-    pick = torch.unique(torch.cat([torch.tensor([0, P - 1]), torch.randint(0, P, (n - 2,), generator=g)]))
-    want = ops.project_3d_to_2d_forw(rec.cpu(), rot[:, pick.to(rot.device)].cpu().contiguous(), shifts[:, pick.to(rot.device)].cpu().contiguous(),
-                                     [PROJ["N"], PROJ["N"]], PROJ["interp"], PROJ["os"], PROJ["cutoff"])
-    return {"poses": int(pick.numel()), "against": kind, "max_rel_err": rel_err(out[:, pick.to(out.device)], want), "tol": 1e-5}
-
-
-def check_backprojection_parity(tp, proj, weights, rot, shifts, dev, n=64):
-    """The first n slices of the timed workload back-projected alone by the same entry point
-    (workspace included) against the CPU reference; runs after the timed region."""
-    from cases import rel_err
-    ops, kind = _cpu_checker()
-    sub = [x[:, :n].contiguous() for x in (proj, weights, rot, shifts)]
-    d, w = tp.backproject_2d_to_3d_forw(sub[0], sub[2], weights=sub[1], shifts=sub[3], interpolation=BACK["interp"], oversampling=BACK["os"])
-    d_want, w_want = ops.backproject_2d_to_3d_forw(sub[0].cpu(), sub[1].cpu(), sub[2].cpu(), sub[3].cpu(), BACK["interp"], BACK["os"], None)
-    return {"slices": n, "against": kind, "max_rel_err_data": rel_err(d, d_want), "max_rel_err_weights": rel_err(w, w_want), "tol": 1e-4}
+def headline_config(world):
+    return {"workload": PROJ["name"], "poses_per_gpu": PROJ["P"], "parallelism": f"poses sharded over {world} GPU(s), volume replicated",
+            "l2": "flushed before every step (256 MiB memset outside the timed events)"}
 
 
 def reference_arm(args):
-    """Time the reference's CPU operators; rank 0 only."""
+    """Time the reference's CPU operators on the host cores; rank 0 only.  W warm-up and exactly K
+    timed steps; each step is the same bounded sample of the workload's poses (about a second of
+    CPU work), so that the whole run ends within a few minutes whatever K is."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    per_step = []
-    kind = cores = sample = None
-    for k in range(args.warmup + args.steps):
-        if k < args.warmup and k > 0:
-            continue                                   # one warm-up pass is enough for a CPU loop
-        v, kind, cores, sample = run_cpu_sample("reference")
-        if k >= args.warmup:
-            per_step.append(v)
-        if len(per_step) >= 3:
-            break                                      # bounded: a few samples of ~12 s each
+    run, kind, cores = _cpu_projector("reference")
+    probe = 64 if kind == "reference" else 8
+    dt = run(0, probe)
+    budget_s = min(1.5, 150.0 / max(1, args.steps + args.warmup))       # per step; the whole run stays within minutes
+    n = int(min(PROJ["P"], max(probe, probe * budget_s / max(dt, 1e-4))))
+    for _ in range(args.warmup):
+        run(0, n)
+    per_step = [n / run(0, n) for _ in range(args.steps)]
     value = statistics.median(per_step)
+    sample = f"each step: the first {n} of the {PROJ['P']} poses of the projection workload ({n / value:.2f} s wall), {kind} CPU operators"
     line = {
         "impl": "reference", "metric": "Fourier slices/sec (project_3d_to_2d_forw, box 256, 2x oversampling)",
-        "value": value, "unit": "slices/s", "n_gpus": args.gpus, "steps": len(per_step), "warmup": min(args.warmup, 1),
+        "value": value, "unit": "slices/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": 1e3 * PROJ["P"] / value, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
-        "config": {"workload": PROJ["name"], "device": "host CPU", "note": "each step is a bounded sample of the poses; ms_per_step is extrapolated to all 10000"},
-        "cpu_baseline": {"value": value, "unit": "slices/s", "cores": cores, "cpu_model": cpu_model(), "kind": kind, "sample": sample},
+        "config": headline_config(args.gpus),
+        "cpu_baseline": {"value": value, "unit": "slices/s", "cores": cores, "cpu_model": cpu_model(), "kind": kind, "sample": sample,
+                         "note": "runs on the host CPU; ms_per_step is extrapolated to all 10000 poses"},
         "e2e": {"value": value, "unit": "slices/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -1118,8 +1097,7 @@ def main():
             "value": value, "unit": "slices/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "f32", "data": "synthetic",
-            "config": {"workload": PROJ["name"], "poses_per_gpu": PROJ["P"], "parallelism": f"poses sharded over {world} GPU(s), volume replicated",
-                       "l2": "flushed before every step (256 MiB memset outside the timed events)"},
+            "config": headline_config(world),
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "e2e_packed": e2e_packed, "gpu_launches": launches, "clocks": clocks,
             "parity_check": parity, "backproject": back, "sharded_backproject": sharded,
         }

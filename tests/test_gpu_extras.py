@@ -105,3 +105,24 @@ def test_two_pixels_per_lane_forward_kernel_is_bit_identical_to_the_one_pixel_ke
     assert results["1"].keys() == results["0"].keys()
     for k in results["1"]:
         assert torch.equal(results["1"][k], results["0"][k]), k
+
+
+def test_raw_operators_pass_opcheck_schema_and_fake_tensor(tp):
+    """torch.library.opcheck on the compiled operators: the schemas tell the truth about aliasing and
+    mutation, and the Meta implementations agree with the CUDA ones on shapes, dtypes and strides (what
+    tracing relies on).  The operators have no autograd registration (autograd lives in the Python
+    functions, as in the reference), so the autograd-related checks are not asked for."""
+    ops = torch.ops.torch_projectors_b200
+    case = Case("opcheck", 3, "cubic", 2, 5, 8, 16, 2.0, None, 1, 2, seed=91)
+    t = {k: (v.cuda() if v is not None else None) for k, v in make_inputs(case).items()}
+    rot_g = t["rot"].clone().requires_grad_(True)
+    which = ("test_schema", "test_faketensor")
+    torch.library.opcheck(ops.project_3d_to_2d_forw.default, (t["rec"], t["rot"], t["shifts"], [8, 8], "cubic", 2.0, None), test_utils=which)
+    torch.library.opcheck(ops.project_3d_to_2d_back.default, (t["proj"], t["rec"], rot_g, t["shifts"], "cubic", 2.0, None), test_utils=which)
+    torch.library.opcheck(ops.backproject_2d_to_3d_forw.default, (t["proj"], t["weights"], t["rot"], t["shifts"], "linear", 2.0, None), test_utils=which)
+    torch.library.opcheck(ops.backproject_2d_to_3d_back.default,
+                          (t["grad_data"], t["grad_weight"], t["proj"], t["weights"], rot_g, t["shifts"], "linear", 2.0, None), test_utils=which)
+    case2 = Case("opcheck2", 2, "linear", 1, 4, 8, 16, 2.0, None, 1, 0, weights=False, seed=92)
+    t2 = {k: (v.cuda() if v is not None else None) for k, v in make_inputs(case2).items()}
+    torch.library.opcheck(ops.project_2d_forw.default, (t2["rec"], t2["rot"], None, [8, 8], "linear", 2.0, 3.5), test_utils=which)
+    torch.library.opcheck(ops.backproject_2d_forw.default, (t2["proj"], None, t2["rot"], None, "linear", 2.0, None), test_utils=which)

@@ -17,6 +17,9 @@ namespace b200proj {
 #ifndef PB_MIN_BLOCKS
 #define PB_MIN_BLOCKS 4
 #endif
+#ifndef B200PROJ_SLAB_TWO_IN_FLIGHT
+#define B200PROJ_SLAB_TWO_IN_FLIGHT 1
+#endif
 
 struct BlockWork {
     int b, p, i, j;
@@ -501,8 +504,9 @@ backproject_slab_kernel(const float2* __restrict__ proj, const float* __restrict
             if (lane >= o) incl += up;
         }
         const int total = __shfl_sync(kFull, incl, 31);
-        for (int k0 = 0; k0 < total; k0 += 32) {                                  // warp-uniform trip count
-            const int k = k0 + lane;
+        // candidate k of this batch of rows -> its pixel (i, j), whether this pass has work for it,
+        // and its sample position
+        auto candidate = [&](int k, int& i, int& j, Pixel& px) -> bool {
             // smallest row whose inclusive count exceeds k
             int row = 0;
 #pragma unroll
@@ -515,15 +519,14 @@ backproject_slab_kernel(const float2* __restrict__ proj, const float* __restrict
             const int r_len0 = __shfl_sync(kFull, len0, row), r_len1 = __shfl_sync(kFull, len1, row);
             const int r_a0 = __shfl_sync(kFull, run_a[0], row), r_a1 = __shfl_sync(kFull, run_a[1], row);
             const int local = k - (r_incl - r_len0 - r_len1);
-            const int j = local < r_len0 ? r_a0 + local : r_a1 + (local - r_len0);
-            const int i = (n0 + row) * kWarps + warp;
+            j = local < r_len0 ? r_a0 + local : r_a1 + (local - r_len0);
+            i = (n0 + row) * kWarps + warp;
             const float kr = (float)((i <= g.N / 2) ? i : i - g.N);
             // one-FMA prefilter with the linear estimates, then the exact test
             const float de = fmaf(ad, (float)j, bd * kr), ce = fmaf(ac, (float)j, bc * kr);
             bool active = k < total && !(j == 0 && i >= g.N / 2) &&
                           ((de >= band_lo && de <= band_hi && ce >= c_direct_min) ||
                            (-de >= band_lo && -de <= band_hi && ce <= c_mirror_max));
-            Pixel px;
             px.c = px.r = px.d = 0.f;
             if (active) active = pixel_setup<3>(g, rm, i, j, px);
             if (active) {
@@ -533,19 +536,57 @@ backproject_slab_kernel(const float2* __restrict__ proj, const float* __restrict
                 const bool mirror = pc <= 0 && -(pd + T - 1) < z_hi && -pd >= z_lo;
                 active = direct || mirror;
             }
-            if (!__any_sync(kFull, active)) continue;
-            float2 v = make_float2(0.f, 0.f);
-            float wv = 0.f;
+            return active;
+        };
+        auto load_pixel = [&](bool active, int i, int j, float2& v, float& wv) {
+            v = make_float2(0.f, 0.f);
+            wv = 0.f;
             if (active) {
                 const size_t pix = ((size_t)bp * (size_t)g.N + (size_t)i) * (size_t)g.Nh + (size_t)j;
                 v = __ldcs(proj + pix);
-                if (g.has_shift) {
-                    const float* s = pose_shift(g, shifts, b, p);
-                    v = cmul_conj(v, phase_ramp(g, px, __ldg(s), __ldg(s + 1)));
-                }
                 if (WEIGHTS) wv = __ldcs(weights + pix);
             }
+        };
+        auto scatter_pixel = [&](bool active, const Pixel& px, float2 v, float wv) {
+            if (active && g.has_shift) {
+                const float* s = pose_shift(g, shifts, b, p);
+                v = cmul_conj(v, phase_ramp(g, px, __ldg(s), __ldg(s + 1)));
+            }
             scatter_coop<3, CUBIC, WEIGHTS, true, INTERLEAVED, true>(g, data_b, wrec_b, accum_b, px, active, v, wv, z_lo, z_hi);
+        };
+        if constexpr (B200PROJ_SLAB_TWO_IN_FLIGHT && !CUBIC) {
+        // Two batches of 32 candidates per trip: the streamed pixels of the second batch are in
+        // flight while the first is scattered (the warps otherwise wait on these loads).  Linear
+        // only: with cubic footprints the extra registers cost a resident block.
+        for (int k0 = 0; k0 < total; k0 += 64) {                                  // warp-uniform trip count
+            int i0, j0, i1, j1;
+            Pixel px0, px1;
+            const bool a0 = candidate(k0 + lane, i0, j0, px0);
+            const bool any0 = __any_sync(kFull, a0);
+            bool a1 = false;
+            bool any1 = false;
+            if (k0 + 32 < total) {
+                a1 = candidate(k0 + 32 + lane, i1, j1, px1);
+                any1 = __any_sync(kFull, a1);
+            }
+            float2 v0, v1;
+            float w0, w1;
+            if (any0) load_pixel(a0, i0, j0, v0, w0);
+            if (any1) load_pixel(a1, i1, j1, v1, w1);
+            if (any0) scatter_pixel(a0, px0, v0, w0);
+            if (any1) scatter_pixel(a1, px1, v1, w1);
+        }
+        } else {
+        for (int k0 = 0; k0 < total; k0 += 32) {                                  // warp-uniform trip count
+            int i, j;
+            Pixel px;
+            const bool active = candidate(k0 + lane, i, j, px);
+            if (!__any_sync(kFull, active)) continue;
+            float2 v;
+            float wv;
+            load_pixel(active, i, j, v, wv);
+            scatter_pixel(active, px, v, wv);
+        }
         }
     }
 }
