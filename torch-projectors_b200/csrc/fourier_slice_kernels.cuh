@@ -17,9 +17,6 @@ namespace b200proj {
 #ifndef PB_MIN_BLOCKS
 #define PB_MIN_BLOCKS 4
 #endif
-#ifndef B200PROJ_SLAB_TWO_IN_FLIGHT
-#define B200PROJ_SLAB_TWO_IN_FLIGHT 1
-#endif
 
 struct BlockWork {
     int b, p, i, j;
@@ -479,8 +476,10 @@ backproject_slab_kernel(const float2* __restrict__ proj, const float* __restrict
                         clip_run(ac, c0, -3.0e38f, c_mirror_max, ja, jb);
                     }
                     if (jb >= ja) {
-                        run_a[t] = max(0, (int)floorf(ja) - 1);
-                        run_b[t] = min((int)jmax, (int)ceilf(jb) + 1);
+                        // the bands carry kEps of slack in plane units, i.e. at least kEps / 2 columns: far more than
+                        // the rounding of these estimates (< 1e-2 columns), so floor / ceil need no extra column
+                        run_a[t] = max(0, (int)floorf(ja));
+                        run_b[t] = min((int)jmax, (int)ceilf(jb));
                     }
                 }
                 // overlapping or adjacent runs become one (pixels must be visited once per slab)
@@ -554,29 +553,6 @@ backproject_slab_kernel(const float2* __restrict__ proj, const float* __restrict
             }
             scatter_coop<3, CUBIC, WEIGHTS, true, INTERLEAVED, true>(g, data_b, wrec_b, accum_b, px, active, v, wv, z_lo, z_hi);
         };
-        if constexpr (B200PROJ_SLAB_TWO_IN_FLIGHT && !CUBIC) {
-        // Two batches of 32 candidates per trip: the streamed pixels of the second batch are in
-        // flight while the first is scattered (the warps otherwise wait on these loads).  Linear
-        // only: with cubic footprints the extra registers cost a resident block.
-        for (int k0 = 0; k0 < total; k0 += 64) {                                  // warp-uniform trip count
-            int i0, j0, i1, j1;
-            Pixel px0, px1;
-            const bool a0 = candidate(k0 + lane, i0, j0, px0);
-            const bool any0 = __any_sync(kFull, a0);
-            bool a1 = false;
-            bool any1 = false;
-            if (k0 + 32 < total) {
-                a1 = candidate(k0 + 32 + lane, i1, j1, px1);
-                any1 = __any_sync(kFull, a1);
-            }
-            float2 v0, v1;
-            float w0, w1;
-            if (any0) load_pixel(a0, i0, j0, v0, w0);
-            if (any1) load_pixel(a1, i1, j1, v1, w1);
-            if (any0) scatter_pixel(a0, px0, v0, w0);
-            if (any1) scatter_pixel(a1, px1, v1, w1);
-        }
-        } else {
         for (int k0 = 0; k0 < total; k0 += 32) {                                  // warp-uniform trip count
             int i, j;
             Pixel px;
@@ -586,7 +562,6 @@ backproject_slab_kernel(const float2* __restrict__ proj, const float* __restrict
             float wv;
             load_pixel(active, i, j, v, wv);
             scatter_pixel(active, px, v, wv);
-        }
         }
     }
 }
