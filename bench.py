@@ -249,6 +249,40 @@ def run_cpu_sample(kind_wanted="reference"):
             f"{n} of the {PROJ['P']} poses of the projection workload, {passes} call(s) of {dt:.1f} s wall each")
 
 
+def _cpu_checker():
+    """(operators, kind): the reference's CPU operators where built, else the C restatement."""
+    import oracle
+    if oracle.reference_available():
+        set_all_threads()
+        return oracle.reference_ops(), "reference"
+    from oracle import port
+    return port, "port"
+
+
+def check_projection_parity(out, rec, rot, shifts, n=64):
+    """n poses of the last timed step's output (the first, the last and seeded random ones)
+    against the CPU reference on the same inputs; runs after the timed region."""
+    from cases import rel_err
+    ops, kind = _cpu_checker()
+    P = rot.shape[1]
+    g = torch.Generator().manual_seed(99)
+    pick = torch.unique(torch.cat([torch.tensor([0, P - 1]), torch.randint(0, P, (n - 2,), generator=g)]))
+    want = ops.project_3d_to_2d_forw(rec.cpu(), rot[:, pick.to(rot.device)].cpu().contiguous(), shifts[:, pick.to(rot.device)].cpu().contiguous(),
+                                     [PROJ["N"], PROJ["N"]], PROJ["interp"], PROJ["os"], PROJ["cutoff"])
+    return {"poses": int(pick.numel()), "against": kind, "max_rel_err": rel_err(out[:, pick.to(out.device)], want), "tol": 1e-5}
+
+
+def check_backprojection_parity(tp, proj, weights, rot, shifts, dev, n=64):
+    """The first n slices of the timed workload back-projected alone by the same entry point
+    (workspace included) against the CPU reference; runs after the timed region."""
+    from cases import rel_err
+    ops, kind = _cpu_checker()
+    sub = [x[:, :n].contiguous() for x in (proj, weights, rot, shifts)]
+    d, w = tp.backproject_2d_to_3d_forw(sub[0], sub[2], weights=sub[1], shifts=sub[3], interpolation=BACK["interp"], oversampling=BACK["os"])
+    d_want, w_want = ops.backproject_2d_to_3d_forw(sub[0].cpu(), sub[1].cpu(), sub[2].cpu(), sub[3].cpu(), BACK["interp"], BACK["os"], None)
+    return {"slices": n, "against": kind, "max_rel_err_data": rel_err(d, d_want), "max_rel_err_weights": rel_err(w, w_want), "tol": 1e-4}
+
+
 def headline_config(world):
     return {"workload": PROJ["name"], "poses_per_gpu": PROJ["P"], "parallelism": f"poses sharded over {world} GPU(s), volume replicated",
             "l2": "flushed before every step (256 MiB memset outside the timed events)"}

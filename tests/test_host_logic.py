@@ -301,3 +301,28 @@ def test_normalize_by_weights():
     w = torch.tensor([2.0, 0.0, 1e-6])
     out = prep.normalize_by_weights(d, w, eps=0.5)
     assert torch.allclose(out, torch.tensor([1.0 + 1j, 2.0 + 0j, 10.0 + 0j]))
+
+
+def test_bench_script_refers_to_no_undefined_name():
+    """bench.py cannot run here (no GPU), so at least make sure that every name it loads is defined
+    somewhere in it (a function moved or deleted by an edit would otherwise only show on the GPU box)."""
+    import ast
+    import builtins
+    tree = ast.parse((ROOT / "bench.py").read_text())
+    defined = set(dir(builtins)) | {"__file__"}
+    for n in ast.walk(tree):
+        if isinstance(n, (ast.FunctionDef, ast.ClassDef)):
+            defined.add(n.name)
+        if isinstance(n, (ast.FunctionDef, ast.Lambda)):
+            a = n.args
+            defined |= {x.arg for x in a.args + a.kwonlyargs + a.posonlyargs} | ({a.vararg.arg} if a.vararg else set()) | ({a.kwarg.arg} if a.kwarg else set())
+        if isinstance(n, ast.Import):
+            defined |= {x.asname or x.name.split(".")[0] for x in n.names}
+        if isinstance(n, ast.ImportFrom):
+            defined |= {x.asname or x.name for x in n.names}
+        if isinstance(n, ast.ExceptHandler) and n.name:
+            defined.add(n.name)
+        if isinstance(n, ast.Name) and isinstance(n.ctx, (ast.Store, ast.Del)):
+            defined.add(n.id)
+    loaded = {n.id for n in ast.walk(tree) if isinstance(n, ast.Name) and isinstance(n.ctx, ast.Load)}
+    assert loaded - defined == set(), sorted(loaded - defined)

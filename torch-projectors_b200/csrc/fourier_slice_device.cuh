@@ -509,14 +509,18 @@ __device__ __forceinline__ void interpolate_coop(const SliceGeom& g, const C2<R>
 // dots ITS column's partial sums with the pixel's u (sent along with the position) and the group
 // adds four scalars instead of eight complex components; only four registers per pixel outlive
 // the gather.  MUST be called by all 32 lanes of the warp.
-template <int DIM, bool CUBIC, bool NEED_ROT, typename R>
+// WITH_VALUE (the backward of back-projection, which also writes the interpolated value out): the
+// complex value v comes back in `value` as well (two more scalars through the group's reduction),
+// and dots[3] is then formed from it by the owner instead of being reduced.
+template <int DIM, bool CUBIC, bool NEED_ROT, bool WITH_VALUE = false, typename R>
 __device__ __forceinline__ void gather_pose_dots(const SliceGeom& g, const C2<R>* __restrict__ vol,
                                                  const PixelT<R>& px, bool valid_own, C2<R> u_own,
-                                                 R (&dots)[4]) {
+                                                 R (&dots)[4], C2<R>* value = nullptr) {
     constexpr int T = CUBIC ? 4 : 2;
     constexpr unsigned kFull = 0xffffffffu;
 #pragma unroll
     for (int v = 0; v < 4; ++v) dots[v] = 0.f;
+    if (WITH_VALUE) *value = make2<R>(0.f, 0.f);
     if (!(CUBIC || (DIM == 3 && g.sparse_samples))) {            // warp-uniform: one lane per pixel
         if (valid_own) {
             C2<R> val, gc, gr, gd;
@@ -527,6 +531,7 @@ __device__ __forceinline__ void gather_pose_dots(const SliceGeom& g, const C2<R>
                 if (DIM == 3) dots[2] = u_own.x * gd.x + u_own.y * gd.y;
             }
             dots[3] = u_own.y * val.x - u_own.x * val.y;
+            if (WITH_VALUE) *value = val;
         }
         return;
     }
@@ -542,6 +547,7 @@ __device__ __forceinline__ void gather_pose_dots(const SliceGeom& g, const C2<R>
         const R uy = __shfl_sync(kFull, u_own.y, src);
         const bool valid = __shfl_sync(kFull, (int)valid_own, src) != 0;
         R part[4] = {0.f, 0.f, 0.f, 0.f};
+        C2<R> cv = make2<R>(0.f, 0.f);
         if (valid) {
             R wc, dwc;
             bool m;
@@ -553,17 +559,26 @@ __device__ __forceinline__ void gather_pose_dots(const SliceGeom& g, const C2<R>
                 part[1] = wc * (ux * Bq.x + uys * Bq.y);
                 if (DIM == 3) part[2] = wc * (ux * Dq.x + uys * Dq.y);
             }
-            part[3] = wc * (uy * A.x - (m ? -ux : ux) * A.y);
+            if (WITH_VALUE) cv = make2<R>(wc * A.x, (m ? -wc : wc) * A.y);
+            else part[3] = wc * (uy * A.x - (m ? -ux : ux) * A.y);
         }
 #pragma unroll
         for (int o = 1; o < T; o <<= 1) {
 #pragma unroll
             for (int v = 0; v < 4; ++v)
-                if ((v < 3 && NEED_ROT && (v < 2 || DIM == 3)) || v == 3) part[v] += __shfl_xor_sync(kFull, part[v], o);
+                if ((v < 3 && NEED_ROT && (v < 2 || DIM == 3)) || (v == 3 && !WITH_VALUE)) part[v] += __shfl_xor_sync(kFull, part[v], o);
+            if (WITH_VALUE) {
+                cv.x += __shfl_xor_sync(kFull, cv.x, o);
+                cv.y += __shfl_xor_sync(kFull, cv.y, o);
+            }
         }
         if (q == s) {
 #pragma unroll
             for (int v = 0; v < 4; ++v) dots[v] = part[v];
+            if (WITH_VALUE) {
+                *value = cv;
+                dots[3] = u_own.y * cv.x - u_own.x * cv.y;
+            }
         }
     }
 }

@@ -408,13 +408,14 @@ fold_normalized_kernel(const float4* __restrict__ accum, float2* __restrict__ ou
 // gridDim.y select the slabs of a launch).
 // One block = one slice x one slab; its 8 warps take the rows round-robin and each prepares 32
 // of its rows at a time, one per lane.
-// Restrict the column run [ja, jb] to the columns where a*j + b lies in [lo, hi].
-__device__ __forceinline__ void clip_run(float a, float b, float lo, float hi, float& ja, float& jb) {
+// Restrict the column run [ja, jb] to the columns where a*j + b lies in [lo, hi]; inv_a = 1 / a
+// (a is the same for every row of a slice, so the caller divides once per block).
+__device__ __forceinline__ void clip_run(float a, float inv_a, float b, float lo, float hi, float& ja, float& jb) {
     if (fabsf(a) < 1e-6f) {
         if (b < lo || b > hi) jb = ja - 1.f;        // empty
         return;
     }
-    const float x0 = (lo - b) / a, x1 = (hi - b) / a;
+    const float x0 = (lo - b) * inv_a, x1 = (hi - b) * inv_a;
     ja = fmaxf(ja, fminf(x0, x1));
     jb = fminf(jb, fmaxf(x0, x1));
 }
@@ -439,6 +440,7 @@ backproject_slab_kernel(const float2* __restrict__ proj, const float* __restrict
     const float osf = (float)g.os;
     const float ac = osf * __ldg(rm + 0), bc = osf * __ldg(rm + 1);
     const float ad = osf * __ldg(rm + 6), bd = osf * __ldg(rm + 7);
+    const float inv_ac = 1.f / (fabsf(ac) < 1e-6f ? 1.f : ac), inv_ad = 1.f / (fabsf(ad) < 1e-6f ? 1.f : ad);
     // taps of a pixel use planes floor(d)-T/2+1 .. floor(d)+T/2 (mirrored taps their negatives)
     // and columns floor(c)-T/2+1 .. floor(c)+T/2; direct taps need a column >= 0, mirrored taps a
     // column < 0, and the duplicate of a column-0 tap (which lands in the mirrored plane) a column == 0
@@ -469,11 +471,11 @@ backproject_slab_kernel(const float2* __restrict__ proj, const float* __restrict
                 for (int t = 0; t < 2; ++t) {
                     float ja = 0.f, jb = jmax;
                     if (t == 0) {
-                        clip_run(ad, d0, band_lo, band_hi, ja, jb);
-                        clip_run(ac, c0, c_direct_min, 3.0e38f, ja, jb);
+                        clip_run(ad, inv_ad, d0, band_lo, band_hi, ja, jb);
+                        clip_run(ac, inv_ac, c0, c_direct_min, 3.0e38f, ja, jb);
                     } else {
-                        clip_run(ad, d0, -band_hi, -band_lo, ja, jb);
-                        clip_run(ac, c0, -3.0e38f, c_mirror_max, ja, jb);
+                        clip_run(ad, inv_ad, d0, -band_hi, -band_lo, ja, jb);
+                        clip_run(ac, inv_ac, c0, -3.0e38f, c_mirror_max, ja, jb);
                     }
                     if (jb >= ja) {
                         // the bands carry kEps of slack in plane units, i.e. at least kEps / 2 columns: far more than
@@ -586,25 +588,38 @@ backproject_back_kernel(const C2<R>* __restrict__ grad_data_rec,
                         pixel_setup<DIM>(g, pose_rot<DIM>(g, rot, w.b, w.p), w.i, w.j, px) &&
                         !(w.j == 0 && w.i >= g.N / 2);
     const bool write_w = grad_weight_rec != nullptr && grad_weights != nullptr;
-    C2<R> raw, gc, gr, gd;
-    // cooperative gather: every lane of the warp takes part
-    interpolate_any<DIM, CUBIC, NEED_ROT>(g, grad_data_rec + (size_t)w.b * g.vol_elems, px, active, raw, gc, gr, gd);
+    // the slice's own value with the conjugate shift ramp (what was back-projected): the pose
+    // gradients are its dot products with the derivatives of the gathered gradient volume
+    C2<R> ph = make2<R>(1.f, 0.f), pv = make2<R>(0.f, 0.f);
     if (active) {
-        C2<R> ph = make2<R>(1.f, 0.f);
-        C2<R> v = raw;
         if (g.has_shift) {
             const R* s = pose_shift(g, shifts, w.b, w.p);
             ph = phase_ramp(g, px, __ldg(s), __ldg(s + 1));
-            v = cmul(raw, ph);
         }
-        __stcs(grad_proj + w.pix, v);
+        if (NEED_ROT || NEED_SHIFT) {
+            pv = __ldcs(proj + w.pix);
+            if (g.has_shift) pv = cmul_conj(pv, ph);
+        }
+    }
+    C2<R> raw;
+    R dots[4];
+    // cooperative gather: every lane of the warp takes part
+    gather_pose_dots<DIM, CUBIC, NEED_ROT, true>(g, grad_data_rec + (size_t)w.b * g.vol_elems, px, active, pv, dots, &raw);
+    if (active) {
+        __stcs(grad_proj + w.pix, g.has_shift ? cmul(raw, ph) : raw);
         if (write_w)
             __stcs(grad_weights + w.pix,
                    gather_weight_grad<DIM>(g, grad_weight_rec + (size_t)w.b * g.vol_elems, px));
-        if (NEED_ROT || NEED_SHIFT) {
-            C2<R> pv = __ldcs(proj + w.pix);
-            if (g.has_shift) pv = cmul_conj(pv, ph);
-            pose_grad_terms<DIM, NEED_ROT, NEED_SHIFT>(g, px, pv, pv, raw, gc, gr, gd, acc);
+        if (NEED_ROT) {
+#pragma unroll
+            for (int a = 0; a < DIM; ++a) {
+                acc[2 * a + 0] = dots[a] * px.sc;
+                acc[2 * a + 1] = dots[a] * px.sr;
+            }
+        }
+        if (NEED_SHIFT) {
+            acc[2 * DIM + 0] = (R)(g.shift_scale * (double)px.kr) * dots[3];
+            acc[2 * DIM + 1] = (R)(g.shift_scale * (double)px.kc) * dots[3];
         }
     } else if (w.in_image) {
         __stcs(grad_proj + w.pix, make2<R>(0.f, 0.f));
