@@ -39,7 +39,10 @@ def main():
     local_only = sharding.project_3d_to_2d_sharded(rec, rot, sh, output_shape=(N, N), **kw)
     assert torch.equal(local_only, full[:, lo:hi])
 
-    # back-projection: local slices in chunks through the accumulator, fold + reduce in ranges
+    # back-projection: local slices in chunks through the accumulator; the last chunk is the final
+    # stage (scattered slab group by slab group, finished groups folded and reduced meanwhile)
+    slabs, _ = tp._abi.accumulator_slab_plan(R)
+    assert slabs > 1, "the launcher forces small slabs so that the per-slab path is exercised"
     want_d, want_w = tp.backproject_2d_to_3d_forw(proj, rot, weights=wts, shifts=sh, **kw)
     for dst in (0, None):
         vols = sharding.backproject_2d_to_3d_sharded(proj[:, lo:hi], rot[:, lo:hi], wts[:, lo:hi], sh[:, lo:hi],

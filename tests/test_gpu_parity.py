@@ -406,6 +406,31 @@ for interp, weights in (("linear", True), ("cubic", True), ("linear", False)):
                                                             c(t["shifts"])[:, lo:hi], interpolation=interp, oversampling=2.0)
         da, wa = tp.fold_backprojection_accumulator(acc)
         assert rel_err(da, dw) <= TOL_ATOMIC and rel_err(wa, ww) <= TOL_ATOMIC, (interp, rel_err(da, dw), rel_err(wa, ww))
+        # slab by slab: every slab's pass alone, in reverse order, adds up to the same sums, and a pass
+        # writes nothing outside the voxels it owns
+        slabs, planes = tp._abi.accumulator_slab_plan(40)
+        assert slabs > 4
+        acc2 = tp.new_backprojection_accumulator(2, 40, "cuda")
+        call = tp.ops.prepare_accumulate_interleaved(acc2, c(t["proj"]), c(t["rot"]), c(t["weights"]), c(t["shifts"]), interpolation=interp, oversampling=2.0)
+        per_item = 40 * 40 * 21
+        for k in reversed(range(slabs)):
+            before = acc2.clone()
+            tp._abi.backproject_accumulate_slabs(*call, k, 1)
+            changed = (acc2 != before).any(dim=-1).flatten()
+            owned = torch.zeros(2 * per_item, dtype=torch.bool, device="cuda")
+            for b in range(2):
+                for first, stop in tp._abi.accumulator_slab_voxels(40, k, 1):
+                    owned[b * per_item + first: b * per_item + stop] = True
+            assert not (changed & ~owned).any(), (interp, k)
+        assert rel_err(acc2, acc) <= TOL_ATOMIC, (interp, rel_err(acc2, acc))
+        # and PartialVolumes with the last chunk as the final stage (fold of finished slab groups on a second stream)
+        vols = tp.sharding.PartialVolumes(2, 40, "cuda")
+        vols.slab_groups = 5
+        vols.add_(c(t["proj"])[:, :4], c(t["rot"])[:, :4], c(t["weights"])[:, :4], c(t["shifts"])[:, :4], interpolation=interp, oversampling=2.0)
+        vols.add_(c(t["proj"])[:, 4:], c(t["rot"])[:, 4:], c(t["weights"])[:, 4:], c(t["shifts"])[:, 4:], interpolation=interp, oversampling=2.0, final=True)
+        vols.flush()
+        torch.cuda.synchronize()
+        assert rel_err(vols.data, dw) <= TOL_ATOMIC and rel_err(vols.weights, ww) <= TOL_ATOMIC, (interp, rel_err(vols.data, dw))
 print("SLAB-OK")
 """
 
