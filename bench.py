@@ -503,7 +503,7 @@ def autograd_step_workload(args):
         dist.destroy_process_group()
 
 
-def run_sharded_backprojection(dist, rank, world, local_rank, dev, total, overlap_tail=True, check_slices=0):
+def run_sharded_backprojection(dist, rank, world, local_rank, dev, total, overlap_tail=True, check_slices=0, slab_groups=0):
     """Sharded back-projection workload: `total` box-400 slices split over the ranks (strong scaling),
     generated on the device per rank seed in chunks of 8192 outside the timed region; CUDA events
     around the accumulate calls, then the final stage: the rank's last chunk(s), scattered slab by
@@ -517,6 +517,8 @@ def run_sharded_backprojection(dist, rank, world, local_rank, dev, total, overla
     kw = dict(interpolation="linear", oversampling=2.0)
     vols = sharding.PartialVolumes(1, R, dev, with_weights=True)
     vols.timing = True
+    if slab_groups:
+        vols.slab_groups = slab_groups
     gen = torch.Generator(device=dev).manual_seed(900 + rank)
     cgen = torch.Generator().manual_seed(900 + rank)
     # untimed warm-up: the first launch of a kernel pays for loading it (tens of ms when eight
@@ -640,7 +642,8 @@ def check_sharded_parity(final, n, dev):
 def sharded_backprojection_workload(args):
     dist, rank, world, local_rank, dev = _dist_setup()
     res = run_sharded_backprojection(dist, rank, world, local_rank, dev, args.total_slices or SHARD["P_total"],
-                                     overlap_tail=not args.no_overlap_tail, check_slices=0 if args.skip_cpu else 32)
+                                     overlap_tail=not args.no_overlap_tail, check_slices=0 if args.skip_cpu else 32,
+                                     slab_groups=args.slab_groups)
     if rank == 0:
         print(json.dumps(res), flush=True)
     if world > 1:
@@ -946,6 +949,7 @@ def main():
                     help="default: projection (+ back-projection) headline line; the other two print their own line")
     ap.add_argument("--total-slices", type=int, default=0, help="sharded_backproject: total slices over all ranks (default 200000)")
     ap.add_argument("--no-overlap-tail", action="store_true", help="sharded_backproject: fold and reduce after the last chunk instead of overlapping them with it")
+    ap.add_argument("--slab-groups", type=int, default=0, help="sharded_backproject: launches the final stage is cut into (default: the library's 12)")
     ap.add_argument("--skip-sharded", action="store_true", help="default workload: leave the sharded box-400 back-projection out (quick runs)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
