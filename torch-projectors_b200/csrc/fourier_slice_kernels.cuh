@@ -17,9 +17,6 @@ namespace b200proj {
 #ifndef PB_MIN_BLOCKS
 #define PB_MIN_BLOCKS 4
 #endif
-#ifndef SLAB_MIN_BLOCKS
-#define SLAB_MIN_BLOCKS 1
-#endif
 
 struct BlockWork {
     int b, p, i, j;
@@ -426,7 +423,7 @@ __device__ __forceinline__ void clip_run(float a, float inv_a, float b, float lo
 // INTERLEAVED: reductions go to a 16-byte-per-voxel (re, im, w, 0) accumulator `accum` (one v4
 // reduction per tap) instead of data_rec / weight_rec.
 template <bool CUBIC, bool WEIGHTS, bool INTERLEAVED = false>
-__global__ void __launch_bounds__(kBlockThreads, CUBIC ? 1 : SLAB_MIN_BLOCKS)
+__global__ void __launch_bounds__(kBlockThreads)
 backproject_slab_kernel(const float2* __restrict__ proj, const float* __restrict__ weights,
                         const float* __restrict__ rot, const float* __restrict__ shifts,
                         float2* __restrict__ data_rec, float* __restrict__ weight_rec,
