@@ -56,6 +56,7 @@ def _forw(lib, **over):
     (dict(B_rot=3, B=2), "rotations must be 1 or same"),
     (dict(shifts=1, B_shift=3, B=2), "shifts must be 1 or same"),
     (dict(os=0.0), "oversampling"),
+    (dict(os=1.0e9), "beyond 2^30"),
     (dict(rot=0), "NULL"),
     (dict(rec=0), "NULL"),
     (dict(R=4096), "exceeds"),

@@ -144,3 +144,21 @@ def test_pose_counts_beyond_one_grid_row(tp, B, P, interp):
         # and the tail of the pose-major tensors on its own (a wrong decoding would leave it unwritten or misplaced)
         if got[key].dim() >= 2 and got[key].shape[1] == P:
             assert rel_err(got[key][:, -500:], want[key][:, -500:]) <= tolerance_for(key), key
+
+
+def test_raw_operator_traces_under_torch_compile(tp):
+    """A function around a raw operator is captured as ONE graph (no graph break at the operator:
+    its Meta implementation supplies the shapes) and gives the eager result.  The aot_eager backend
+    keeps the test independent of code generation for complex tensors."""
+    ops = torch.ops.torch_projectors_b200
+    case = Case("compile", 3, "linear", 1, 6, 8, 16, 2.0, None, 1, 1, seed=93)
+    t = {k: (v.cuda() if v is not None else None) for k, v in make_inputs(case).items()}
+
+    def f(rec, rot, shifts):
+        return ops.project_3d_to_2d_forw(rec * 2.0, rot, shifts, [8, 8], "linear", 2.0, None)
+
+    compiled = torch.compile(f, backend="aot_eager", fullgraph=True)
+    with torch.no_grad():
+        got = compiled(t["rec"], t["rot"], t["shifts"])
+        want = f(t["rec"], t["rot"], t["shifts"])
+    assert torch.equal(got, want)
