@@ -332,7 +332,7 @@ def profile_case(args):
     P = args.profile_poses
     rec, rot, shifts = make_projection_inputs(dev, seed=1234)
     rot, shifts = rot[:, :P].contiguous(), shifts[:, :P].contiguous()
-    kw = dict(interpolation=PROJ["interp"], oversampling=PROJ["os"], fourier_radius_cutoff=PROJ["cutoff"])
+    kw = dict(interpolation=args.profile_interp or PROJ["interp"], oversampling=PROJ["os"], fourier_radius_cutoff=PROJ["cutoff"])
     if args.profile_case == "autograd_step":
         # box-512 volume (539 MB), 256x256 slices, cubic, all gradients: forward + backward kernels
         gen = torch.Generator(device=dev).manual_seed(6)
@@ -945,6 +945,7 @@ def main():
     ap.add_argument("--profile-case", choices=["project", "backproject", "project_back", "backproject_slab", "accumulate_slab", "autograd_step", "project_2d"], default=None,
                     help="run a few launches of one kernel on a reduced pose count (for ncu captures); prints no bench line")
     ap.add_argument("--profile-poses", type=int, default=2048)
+    ap.add_argument("--profile-interp", choices=["linear", "cubic"], default=None, help="--profile-case project: interpolation (default: the workload's cubic)")
     ap.add_argument("--workload", choices=["default", "autograd_step", "sharded_backproject", "ops_table", "reference_cuda", "paper_matrix", "red_ceiling", "latency"], default="default",
                     help="default: projection (+ back-projection) headline line; the other two print their own line")
     ap.add_argument("--total-slices", type=int, default=0, help="sharded_backproject: total slices over all ranks (default 200000)")
