@@ -139,6 +139,11 @@ def test_meta_implementations_give_the_output_shapes():
     gp, gw, grot, gsh = ops.backproject_2d_to_3d_back(d, wr, g, w, rot, sh, "linear", 2.0, None)
     assert gp.shape == g.shape and gw.shape == w.shape and grot.shape == rot.shape and gsh.shape == (0,)
     assert ops.plane_locality_order(rot, 2).shape == (10,)
+    # the variants with an explicit processing order of the slices
+    order = torch.empty(10, dtype=torch.int32, **m)
+    assert ops.project_3d_to_2d_forw_ordered(rec, rot, sh, [8, 8], "cubic", 2.0, None, order).shape == (2, 5, 8, 5)
+    assert ops.project_3d_to_2d_back_ordered(g, rec, rot, sh, "cubic", 2.0, None, None)[0].shape == rec.shape
+    assert ops.backproject_2d_to_3d_back_ordered(d, wr, g, w, rot, sh, "linear", 2.0, None, order)[0].shape == g.shape
 
 
 @pytest.mark.parametrize("P,world", [(10, 1), (10, 2), (10, 3), (7, 8), (0, 4), (200000, 8)])
