@@ -10,10 +10,17 @@ rfftn'd to [1,256,256,129] complex64), 10,000 uniform-SO(3) poses with shifts in
 carries the back-projection workload (50,000 slices of 128x128 with weights into a box-256
 volume, linear interpolation) under ``"backproject"``.
 
+``"sharded_backproject"`` holds the sharded workload: 200,000 slices of 400x400 with weights
+into box-800 volumes, split over the ranks (strong scaling), the reduce of the partial volumes
+overlapped with the scatter of each rank's last chunk.  ``"parity_check"`` objects compare parts
+of the timed outputs with the CPU reference after the timed regions.
+
 With N > 1 (launched by torch.distributed.run, one rank per GPU) every rank processes the
 same number of poses on its own replica of the volume (weak scaling, no collective on the
 projection path); the back-projection step ends with one NCCL reduce of the partial
-data+weight volumes onto rank 0.
+data+weight volumes onto rank 0.  Other workloads (``--workload``): the autograd step, the
+sharded workload alone, a table of all eight operators, the reference's CUDA kernels and its
+published benchmark rows, the reduction-rate ceilings and per-call latency.
 
 ``--impl reference`` times the reference's own CPU operators (built by
 ``oracle/build_ref.py`` into ``oracle/_ref``; the C restatement oracle when that build is
