@@ -386,6 +386,44 @@ def profile_case(args):
         torch.cuda.synchronize()
         print(f"profile case backproject_slab: {P} slices of 256x256 into box 512, 2 launches done")
         return
+    if args.profile_case in ("backproject_back", "backproject_cubic", "backproject_2d", "prep"):
+        interp = args.profile_interp or "cubic"
+        if args.profile_case == "prep":
+            # the steps either side: pad + fftshift of a 256^3 map to 512^3, and the way back
+            from torch_projectors_b200 import prep
+            real = torch.randn(1, 256, 256, 256, device=dev)
+            for _ in range(2):
+                padded = prep._PadShift.apply(real, 3, 512)
+                prep._CropUnshift.apply(padded, 3, 256)
+            torch.cuda.synchronize()
+            print("profile case prep: 256^3 <-> 512^3, 2 launches of each kernel done")
+            return
+        if args.profile_case == "backproject_2d":
+            # 2D back-projection: P slices of 64x33 with weights into one 128x65 reconstruction
+            from cases import random_rotations_2d
+            gen = torch.Generator(device=dev).manual_seed(8)
+            proj2 = torch.complex(torch.randn(1, P, 64, 33, generator=gen, device=dev), torch.randn(1, P, 64, 33, generator=gen, device=dev))
+            w2 = torch.rand(1, P, 64, 33, generator=gen, device=dev)
+            rot2 = random_rotations_2d(P, torch.Generator().manual_seed(8)).reshape(1, P, 2, 2).to(dev)
+            sh2 = torch.randn(1, P, 2, generator=gen, device=dev) * 3.0
+            for _ in range(2):
+                tp.backproject_2d_forw(proj2, rot2, weights=w2, shifts=sh2, interpolation=interp, oversampling=2.0)
+            torch.cuda.synchronize()
+            print(f"profile case backproject_2d: {P} slices of 64x33, {interp}, 2 launches done")
+            return
+        proj, weights, brot, bshifts = make_backprojection_inputs(dev, 4321, P)
+        if args.profile_case == "backproject_cubic":
+            for _ in range(2):
+                tp.backproject_2d_to_3d_forw(proj, brot, weights=weights, shifts=bshifts, interpolation=interp, oversampling=BACK["os"])
+        else:
+            gd = torch.randn(1, 256, 256, 129, dtype=torch.complex64, device=dev)
+            gw = torch.randn(1, 256, 256, 129, device=dev)
+            r_g, s_g = brot.clone().requires_grad_(True), bshifts.clone().requires_grad_(True)
+            for _ in range(2):
+                torch.ops.torch_projectors_b200.backproject_2d_to_3d_back(gd, gw, proj, weights, r_g, s_g, interp, BACK["os"], None)
+        torch.cuda.synchronize()
+        print(f"profile case {args.profile_case}: {P} slices, {interp}, 2 launches done")
+        return
     for _ in range(2):
         if args.profile_case == "project":
             tp.project_3d_to_2d_forw(rec, rot, shifts, output_shape=(PROJ["N"], PROJ["N"]), **kw)
@@ -949,7 +987,8 @@ def main():
     ap.add_argument("--skip-backproject", action="store_true")
     ap.add_argument("--natural-order", action="store_true",
                     help="process slices in the order given (switch the plane-locality order of beyond-L2 volumes off), for comparisons")
-    ap.add_argument("--profile-case", choices=["project", "backproject", "project_back", "backproject_slab", "accumulate_slab", "autograd_step", "project_2d"], default=None,
+    ap.add_argument("--profile-case", choices=["project", "backproject", "project_back", "backproject_slab", "accumulate_slab", "autograd_step", "project_2d",
+                                               "backproject_back", "backproject_cubic", "backproject_2d", "prep"], default=None,
                     help="run a few launches of one kernel on a reduced pose count (for ncu captures); prints no bench line")
     ap.add_argument("--profile-poses", type=int, default=2048)
     ap.add_argument("--profile-interp", choices=["linear", "cubic"], default=None, help="--profile-case project: interpolation (default: the workload's cubic)")
