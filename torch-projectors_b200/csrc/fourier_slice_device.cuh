@@ -79,6 +79,8 @@ struct SliceGeom {
     long long vol_elems;    // voxels per batch item
     const int* order;       // optional processing order: block k handles slice order[k] (a permutation of
                             // [0, BP)); nullptr = natural order.  Changes which blocks run together, not results.
+    int replicas;           // interleaved workspace of a small reconstruction: number of copies (a power of two) the
+    long long replica_stride;   // slices are spread over, and the voxels between copies; 1 / 0 = a single copy
     const int* pack_index;  // packed output of the forward projection: position of pixel i*Nh + j among the
     int pack_count;         // pack_count pixels inside the cutoff (-1 outside); nullptr = dense [N, Nh] slices
 };

@@ -351,17 +351,28 @@ backproject_forw_interleaved_kernel(const float2* __restrict__ proj, const float
     float2 v;
     float wv;
     const bool active = backproject_pixel<DIM, true>(g, w, proj, weights, rot, shifts, px, v, wv);
-    scatter_coop<DIM, CUBIC, true, true, true>(g, nullptr, nullptr, accum + (size_t)w.b * g.vol_elems,
+    // A reconstruction of less than ~2 MB takes reductions at half the rate of a larger one (they pile
+    // up on too few sectors), so the slices of a call are spread over g.replicas copies of it, which
+    // the fold adds up.
+    const size_t copy = (size_t)(w.p & (g.replicas - 1)) * (size_t)g.replica_stride;
+    scatter_coop<DIM, CUBIC, true, true, true>(g, nullptr, nullptr, accum + copy + (size_t)w.b * g.vol_elems,
                                                px, active, v, wv);
 }
 
-// data[k] (+)= accum[k].xy, weight[k] (+)= accum[k].z
+// data[k] (+)= sum over copies of accum[k].xy, weight[k] (+)= sum over copies of accum[k].z
 __global__ void __launch_bounds__(256)
 fold_interleaved_kernel(const float4* __restrict__ accum, float2* __restrict__ data,
-                        float* __restrict__ weight, size_t n, int accumulate) {
+                        float* __restrict__ weight, size_t n, int accumulate, int replicas = 1,
+                        size_t replica_stride = 0) {
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (size_t k = (size_t)blockIdx.x * blockDim.x + threadIdx.x; k < n; k += stride) {
-        const float4 a = __ldcs(accum + k);
+        float4 a = __ldcs(accum + k);
+        for (int r = 1; r < replicas; ++r) {
+            const float4 c = __ldcs(accum + (size_t)r * replica_stride + k);
+            a.x += c.x;
+            a.y += c.y;
+            a.z += c.z;
+        }
         float2 d = make_float2(a.x, a.y);
         float wv = a.z;
         if (accumulate) {
