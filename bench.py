@@ -911,6 +911,17 @@ def red_ceiling_workload(args):
             rows.setdefault(name, {})[label] = {"ms": ms, "g_taps_per_s": taps / (ms * 1e-3) / 1e9}
         del buf
         torch.cuda.empty_cache()
+    # the slab-ordered scatter's memory traffic around the same reductions: a window that fits L2 moves
+    # through a 3 GiB target (16 reductions per slot while it is resident), 2 bytes per tap streamed
+    target = torch.zeros((3 << 30) // 4, dtype=torch.float32, device=dev)
+    source = torch.zeros((1 << 30) // 4, dtype=torch.float32, device=dev)
+    s_blocks = 16 * (target.numel() // 4) // (256 * iters)
+    for window_mib in (32, 64, 96):
+        ms = statistics.median(timed_steps(lambda: tp._abi.reduction_rate_probe_streaming(target, window_mib << 20, source, s_blocks, iters),
+                                           max(args.steps, 5), args.warmup, lambda: None, lambda: None))
+        rows.setdefault(RED_PATTERNS[1], {})[f"{window_mib} MiB window moving through 3 GiB, 2 B per tap streamed from 1 GiB"] = {
+            "ms": ms, "g_taps_per_s": s_blocks * 256 * iters / (ms * 1e-3) / 1e9}
+    del target, source
     print(json.dumps({"metric": "red.global.add retired per second by access pattern (10^9 taps/s)", "data": "synthetic",
                       "config": {"workload": f"{blocks} blocks x 256 lanes x {iters} reductions to pseudo-random places"},
                       "rows": rows, "clocks": sampler.stop()}), flush=True)

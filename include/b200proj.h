@@ -309,6 +309,17 @@ int b200proj_ifftshift_crop_f64(const double* full, int64_t batch, int dims, int
  * The buffer's contents are added to, not preserved. */
 int b200proj_reduction_rate_probe(int pattern, float* buffer, size_t buffer_bytes, int blocks,
                                   int iterations, void* stream);
+/* The same probe with the memory traffic of the slab-ordered scatter (pattern 1 otherwise): the lane
+ * pairs of block b work inside window  b * n_windows / blocks  of `target` (windows of window_bytes,
+ * sized to fit L2; target far beyond L2), so the window moves through the target as the grid
+ * advances and every slot is filled from and written back to HBM once, and every lane reads 8 bytes
+ * per four reductions from `source` (source_bytes, beyond L2; read cyclically) with streaming
+ * loads.  With blocks * 256 * iterations = 16 reductions per 16-byte slot of the target this moves
+ * 2 + 2 bytes per reduction through HBM, as that kernel does per tap.  `source` must hold finite numbers (they are
+ * added to the target's second and third floats); the target's contents are added to. */
+int b200proj_reduction_rate_probe_streaming(float* target, size_t target_bytes, size_t window_bytes,
+                                            const float* source, size_t source_bytes, int blocks,
+                                            int iterations, void* stream);
 
 /* ---- backward of back-projection (gather) ----------------------------------------------
  * grad_proj [B,P,N,Nh] complex is fully written.  grad_weights [B,P,N,Nh] float is written

@@ -69,6 +69,21 @@ def test_reduction_rate_probe_issues_every_reduction(tp, pattern, per_tap):
         tp._abi.reduction_rate_probe(9, buf, blocks=1, iterations=1)
 
 
+def test_streaming_reduction_rate_probe_issues_every_reduction_inside_its_windows(tp):
+    target = torch.zeros(1 << 18, dtype=torch.float32, device="cuda")         # 1 MiB = 4 windows of 256 KiB
+    source = torch.full((1 << 16,), 0.5, dtype=torch.float32, device="cuda")
+    tp._abi.reduction_rate_probe_streaming(target, 1 << 18, source, blocks=8, iterations=6)
+    torch.cuda.synchronize()
+    slots = target.view(-1, 4).double()
+    taps = 8 * 256 * 6
+    assert slots[:, 0].sum().item() == taps and slots[:, 3].sum().item() == 0
+    assert slots[:, 1].sum().item() == 1.5 * taps == slots[:, 2].sum().item()   # 1 + the streamed 0.5
+    per_window = slots[:, 0].view(4, -1).sum(dim=1)
+    assert per_window.tolist() == [taps / 4] * 4                               # blocks 2k, 2k+1 work in window k
+    with pytest.raises(RuntimeError, match="out of range"):
+        tp._abi.reduction_rate_probe_streaming(target, 1 << 21, source, blocks=1, iterations=1)
+
+
 _ROWS_SCRIPT = r"""
 import sys, torch
 sys.path[:0] = [{root!r}, {root!r} + "/tests", {root!r} + "/torch-projectors_b200"]

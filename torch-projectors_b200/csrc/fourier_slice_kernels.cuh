@@ -752,6 +752,30 @@ reduction_rate_kernel(float* __restrict__ buf, unsigned units, int iters) {
     }
 }
 
+// The memory traffic of the slab-ordered scatter, without its arithmetic: lane pairs add to adjacent
+// 16-byte slots inside a window of `window` slots that moves through the target as the grid
+// advances (block b works in window b * n_windows / gridDim.x, as the slab index is the slow grid
+// axis there), and every lane streams 8 bytes per four reductions from `src` (the slices).  With a
+// window that fits L2, a target far beyond it and ~16 reductions per slot of a window this has the
+// kernel's proportions: 2 bytes per tap of target fill + write-back, 2 bytes per tap streamed.
+__global__ void __launch_bounds__(256)
+reduction_stream_kernel(float* __restrict__ buf, unsigned units, unsigned window,
+                        const float2* __restrict__ src, unsigned src_units, int iters) {
+    const unsigned t = blockIdx.x * blockDim.x + threadIdx.x;
+    const unsigned n_windows = units / window;
+    const unsigned base = (unsigned)(((unsigned long long)blockIdx.x * n_windows) / gridDim.x) * window;
+    const unsigned per_block = (unsigned)(iters + 3) / 4;
+    float2 v = make_float2(0.f, 0.f);
+    for (int i = 0; i < iters; ++i) {
+        if ((i & 3) == 0) {
+            const unsigned long long k = ((unsigned long long)blockIdx.x * per_block + (unsigned)(i >> 2)) * 256u + threadIdx.x;
+            v = __ldcs(src + (unsigned)(k % src_units));
+        }
+        const unsigned s = base + probe_hash((t >> 1) * 977u + i * 7919u) % (window - 1) + (t & 1);
+        red_add_v4(reinterpret_cast<float4*>(buf) + s, 1.f, 1.f + v.x, 1.f + v.y, 0.f);
+    }
+}
+
 // ---- the steps either side of the operators: pad + fftshift, ifftshift + crop ----------------
 // Real-space image / volume (box n) <-> zero-padded, origin-at-index-0 array (box m >= n, both
 // even or n odd is fine; lo = (m - n) / 2) that cuFFT transforms.  One pass each instead of
