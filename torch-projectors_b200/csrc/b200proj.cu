@@ -142,8 +142,8 @@ SlabPlan slab_plan(int64_t R, bool has_weights, bool interleaved = false, bool e
     const double plane_bytes = (double)R * (double)(R / 2 + 1) * (interleaved ? 16.0 : has_weights ? 12.0 : 8.0);
     const double threshold = (eager && min_mb_e < min_mb) ? min_mb_e : min_mb;
     if (slab_mb <= 0.0 || plane_bytes * (double)R <= threshold * 1e6) return {1, (int)R};
-    // 16-byte voxels: fewer, larger reductions per plane leave room for 1.25x the bytes (measured)
-    int planes = (int)(slab_mb * (interleaved ? 1.25 : 1.0) * 1e6 / plane_bytes);
+    // 16-byte voxels: fewer, larger reductions per plane leave room for 1.4x the bytes (measured)
+    int planes = (int)(slab_mb * (interleaved ? 1.4 : 1.0) * 1e6 / plane_bytes);
     if (planes < 1) planes = 1;
     const int slabs = (int)((R + planes - 1) / planes);
     return {slabs, planes};

@@ -639,6 +639,26 @@ __device__ __forceinline__ void red_add_v2(double2* addr, double a, double b) { 
 __device__ __forceinline__ void red_add_v4(float4* addr, float a, float b, float c, float d) {
     asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
 }
+// The same with an L2 eviction priority: lines written this way are the last to be evicted.  The
+// slab-ordered scatter uses them so that its slab of planes holds its place in L2 against the
+// slices streaming through (measured on B200: 19.4 -> 18.8 ms per 8,192 slices of 400x201 into
+// box 800; no effect on the kernels whose volume fits L2, which keep the plain forms).
+__device__ __forceinline__ unsigned long long l2_keep_policy() {
+    unsigned long long policy;
+    asm("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(policy));
+    return policy;
+}
+__device__ __forceinline__ void red_add_v2_keep(float2* addr, float a, float b, unsigned long long policy) {
+    asm volatile("red.global.add.L2::cache_hint.v2.f32 [%0], {%1, %2}, %3;" ::"l"(addr), "f"(a), "f"(b), "l"(policy) : "memory");
+}
+__device__ __forceinline__ void red_add_keep(float* addr, float a, unsigned long long policy) {
+    asm volatile("red.global.add.L2::cache_hint.f32 [%0], %1, %2;" ::"l"(addr), "f"(a), "l"(policy) : "memory");
+}
+__device__ __forceinline__ void red_add_v2_keep(double2* addr, double a, double b, unsigned long long) { red_add_v2(addr, a, b); }
+__device__ __forceinline__ void red_add_keep(double* addr, double a, unsigned long long) { red_add(addr, a); }
+__device__ __forceinline__ void red_add_v4_keep(float4* addr, float a, float b, float c, float d, unsigned long long policy) {
+    asm volatile("red.global.add.L2::cache_hint.v4.f32 [%0], {%1, %2, %3, %4}, %5;" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d), "l"(policy) : "memory");
+}
 
 // Cooperative scatter of a complex value (and, when WEIGHTS, of wval * |tap weight|) to the
 // 2^dim / 4^dim taps around a pixel's sample position.  The T lanes of a group (T = 2 linear,
@@ -728,7 +748,11 @@ __device__ __forceinline__ void scatter_coop(const SliceGeom& g, C2<R>* __restri
                 const R fw = WEIGHTS ? wval * rabs(w) : 0.f;
                 if (!SLAB || tap_here) {
                     if (INTERLEAVED) {
-                        red_add_v4(vol4 + off, re, im, fw, 0.f);
+                        if (SLAB) red_add_v4_keep(vol4 + off, re, im, fw, 0.f, l2_keep_policy());
+                        else red_add_v4(vol4 + off, re, im, fw, 0.f);
+                    } else if (SLAB) {
+                        red_add_v2_keep(vol + off, re, im, l2_keep_policy());
+                        if (WEIGHTS) red_add_keep(wvol + off, fw, l2_keep_policy());
                     } else {
                         red_add_v2(vol + off, re, im);
                         if (WEIGHTS) red_add(wvol + off, fw);
@@ -741,7 +765,11 @@ __device__ __forceinline__ void scatter_coop(const SliceGeom& g, C2<R>* __restri
                     if (rl2 != rl || dl2 != dl) {
                         const int off2 = dl2 * plane_stride + rl2 * g.Rh;
                         if (INTERLEAVED) {
-                            red_add_v4(vol4 + off2, re, -im, fw, 0.f);
+                            if (SLAB) red_add_v4_keep(vol4 + off2, re, -im, fw, 0.f, l2_keep_policy());
+                            else red_add_v4(vol4 + off2, re, -im, fw, 0.f);
+                        } else if (SLAB) {
+                            red_add_v2_keep(vol + off2, re, -im, l2_keep_policy());
+                            if (WEIGHTS) red_add_keep(wvol + off2, fw, l2_keep_policy());
                         } else {
                             red_add_v2(vol + off2, re, -im);
                             if (WEIGHTS) red_add(wvol + off2, fw);
