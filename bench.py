@@ -917,10 +917,11 @@ def red_ceiling_workload(args):
     source = torch.zeros((1 << 30) // 4, dtype=torch.float32, device=dev)
     s_blocks = 16 * (target.numel() // 4) // (256 * iters)
     for window_mib in (32, 64, 96):
-        ms = statistics.median(timed_steps(lambda: tp._abi.reduction_rate_probe_streaming(target, window_mib << 20, source, s_blocks, iters),
-                                           max(args.steps, 5), args.warmup, lambda: None, lambda: None))
-        rows.setdefault(RED_PATTERNS[1], {})[f"{window_mib} MiB window moving through 3 GiB, 2 B per tap streamed from 1 GiB"] = {
-            "ms": ms, "g_taps_per_s": s_blocks * 256 * iters / (ms * 1e-3) / 1e9}
+        for keep in (False, True):
+            ms = statistics.median(timed_steps(lambda: tp._abi.reduction_rate_probe_streaming(target, window_mib << 20, source, s_blocks, iters, keep),
+                                               max(args.steps, 5), args.warmup, lambda: None, lambda: None))
+            label = f"{window_mib} MiB window moving through 3 GiB, 2 B per tap streamed from 1 GiB" + (", L2 evict-last hint" if keep else "")
+            rows.setdefault(RED_PATTERNS[1], {})[label] = {"ms": ms, "g_taps_per_s": s_blocks * 256 * iters / (ms * 1e-3) / 1e9}
     del target, source
     print(json.dumps({"metric": "red.global.add retired per second by access pattern (10^9 taps/s)", "data": "synthetic",
                       "config": {"workload": f"{blocks} blocks x 256 lanes x {iters} reductions to pseudo-random places"},

@@ -319,7 +319,7 @@ int b200proj_reduction_rate_probe(int pattern, float* buffer, size_t buffer_byte
  * added to the target's second and third floats); the target's contents are added to. */
 int b200proj_reduction_rate_probe_streaming(float* target, size_t target_bytes, size_t window_bytes,
                                             const float* source, size_t source_bytes, int blocks,
-                                            int iterations, void* stream);
+                                            int iterations, int evict_last, void* stream);
 
 /* ---- backward of back-projection (gather) ----------------------------------------------
  * grad_proj [B,P,N,Nh] complex is fully written.  grad_weights [B,P,N,Nh] float is written

@@ -69,10 +69,11 @@ def test_reduction_rate_probe_issues_every_reduction(tp, pattern, per_tap):
         tp._abi.reduction_rate_probe(9, buf, blocks=1, iterations=1)
 
 
-def test_streaming_reduction_rate_probe_issues_every_reduction_inside_its_windows(tp):
+@pytest.mark.parametrize("evict_last", [False, True])
+def test_streaming_reduction_rate_probe_issues_every_reduction_inside_its_windows(tp, evict_last):
     target = torch.zeros(1 << 18, dtype=torch.float32, device="cuda")         # 1 MiB = 4 windows of 256 KiB
     source = torch.full((1 << 16,), 0.5, dtype=torch.float32, device="cuda")
-    tp._abi.reduction_rate_probe_streaming(target, 1 << 18, source, blocks=8, iterations=6)
+    tp._abi.reduction_rate_probe_streaming(target, 1 << 18, source, blocks=8, iterations=6, evict_last=evict_last)
     torch.cuda.synchronize()
     slots = target.view(-1, 4).double()
     taps = 8 * 256 * 6

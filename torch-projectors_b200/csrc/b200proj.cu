@@ -786,7 +786,7 @@ int b200proj_reduction_rate_probe(int pattern, float* buffer, size_t buffer_byte
 
 int b200proj_reduction_rate_probe_streaming(float* target, size_t target_bytes, size_t window_bytes,
                                             const float* source, size_t source_bytes, int blocks,
-                                            int iterations, void* stream) {
+                                            int iterations, int evict_last, void* stream) {
     g_error[0] = 0;
     if (target == nullptr || (reinterpret_cast<uintptr_t>(target) & 15u) != 0 || source == nullptr || (reinterpret_cast<uintptr_t>(source) & 7u) != 0)
         return fail(B200PROJ_ERR_ARGUMENT, "target must be a 16-byte and source an 8-byte aligned device pointer");
@@ -794,8 +794,12 @@ int b200proj_reduction_rate_probe_streaming(float* target, size_t target_bytes, 
     const size_t units = target_bytes / 16, window = window_bytes / 16, src_units = source_bytes / 8;
     if (window < 16 || units < window || units > 0xffffffffull || src_units < 256 || src_units > 0xffffffffull)
         return fail(B200PROJ_ERR_LIMIT, "target of %zu bytes, window of %zu bytes or source of %zu bytes out of range", target_bytes, window_bytes, source_bytes);
-    reduction_stream_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(target, (unsigned)units, (unsigned)window,
-                                                                     reinterpret_cast<const float2*>(source), (unsigned)src_units, iterations);
+    if (evict_last)
+        reduction_stream_kernel<true><<<blocks, 256, 0, (cudaStream_t)stream>>>(target, (unsigned)units, (unsigned)window,
+                                                                               reinterpret_cast<const float2*>(source), (unsigned)src_units, iterations);
+    else
+        reduction_stream_kernel<false><<<blocks, 256, 0, (cudaStream_t)stream>>>(target, (unsigned)units, (unsigned)window,
+                                                                                reinterpret_cast<const float2*>(source), (unsigned)src_units, iterations);
     return check_launch("reduction_rate_probe_streaming launch");
 }
 

@@ -758,6 +758,8 @@ reduction_rate_kernel(float* __restrict__ buf, unsigned units, int iters) {
 // axis there), and every lane streams 8 bytes per four reductions from `src` (the slices).  With a
 // window that fits L2, a target far beyond it and ~16 reductions per slot of a window this has the
 // kernel's proportions: 2 bytes per tap of target fill + write-back, 2 bytes per tap streamed.
+// KEEP: the reductions carry the L2 evict-last hint that the slab-ordered kernel gives them.
+template <bool KEEP>
 __global__ void __launch_bounds__(256)
 reduction_stream_kernel(float* __restrict__ buf, unsigned units, unsigned window,
                         const float2* __restrict__ src, unsigned src_units, int iters) {
@@ -772,7 +774,8 @@ reduction_stream_kernel(float* __restrict__ buf, unsigned units, unsigned window
             v = __ldcs(src + (unsigned)(k % src_units));
         }
         const unsigned s = base + probe_hash((t >> 1) * 977u + i * 7919u) % (window - 1) + (t & 1);
-        red_add_v4(reinterpret_cast<float4*>(buf) + s, 1.f, 1.f + v.x, 1.f + v.y, 0.f);
+        if (KEEP) red_add_v4_keep(reinterpret_cast<float4*>(buf) + s, 1.f, 1.f + v.x, 1.f + v.y, 0.f, l2_keep_policy());
+        else red_add_v4(reinterpret_cast<float4*>(buf) + s, 1.f, 1.f + v.x, 1.f + v.y, 0.f);
     }
 }
 

@@ -46,7 +46,7 @@ SIGNATURES["b200proj_accumulator_fold_range"] = [_ptr, _i64, _i64, _ptr, _ptr, _
 SIGNATURES["b200proj_accumulator_fold_normalized"] = [_ptr, _i64, _i64, _dbl, _ptr, _ptr]
 SIGNATURES["b200proj_project_3d_to_2d_forw_packed"] = [_ptr] + _COMMON + [_ptr, _ptr, _i64, _ptr, _ptr]
 SIGNATURES["b200proj_reduction_rate_probe"] = [_int, _ptr, C.c_size_t, _int, _int, _ptr]
-SIGNATURES["b200proj_reduction_rate_probe_streaming"] = [_ptr, C.c_size_t, C.c_size_t, _ptr, C.c_size_t, _int, _int, _ptr]
+SIGNATURES["b200proj_reduction_rate_probe_streaming"] = [_ptr, C.c_size_t, C.c_size_t, _ptr, C.c_size_t, _int, _int, _int, _ptr]
 SIGNATURES["b200proj_backproject_2d_to_3d_accumulate_slabs"] = [_ptr, _ptr] + _COMMON + [_ptr, _int, _int, _ptr]
 EXPORTS = list(SIGNATURES) + ["b200proj_version", "b200proj_last_error", "b200proj_rec_boxsize",
                                 "b200proj_backproject_workspace_bytes", "b200proj_accumulator_bytes",
@@ -311,8 +311,9 @@ def reduction_rate_probe(pattern: int, buffer, blocks: int, iterations: int):
     _call("b200proj_reduction_rate_probe", buffer, int(pattern), _p(buffer), buffer.numel() * buffer.element_size(), int(blocks), int(iterations))
 
 
-def reduction_rate_probe_streaming(target, window_bytes: int, source, blocks: int, iterations: int):
+def reduction_rate_probe_streaming(target, window_bytes: int, source, blocks: int, iterations: int, evict_last: bool = False):
     """Pattern 1 of the probe inside a window that moves through `target`, with 8 bytes per four
-    reductions streamed from `source` (both float32 CUDA tensors)."""
+    reductions streamed from `source` (both float32 CUDA tensors); evict_last: with the L2 hint
+    of the slab-ordered kernel."""
     _call("b200proj_reduction_rate_probe_streaming", target, _p(target), target.numel() * target.element_size(), int(window_bytes),
-          _p(source), source.numel() * source.element_size(), int(blocks), int(iterations))
+          _p(source), source.numel() * source.element_size(), int(blocks), int(iterations), int(bool(evict_last)))
