@@ -76,7 +76,7 @@ def reduction_ceiling(taps, ms, pattern):
     """The ceiling that binds the scatter kernels: reductions retired per second against the rate a
     microbenchmark of the same access pattern reaches on an L2-resident buffer."""
     rate = taps / (ms * 1e-3) / 1e9
-    return {"bound": "L2 reduction rate", "achieved": rate, "peak": RED_CEILING_GTAPS[pattern], "unit": "G taps/s",
+    return {"bound": "reduction request rate (SM L1TEX-to-crossbar port, measured by the probe)", "achieved": rate, "peak": RED_CEILING_GTAPS[pattern], "unit": "G taps/s",
             "frac": rate / RED_CEILING_GTAPS[pattern], "pattern": pattern,
             "peak_source": "python bench.py --workload red_ceiling (profiles/red_ceiling_b200.md)"}
 
