@@ -63,6 +63,28 @@ def make_rotations(dim: int, B_rot: int, P: int, gen: torch.Generator, special: 
     return rot
 
 
+def axis_aligned_rotations(gen: torch.Generator, perturbed: int = 8) -> torch.Tensor:
+    """The 24 proper rotations that map the axes onto each other (every sample of a slice hits
+    the lattice exactly, whole rows and columns land on one plane) followed by `perturbed` of them
+    turned by 1e-6 .. 1e-3 rad about all three axes (samples a hair off the lattice)."""
+    import itertools
+    out = []
+    for perm in itertools.permutations(range(3)):
+        for signs in itertools.product((1.0, -1.0), repeat=3):
+            m = torch.zeros(3, 3, dtype=torch.float64)
+            for r, c in enumerate(perm):
+                m[r, c] = signs[r]
+            if abs(torch.det(m).item() - 1.0) < 1e-9:
+                out.append(m)
+    for k in range(perturbed):
+        ax, ay, az = ((torch.rand(3, generator=gen, dtype=torch.float64) - 0.5) * 2e-6 * 10 ** (k % 4)).tolist()
+        rx = torch.tensor([[1, 0, 0], [0, math.cos(ax), -math.sin(ax)], [0, math.sin(ax), math.cos(ax)]], dtype=torch.float64)
+        ry = torch.tensor([[math.cos(ay), 0, math.sin(ay)], [0, 1, 0], [-math.sin(ay), 0, math.cos(ay)]], dtype=torch.float64)
+        rz = torch.tensor([[math.cos(az), -math.sin(az), 0], [math.sin(az), math.cos(az), 0], [0, 0, 1]], dtype=torch.float64)
+        out.append(rz @ ry @ rx @ out[(k * 5) % 24])
+    return torch.stack(out).float()
+
+
 def hermitian_dc_column_(proj: torch.Tensor) -> torch.Tensor:
     """Make the j = 0 column of rfft-format slices [..., N, Nh] consistent with a real image:
     p[N-i, 0] = conj(p[i, 0]); imaginary part 0 at i = 0 and i = N/2."""

@@ -449,6 +449,92 @@ def test_slab_ordered_backprojection_matches_oracle(tp):
 
 
 
+@pytest.mark.parametrize("interp", ["linear", "cubic"])
+@pytest.mark.parametrize("geom", [(12, 24, 2.0, 3.0), (16, 24, 1.5, 6.7), (34, 34, 1.0, 2.0), (10, 30, 3.0, None)], ids=str)
+def test_all_3d_operators_on_lattice_poses(tp, geom, interp):
+    """The 24 axis-aligned rotations, exact and turned by 1e-6 .. 1e-3 rad: every sample on or a hair
+    off a voxel, zero-weight taps, taps on the volume's edge planes and on the Friedel column, for all
+    eight outputs of the four 3D operators against the oracle."""
+    from cases import axis_aligned_rotations
+    N, R, os_, cut = geom
+    special = axis_aligned_rotations(torch.Generator().manual_seed(N))
+    case = Case("lattice", 3, interp, 2, special.shape[0] + 4, N, R, os_, cut, 1, 1, weights=True, seed=2000 + N, shift_range=3.0)
+    t = make_inputs(case)
+    t["rot"][0, : special.shape[0]] = special
+    got = run_case("cuda", case, t)
+    want = run_case("port", case, t)
+    assert set(got) == set(want)
+    for k in want:
+        assert rel_err(got[k], want[k]) <= (TOL_FORWARD if k == "fwd" else TOL_ATOMIC), (k, rel_err(got[k], want[k]))
+
+
+@pytest.mark.parametrize("interp", ["linear", "cubic"])
+@pytest.mark.parametrize("geom", [(12, 24, 2.0, 3.0), (16, 24, 1.5, 6.7), (34, 34, 1.0, None)], ids=str)
+def test_all_2d_operators_on_lattice_poses(tp, geom, interp):
+    """Quarter turns, exact and off by +-1e-6 .. 1e-3 rad, for the four 2D operators."""
+    import math
+    N, R, os_, cut = geom
+    angles = [q * math.pi / 2 + d for q in range(4) for d in (0.0, 1e-6, -1e-5, 1e-4, -1e-3)]
+    special = torch.tensor([[[round(math.cos(a), 15), -round(math.sin(a), 15)], [round(math.sin(a), 15), round(math.cos(a), 15)]] for a in angles],
+                           dtype=torch.float64).float()
+    case = Case("lattice2d", 2, interp, 2, special.shape[0] + 4, N, R, os_, cut, 1, 1, weights=True, seed=2100 + N, shift_range=3.0)
+    t = make_inputs(case)
+    t["rot"][0, : special.shape[0]] = special
+    got = run_case("cuda", case, t)
+    want = run_case("port", case, t)
+    assert set(got) == set(want)
+    for k in want:
+        assert rel_err(got[k], want[k]) <= (TOL_FORWARD if k == "fwd" else TOL_ATOMIC), (k, rel_err(got[k], want[k]))
+
+
+_SLAB_LATTICE_SCRIPT = r"""
+import sys, math, torch
+sys.path[:0] = [{root!r}, {root!r} + "/tests", {root!r} + "/torch-projectors_b200"]
+import torch_projectors_b200 as tp
+from oracle import port
+from cases import Case, make_inputs, rel_err, TOL_ATOMIC, axis_aligned_rotations
+gen = torch.Generator().manual_seed(7)
+worst = 0.0
+for k, (N, os_, cut, interp, B) in enumerate([(8, 1.0, None, "linear", 1), (12, 2.0, 3.0, "cubic", 2), (16, 1.5, 6.7, "linear", 2),
+                                              (20, 3.0, None, "cubic", 1), (26, 2.0, 11.7, "linear", 1), (34, 1.0, 2.0, "cubic", 1)]):
+    special = axis_aligned_rotations(gen)
+    P = special.shape[0] + 6
+    case = Case("lattice", 3, interp, B, P, N, N, os_, cut, 1, 1, weights=True, seed=700 + k)
+    t = make_inputs(case)
+    t["rot"][0, : special.shape[0]] = special
+    c = lambda x: None if x is None else x.cuda()
+    raw = math.ceil(N * os_)
+    R = raw + raw % 2
+    dw, ww = port.backproject_2d_to_3d_forw(t["proj"], t["weights"], t["rot"], t["shifts"], interp, os_, cut)
+    d, w = tp.backproject_2d_to_3d_forw(c(t["proj"]), c(t["rot"]), weights=c(t["weights"]), shifts=c(t["shifts"]),
+                                        interpolation=interp, oversampling=os_, fourier_radius_cutoff=cut)
+    acc = tp.new_backprojection_accumulator(B, R, "cuda")
+    tp.backproject_2d_to_3d_accumulate_interleaved_(acc, c(t["proj"]), c(t["rot"]), c(t["weights"]), c(t["shifts"]),
+                                                    interpolation=interp, oversampling=os_, fourier_radius_cutoff=cut)
+    da, wa = tp.fold_backprojection_accumulator(acc)
+    assert tp._abi.accumulator_slab_plan(R) == (R, 1), tp._abi.accumulator_slab_plan(R)
+    errs = [rel_err(d, dw), rel_err(w, ww), rel_err(da, dw), rel_err(wa, ww)]
+    assert max(errs) <= TOL_ATOMIC, (N, os_, cut, interp, errs)
+    worst = max(worst, max(errs))
+print("LATTICE-OK", worst)
+"""
+
+
+def test_slab_ordered_backprojection_with_one_plane_slabs_and_lattice_poses(tp):
+    """The hardest inputs for the slab-ordered kernel's search: slabs of a single plane (every
+    footprint straddles slabs) and the 24 axis-aligned rotations, exact and turned by 1e-6 .. 1e-3 rad
+    (whole rows and columns of a slice lie in one plane, samples on or a hair off the lattice, the
+    linear estimates of the search have zero slopes), over six geometries; both the plain entry point
+    and the interleaved accumulator against the oracle."""
+    import os
+    import subprocess
+    import sys
+    root = str(Path(__file__).resolve().parent.parent)
+    env = dict(os.environ, B200PROJ_SLAB_MIN_MB="0", B200PROJ_SLAB_MIN_MB_EAGER="0", B200PROJ_SLAB_MB="0.00001")
+    r = subprocess.run([sys.executable, "-c", _SLAB_LATTICE_SCRIPT.format(root=root)], env=env, capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0 and "LATTICE-OK" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
+
+
 # ---- complex128 / float64: the same kernels instantiated for double ---------------------------
 F64_TOL = 1e-11      # against the fp64 oracle; sums are re-associated, reductions unordered
 
