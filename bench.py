@@ -566,6 +566,10 @@ def run_sharded_backprojection(dist, rank, world, local_rank, dev, total, overla
         vols.slab_groups = slab_groups
     gen = torch.Generator(device=dev).manual_seed(900 + rank)
     cgen = torch.Generator().manual_seed(900 + rank)
+    # the clock sampler starts here: nvidia-smi needs longer to deliver its first sample than the
+    # timed region of an 8-GPU run lasts (two chunks and the final stage), so it also sees the warm-up
+    sampler = ClockSampler(local_rank)
+    sampler.start()
     # untimed warm-up: the first launch of a kernel pays for loading it (tens of ms when eight
     # processes do so at once), and the first collective for its set-up; a few slices through both
     # stages, then the volumes are cleared again
@@ -594,8 +598,6 @@ def run_sharded_backprojection(dist, rank, world, local_rank, dev, total, overla
     if not overlap_tail:
         n_final = 0
     chunk_ms = []
-    sampler = ClockSampler(local_rank)
-    sampler.start()
     if world > 1:
         dist.barrier()
     torch.cuda.synchronize()
