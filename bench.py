@@ -493,6 +493,9 @@ def autograd_step_workload(args):
     target = torch.complex(torch.randn(shape, generator=ggen, device=dev), torch.randn(shape, generator=ggen, device=dev))
     flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     fwd_ev, bwd_ev = [], []
+    # the forward pass keeps its pixels' derivatives for the backward pass (3.2 GB here) unless told otherwise
+    saving = not args.no_save_derivatives
+    tp.set_save_derivatives(saving)
 
     def step():
         for t in (rec, rot, shifts):
@@ -538,8 +541,11 @@ def autograd_step_workload(args):
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "f32", "data": "synthetic",
             "config": {"workload": STEP["name"], "l2": "inputs (539 MB volume, 1.08 GB projections) exceed L2; 256 MiB flush before every step"},
-            "kernels_ms": {"project_forw_kernel<3,cubic>": f, "project_back_kernel<3,cubic,rot,shift> (+ memsets)": bw,
-                           "loss and its gradient (torch elementwise)": ms_per_step - f - bw},
+            "kernels_ms": ({"project_forw_saving_kernel<3,cubic>": f, "project_back_saved_kernel<3,cubic,rot,shift,rec> (+ memsets)": bw,
+                            "loss and its gradient (torch elementwise)": ms_per_step - f - bw} if saving else
+                           {"project_forw_kernel<3,cubic>": f, "project_back_kernel<3,cubic,rot,shift> (+ memsets)": bw,
+                            "loss and its gradient (torch elementwise)": ms_per_step - f - bw}),
+            "saved_derivatives": saving,
             "roofline": {"bound": "hbm", "kernel": "project_forw + project_back (op time only)", "achieved": achieved, "peak": peak,
                          "peak_source": peak_kind, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
                          "algorithmic_bytes_per_launch": STEP_BYTES_PER_SLICE * STEP["P"], "launch_ms": op_ms},
@@ -1011,6 +1017,7 @@ def main():
     ap.add_argument("--total-slices", type=int, default=0, help="sharded_backproject: total slices over all ranks (default 200000)")
     ap.add_argument("--no-overlap-tail", action="store_true", help="sharded_backproject: fold and reduce after the last chunk instead of overlapping them with it")
     ap.add_argument("--slab-groups", type=int, default=0, help="sharded_backproject: launches the final stage is cut into (default: the library's 12)")
+    ap.add_argument("--no-save-derivatives", action="store_true", help="autograd_step: backward pass that gathers the volume again instead of using derivatives kept by the forward pass")
     ap.add_argument("--skip-sharded", action="store_true", help="default workload: leave the sharded box-400 back-projection out (quick runs)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup

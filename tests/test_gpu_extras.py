@@ -85,6 +85,72 @@ def test_streaming_reduction_rate_probe_issues_every_reduction_inside_its_window
         tp._abi.reduction_rate_probe_streaming(target, 1 << 21, source, blocks=1, iterations=1)
 
 
+@pytest.mark.parametrize("interp,fixed_volume", [("cubic", False), ("cubic", True), ("linear", True)])
+@pytest.mark.parametrize("with_shifts", [True, False])
+def test_saved_derivatives_give_the_gradients_of_the_plain_backward(tp, interp, fixed_volume, with_shifts):
+    """With rotation gradients wanted, the forward pass keeps its pixels' derivatives and the backward
+    pass gathers nothing (and skips the volume's gradient when the volume is fixed).  Outputs and all
+    gradients must equal those of the plain pair of operators (set_save_derivatives(False)) to
+    rounding, and the CPU oracle within the gradient tolerance."""
+    from oracle import port
+    case = Case("saved", 3, interp, 2, 7, 16, 32, 2.0, 6.5, 1, 2 if with_shifts else 0, shift_range=3.0, seed=91)
+    t = make_inputs(case)
+    kw = dict(output_shape=(16, 16), interpolation=interp, oversampling=2.0, fourier_radius_cutoff=6.5)
+    g = t["proj"].cuda()
+    results = {}
+    for saving in (True, False):
+        tp.set_save_derivatives(saving)
+        try:
+            rec = t["rec"].cuda().requires_grad_(not fixed_volume)
+            rot = t["rot"].cuda().requires_grad_(True)
+            sh = t["shifts"].cuda().requires_grad_(True) if with_shifts else None
+            out = tp.project_3d_to_2d_forw(rec, rot, sh, **kw)
+            assert (len(out.grad_fn.saved_tensors) == 5) == saving
+            torch.view_as_real(out).backward(torch.view_as_real(g))
+            results[saving] = (out.detach(), rec.grad, rot.grad, sh.grad if with_shifts else None)
+        finally:
+            tp.set_save_derivatives(True)
+    for a, b in zip(results[True], results[False]):
+        assert (a is None) == (b is None)
+        if a is not None:
+            assert rel_err(a, b) <= 2e-6, rel_err(a, b)
+    assert (results[True][1] is None) == fixed_volume
+    want = port.project_3d_to_2d_back(t["proj"], t["rec"], t["rot"], t["shifts"] if with_shifts else None, interp, 2.0, 6.5,
+                                      need_rot_grad=True, need_shift_grad=with_shifts)
+    if not fixed_volume:
+        assert rel_err(results[True][1], want[0]) <= TOL_ATOMIC
+    assert rel_err(results[True][2], want[1]) <= TOL_ATOMIC
+    if with_shifts:
+        assert rel_err(results[True][3], want[2]) <= TOL_ATOMIC
+
+
+def test_saved_derivatives_respect_the_size_limit_and_the_pose_order(tp):
+    case = Case("saved2", 3, "cubic", 1, 80, 16, 32, 2.0, None, 1, 1, shift_range=3.0, seed=92)
+    t = make_inputs(case)
+    kw = dict(output_shape=(16, 16), interpolation="cubic", oversampling=2.0)
+    rec = t["rec"].cuda().requires_grad_(True)
+    rot = t["rot"].cuda().requires_grad_(True)
+    sh = t["shifts"].cuda().requires_grad_(True)
+    tp.set_save_derivatives(True, max_bytes=1000)                     # too small for 80 x 16 x 9 pixels
+    try:
+        out = tp.project_3d_to_2d_forw(rec, rot, sh, **kw)
+        assert len(out.grad_fn.saved_tensors) == 3
+    finally:
+        tp.set_save_derivatives(True)
+    order = tp.plane_locality_order(rot.detach())
+    grads = []
+    for po in (order, False):
+        for x in (rec, rot, sh):
+            x.grad = None
+        out = tp.project_3d_to_2d_forw(rec, rot, sh, pose_order=po, **kw)
+        assert len(out.grad_fn.saved_tensors) == 5
+        torch.view_as_real(out).backward(torch.view_as_real(t["proj"].cuda()))
+        grads.append((out.detach().clone(), rec.grad.clone(), rot.grad.clone(), sh.grad.clone()))
+    assert torch.equal(grads[0][0], grads[1][0])                        # the order changes no output
+    for a, b in zip(grads[0][1:], grads[1][1:]):
+        assert rel_err(a, b) <= 2e-6
+
+
 _ROWS_SCRIPT = r"""
 import sys, torch
 sys.path[:0] = [{root!r}, {root!r} + "/tests", {root!r} + "/torch-projectors_b200"]

@@ -144,6 +144,12 @@ def test_meta_implementations_give_the_output_shapes():
     assert ops.project_3d_to_2d_forw_ordered(rec, rot, sh, [8, 8], "cubic", 2.0, None, order).shape == (2, 5, 8, 5)
     assert ops.project_3d_to_2d_back_ordered(g, rec, rot, sh, "cubic", 2.0, None, None)[0].shape == rec.shape
     assert ops.backproject_2d_to_3d_back_ordered(d, wr, g, w, rot, sh, "linear", 2.0, None, order)[0].shape == g.shape
+    # the forward projection that keeps its pixels' derivatives, and its backward pass
+    out, der = ops.project_3d_to_2d_forw_saving(rec, rot, sh, [8, 8], "cubic", 2.0, None, order)
+    assert out.shape == (2, 5, 8, 5) and der.shape == (3, 2, 5, 8, 5) and der.dtype == torch.complex64
+    gr, grot, gsh = ops.project_3d_to_2d_back_saved(g, out, der, rec, rot, sh, "cubic", 2.0, None, order, True)
+    assert gr.shape == rec.shape and gr.dtype == torch.complex64 and grot.shape == rot.shape and gsh.shape == (0,)
+    assert ops.project_3d_to_2d_back_saved(g, out, der, rec, rot, sh, "cubic", 2.0, None, None, False)[0].shape == (0,)
 
 
 @pytest.mark.parametrize("P,world", [(10, 1), (10, 2), (10, 3), (7, 8), (0, 4), (200000, 8)])

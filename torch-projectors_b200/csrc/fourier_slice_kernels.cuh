@@ -113,6 +113,41 @@ project_forw_kernel(const C2<R>* __restrict__ rec, const R* __restrict__ rot,
     }
 }
 
+// Forward projection that also writes the derivatives of every output pixel with respect to its
+// sample position (c, r, d), with the shift phase applied like the pixel itself: derivs is planar,
+// [DIM][B, P, N, Nh].  The backward pass of a step that needs pose gradients then has nothing to
+// gather (project_back_saved_kernel): the rotation gradient of a pixel is
+// Re(grad * conj(derivative)) * sample frequency, the same numbers project_back_kernel forms from a
+// second gather of the volume.  Pixels outside the cutoff are not written (and never read).
+template <int DIM, bool CUBIC>
+__global__ void __launch_bounds__(kBlockThreads)
+project_forw_saving_kernel(const float2* __restrict__ rec, const float* __restrict__ rot,
+                           const float* __restrict__ shifts, float2* __restrict__ out,
+                           float2* __restrict__ derivs, const SliceGeom g) {
+    const BlockWork w = block_work(g);
+    Pixel px;
+    px.c = px.r = px.d = 0.f;
+    const bool valid = w.in_image && pixel_setup<DIM>(g, pose_rot<DIM>(g, rot, w.b, w.p), w.i, w.j, px);
+    float2 v, gc, gr, gd;
+    interpolate_any<DIM, CUBIC, true>(g, rec + (size_t)w.b * g.vol_elems, px, valid, v, gc, gr, gd);
+    if (!w.in_image) return;
+    if (valid && g.has_shift) {
+        const float* s = pose_shift(g, shifts, w.b, w.p);
+        const float2 ph = phase_ramp(g, px, __ldg(s), __ldg(s + 1));
+        v = cmul(v, ph);
+        gc = cmul(gc, ph);
+        gr = cmul(gr, ph);
+        if (DIM == 3) gd = cmul(gd, ph);
+    }
+    __stcs(out + w.pix, v);
+    if (valid) {
+        const size_t plane = (size_t)g.BP * (size_t)g.slice_pixels;
+        __stcs(derivs + w.pix, gc);
+        __stcs(derivs + plane + w.pix, gr);
+        if (DIM == 3) __stcs(derivs + 2 * plane + w.pix, gd);
+    }
+}
+
 // Linear interpolation, two pixels per lane: the 4- and 8-tap gathers are bound by instruction
 // issue, and a good part of a pixel's instructions does not depend on its row (block decoding,
 // pose loads, the column's share of the rotated position and of the shift phase).  Here a block
@@ -295,6 +330,54 @@ project_back_kernel(const C2<R>* __restrict__ grad_proj, const C2<R>* __restrict
     // cooperative scatter: every lane of the warp takes part
     scatter_coop<DIM, CUBIC, false, false, false>(g, grad_rec + (size_t)w.b * g.vol_elems, nullptr, nullptr,
                                                   px, active, u, 0.f);
+}
+
+// Backward of project_forw_saving_kernel: pose gradients from the saved derivatives and output
+// (Re(grad * conj(derivative)) for the rotation, Im(grad * conj(output)) for the shift: the shift
+// phase cancels in both), then the same scatter of the gradient into the volume (NEED_REC).
+template <int DIM, bool CUBIC, bool NEED_ROT, bool NEED_SHIFT, bool NEED_REC>
+__global__ void __launch_bounds__(kBlockThreads)
+project_back_saved_kernel(const float2* __restrict__ grad_proj, const float2* __restrict__ out,
+                          const float2* __restrict__ derivs, const float* __restrict__ rot,
+                          const float* __restrict__ shifts, float2* __restrict__ grad_rec,
+                          float* __restrict__ grad_rot, float* __restrict__ grad_shift, const SliceGeom g) {
+    const BlockWork w = block_work(g);
+    float acc[2 * DIM + 2];
+#pragma unroll
+    for (int q = 0; q < 2 * DIM + 2; ++q) acc[q] = 0.f;
+    Pixel px;
+    px.c = px.r = px.d = px.sc = px.sr = px.kr = px.kc = 0.f;
+    const bool active = w.in_image &&
+                        pixel_setup<DIM>(g, pose_rot<DIM>(g, rot, w.b, w.p), w.i, w.j, px) &&
+                        !(w.j == 0 && w.i >= g.N / 2);
+    float2 u = make_float2(0.f, 0.f);
+    if (active) {
+        u = __ldcs(grad_proj + w.pix);
+        if (NEED_ROT) {
+            const size_t plane = (size_t)g.BP * (size_t)g.slice_pixels;
+#pragma unroll
+            for (int a = 0; a < DIM; ++a) {
+                const float2 d = __ldcs(derivs + (size_t)a * plane + w.pix);
+                const float dot = u.x * d.x + u.y * d.y;
+                acc[2 * a + 0] = dot * px.sc;
+                acc[2 * a + 1] = dot * px.sr;
+            }
+        }
+        if (NEED_SHIFT) {
+            const float2 o = __ldcs(out + w.pix);
+            const float cross = u.y * o.x - u.x * o.y;
+            acc[2 * DIM + 0] = (float)(g.shift_scale * (double)px.kr) * cross;
+            acc[2 * DIM + 1] = (float)(g.shift_scale * (double)px.kc) * cross;
+        }
+        if (NEED_REC && g.has_shift) {
+            const float* s = pose_shift(g, shifts, w.b, w.p);
+            u = cmul_conj(u, phase_ramp(g, px, __ldg(s), __ldg(s + 1)));
+        }
+    }
+    if (NEED_ROT || NEED_SHIFT) pose_grad_flush<DIM>(g, acc, grad_rot, grad_shift, w.b, w.p);
+    if (NEED_REC)
+        scatter_coop<DIM, CUBIC, false, false, false>(g, grad_rec + (size_t)w.b * g.vol_elems, nullptr, nullptr,
+                                                      px, active, u, 0.f);
 }
 
 // ---- back-projection --------------------------------------------------------------------

@@ -25,6 +25,7 @@ from .ops import (  # noqa: E402
     new_backprojection_accumulator,
     plane_locality_order,
     set_pose_order_thresholds,
+    set_save_derivatives,
     backproject_2d_to_3d_back,
     backproject_2d_to_3d_forw,
     project_2d_back,
@@ -44,7 +45,7 @@ __all__ = [
     "backproject_2d_forw", "backproject_2d_to_3d_forw", "backproject_2d_to_3d_back",
     "backproject_2d_to_3d_accumulate_", "backproject_2d_to_3d_accumulate_interleaved_",
     "new_backprojection_accumulator", "fold_backprojection_accumulator", "plane_locality_order",
-    "set_pose_order_thresholds", "fold_backprojection_accumulator_normalized", "project_3d_to_2d_forw_packed",
+    "set_pose_order_thresholds", "set_save_derivatives", "fold_backprojection_accumulator_normalized", "project_3d_to_2d_forw_packed",
     "unpack_projections", "sharding", "streaming", "prep",
     "project_3d_to_2d_to_host", "backproject_2d_to_3d_from_host",
 ]

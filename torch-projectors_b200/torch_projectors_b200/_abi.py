@@ -44,6 +44,8 @@ SIGNATURES["b200proj_backproject_2d_to_3d_accumulate"] = [_ptr, _ptr] + _COMMON 
 SIGNATURES["b200proj_accumulator_fold"] = [_ptr, _i64, _i64, _ptr, _ptr, _int, _ptr]
 SIGNATURES["b200proj_accumulator_fold_range"] = [_ptr, _i64, _i64, _ptr, _ptr, _int, _ptr]
 SIGNATURES["b200proj_accumulator_fold_normalized"] = [_ptr, _i64, _i64, _dbl, _ptr, _ptr]
+SIGNATURES["b200proj_project_3d_to_2d_forw_saving"] = [_ptr] + _COMMON + [_ptr, _ptr, _ptr, _ptr]
+SIGNATURES["b200proj_project_3d_to_2d_back_saved"] = [_ptr, _ptr, _ptr] + _COMMON + [_ptr, _ptr, _ptr, _ptr, _ptr]
 SIGNATURES["b200proj_project_3d_to_2d_forw_packed"] = [_ptr] + _COMMON + [_ptr, _ptr, _i64, _ptr, _ptr]
 SIGNATURES["b200proj_reduction_rate_probe"] = [_int, _ptr, C.c_size_t, _int, _int, _ptr]
 SIGNATURES["b200proj_reduction_rate_probe_streaming"] = [_ptr, C.c_size_t, C.c_size_t, _ptr, C.c_size_t, _int, _int, _int, _ptr]
@@ -180,6 +182,20 @@ def project_back(dim, grad_proj, rec, rot, shifts, P, N, interp, oversampling, c
     B, R = rec.shape[0], rec.shape[-2]
     _call(name, rec, _p(grad_proj), _p(rec), *_geom(B, R, rot, shifts, P, N, interp, oversampling, cutoff),
           _p(grad_rec), _p(grad_rot), _p(grad_shifts), *_order_arg(dim, order))
+
+
+def project_3d_to_2d_forw_saving(rec, rot, shifts, P, N, interp, oversampling, cutoff, out, derivatives, order=None):
+    """Forward projection that also writes the pixels' derivatives [3, B, P, N, Nh] (complex64)."""
+    B, R = rec.shape[0], rec.shape[-2]
+    _call("b200proj_project_3d_to_2d_forw_saving", rec, _p(rec), *_geom(B, R, rot, shifts, P, N, interp, oversampling, cutoff),
+          _p(out), _p(derivatives), _p(order))
+
+
+def project_3d_to_2d_back_saved(grad_proj, out, derivatives, B, R, rot, shifts, P, N, interp, oversampling, cutoff,
+                                grad_rec, grad_rot, grad_shifts, order=None):
+    """Backward pass from the saved projections and derivatives (any of the three outputs may be None)."""
+    _call("b200proj_project_3d_to_2d_back_saved", grad_proj, _p(grad_proj), _p(out), _p(derivatives),
+          *_geom(B, R, rot, shifts, P, N, interp, oversampling, cutoff), _p(grad_rec), _p(grad_rot), _p(grad_shifts), _p(order))
 
 
 def backproject_forw(dim, proj, weights, rot, shifts, interp, oversampling, cutoff,

@@ -124,6 +124,24 @@ def set_pose_order_thresholds(min_volume_bytes: int = 96 << 20, min_poses: int =
     _ops._set_pose_order_thresholds(POSE_ORDER_MIN_BYTES, POSE_ORDER_MIN_POSES)
 
 
+# Saved derivatives: when the rotations of a cubic 3D projection need gradients, the forward pass can
+# also write every pixel's derivatives with respect to its sample position (three more tensors of
+# the projections' size), and the backward pass then forms the pose gradients from them instead of
+# gathering the volume a second time -- and skips the scatter into the volume's gradient altogether
+# when the volume needs none.  Measured on B200, box 512, 4,096 poses of 256 x 256, cubic: forward
+# 6.5 -> 8.9 ms, backward 20.3 -> 15.1 ms (1.0 ms with a fixed volume).
+SAVE_DERIVATIVES = True
+SAVE_DERIVATIVES_MAX_BYTES = 16 << 30
+
+
+def set_save_derivatives(enabled: bool = True, max_bytes: int = 16 << 30) -> None:
+    """Whether ``project_3d_to_2d_forw`` keeps its pixels' derivatives for the backward pass when the
+    rotations require gradients (complex64, cubic interpolation -- or any interpolation when the
+    volume needs no gradient), and up to which size of that extra tensor (3 x the projections)."""
+    global SAVE_DERIVATIVES, SAVE_DERIVATIVES_MAX_BYTES
+    SAVE_DERIVATIVES, SAVE_DERIVATIVES_MAX_BYTES = bool(enabled), int(max_bytes)
+
+
 def plane_locality_order(rotations: torch.Tensor, batch: int = 1) -> torch.Tensor:
     """int32 [batch * P] processing order of the slices of a 3D operator that reads a volume:
     slices whose planes lie close together come one after the other, so that a volume larger than
@@ -562,9 +580,21 @@ class _Project3DTo2D(torch.autograd.Function):
         reconstruction, rotations, shifts = _canon_project(3, reconstruction, rotations, shifts)
         # the processing order of the slices is settled once here and kept for the backward pass
         order = _resolve_order(pose_order, reconstruction, rotations)
-        projection = _ops.project_3d_to_2d_forw_ordered(reconstruction, rotations, shifts, output_shape, interpolation,
-                                                        oversampling, fourier_radius_cutoff, order)
-        ctx.save_for_backward(reconstruction, rotations, shifts)
+        need_rec, need_rot = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
+        N = int(output_shape[0])
+        saving = (SAVE_DERIVATIVES and need_rot and reconstruction.is_cuda and reconstruction.dtype == torch.complex64
+                  and rotations.dtype == torch.float32 and (interpolation == "cubic" or not need_rec)
+                  and 24 * reconstruction.size(0) * rotations.size(1) * N * (N // 2 + 1) <= SAVE_DERIVATIVES_MAX_BYTES)
+        ctx.saving = saving
+        ctx.need_rec = need_rec
+        if saving:
+            projection, derivatives = _ops.project_3d_to_2d_forw_saving(reconstruction, rotations, shifts, output_shape, interpolation,
+                                                                        oversampling, fourier_radius_cutoff, order)
+            ctx.save_for_backward(reconstruction, rotations, shifts, projection, derivatives)
+        else:
+            projection = _ops.project_3d_to_2d_forw_ordered(reconstruction, rotations, shifts, output_shape, interpolation,
+                                                            oversampling, fourier_radius_cutoff, order)
+            ctx.save_for_backward(reconstruction, rotations, shifts)
         ctx.pose_order = order
         ctx.interpolation = interpolation
         ctx.oversampling = oversampling
@@ -573,10 +603,18 @@ class _Project3DTo2D(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, grad_output):
-        reconstruction, rotations, shifts = ctx.saved_tensors
-        grad_reconstruction, grad_rotations, grad_shifts = _ops.project_3d_to_2d_back_ordered(
-            grad_output.contiguous(), reconstruction, rotations, shifts, ctx.interpolation,
-            ctx.oversampling, ctx.fourier_radius_cutoff, ctx.pose_order)
+        if ctx.saving:
+            reconstruction, rotations, shifts, projection, derivatives = ctx.saved_tensors
+            grad_reconstruction, grad_rotations, grad_shifts = _ops.project_3d_to_2d_back_saved(
+                grad_output.contiguous(), projection, derivatives, reconstruction, rotations, shifts, ctx.interpolation,
+                ctx.oversampling, ctx.fourier_radius_cutoff, ctx.pose_order, ctx.need_rec)
+            if not ctx.need_rec:
+                grad_reconstruction = None
+        else:
+            reconstruction, rotations, shifts = ctx.saved_tensors
+            grad_reconstruction, grad_rotations, grad_shifts = _ops.project_3d_to_2d_back_ordered(
+                grad_output.contiguous(), reconstruction, rotations, shifts, ctx.interpolation,
+                ctx.oversampling, ctx.fourier_radius_cutoff, ctx.pose_order)
         if shifts is None:
             grad_shifts = None
         return grad_reconstruction, grad_rotations, grad_shifts, None, None, None, None, None
