@@ -129,7 +129,7 @@ def set_pose_order_thresholds(min_volume_bytes: int = 96 << 20, min_poses: int =
 # the projections' size), and the backward pass then forms the pose gradients from them instead of
 # gathering the volume a second time -- and skips the scatter into the volume's gradient altogether
 # when the volume needs none.  Measured on B200, box 512, 4,096 poses of 256 x 256, cubic: forward
-# 6.5 -> 8.9 ms, backward 20.3 -> 15.1 ms (1.0 ms with a fixed volume).
+# 6.5 -> 8.9 ms, backward 20.3 -> 15.1 ms (1.9 ms with a fixed volume).
 SAVE_DERIVATIVES = True
 SAVE_DERIVATIVES_MAX_BYTES = 16 << 30
 
