@@ -485,7 +485,7 @@ def autograd_step_workload(args):
     pad = torch.nn.functional.pad(vol, (b // 2, b // 2) * 3)
     rec = torch.fft.rfftn(torch.fft.fftshift(pad), norm="forward").to(torch.complex64).unsqueeze(0).contiguous()
     del vol, pad
-    rec.requires_grad_(True)
+    rec.requires_grad_(not args.fixed_volume)
     rot = uniform_rotations(STEP["P"], gen, dev).requires_grad_(True)
     shifts = ((torch.rand(1, STEP["P"], 2, generator=gen) * 2 - 1) * STEP["shift"]).to(dev).requires_grad_(True)
     ggen = torch.Generator(device=dev).manual_seed(78 + rank)
@@ -541,11 +541,11 @@ def autograd_step_workload(args):
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "f32", "data": "synthetic",
             "config": {"workload": STEP["name"], "l2": "inputs (539 MB volume, 1.08 GB projections) exceed L2; 256 MiB flush before every step"},
-            "kernels_ms": ({"project_forw_saving_kernel<3,cubic>": f, "project_back_saved_kernel<3,cubic,rot,shift,rec> (+ memsets)": bw,
+            "kernels_ms": ({"project_forw_saving_kernel<3,cubic>": f, ("project_back_saved_kernel<3,cubic,rot,shift> (+ memsets)" if args.fixed_volume else "project_back_saved_kernel<3,cubic,rot,shift,rec> (+ memsets)"): bw,
                             "loss and its gradient (torch elementwise)": ms_per_step - f - bw} if saving else
                            {"project_forw_kernel<3,cubic>": f, "project_back_kernel<3,cubic,rot,shift> (+ memsets)": bw,
                             "loss and its gradient (torch elementwise)": ms_per_step - f - bw}),
-            "saved_derivatives": saving,
+            "saved_derivatives": saving, "fixed_volume": bool(args.fixed_volume),
             "roofline": {"bound": "hbm", "kernel": "project_forw + project_back (op time only)", "achieved": achieved, "peak": peak,
                          "peak_source": peak_kind, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
                          "algorithmic_bytes_per_launch": STEP_BYTES_PER_SLICE * STEP["P"], "launch_ms": op_ms},
@@ -1017,6 +1017,7 @@ def main():
     ap.add_argument("--total-slices", type=int, default=0, help="sharded_backproject: total slices over all ranks (default 200000)")
     ap.add_argument("--no-overlap-tail", action="store_true", help="sharded_backproject: fold and reduce after the last chunk instead of overlapping them with it")
     ap.add_argument("--slab-groups", type=int, default=0, help="sharded_backproject: launches the final stage is cut into (default: the library's 12)")
+    ap.add_argument("--fixed-volume", action="store_true", help="autograd_step: the volume needs no gradient (pose refinement against a fixed reference)")
     ap.add_argument("--no-save-derivatives", action="store_true", help="autograd_step: backward pass that gathers the volume again instead of using derivatives kept by the forward pass")
     ap.add_argument("--skip-sharded", action="store_true", help="default workload: leave the sharded box-400 back-projection out (quick runs)")
     args = ap.parse_args()
