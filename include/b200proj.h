@@ -324,13 +324,23 @@ int b200proj_reduction_rate_probe_streaming(float* target, size_t target_bytes, 
 /* ---- forward projection that keeps what its backward pass needs ---------------------------
  * No counterpart in the reference (its backward gathers the volume a second time for the pose
  * gradients).  _forw_saving writes the projections [B,P,N,Nh] and, besides, the derivatives of every
- * pixel inside the cutoff with respect to its sample position (c, r, d), shift phase applied:
- * derivatives = 3 planes of [B,P,N,Nh] complex (3 * B*P*N*Nh*8 bytes; pixels outside the cutoff are
- * left unwritten and are never read).  _back_saved is the backward pass from those: grad_rot from
+ * pixel inside the cutoff with respect to its sample position (c, r[, d]), shift phase applied:
+ * derivatives = dim planes of [B,P,N,Nh] complex (dim * B*P*N*Nh*8 bytes, dim = 2 for the 2D pair and 3
+ * for the 3D pair; pixels outside the cutoff are left unwritten and are never read).  _back_saved is the backward pass from those: grad_rot from
  * grad_proj and the derivatives, grad_shifts from grad_proj and the saved projections `out`, and --
- * when grad_rec is not NULL -- the same scatter of grad_proj into grad_rec [B,R,R,Rh] as
- * b200proj_project_3d_to_2d_back (all outputs zero-filled here; NULL = not needed).  Same values as
+ * when grad_rec is not NULL -- the same scatter of grad_proj into grad_rec [B,(R,)R,Rh] as
+ * b200proj_project_{2d,3d_to_2d}_back (all outputs zero-filled here; NULL = not needed).  Same values as
  * the plain pair of entry points up to rounding (~1e-7); fp32 only. */
+int b200proj_project_2d_forw_saving(const float* rec, int64_t B, int64_t R, const float* rot,
+                                    int64_t B_rot, const float* shifts, int64_t B_shift, int64_t P,
+                                    int64_t N, int interpolation, double oversampling,
+                                    double fourier_radius_cutoff, float* out, float* derivatives,
+                                    void* stream);
+int b200proj_project_2d_back_saved(const float* grad_proj, const float* out, const float* derivatives,
+                                   int64_t B, int64_t R, const float* rot, int64_t B_rot,
+                                   const float* shifts, int64_t B_shift, int64_t P, int64_t N,
+                                   int interpolation, double oversampling, double fourier_radius_cutoff,
+                                   float* grad_rec, float* grad_rot, float* grad_shifts, void* stream);
 int b200proj_project_3d_to_2d_forw_saving(const float* rec, int64_t B, int64_t R, const float* rot,
                                           int64_t B_rot, const float* shifts, int64_t B_shift, int64_t P,
                                           int64_t N, int interpolation, double oversampling,

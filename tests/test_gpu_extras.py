@@ -87,15 +87,17 @@ def test_streaming_reduction_rate_probe_issues_every_reduction_inside_its_window
 
 @pytest.mark.parametrize("interp,fixed_volume", [("cubic", False), ("cubic", True), ("linear", True)])
 @pytest.mark.parametrize("with_shifts", [True, False])
-def test_saved_derivatives_give_the_gradients_of_the_plain_backward(tp, interp, fixed_volume, with_shifts):
+@pytest.mark.parametrize("dim,os_", [(3, 2.0), (3, 1.0), (2, 2.0), (2, 1.0)])
+def test_saved_derivatives_give_the_gradients_of_the_plain_backward(tp, interp, fixed_volume, with_shifts, dim, os_):
     """With rotation gradients wanted, the forward pass keeps its pixels' derivatives and the backward
     pass gathers nothing (and skips the volume's gradient when the volume is fixed).  Outputs and all
     gradients must equal those of the plain pair of operators (set_save_derivatives(False)) to
     rounding, and the CPU oracle within the gradient tolerance."""
     from oracle import port
-    case = Case("saved", 3, interp, 2, 7, 16, 32, 2.0, 6.5, 1, 2 if with_shifts else 0, shift_range=3.0, seed=91)
+    case = Case("saved", dim, interp, 2, 7, 16, 32, os_, 6.5, 1, 2 if with_shifts else 0, shift_range=3.0, seed=91)
     t = make_inputs(case)
-    kw = dict(output_shape=(16, 16), interpolation=interp, oversampling=2.0, fourier_radius_cutoff=6.5)
+    kw = dict(output_shape=(16, 16), interpolation=interp, oversampling=os_, fourier_radius_cutoff=6.5)
+    project = tp.project_3d_to_2d_forw if dim == 3 else tp.project_2d_forw
     g = t["proj"].cuda()
     results = {}
     for saving in (True, False):
@@ -104,7 +106,7 @@ def test_saved_derivatives_give_the_gradients_of_the_plain_backward(tp, interp, 
             rec = t["rec"].cuda().requires_grad_(not fixed_volume)
             rot = t["rot"].cuda().requires_grad_(True)
             sh = t["shifts"].cuda().requires_grad_(True) if with_shifts else None
-            out = tp.project_3d_to_2d_forw(rec, rot, sh, **kw)
+            out = project(rec, rot, sh, **kw)
             assert (len(out.grad_fn.saved_tensors) == 5) == saving
             torch.view_as_real(out).backward(torch.view_as_real(g))
             results[saving] = (out.detach(), rec.grad, rot.grad, sh.grad if with_shifts else None)
@@ -115,8 +117,9 @@ def test_saved_derivatives_give_the_gradients_of_the_plain_backward(tp, interp, 
         if a is not None:
             assert rel_err(a, b) <= 2e-6, rel_err(a, b)
     assert (results[True][1] is None) == fixed_volume
-    want = port.project_3d_to_2d_back(t["proj"], t["rec"], t["rot"], t["shifts"] if with_shifts else None, interp, 2.0, 6.5,
-                                      need_rot_grad=True, need_shift_grad=with_shifts)
+    back = port.project_3d_to_2d_back if dim == 3 else port.project_2d_back
+    want = back(t["proj"], t["rec"], t["rot"], t["shifts"] if with_shifts else None, interp, os_, 6.5,
+                need_rot_grad=True, need_shift_grad=with_shifts)
     if not fixed_volume:
         assert rel_err(results[True][1], want[0]) <= TOL_ATOMIC
     assert rel_err(results[True][2], want[1]) <= TOL_ATOMIC

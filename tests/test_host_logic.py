@@ -150,6 +150,11 @@ def test_meta_implementations_give_the_output_shapes():
     gr, grot, gsh = ops.project_3d_to_2d_back_saved(g, out, der, rec, rot, sh, "cubic", 2.0, None, order, True)
     assert gr.shape == rec.shape and gr.dtype == torch.complex64 and grot.shape == rot.shape and gsh.shape == (0,)
     assert ops.project_3d_to_2d_back_saved(g, out, der, rec, rot, sh, "cubic", 2.0, None, None, False)[0].shape == (0,)
+    rec2, rot2 = torch.empty(2, 16, 9, dtype=torch.complex64, **m), torch.empty(1, 5, 2, 2, **m).requires_grad_(True)
+    out2, der2 = ops.project_2d_forw_saving(rec2, rot2, sh, [8, 8], "linear", 2.0, None)
+    assert out2.shape == (2, 5, 8, 5) and der2.shape == (2, 2, 5, 8, 5)
+    gr2, grot2, _ = ops.project_2d_back_saved(g, out2, der2, rec2, rot2, sh, "linear", 2.0, None, True)
+    assert gr2.shape == rec2.shape and grot2.shape == rot2.shape
 
 
 @pytest.mark.parametrize("P,world", [(10, 1), (10, 2), (10, 3), (7, 8), (0, 4), (200000, 8)])

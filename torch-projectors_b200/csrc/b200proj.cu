@@ -215,17 +215,66 @@ void launch_project_back(const Launch& L, cudaStream_t s, const C2<Real>* gp, co
 #undef B200PROJ_PB
 }
 
-template <bool CUBIC, bool NEED_REC>
+template <int DIM, bool CUBIC, bool NEED_REC>
 void launch_project_back_saved(const Launch& L, cudaStream_t s, const float2* gp, const float2* out, const float2* derivs,
                                const float* rot, const float* shifts, float2* grad_rec, float* grad_rot, float* grad_shift) {
     const bool nr = grad_rot != nullptr, ns = grad_shift != nullptr;
 #define B200PROJ_PBS(NR, NS) \
-    project_back_saved_kernel<3, CUBIC, NR, NS, NEED_REC><<<L.grid, kBlockThreads, 0, s>>>(gp, out, derivs, rot, shifts, grad_rec, grad_rot, grad_shift, L.g)
+    project_back_saved_kernel<DIM, CUBIC, NR, NS, NEED_REC><<<L.grid, kBlockThreads, 0, s>>>(gp, out, derivs, rot, shifts, grad_rec, grad_rot, grad_shift, L.g)
     if (nr && ns) B200PROJ_PBS(true, true);
     else if (nr) B200PROJ_PBS(true, false);
     else if (ns) B200PROJ_PBS(false, true);
     else B200PROJ_PBS(false, false);
 #undef B200PROJ_PBS
+}
+
+// Forward projection that also writes the pixels' derivatives, and the backward pass from them (fp32).
+template <int DIM>
+int project_forw_saving(const float* rec, int64_t B, int64_t R, const float* rot, int64_t B_rot, const float* shifts,
+                        int64_t B_shift, int64_t P, int64_t N, int interpolation, double os, double cutoff,
+                        float* out, float* derivatives, const int32_t* pose_order, void* stream) {
+    Launch L;
+    if (int rc = prepare(L, DIM, B, R, B_rot, rot, shifts, B_shift, P, N, interpolation, os, cutoff)) return rc;
+    if (rec == nullptr || out == nullptr || derivatives == nullptr) return fail(B200PROJ_ERR_ARGUMENT, "reconstruction / output / derivatives pointer is NULL");
+    L.g.order = pose_order;
+    if (P == 0) return B200PROJ_OK;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (interpolation == B200PROJ_CUBIC)
+        project_forw_saving_kernel<DIM, true><<<L.grid, kBlockThreads, 0, s>>>((const float2*)rec, rot, shifts, (float2*)out, (float2*)derivatives, L.g);
+    else
+        project_forw_saving_kernel<DIM, false><<<L.grid, kBlockThreads, 0, s>>>((const float2*)rec, rot, shifts, (float2*)out, (float2*)derivatives, L.g);
+    return check_launch("project_forw (saving derivatives) launch");
+}
+
+template <int DIM>
+int project_back_saved(const float* grad_proj, const float* out, const float* derivatives, int64_t B, int64_t R,
+                       const float* rot, int64_t B_rot, const float* shifts, int64_t B_shift, int64_t P, int64_t N,
+                       int interpolation, double os, double cutoff, float* grad_rec, float* grad_rot, float* grad_shifts,
+                       const int32_t* pose_order, void* stream) {
+    Launch L;
+    if (int rc = prepare(L, DIM, B, R, B_rot, rot, shifts, B_shift, P, N, interpolation, os, cutoff)) return rc;
+    L.g.order = pose_order;
+    if (grad_proj == nullptr) return fail(B200PROJ_ERR_ARGUMENT, "grad_projections pointer is NULL");
+    if (grad_rot != nullptr && derivatives == nullptr) return fail(B200PROJ_ERR_ARGUMENT, "grad_rotations requested but no saved derivatives given");
+    if (grad_shifts != nullptr && (shifts == nullptr || out == nullptr))
+        return fail(B200PROJ_ERR_ARGUMENT, "grad_shifts requested but no shifts / saved projections given");
+    if (grad_rec == nullptr && grad_rot == nullptr && grad_shifts == nullptr) return B200PROJ_OK;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (int rc = zero_async(grad_rec, L.rec_count * sizeof(float2), s)) return rc;
+    if (int rc = zero_async(grad_rot, (size_t)B_rot * P * DIM * DIM * sizeof(float), s)) return rc;
+    if (int rc = zero_async(grad_shifts, (size_t)(shifts ? B_shift : 0) * P * 2 * sizeof(float), s)) return rc;
+    if (P == 0) return B200PROJ_OK;
+    const float2* gp = (const float2*)grad_proj;
+    const float2* o = (const float2*)out;
+    const float2* d = (const float2*)derivatives;
+    const bool cubic = interpolation == B200PROJ_CUBIC;
+    if (grad_rec != nullptr) {
+        if (cubic) launch_project_back_saved<DIM, true, true>(L, s, gp, o, d, rot, shifts, (float2*)grad_rec, grad_rot, grad_shifts);
+        else launch_project_back_saved<DIM, false, true>(L, s, gp, o, d, rot, shifts, (float2*)grad_rec, grad_rot, grad_shifts);
+    } else {
+        launch_project_back_saved<DIM, false, false>(L, s, gp, o, d, rot, shifts, nullptr, grad_rot, grad_shifts);
+    }
+    return check_launch("project_back (saved derivatives) launch");
 }
 
 template <int DIM, typename Real>
@@ -558,53 +607,32 @@ int b200proj_project_3d_to_2d_back(const float* grad_proj, const float* rec, int
     return project_back<3>(grad_proj, rec, B, R, rot, B_rot, shifts, B_shift, P, N, interpolation, oversampling, cutoff, grad_rec, grad_rot, grad_shifts, pose_order, stream);
 }
 
+int b200proj_project_2d_forw_saving(const float* rec, int64_t B, int64_t R, const float* rot,
+                                    int64_t B_rot, const float* shifts, int64_t B_shift, int64_t P,
+                                    int64_t N, int interpolation, double oversampling, double cutoff,
+                                    float* out, float* derivatives, void* stream) {
+    return project_forw_saving<2>(rec, B, R, rot, B_rot, shifts, B_shift, P, N, interpolation, oversampling, cutoff, out, derivatives, nullptr, stream);
+}
 int b200proj_project_3d_to_2d_forw_saving(const float* rec, int64_t B, int64_t R, const float* rot,
                                           int64_t B_rot, const float* shifts, int64_t B_shift, int64_t P,
                                           int64_t N, int interpolation, double oversampling, double cutoff,
                                           float* out, float* derivatives, const int32_t* pose_order, void* stream) {
-    Launch L;
-    if (int rc = prepare(L, 3, B, R, B_rot, rot, shifts, B_shift, P, N, interpolation, oversampling, cutoff)) return rc;
-    if (rec == nullptr || out == nullptr || derivatives == nullptr) return fail(B200PROJ_ERR_ARGUMENT, "reconstruction / output / derivatives pointer is NULL");
-    L.g.order = pose_order;
-    if (P == 0) return B200PROJ_OK;
-    cudaStream_t s = (cudaStream_t)stream;
-    if (interpolation == B200PROJ_CUBIC)
-        project_forw_saving_kernel<3, true><<<L.grid, kBlockThreads, 0, s>>>((const float2*)rec, rot, shifts, (float2*)out, (float2*)derivatives, L.g);
-    else
-        project_forw_saving_kernel<3, false><<<L.grid, kBlockThreads, 0, s>>>((const float2*)rec, rot, shifts, (float2*)out, (float2*)derivatives, L.g);
-    return check_launch("project_forw (saving derivatives) launch");
+    return project_forw_saving<3>(rec, B, R, rot, B_rot, shifts, B_shift, P, N, interpolation, oversampling, cutoff, out, derivatives, pose_order, stream);
 }
-
+int b200proj_project_2d_back_saved(const float* grad_proj, const float* out, const float* derivatives,
+                                   int64_t B, int64_t R, const float* rot, int64_t B_rot,
+                                   const float* shifts, int64_t B_shift, int64_t P, int64_t N,
+                                   int interpolation, double oversampling, double cutoff,
+                                   float* grad_rec, float* grad_rot, float* grad_shifts, void* stream) {
+    return project_back_saved<2>(grad_proj, out, derivatives, B, R, rot, B_rot, shifts, B_shift, P, N, interpolation, oversampling, cutoff, grad_rec, grad_rot, grad_shifts, nullptr, stream);
+}
 int b200proj_project_3d_to_2d_back_saved(const float* grad_proj, const float* out, const float* derivatives,
                                          int64_t B, int64_t R, const float* rot, int64_t B_rot,
                                          const float* shifts, int64_t B_shift, int64_t P, int64_t N,
                                          int interpolation, double oversampling, double cutoff,
                                          float* grad_rec, float* grad_rot, float* grad_shifts,
                                          const int32_t* pose_order, void* stream) {
-    Launch L;
-    if (int rc = prepare(L, 3, B, R, B_rot, rot, shifts, B_shift, P, N, interpolation, oversampling, cutoff)) return rc;
-    L.g.order = pose_order;
-    if (grad_proj == nullptr) return fail(B200PROJ_ERR_ARGUMENT, "grad_projections pointer is NULL");
-    if (grad_rot != nullptr && derivatives == nullptr) return fail(B200PROJ_ERR_ARGUMENT, "grad_rotations requested but no saved derivatives given");
-    if (grad_shifts != nullptr && (shifts == nullptr || out == nullptr))
-        return fail(B200PROJ_ERR_ARGUMENT, "grad_shifts requested but no shifts / saved projections given");
-    if (grad_rec == nullptr && grad_rot == nullptr && grad_shifts == nullptr) return B200PROJ_OK;
-    cudaStream_t s = (cudaStream_t)stream;
-    if (int rc = zero_async(grad_rec, L.rec_count * sizeof(float2), s)) return rc;
-    if (int rc = zero_async(grad_rot, (size_t)B_rot * P * 9 * sizeof(float), s)) return rc;
-    if (int rc = zero_async(grad_shifts, (size_t)(shifts ? B_shift : 0) * P * 2 * sizeof(float), s)) return rc;
-    if (P == 0) return B200PROJ_OK;
-    const float2* gp = (const float2*)grad_proj;
-    const float2* o = (const float2*)out;
-    const float2* d = (const float2*)derivatives;
-    const bool cubic = interpolation == B200PROJ_CUBIC;
-    if (grad_rec != nullptr) {
-        if (cubic) launch_project_back_saved<true, true>(L, s, gp, o, d, rot, shifts, (float2*)grad_rec, grad_rot, grad_shifts);
-        else launch_project_back_saved<false, true>(L, s, gp, o, d, rot, shifts, (float2*)grad_rec, grad_rot, grad_shifts);
-    } else {
-        launch_project_back_saved<false, false>(L, s, gp, o, d, rot, shifts, nullptr, grad_rot, grad_shifts);
-    }
-    return check_launch("project_back (saved derivatives) launch");
+    return project_back_saved<3>(grad_proj, out, derivatives, B, R, rot, B_rot, shifts, B_shift, P, N, interpolation, oversampling, cutoff, grad_rec, grad_rot, grad_shifts, pose_order, stream);
 }
 
 int b200proj_backproject_2d_forw(const float* proj, const float* weights, int64_t B, int64_t R,

@@ -235,50 +235,53 @@ std::tuple<Tensor, Tensor, Tensor> project_back(int dim, const Tensor& grad_proj
 // ---- forward projection that keeps the pixels' derivatives, and its backward pass --------------------
 // (additions; complex64 only: the step of an optimisation over poses needs no second gather of the
 // volume in its backward pass, and none of the volume's gradient when the volume is fixed)
-std::tuple<Tensor, Tensor> project_3d_to_2d_forw_saving(const Tensor& reconstruction, const Tensor& rotations, const OptTensor& shifts,
-                                                        at::IntArrayRef output_shape, std::string interpolation, double oversampling,
-                                                        c10::optional<double> cutoff, const OptTensor& pose_order) {
+std::tuple<Tensor, Tensor> project_forw_saving(int dim, const Tensor& reconstruction, const Tensor& rotations, const OptTensor& shifts,
+                                               at::IntArrayRef output_shape, const std::string& interpolation, double oversampling,
+                                               const c10::optional<double>& cutoff, const OptTensor& pose_order) {
     TORCH_CHECK(reconstruction.is_cuda(), "Input reconstruction must be on CUDA device");
     TORCH_CHECK(reconstruction.scalar_type() == at::kComplexFloat, "the derivative-saving projection takes complex64 volumes");
     const int interp = interp_code(interpolation);
-    check_rec(3, reconstruction);
+    check_rec(dim, reconstruction);
     const int64_t B = reconstruction.size(0), R = reconstruction.size(-2);
-    const Poses p = check_poses(3, "reconstruction", B, rotations, shifts, reconstruction);
+    const Poses p = check_poses(dim, "reconstruction", B, rotations, shifts, reconstruction);
     TORCH_CHECK(output_shape.size() >= 1, "output_shape must have at least one element");
     const int64_t N = output_shape[0];
     TORCH_CHECK(N >= 2 && N % 2 == 0, "Output boxsize ", N, " must be even");
     const Tensor rec = reconstruction.contiguous();
     c10::cuda::CUDAGuard guard(rec.device());
     Tensor out = at::empty({B, p.P, N, N / 2 + 1}, rec.options());
-    Tensor derivs = at::empty({3, B, p.P, N, N / 2 + 1}, rec.options());
+    Tensor derivs = at::empty({dim, B, p.P, N, N / 2 + 1}, rec.options());
     if (out.numel() == 0) return std::make_tuple(out, derivs);
-    Tensor order = resolve_order(3, rec, B, p, pose_order);
-    status(b200proj_project_3d_to_2d_forw_saving(cptr<float>(rec), B, R, cptr<float>(p.rot), p.B_rot, cptr<float>(p.shifts), p.B_shift, p.P, N, interp,
-                                                 oversampling, cutoff_of(cutoff, N), mptr<float>(out), mptr<float>(derivs), cptr<int32_t>(order),
-                                                 current_stream(rec)),
-           "project_3d_to_2d_forw_saving");
+    Tensor order = resolve_order(dim, rec, B, p, pose_order);
+    const double cut = cutoff_of(cutoff, N);
+    const int rc = dim == 2
+        ? b200proj_project_2d_forw_saving(cptr<float>(rec), B, R, cptr<float>(p.rot), p.B_rot, cptr<float>(p.shifts), p.B_shift, p.P, N, interp,
+                                          oversampling, cut, mptr<float>(out), mptr<float>(derivs), current_stream(rec))
+        : b200proj_project_3d_to_2d_forw_saving(cptr<float>(rec), B, R, cptr<float>(p.rot), p.B_rot, cptr<float>(p.shifts), p.B_shift, p.P, N, interp,
+                                                oversampling, cut, mptr<float>(out), mptr<float>(derivs), cptr<int32_t>(order), current_stream(rec));
+    status(rc, dim == 2 ? "project_2d_forw_saving" : "project_3d_to_2d_forw_saving");
     return std::make_tuple(out, derivs);
 }
 
-std::tuple<Tensor, Tensor, Tensor> project_3d_to_2d_back_saved(const Tensor& grad_projections, const Tensor& projections, const Tensor& derivatives,
-                                                               const Tensor& reconstruction, const Tensor& rotations, const OptTensor& shifts,
-                                                               std::string interpolation, double oversampling, c10::optional<double> cutoff,
-                                                               const OptTensor& pose_order, bool need_rec_grad) {
+std::tuple<Tensor, Tensor, Tensor> project_back_saved(int dim, const Tensor& grad_projections, const Tensor& projections, const Tensor& derivatives,
+                                                      const Tensor& reconstruction, const Tensor& rotations, const OptTensor& shifts,
+                                                      const std::string& interpolation, double oversampling, const c10::optional<double>& cutoff,
+                                                      const OptTensor& pose_order, bool need_rec_grad) {
     TORCH_CHECK(grad_projections.is_cuda() && reconstruction.is_cuda(), "Inputs must be on CUDA device");
     TORCH_CHECK(grad_projections.scalar_type() == at::kComplexFloat && reconstruction.scalar_type() == at::kComplexFloat,
                 "the derivative-saving projection takes complex64 tensors");
     const int interp = interp_code(interpolation);
     TORCH_CHECK(grad_projections.dim() == 4, "Projections must be a 4D tensor (B, P, H, W/2+1)");
-    check_rec(3, reconstruction);
+    check_rec(dim, reconstruction);
     const int64_t B = grad_projections.size(0), P_g = grad_projections.size(1), N = grad_projections.size(2), Nh = grad_projections.size(3);
     TORCH_CHECK(N % 2 == 0 && Nh == N / 2 + 1, "grad_projections must be rfft-shaped with an even box");
     TORCH_CHECK(reconstruction.size(0) == B, "Batch size of grad_projections must match reconstruction");
-    const Poses p = check_poses(3, "reconstruction", B, rotations, shifts, reconstruction);
+    const Poses p = check_poses(dim, "reconstruction", B, rotations, shifts, reconstruction);
     TORCH_CHECK(p.P == P_g, "Number of poses in rotations must match grad_projections");
     TORCH_CHECK(projections.sizes() == grad_projections.sizes() && projections.scalar_type() == at::kComplexFloat && projections.is_cuda(),
                 "saved projections must match grad_projections");
-    TORCH_CHECK(derivatives.dim() == 5 && derivatives.size(0) == 3 && derivatives.sizes().slice(1) == grad_projections.sizes() &&
-                derivatives.scalar_type() == at::kComplexFloat && derivatives.is_cuda(), "saved derivatives must be (3, B, P, H, W/2+1) complex64");
+    TORCH_CHECK(derivatives.dim() == 5 && derivatives.size(0) == dim && derivatives.sizes().slice(1) == grad_projections.sizes() &&
+                derivatives.scalar_type() == at::kComplexFloat && derivatives.is_cuda(), "saved derivatives must be (dim, B, P, H, W/2+1) complex64");
     const bool need_rot = rotations.requires_grad();
     const bool need_shift = p.shifts.defined() && shifts->requires_grad();
     const Tensor gp = grad_projections.contiguous();
@@ -292,12 +295,16 @@ std::tuple<Tensor, Tensor, Tensor> project_3d_to_2d_back_saved(const Tensor& gra
     if (p.P == 0 || gp.numel() == 0) {
         if (need_rec_grad) grad_rec.zero_();
     } else {
-        Tensor order = resolve_order(3, reconstruction, B, p, pose_order);
-        status(b200proj_project_3d_to_2d_back_saved(cptr<float>(gp), cptr<float>(out), cptr<float>(der), B, R, cptr<float>(p.rot), p.B_rot,
-                                                    cptr<float>(p.shifts), p.B_shift, p.P, N, interp, oversampling, cutoff_of(cutoff, N),
-                                                    mptr<float>(grad_rec), mptr<float>(grad_rot), mptr<float>(grad_sh), cptr<int32_t>(order),
-                                                    current_stream(gp)),
-               "project_3d_to_2d_back_saved");
+        Tensor order = resolve_order(dim, reconstruction, B, p, pose_order);
+        const double cut = cutoff_of(cutoff, N);
+        const int rc = dim == 2
+            ? b200proj_project_2d_back_saved(cptr<float>(gp), cptr<float>(out), cptr<float>(der), B, R, cptr<float>(p.rot), p.B_rot, cptr<float>(p.shifts),
+                                             p.B_shift, p.P, N, interp, oversampling, cut, mptr<float>(grad_rec), mptr<float>(grad_rot), mptr<float>(grad_sh),
+                                             current_stream(gp))
+            : b200proj_project_3d_to_2d_back_saved(cptr<float>(gp), cptr<float>(out), cptr<float>(der), B, R, cptr<float>(p.rot), p.B_rot, cptr<float>(p.shifts),
+                                                   p.B_shift, p.P, N, interp, oversampling, cut, mptr<float>(grad_rec), mptr<float>(grad_rot), mptr<float>(grad_sh),
+                                                   cptr<int32_t>(order), current_stream(gp));
+        status(rc, dim == 2 ? "project_2d_back_saved" : "project_3d_to_2d_back_saved");
     }
     const at::ScalarType rd = p.rot.scalar_type();
     return std::make_tuple(need_rec_grad ? grad_rec : empty_real0(gp, rd), need_rot ? grad_rot : empty_real0(gp, rd),
@@ -457,6 +464,21 @@ std::tuple<Tensor, Tensor, Tensor, Tensor> backproject_2d_to_3d_back_ordered(con
     return backproject_back(3, gd, gw, proj, w, rot, sh, interp, os, cut, order);
 }
 
+std::tuple<Tensor, Tensor> project_2d_forw_saving(const Tensor& rec, const Tensor& rot, const OptTensor& sh, at::IntArrayRef shape, std::string interp, double os, Cut cut) {
+    return project_forw_saving(2, rec, rot, sh, shape, interp, os, cut, c10::nullopt);
+}
+std::tuple<Tensor, Tensor> project_3d_to_2d_forw_saving(const Tensor& rec, const Tensor& rot, const OptTensor& sh, at::IntArrayRef shape, std::string interp, double os, Cut cut, const OptTensor& order) {
+    return project_forw_saving(3, rec, rot, sh, shape, interp, os, cut, order);
+}
+std::tuple<Tensor, Tensor, Tensor> project_2d_back_saved(const Tensor& g, const Tensor& proj, const Tensor& der, const Tensor& rec, const Tensor& rot, const OptTensor& sh,
+                                                         std::string interp, double os, Cut cut, bool need_rec) {
+    return project_back_saved(2, g, proj, der, rec, rot, sh, interp, os, cut, c10::nullopt, need_rec);
+}
+std::tuple<Tensor, Tensor, Tensor> project_3d_to_2d_back_saved(const Tensor& g, const Tensor& proj, const Tensor& der, const Tensor& rec, const Tensor& rot, const OptTensor& sh,
+                                                               std::string interp, double os, Cut cut, const OptTensor& order, bool need_rec) {
+    return project_back_saved(3, g, proj, der, rec, rot, sh, interp, os, cut, order, need_rec);
+}
+
 void set_pose_order_thresholds(int64_t min_bytes, int64_t min_poses) {
     g_order_min_bytes.store(min_bytes);
     g_order_min_poses.store(min_poses);
@@ -500,6 +522,16 @@ std::tuple<Tensor, Tensor> meta_project_forw_saving(const Tensor& rec, const Ten
     Tensor out = meta_project_forw(rec, rot, sh, shape, i, os, c);
     return std::make_tuple(out, at::empty({3, out.size(0), out.size(1), out.size(2), out.size(3)}, out.options()));
 }
+std::tuple<Tensor, Tensor> meta_project_2d_forw_saving(const Tensor& rec, const Tensor& rot, const OptTensor& sh, at::IntArrayRef shape, std::string i, double os, Cut c) {
+    Tensor out = meta_project_forw(rec, rot, sh, shape, i, os, c);
+    return std::make_tuple(out, at::empty({2, out.size(0), out.size(1), out.size(2), out.size(3)}, out.options()));
+}
+std::tuple<Tensor, Tensor, Tensor> meta_project_2d_back_saved(const Tensor& g, const Tensor&, const Tensor&, const Tensor& rec, const Tensor& rot, const OptTensor& sh,
+                                                              std::string, double, Cut, bool need_rec_grad) {
+    const bool ns = sh.has_value() && sh->defined() && sh->requires_grad();
+    return std::make_tuple(need_rec_grad ? at::empty(rec.sizes(), g.options()) : at::empty({0}, rot.options()),
+                           rot.requires_grad() ? at::empty_like(rot) : at::empty({0}, rot.options()), ns ? at::empty_like(*sh) : at::empty({0}, rot.options()));
+}
 std::tuple<Tensor, Tensor, Tensor> meta_project_back_saved(const Tensor& g, const Tensor&, const Tensor&, const Tensor& rec, const Tensor& rot, const OptTensor& sh,
                                                            std::string, double, Cut, const OptTensor&, bool need_rec_grad) {
     const bool ns = sh.has_value() && sh->defined() && sh->requires_grad();
@@ -531,7 +563,9 @@ TORCH_LIBRARY(torch_projectors_b200, m) {
     m.def("backproject_2d_to_3d_back_ordered(Tensor grad_data_rec, Tensor? grad_weight_rec, Tensor projections, Tensor? weights, Tensor rotations, Tensor? shifts, str interpolation, float oversampling, float? fourier_radius_cutoff, Tensor? pose_order) -> (Tensor, Tensor, Tensor, Tensor)");
     m.def("plane_locality_order(Tensor rotations, int batch) -> Tensor");
     // additions: forward projection that also returns the pixels' derivatives with respect to their sample positions
-    // [3, B, P, H, W/2+1], and the backward pass that uses them instead of gathering the volume again
+    // [dim, B, P, H, W/2+1], and the backward pass that uses them instead of gathering the volume again
+    m.def("project_2d_forw_saving(Tensor reconstruction, Tensor rotations, Tensor? shifts, int[] output_shape, str interpolation, float oversampling, float? fourier_radius_cutoff) -> (Tensor, Tensor)");
+    m.def("project_2d_back_saved(Tensor grad_projections, Tensor projections, Tensor derivatives, Tensor reconstruction, Tensor rotations, Tensor? shifts, str interpolation, float oversampling, float? fourier_radius_cutoff, bool need_reconstruction_grad) -> (Tensor, Tensor, Tensor)");
     m.def("project_3d_to_2d_forw_saving(Tensor reconstruction, Tensor rotations, Tensor? shifts, int[] output_shape, str interpolation, float oversampling, float? fourier_radius_cutoff, Tensor? pose_order) -> (Tensor, Tensor)");
     m.def("project_3d_to_2d_back_saved(Tensor grad_projections, Tensor projections, Tensor derivatives, Tensor reconstruction, Tensor rotations, Tensor? shifts, str interpolation, float oversampling, float? fourier_radius_cutoff, Tensor? pose_order, bool need_reconstruction_grad) -> (Tensor, Tensor, Tensor)");
     m.def("_set_pose_order_thresholds(int min_volume_bytes, int min_poses) -> ()", &set_pose_order_thresholds);
@@ -551,6 +585,8 @@ TORCH_LIBRARY_IMPL(torch_projectors_b200, CUDA, m) {
     m.impl("project_3d_to_2d_back_ordered", &project_3d_to_2d_back_ordered);
     m.impl("backproject_2d_to_3d_back_ordered", &backproject_2d_to_3d_back_ordered);
     m.impl("plane_locality_order", &plane_locality_order);
+    m.impl("project_2d_forw_saving", &project_2d_forw_saving);
+    m.impl("project_2d_back_saved", &project_2d_back_saved);
     m.impl("project_3d_to_2d_forw_saving", &project_3d_to_2d_forw_saving);
     m.impl("project_3d_to_2d_back_saved", &project_3d_to_2d_back_saved);
 }
@@ -568,6 +604,8 @@ TORCH_LIBRARY_IMPL(torch_projectors_b200, Meta, m) {
     m.impl("backproject_2d_to_3d_back", &meta_backproject_back);
     m.impl("backproject_2d_to_3d_back_ordered", &meta_backproject_back_ordered);
     m.impl("plane_locality_order", &meta_plane_locality_order);
+    m.impl("project_2d_forw_saving", &meta_project_2d_forw_saving);
+    m.impl("project_2d_back_saved", &meta_project_2d_back_saved);
     m.impl("project_3d_to_2d_forw_saving", &meta_project_forw_saving);
     m.impl("project_3d_to_2d_back_saved", &meta_project_back_saved);
 }

@@ -44,6 +44,8 @@ SIGNATURES["b200proj_backproject_2d_to_3d_accumulate"] = [_ptr, _ptr] + _COMMON 
 SIGNATURES["b200proj_accumulator_fold"] = [_ptr, _i64, _i64, _ptr, _ptr, _int, _ptr]
 SIGNATURES["b200proj_accumulator_fold_range"] = [_ptr, _i64, _i64, _ptr, _ptr, _int, _ptr]
 SIGNATURES["b200proj_accumulator_fold_normalized"] = [_ptr, _i64, _i64, _dbl, _ptr, _ptr]
+SIGNATURES["b200proj_project_2d_forw_saving"] = [_ptr] + _COMMON + [_ptr, _ptr, _ptr]
+SIGNATURES["b200proj_project_2d_back_saved"] = [_ptr, _ptr, _ptr] + _COMMON + [_ptr, _ptr, _ptr, _ptr]
 SIGNATURES["b200proj_project_3d_to_2d_forw_saving"] = [_ptr] + _COMMON + [_ptr, _ptr, _ptr, _ptr]
 SIGNATURES["b200proj_project_3d_to_2d_back_saved"] = [_ptr, _ptr, _ptr] + _COMMON + [_ptr, _ptr, _ptr, _ptr, _ptr]
 SIGNATURES["b200proj_project_3d_to_2d_forw_packed"] = [_ptr] + _COMMON + [_ptr, _ptr, _i64, _ptr, _ptr]

@@ -135,9 +135,10 @@ SAVE_DERIVATIVES_MAX_BYTES = 16 << 30
 
 
 def set_save_derivatives(enabled: bool = True, max_bytes: int = 16 << 30) -> None:
-    """Whether ``project_3d_to_2d_forw`` keeps its pixels' derivatives for the backward pass when the
-    rotations require gradients (complex64, cubic interpolation -- or any interpolation when the
-    volume needs no gradient), and up to which size of that extra tensor (3 x the projections)."""
+    """Whether ``project_2d_forw`` / ``project_3d_to_2d_forw`` keep their pixels' derivatives for the
+    backward pass when the rotations require gradients (complex64, cubic interpolation -- or any
+    interpolation when the reconstruction needs no gradient), and up to which size of that extra tensor
+    (2 or 3 x the projections)."""
     global SAVE_DERIVATIVES, SAVE_DERIVATIVES_MAX_BYTES
     SAVE_DERIVATIVES, SAVE_DERIVATIVES_MAX_BYTES = bool(enabled), int(max_bytes)
 
@@ -549,14 +550,31 @@ def _canon_project(rec_rank: int, reconstruction, rotations, shifts):
     return reconstruction, rotations, shifts
 
 
+def _save_derivatives(dim, reconstruction, rotations, output_shape, interpolation, need_rec, need_rot) -> bool:
+    """Whether a projection's forward pass keeps its pixels' derivatives for the backward pass."""
+    if not (SAVE_DERIVATIVES and need_rot and reconstruction.is_cuda and reconstruction.dtype == torch.complex64
+            and rotations.dtype == torch.float32 and (interpolation == "cubic" or not need_rec)):
+        return False
+    N = int(output_shape[0])
+    return 8 * dim * reconstruction.size(0) * rotations.size(1) * N * (N // 2 + 1) <= SAVE_DERIVATIVES_MAX_BYTES
+
+
 class _Project2D(torch.autograd.Function):
     @staticmethod
     def forward(ctx, reconstruction, rotations, shifts, output_shape, interpolation, oversampling,
                 fourier_radius_cutoff):
         reconstruction, rotations, shifts = _canon_project(2, reconstruction, rotations, shifts)
-        projection = _ops.project_2d_forw(reconstruction, rotations, shifts, output_shape, interpolation,
-                                          oversampling, fourier_radius_cutoff)
-        ctx.save_for_backward(reconstruction, rotations, shifts)
+        need_rec = ctx.needs_input_grad[0]
+        ctx.saving = _save_derivatives(2, reconstruction, rotations, output_shape, interpolation, need_rec, ctx.needs_input_grad[1])
+        ctx.need_rec = need_rec
+        if ctx.saving:
+            projection, derivatives = _ops.project_2d_forw_saving(reconstruction, rotations, shifts, output_shape, interpolation,
+                                                                  oversampling, fourier_radius_cutoff)
+            ctx.save_for_backward(reconstruction, rotations, shifts, projection, derivatives)
+        else:
+            projection = _ops.project_2d_forw(reconstruction, rotations, shifts, output_shape, interpolation,
+                                              oversampling, fourier_radius_cutoff)
+            ctx.save_for_backward(reconstruction, rotations, shifts)
         ctx.interpolation = interpolation
         ctx.oversampling = oversampling
         ctx.fourier_radius_cutoff = fourier_radius_cutoff
@@ -564,10 +582,18 @@ class _Project2D(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, grad_output):
-        reconstruction, rotations, shifts = ctx.saved_tensors
-        grad_reconstruction, grad_rotations, grad_shifts = _ops.project_2d_back(
-            grad_output.contiguous(), reconstruction, rotations, shifts, ctx.interpolation,
-            ctx.oversampling, ctx.fourier_radius_cutoff)
+        if ctx.saving:
+            reconstruction, rotations, shifts, projection, derivatives = ctx.saved_tensors
+            grad_reconstruction, grad_rotations, grad_shifts = _ops.project_2d_back_saved(
+                grad_output.contiguous(), projection, derivatives, reconstruction, rotations, shifts, ctx.interpolation,
+                ctx.oversampling, ctx.fourier_radius_cutoff, ctx.need_rec)
+            if not ctx.need_rec:
+                grad_reconstruction = None
+        else:
+            reconstruction, rotations, shifts = ctx.saved_tensors
+            grad_reconstruction, grad_rotations, grad_shifts = _ops.project_2d_back(
+                grad_output.contiguous(), reconstruction, rotations, shifts, ctx.interpolation,
+                ctx.oversampling, ctx.fourier_radius_cutoff)
         if shifts is None:
             grad_shifts = None
         return grad_reconstruction, grad_rotations, grad_shifts, None, None, None, None
@@ -580,11 +606,8 @@ class _Project3DTo2D(torch.autograd.Function):
         reconstruction, rotations, shifts = _canon_project(3, reconstruction, rotations, shifts)
         # the processing order of the slices is settled once here and kept for the backward pass
         order = _resolve_order(pose_order, reconstruction, rotations)
-        need_rec, need_rot = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
-        N = int(output_shape[0])
-        saving = (SAVE_DERIVATIVES and need_rot and reconstruction.is_cuda and reconstruction.dtype == torch.complex64
-                  and rotations.dtype == torch.float32 and (interpolation == "cubic" or not need_rec)
-                  and 24 * reconstruction.size(0) * rotations.size(1) * N * (N // 2 + 1) <= SAVE_DERIVATIVES_MAX_BYTES)
+        need_rec = ctx.needs_input_grad[0]
+        saving = _save_derivatives(3, reconstruction, rotations, output_shape, interpolation, need_rec, ctx.needs_input_grad[1])
         ctx.saving = saving
         ctx.need_rec = need_rec
         if saving:
