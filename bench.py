@@ -739,6 +739,13 @@ def ops_table_workload(args):
             time_op("project_2d_back" + tag, lambda: ops.project_2d_back(proj2, rec2, rot2, sh2, interp, 2.0, None), P2)
             time_op("backproject_2d_forw" + tag, lambda: ops.backproject_2d_forw(proj2, w2, rot2, sh2, interp, 2.0, None), P2)
             time_op("backproject_2d_back" + tag, lambda: ops.backproject_2d_back(gd2, gw2, proj2, w2, rot2, sh2, interp, 2.0, None), P2)
+            if P2 == 65536:
+                time_op("project_2d_forw_saving" + tag, lambda: ops.project_2d_forw_saving(rec2, rot2, sh2, [64, 64], interp, 2.0, None), P2)
+                o2, d2 = ops.project_2d_forw_saving(rec2, rot2, sh2, [64, 64], interp, 2.0, None)
+                time_op("project_2d_back_saved" + tag, lambda: ops.project_2d_back_saved(proj2, o2, d2, rec2, rot2, sh2, interp, 2.0, None, True), P2)
+                time_op("project_2d_back_saved, fixed reference" + tag,
+                        lambda: ops.project_2d_back_saved(proj2, o2, d2, rec2, rot2, sh2, interp, 2.0, None, False), P2)
+                del o2, d2
     # ---- 3D quartet on the box-256 volume ----
     rec3, rot3, sh3 = make_projection_inputs(dev, seed=12)
     P3 = 4096
@@ -753,6 +760,12 @@ def ops_table_workload(args):
         time_op("project_3d_to_2d_back" + tag, lambda: ops.project_3d_to_2d_back(proj3, rec3, rot3, sh3, interp, 2.0, None), P3)
         time_op("backproject_2d_to_3d_forw" + tag, lambda: ops.backproject_2d_to_3d_forw(proj3, w3, rot3, sh3, interp, 2.0, None), P3)
         time_op("backproject_2d_to_3d_back" + tag, lambda: ops.backproject_2d_to_3d_back(gd3, gw3, proj3, w3, rot3, sh3, interp, 2.0, None), P3)
+        time_op("project_3d_to_2d_forw_saving" + tag, lambda: ops.project_3d_to_2d_forw_saving(rec3, rot3, sh3, [128, 128], interp, 2.0, None, None), P3)
+        o3, d3 = ops.project_3d_to_2d_forw_saving(rec3, rot3, sh3, [128, 128], interp, 2.0, None, None)
+        time_op("project_3d_to_2d_back_saved" + tag, lambda: ops.project_3d_to_2d_back_saved(proj3, o3, d3, rec3, rot3, sh3, interp, 2.0, None, None, True), P3)
+        time_op("project_3d_to_2d_back_saved, fixed volume" + tag,
+                lambda: ops.project_3d_to_2d_back_saved(proj3, o3, d3, rec3, rot3, sh3, interp, 2.0, None, None, False), P3)
+        del o3, d3
     if rank == 0:
         print(json.dumps({"metric": "per-operator device time (all gradients requested in the *_back operators)", "unit": "ms / slices/s",
                           "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "data": "synthetic", "dtype": "f32",

@@ -101,7 +101,7 @@ def test_saved_derivatives_give_the_gradients_of_the_plain_backward(tp, interp, 
     g = t["proj"].cuda()
     results = {}
     for saving in (True, False):
-        tp.set_save_derivatives(saving)
+        tp.set_save_derivatives(saving, min_volume_bytes=0)           # the small test volumes are below the default limit
         try:
             rec = t["rec"].cuda().requires_grad_(not fixed_volume)
             rot = t["rot"].cuda().requires_grad_(True)
@@ -127,6 +127,18 @@ def test_saved_derivatives_give_the_gradients_of_the_plain_backward(tp, interp, 
         assert rel_err(results[True][3], want[2]) <= TOL_ATOMIC
 
 
+def test_saved_derivatives_are_not_kept_for_small_reconstructions_that_need_a_gradient(tp):
+    """Onto a small reconstruction the backward scatter is bound by contention either way, so the plain
+    pair stays unless the reconstruction is fixed."""
+    case = Case("saved3", 2, "cubic", 1, 8, 16, 32, 2.0, None, 1, 1, seed=93)
+    t = make_inputs(case)
+    rot = t["rot"].cuda().requires_grad_(True)
+    for needs_grad, kept in ((True, 3), (False, 5)):
+        out = tp.project_2d_forw(t["rec"].cuda().requires_grad_(needs_grad), rot, t["shifts"].cuda(), output_shape=(16, 16),
+                                 interpolation="cubic", oversampling=2.0)
+        assert len(out.grad_fn.saved_tensors) == kept
+
+
 def test_saved_derivatives_respect_the_size_limit_and_the_pose_order(tp):
     case = Case("saved2", 3, "cubic", 1, 80, 16, 32, 2.0, None, 1, 1, shift_range=3.0, seed=92)
     t = make_inputs(case)
@@ -134,7 +146,7 @@ def test_saved_derivatives_respect_the_size_limit_and_the_pose_order(tp):
     rec = t["rec"].cuda().requires_grad_(True)
     rot = t["rot"].cuda().requires_grad_(True)
     sh = t["shifts"].cuda().requires_grad_(True)
-    tp.set_save_derivatives(True, max_bytes=1000)                     # too small for 80 x 16 x 9 pixels
+    tp.set_save_derivatives(True, max_bytes=1000, min_volume_bytes=0)   # too small for 80 x 16 x 9 pixels
     try:
         out = tp.project_3d_to_2d_forw(rec, rot, sh, **kw)
         assert len(out.grad_fn.saved_tensors) == 3
@@ -142,6 +154,7 @@ def test_saved_derivatives_respect_the_size_limit_and_the_pose_order(tp):
         tp.set_save_derivatives(True)
     order = tp.plane_locality_order(rot.detach())
     grads = []
+    tp.set_save_derivatives(True, min_volume_bytes=0)
     for po in (order, False):
         for x in (rec, rot, sh):
             x.grad = None
@@ -149,6 +162,7 @@ def test_saved_derivatives_respect_the_size_limit_and_the_pose_order(tp):
         assert len(out.grad_fn.saved_tensors) == 5
         torch.view_as_real(out).backward(torch.view_as_real(t["proj"].cuda()))
         grads.append((out.detach().clone(), rec.grad.clone(), rot.grad.clone(), sh.grad.clone()))
+    tp.set_save_derivatives(True)
     assert torch.equal(grads[0][0], grads[1][0])                        # the order changes no output
     for a, b in zip(grads[0][1:], grads[1][1:]):
         assert rel_err(a, b) <= 2e-6

@@ -130,17 +130,23 @@ def set_pose_order_thresholds(min_volume_bytes: int = 96 << 20, min_poses: int =
 # gathering the volume a second time -- and skips the scatter into the volume's gradient altogether
 # when the volume needs none.  Measured on B200, box 512, 4,096 poses of 256 x 256, cubic: forward
 # 6.5 -> 8.9 ms, backward 20.3 -> 15.1 ms (1.9 ms with a fixed volume).
+# When the reconstruction needs a gradient too, the backward pass still scatters, and onto a small
+# reconstruction that scatter is bound by contention, not by the gather beside it (one 128 x 65
+# reference, 65,536 poses, cubic: 9.8 ms either way, while the forward pass pays 1.4 ms for the
+# derivatives): below SAVE_DERIVATIVES_MIN_VOLUME_BYTES per batch item the plain pair stays.
 SAVE_DERIVATIVES = True
 SAVE_DERIVATIVES_MAX_BYTES = 16 << 30
+SAVE_DERIVATIVES_MIN_VOLUME_BYTES = 2 << 20
 
 
-def set_save_derivatives(enabled: bool = True, max_bytes: int = 16 << 30) -> None:
+def set_save_derivatives(enabled: bool = True, max_bytes: int = 16 << 30, min_volume_bytes: int = 2 << 20) -> None:
     """Whether ``project_2d_forw`` / ``project_3d_to_2d_forw`` keep their pixels' derivatives for the
-    backward pass when the rotations require gradients (complex64, cubic interpolation -- or any
-    interpolation when the reconstruction needs no gradient), and up to which size of that extra tensor
-    (2 or 3 x the projections)."""
-    global SAVE_DERIVATIVES, SAVE_DERIVATIVES_MAX_BYTES
+    backward pass when the rotations require gradients (complex64; when the reconstruction needs a
+    gradient as well: cubic interpolation and at least `min_volume_bytes` per batch item), and up to
+    which size of that extra tensor (2 or 3 x the projections)."""
+    global SAVE_DERIVATIVES, SAVE_DERIVATIVES_MAX_BYTES, SAVE_DERIVATIVES_MIN_VOLUME_BYTES
     SAVE_DERIVATIVES, SAVE_DERIVATIVES_MAX_BYTES = bool(enabled), int(max_bytes)
+    SAVE_DERIVATIVES_MIN_VOLUME_BYTES = int(min_volume_bytes)
 
 
 def plane_locality_order(rotations: torch.Tensor, batch: int = 1) -> torch.Tensor:
@@ -553,7 +559,9 @@ def _canon_project(rec_rank: int, reconstruction, rotations, shifts):
 def _save_derivatives(dim, reconstruction, rotations, output_shape, interpolation, need_rec, need_rot) -> bool:
     """Whether a projection's forward pass keeps its pixels' derivatives for the backward pass."""
     if not (SAVE_DERIVATIVES and need_rot and reconstruction.is_cuda and reconstruction.dtype == torch.complex64
-            and rotations.dtype == torch.float32 and (interpolation == "cubic" or not need_rec)):
+            and rotations.dtype == torch.float32):
+        return False
+    if need_rec and not (interpolation == "cubic" and reconstruction[0].numel() * 8 >= SAVE_DERIVATIVES_MIN_VOLUME_BYTES):
         return False
     N = int(output_shape[0])
     return 8 * dim * reconstruction.size(0) * rotations.size(1) * N * (N // 2 + 1) <= SAVE_DERIVATIVES_MAX_BYTES
