@@ -349,6 +349,21 @@ __device__ __forceinline__ void interpolate_lane(const SliceGeom& g, const C2<R>
     }
 }
 
+// Two floats in one 64-bit register and the packed fused multiply-add on them (sm_100).
+__device__ __forceinline__ unsigned long long pack2(float x, float y) {
+    unsigned long long r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(x), "f"(y));
+    return r;
+}
+__device__ __forceinline__ void unpack2(unsigned long long v, float& x, float& y) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(x), "=f"(y) : "l"(v));
+}
+__device__ __forceinline__ unsigned long long fma2(unsigned long long a, unsigned long long b, unsigned long long c) {
+    unsigned long long r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+
 // One lane's share of a cooperative gather: column tap q of every footprint row of the pixel at
 // (pc, pr, pd).  Returns the lane's column weight and its derivative (wc, dwc), whether the
 // column is a Friedel mate (m: its values are conjugates), and the sums over the footprint's rows
@@ -393,6 +408,58 @@ __device__ __forceinline__ void coop_column_sums(const SliceGeom& g, const C2<R>
     A = make2<R>(0.f, 0.f);
     Bq = A;
     Dq = A;
+#ifndef B200PROJ_NO_FMA2
+    if constexpr (sizeof(R) == 4 && !WITH_DERIV) {
+        // fp32, value only: both components of a complex sum advance in one packed fused
+        // multiply-add (fma.rn.f32x2, the same two roundings as two scalar ones), which halves the
+        // arithmetic instructions of the gather (measured on B200: cubic forward projection -1 % in
+        // 3D, -3.4 % in 2D; with the derivative sums beside it the packed form was 5-20 % slower, so
+        // those keep scalar operations)
+        unsigned long long w2[T], dw2[T], A2 = 0ull, B2 = 0ull, D2 = 0ull;
+#pragma unroll
+        for (int i = 0; i < T; ++i) {
+            w2[i] = pack2(ar.w[i], ar.w[i]);
+            dw2[i] = WITH_DERIV ? pack2(ar.dw[i], ar.dw[i]) : 0ull;
+        }
+#pragma unroll
+        for (int k = 0; k < TD; ++k) {
+            const float2* __restrict__ pl = (const float2*)vol + ((DIM == 3) ? gather_line<CUBIC>(g, dbase + k, m) * plane_stride : 0);
+            unsigned long long rs2 = 0ull, rds2 = 0ull;
+#pragma unroll
+            for (int i = 0; i < T; ++i) {
+                const float2 v = __ldg(pl + rowcol[i]);
+                const unsigned long long v2 = pack2(v.x, v.y);
+                rs2 = fma2(w2[i], v2, rs2);
+                if (WITH_DERIV) rds2 = fma2(dw2[i], v2, rds2);
+            }
+            float wd = 1.f, dwd = 0.f;
+            if (DIM == 3) {
+                if constexpr (CUBIC) {
+                    wd = k == 0 ? cubic_weight_k<0>((float)fd) : k == 1 ? cubic_weight_k<1>((float)fd) : k == 2 ? cubic_weight_k<2>((float)fd) : cubic_weight_k<3>((float)fd);
+                    if (WITH_DERIV)
+                        dwd = k == 0 ? cubic_dweight_k<0>((float)fd) : k == 1 ? cubic_dweight_k<1>((float)fd) : k == 2 ? cubic_dweight_k<2>((float)fd) : cubic_dweight_k<3>((float)fd);
+                } else {
+                    wd = k ? (float)fd : 1.f - (float)fd;
+                    dwd = k ? 1.f : -1.f;
+                }
+            }
+            const unsigned long long wd2 = pack2(wd, wd);
+            A2 = fma2(wd2, rs2, A2);
+            if (WITH_DERIV) {
+                B2 = fma2(wd2, rds2, B2);
+                if (DIM == 3) D2 = fma2(pack2(dwd, dwd), rs2, D2);
+            }
+        }
+        float ax, ay, bx, by, dx, dy;
+        unpack2(A2, ax, ay);
+        unpack2(B2, bx, by);
+        unpack2(D2, dx, dy);
+        A = make2<R>(ax, ay);
+        Bq = make2<R>(bx, by);
+        Dq = make2<R>(dx, dy);
+        return;
+    }
+#endif
 #pragma unroll
     for (int k = 0; k < TD; ++k) {
         const C2<R>* __restrict__ pl = vol + ((DIM == 3) ? gather_line<CUBIC>(g, dbase + k, m) * plane_stride : 0);
