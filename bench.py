@@ -1137,7 +1137,9 @@ def main():
     d2h = h_out.numel() * 8
     e2e = {"value": world * PROJ["P"] / (e2e_ms_per_step * 1e-3), "unit": "slices/s", "ms_per_step": e2e_ms_per_step,
            "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-           "pcie_gbs": (h2d + d2h) / (e2e_ms_per_step * 1e-3) / 1e9}
+           "pcie_gbs": (h2d + d2h) / (e2e_ms_per_step * 1e-3) / 1e9,
+           # the value is the mean over the timed steps; the spread shows whether the shared host interfered
+           "ms_per_step_median": statistics.median(e2e_ms), "ms_per_step_max": max(e2e_ms)}
     # the same with packed output: only the pixels inside the cutoff leave the device
     n_inside = tp._abi.cutoff_pack_index(PROJ["N"], PROJ["cutoff"], dev)[1]
     h_packed = torch.empty((1, PROJ["P"], n_inside), dtype=torch.complex64).pin_memory()
