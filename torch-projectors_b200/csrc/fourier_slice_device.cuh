@@ -269,6 +269,21 @@ __host__ __device__ __forceinline__ int gather_line(const SliceGeom& g, int r, b
     return r < 0 ? r + g.R : r;
 }
 
+// Two floats in one 64-bit register and the packed fused multiply-add on them (sm_100).
+__device__ __forceinline__ unsigned long long pack2(float x, float y) {
+    unsigned long long r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(x), "f"(y));
+    return r;
+}
+__device__ __forceinline__ void unpack2(unsigned long long v, float& x, float& y) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(x), "=f"(y) : "l"(v));
+}
+__device__ __forceinline__ unsigned long long fma2(unsigned long long a, unsigned long long b, unsigned long long c) {
+    unsigned long long r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+
 // One-lane-per-pixel separable interpolation (used for linear interpolation, whose 2-tap rows
 // are too short for lane groups to pay for their shuffles: the linear gathers are bound by
 // instruction issue, not by the L1TEX data pipe).  Same value and derivative conventions as
@@ -288,6 +303,50 @@ __device__ __forceinline__ void interpolate_lane(const SliceGeom& g, const C2<R>
     g_c = g_r = g_d = val;
     const bool interior = ar.base >= -g.half + 1 && ar.base + T - 1 <= g.half - 1 &&
                           (DIM == 2 || (ad.base >= -g.half + 1 && ad.base + T - 1 <= g.half - 1));
+    if constexpr (sizeof(R) == 4 && !WITH_DERIV) {
+        // fp32, value only: packed two-wide fused multiply-adds for the complex sums (see coop_column_sums)
+        unsigned long long w2[T], val2 = 0ull;
+#pragma unroll
+        for (int i = 0; i < T; ++i) w2[i] = pack2(ar.w[i], ar.w[i]);
+#pragma unroll
+        for (int j = 0; j < T; ++j) {
+            bool m;
+            const int col = gather_col<CUBIC>(g, ac.base + j, m);
+            unsigned long long A2 = 0ull;
+#pragma unroll
+            for (int k = 0; k < TD; ++k) {
+                int pl = 0;
+                if (DIM == 3) {
+                    if (interior) {
+                        const int d = m ? -(ad.base + k) : ad.base + k;
+                        pl = (d < 0 ? d + g.R : d) * plane_stride;
+                    } else {
+                        pl = gather_line<CUBIC>(g, ad.base + k, m) * plane_stride;
+                    }
+                }
+                unsigned long long rs2 = 0ull;
+#pragma unroll
+                for (int i = 0; i < T; ++i) {
+                    int rw;
+                    if (interior) {
+                        const int r = m ? -(ar.base + i) : ar.base + i;
+                        rw = (r < 0 ? r + g.R : r) * g.Rh;
+                    } else {
+                        rw = gather_line<CUBIC>(g, ar.base + i, m) * g.Rh;
+                    }
+                    const float2 v = __ldg((const float2*)vol + (pl + rw + col));
+                    rs2 = fma2(w2[i], pack2(v.x, v.y), rs2);
+                }
+                const float wd = (DIM == 3) ? (float)ad.w[k] : 1.f;
+                A2 = fma2(pack2(wd, wd), rs2, A2);
+            }
+            const float wc = (float)ac.w[j];
+            val2 = fma2(pack2(wc, m ? -wc : wc), A2, val2);
+        }
+        float vx, vy;
+        unpack2(val2, vx, vy);
+        val = make2<R>(vx, vy);
+    } else {
 #pragma unroll
     for (int j = 0; j < T; ++j) {
         bool m;
@@ -347,22 +406,9 @@ __device__ __forceinline__ void interpolate_lane(const SliceGeom& g, const C2<R>
             g_d.y = rfma(sg * wc, Dq.y, g_d.y);
         }
     }
+    }
 }
 
-// Two floats in one 64-bit register and the packed fused multiply-add on them (sm_100).
-__device__ __forceinline__ unsigned long long pack2(float x, float y) {
-    unsigned long long r;
-    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(x), "f"(y));
-    return r;
-}
-__device__ __forceinline__ void unpack2(unsigned long long v, float& x, float& y) {
-    asm("mov.b64 {%0, %1}, %2;" : "=f"(x), "=f"(y) : "l"(v));
-}
-__device__ __forceinline__ unsigned long long fma2(unsigned long long a, unsigned long long b, unsigned long long c) {
-    unsigned long long r;
-    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
-    return r;
-}
 
 // One lane's share of a cooperative gather: column tap q of every footprint row of the pixel at
 // (pc, pr, pd).  Returns the lane's column weight and its derivative (wc, dwc), whether the
@@ -408,7 +454,6 @@ __device__ __forceinline__ void coop_column_sums(const SliceGeom& g, const C2<R>
     A = make2<R>(0.f, 0.f);
     Bq = A;
     Dq = A;
-#ifndef B200PROJ_NO_FMA2
     if constexpr (sizeof(R) == 4 && !WITH_DERIV) {
         // fp32, value only: both components of a complex sum advance in one packed fused
         // multiply-add (fma.rn.f32x2, the same two roundings as two scalar ones), which halves the
@@ -457,9 +502,7 @@ __device__ __forceinline__ void coop_column_sums(const SliceGeom& g, const C2<R>
         A = make2<R>(ax, ay);
         Bq = make2<R>(bx, by);
         Dq = make2<R>(dx, dy);
-        return;
-    }
-#endif
+    } else {
 #pragma unroll
     for (int k = 0; k < TD; ++k) {
         const C2<R>* __restrict__ pl = vol + ((DIM == 3) ? gather_line<CUBIC>(g, dbase + k, m) * plane_stride : 0);
@@ -495,6 +538,7 @@ __device__ __forceinline__ void coop_column_sums(const SliceGeom& g, const C2<R>
                 Dq.y = rfma(dwd, rs.y, Dq.y);
             }
         }
+    }
     }
 }
 
