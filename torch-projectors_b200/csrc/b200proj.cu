@@ -533,7 +533,7 @@ int noalloc_scratch(float4** out) {
 
 extern "C" {
 
-int b200proj_version(void) { return 200; }
+int b200proj_version(void) { return 300; }
 
 #ifndef B200PROJ_SOURCE_STAMP
 #define B200PROJ_SOURCE_STAMP ""
