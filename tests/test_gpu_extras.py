@@ -127,6 +127,34 @@ def test_saved_derivatives_give_the_gradients_of_the_plain_backward(tp, interp, 
         assert rel_err(results[True][3], want[2]) <= TOL_ATOMIC
 
 
+@pytest.mark.parametrize("dim", [2, 3])
+@pytest.mark.parametrize("interp", ["linear", "cubic"])
+def test_shift_gradients_alone_need_only_the_saved_projections(tp, dim, interp):
+    """Fixed reconstruction and rotations, shifts to be optimised: the backward pass reads nothing but
+    the gradient and the projections the forward pass made (no derivatives are kept)."""
+    from oracle import port
+    case = Case("shiftonly", dim, interp, 2, 6, 16, 32, 2.0, None, 1, 2, shift_range=3.0, seed=94)
+    t = make_inputs(case)
+    project = tp.project_3d_to_2d_forw if dim == 3 else tp.project_2d_forw
+    kw = dict(output_shape=(16, 16), interpolation=interp, oversampling=2.0)
+    grads = {}
+    for saving in (True, False):
+        tp.set_save_derivatives(saving)
+        try:
+            sh = t["shifts"].cuda().requires_grad_(True)
+            out = project(t["rec"].cuda(), t["rot"].cuda(), sh, **kw)
+            kept = out.grad_fn.saved_tensors
+            assert len(kept) == (5 if saving else 3) and (not saving or kept[4].numel() == 0)
+            torch.view_as_real(out).backward(torch.view_as_real(t["proj"].cuda()))
+            grads[saving] = sh.grad
+        finally:
+            tp.set_save_derivatives(True)
+    assert rel_err(grads[True], grads[False]) <= 2e-6
+    back = port.project_3d_to_2d_back if dim == 3 else port.project_2d_back
+    want = back(t["proj"], t["rec"], t["rot"], t["shifts"], interp, 2.0, None, need_rot_grad=False, need_shift_grad=True)
+    assert rel_err(grads[True], want[2]) <= TOL_ATOMIC
+
+
 def test_saved_derivatives_are_not_kept_for_small_reconstructions_that_need_a_gradient(tp):
     """Onto a small reconstruction the backward scatter is bound by contention either way, so the plain
     pair stays unless the reconstruction is fixed."""

@@ -280,13 +280,16 @@ std::tuple<Tensor, Tensor, Tensor> project_back_saved(int dim, const Tensor& gra
     TORCH_CHECK(p.P == P_g, "Number of poses in rotations must match grad_projections");
     TORCH_CHECK(projections.sizes() == grad_projections.sizes() && projections.scalar_type() == at::kComplexFloat && projections.is_cuda(),
                 "saved projections must match grad_projections");
-    TORCH_CHECK(derivatives.dim() == 5 && derivatives.size(0) == dim && derivatives.sizes().slice(1) == grad_projections.sizes() &&
-                derivatives.scalar_type() == at::kComplexFloat && derivatives.is_cuda(), "saved derivatives must be (dim, B, P, H, W/2+1) complex64");
     const bool need_rot = rotations.requires_grad();
+    // the derivatives are read for the rotation gradient only: without it an empty tensor will do
+    TORCH_CHECK((!need_rot && derivatives.numel() == 0) ||
+                (derivatives.dim() == 5 && derivatives.size(0) == dim && derivatives.sizes().slice(1) == grad_projections.sizes() &&
+                 derivatives.scalar_type() == at::kComplexFloat && derivatives.is_cuda()),
+                "saved derivatives must be (dim, B, P, H, W/2+1) complex64");
     const bool need_shift = p.shifts.defined() && shifts->requires_grad();
     const Tensor gp = grad_projections.contiguous();
     const Tensor out = projections.contiguous();
-    const Tensor der = derivatives.contiguous();
+    const Tensor der = derivatives.numel() ? derivatives.contiguous() : Tensor();
     const int64_t R = reconstruction.size(-2);
     c10::cuda::CUDAGuard guard(gp.device());
     Tensor grad_rec = need_rec_grad ? at::empty(reconstruction.sizes(), gp.options()) : Tensor();

@@ -556,15 +556,24 @@ def _canon_project(rec_rank: int, reconstruction, rotations, shifts):
     return reconstruction, rotations, shifts
 
 
-def _save_derivatives(dim, reconstruction, rotations, output_shape, interpolation, need_rec, need_rot) -> bool:
-    """Whether a projection's forward pass keeps its pixels' derivatives for the backward pass."""
-    if not (SAVE_DERIVATIVES and need_rot and reconstruction.is_cuda and reconstruction.dtype == torch.complex64
+_PLAIN, _KEEP_DERIVATIVES, _KEEP_OUTPUT = 0, 1, 2
+
+
+def _save_derivatives(dim, reconstruction, rotations, output_shape, interpolation, need_rec, need_rot, need_shift=False) -> int:
+    """What a projection's forward pass keeps for the backward pass: nothing but its inputs (the
+    backward pass gathers the reconstruction again), its pixels' derivatives and its output
+    (rotation gradients wanted), or its output alone (only shift gradients wanted and the
+    reconstruction fixed: they are Im(grad * conj(output)) times the frequency)."""
+    if not (SAVE_DERIVATIVES and reconstruction.is_cuda and reconstruction.dtype == torch.complex64
             and rotations.dtype == torch.float32):
-        return False
+        return _PLAIN
+    if not need_rot:
+        return _KEEP_OUTPUT if (need_shift and not need_rec) else _PLAIN
     if need_rec and not (interpolation == "cubic" and reconstruction[0].numel() * 8 >= SAVE_DERIVATIVES_MIN_VOLUME_BYTES):
-        return False
+        return _PLAIN
     N = int(output_shape[0])
-    return 8 * dim * reconstruction.size(0) * rotations.size(1) * N * (N // 2 + 1) <= SAVE_DERIVATIVES_MAX_BYTES
+    fits = 8 * dim * reconstruction.size(0) * rotations.size(1) * N * (N // 2 + 1) <= SAVE_DERIVATIVES_MAX_BYTES
+    return _KEEP_DERIVATIVES if fits else _PLAIN
 
 
 class _Project2D(torch.autograd.Function):
@@ -573,12 +582,17 @@ class _Project2D(torch.autograd.Function):
                 fourier_radius_cutoff):
         reconstruction, rotations, shifts = _canon_project(2, reconstruction, rotations, shifts)
         need_rec = ctx.needs_input_grad[0]
-        ctx.saving = _save_derivatives(2, reconstruction, rotations, output_shape, interpolation, need_rec, ctx.needs_input_grad[1])
+        ctx.saving = _save_derivatives(2, reconstruction, rotations, output_shape, interpolation, need_rec, ctx.needs_input_grad[1],
+                                       shifts is not None and ctx.needs_input_grad[2])
         ctx.need_rec = need_rec
-        if ctx.saving:
+        if ctx.saving == _KEEP_DERIVATIVES:
             projection, derivatives = _ops.project_2d_forw_saving(reconstruction, rotations, shifts, output_shape, interpolation,
                                                                   oversampling, fourier_radius_cutoff)
             ctx.save_for_backward(reconstruction, rotations, shifts, projection, derivatives)
+        elif ctx.saving == _KEEP_OUTPUT:
+            projection = _ops.project_2d_forw(reconstruction, rotations, shifts, output_shape, interpolation,
+                                              oversampling, fourier_radius_cutoff)
+            ctx.save_for_backward(reconstruction, rotations, shifts, projection, projection.new_empty(0))
         else:
             projection = _ops.project_2d_forw(reconstruction, rotations, shifts, output_shape, interpolation,
                                               oversampling, fourier_radius_cutoff)
@@ -615,13 +629,18 @@ class _Project3DTo2D(torch.autograd.Function):
         # the processing order of the slices is settled once here and kept for the backward pass
         order = _resolve_order(pose_order, reconstruction, rotations)
         need_rec = ctx.needs_input_grad[0]
-        saving = _save_derivatives(3, reconstruction, rotations, output_shape, interpolation, need_rec, ctx.needs_input_grad[1])
+        saving = _save_derivatives(3, reconstruction, rotations, output_shape, interpolation, need_rec, ctx.needs_input_grad[1],
+                                   shifts is not None and ctx.needs_input_grad[2])
         ctx.saving = saving
         ctx.need_rec = need_rec
-        if saving:
+        if saving == _KEEP_DERIVATIVES:
             projection, derivatives = _ops.project_3d_to_2d_forw_saving(reconstruction, rotations, shifts, output_shape, interpolation,
                                                                         oversampling, fourier_radius_cutoff, order)
             ctx.save_for_backward(reconstruction, rotations, shifts, projection, derivatives)
+        elif saving == _KEEP_OUTPUT:
+            projection = _ops.project_3d_to_2d_forw_ordered(reconstruction, rotations, shifts, output_shape, interpolation,
+                                                            oversampling, fourier_radius_cutoff, order)
+            ctx.save_for_backward(reconstruction, rotations, shifts, projection, projection.new_empty(0))
         else:
             projection = _ops.project_3d_to_2d_forw_ordered(reconstruction, rotations, shifts, output_shape, interpolation,
                                                             oversampling, fourier_radius_cutoff, order)
