@@ -38,7 +38,7 @@ from . import streaming  # noqa: E402
 from . import prep  # noqa: E402
 from .streaming import backproject_2d_to_3d_from_host, project_3d_to_2d_to_host  # noqa: E402
 
-__version__ = "0.1.0"
+__version__ = "0.3.0"
 
 __all__ = [
     "project_2d_forw", "project_2d_back", "project_3d_to_2d_forw", "project_3d_to_2d_back",
