@@ -249,10 +249,18 @@ def test_raw_operators_pass_opcheck_schema_and_fake_tensor(tp):
     torch.library.opcheck(ops.backproject_2d_to_3d_forw.default, (t["proj"], t["weights"], t["rot"], t["shifts"], "linear", 2.0, None), test_utils=which)
     torch.library.opcheck(ops.backproject_2d_to_3d_back.default,
                           (t["grad_data"], t["grad_weight"], t["proj"], t["weights"], rot_g, t["shifts"], "linear", 2.0, None), test_utils=which)
+    # the forward projection that keeps its pixels' derivatives, and the backward pass from them
+    torch.library.opcheck(ops.project_3d_to_2d_forw_saving.default, (t["rec"], t["rot"], t["shifts"], [8, 8], "cubic", 2.0, None, None), test_utils=which)
+    out, der = ops.project_3d_to_2d_forw_saving(t["rec"], t["rot"], t["shifts"], [8, 8], "cubic", 2.0, None, None)
+    der = torch.where(torch.isfinite(torch.view_as_real(der)).all(-1), der, torch.zeros_like(der))     # pixels outside the cutoff are not written
+    for need_rec in (True, False):
+        torch.library.opcheck(ops.project_3d_to_2d_back_saved.default,
+                              (t["proj"], out, der, t["rec"], rot_g, t["shifts"], "cubic", 2.0, None, None, need_rec), test_utils=which)
     case2 = Case("opcheck2", 2, "linear", 1, 4, 8, 16, 2.0, None, 1, 0, weights=False, seed=92)
     t2 = {k: (v.cuda() if v is not None else None) for k, v in make_inputs(case2).items()}
     torch.library.opcheck(ops.project_2d_forw.default, (t2["rec"], t2["rot"], None, [8, 8], "linear", 2.0, 3.5), test_utils=which)
     torch.library.opcheck(ops.backproject_2d_forw.default, (t2["proj"], None, t2["rot"], None, "linear", 2.0, None), test_utils=which)
+    torch.library.opcheck(ops.project_2d_forw_saving.default, (t2["rec"], t2["rot"], None, [8, 8], "linear", 2.0, 3.5), test_utils=which)
 
 
 @pytest.mark.parametrize("B,P", [(1, 40_000), (2, 33_000)])
