@@ -353,6 +353,20 @@ def profile_case(args):
         torch.cuda.synchronize()
         print(f"profile case autograd_step: {P} poses of 256x256 on a box-512 volume, 2 forward + 2 backward launches done")
         return
+    if args.profile_case == "step_saving":
+        # the same step through the pair of kernels the autograd path runs when rotation gradients are wanted
+        gen = torch.Generator(device=dev).manual_seed(6)
+        rec5 = torch.complex(torch.randn(1, 512, 512, 257, generator=gen, device=dev), torch.randn(1, 512, 512, 257, generator=gen, device=dev))
+        r5 = uniform_rotations(P, torch.Generator().manual_seed(6), dev).requires_grad_(True)
+        s5 = ((torch.rand(1, P, 2, generator=gen, device=dev) * 2 - 1) * 10.0).requires_grad_(True)
+        g5 = torch.complex(torch.randn(1, P, 256, 129, generator=gen, device=dev), torch.randn(1, P, 256, 129, generator=gen, device=dev))
+        order = tp.plane_locality_order(r5.detach())
+        for _ in range(2):
+            out, der = torch.ops.torch_projectors_b200.project_3d_to_2d_forw_saving(rec5, r5, s5, [256, 256], "cubic", 2.0, None, order)
+            torch.ops.torch_projectors_b200.project_3d_to_2d_back_saved(g5, out, der, rec5, r5, s5, "cubic", 2.0, None, order, True)
+        torch.cuda.synchronize()
+        print(f"profile case step_saving: {P} poses of 256x256 on a box-512 volume, 2 forward + 2 backward launches done")
+        return
     if args.profile_case == "project_2d":
         # paper-protocol 2D case: 8 box-256 images, P poses each, linear, oversampling 1, shifts
         from cases import random_rotations_2d
@@ -1020,7 +1034,7 @@ def main():
     ap.add_argument("--skip-backproject", action="store_true")
     ap.add_argument("--natural-order", action="store_true",
                     help="process slices in the order given (switch the plane-locality order of beyond-L2 volumes off), for comparisons")
-    ap.add_argument("--profile-case", choices=["project", "backproject", "project_back", "backproject_slab", "accumulate_slab", "autograd_step", "project_2d",
+    ap.add_argument("--profile-case", choices=["project", "backproject", "project_back", "backproject_slab", "accumulate_slab", "autograd_step", "step_saving", "project_2d",
                                                "backproject_back", "backproject_cubic", "backproject_2d", "prep"], default=None,
                     help="run a few launches of one kernel on a reduced pose count (for ncu captures); prints no bench line")
     ap.add_argument("--profile-poses", type=int, default=2048)
