@@ -129,9 +129,11 @@ def test_saved_derivatives_give_the_gradients_of_the_plain_backward(tp, interp, 
 
 @pytest.mark.parametrize("dim", [2, 3])
 @pytest.mark.parametrize("interp", ["linear", "cubic"])
-def test_shift_gradients_alone_need_only_the_saved_projections(tp, dim, interp):
-    """Fixed reconstruction and rotations, shifts to be optimised: the backward pass reads nothing but
-    the gradient and the projections the forward pass made (no derivatives are kept)."""
+@pytest.mark.parametrize("fixed_volume", [True, False])
+def test_shift_gradients_alone_need_only_the_saved_projections(tp, dim, interp, fixed_volume):
+    """Fixed rotations, shifts to be optimised (with or without the reconstruction): the shift gradients
+    come from the gradient and the projections the forward pass made; no derivatives are kept and the
+    backward pass gathers nothing."""
     from oracle import port
     case = Case("shiftonly", dim, interp, 2, 6, 16, 32, 2.0, None, 1, 2, shift_range=3.0, seed=94)
     t = make_inputs(case)
@@ -142,17 +144,21 @@ def test_shift_gradients_alone_need_only_the_saved_projections(tp, dim, interp):
         tp.set_save_derivatives(saving)
         try:
             sh = t["shifts"].cuda().requires_grad_(True)
-            out = project(t["rec"].cuda(), t["rot"].cuda(), sh, **kw)
+            rec = t["rec"].cuda().requires_grad_(not fixed_volume)
+            out = project(rec, t["rot"].cuda(), sh, **kw)
             kept = out.grad_fn.saved_tensors
             assert len(kept) == (5 if saving else 3) and (not saving or kept[4].numel() == 0)
             torch.view_as_real(out).backward(torch.view_as_real(t["proj"].cuda()))
-            grads[saving] = sh.grad
+            grads[saving] = (sh.grad, rec.grad)
         finally:
             tp.set_save_derivatives(True)
-    assert rel_err(grads[True], grads[False]) <= 2e-6
+    assert rel_err(grads[True][0], grads[False][0]) <= 2e-6
     back = port.project_3d_to_2d_back if dim == 3 else port.project_2d_back
     want = back(t["proj"], t["rec"], t["rot"], t["shifts"], interp, 2.0, None, need_rot_grad=False, need_shift_grad=True)
-    assert rel_err(grads[True], want[2]) <= TOL_ATOMIC
+    assert rel_err(grads[True][0], want[2]) <= TOL_ATOMIC
+    assert (grads[True][1] is None) == fixed_volume
+    if not fixed_volume:
+        assert rel_err(grads[True][1], grads[False][1]) <= 2e-6 and rel_err(grads[True][1], want[0]) <= TOL_ATOMIC
 
 
 def test_saved_derivatives_are_not_kept_for_small_reconstructions_that_need_a_gradient(tp):

@@ -562,13 +562,13 @@ _PLAIN, _KEEP_DERIVATIVES, _KEEP_OUTPUT = 0, 1, 2
 def _save_derivatives(dim, reconstruction, rotations, output_shape, interpolation, need_rec, need_rot, need_shift=False) -> int:
     """What a projection's forward pass keeps for the backward pass: nothing but its inputs (the
     backward pass gathers the reconstruction again), its pixels' derivatives and its output
-    (rotation gradients wanted), or its output alone (only shift gradients wanted and the
-    reconstruction fixed: they are Im(grad * conj(output)) times the frequency)."""
+    (rotation gradients wanted), or its output alone (shift gradients wanted but no rotation
+    gradients: they are Im(grad * conj(output)) times the frequency)."""
     if not (SAVE_DERIVATIVES and reconstruction.is_cuda and reconstruction.dtype == torch.complex64
             and rotations.dtype == torch.float32):
         return _PLAIN
     if not need_rot:
-        return _KEEP_OUTPUT if (need_shift and not need_rec) else _PLAIN
+        return _KEEP_OUTPUT if need_shift else _PLAIN      # costs the forward pass nothing and spares the backward pass its gather
     if need_rec and not (interpolation == "cubic" and reconstruction[0].numel() * 8 >= SAVE_DERIVATIVES_MIN_VOLUME_BYTES):
         return _PLAIN
     N = int(output_shape[0])
